@@ -1,0 +1,124 @@
+"""ctypes binding of libcanopy_fp8.so (the C ABI declared in include/canopy_fp8.h).
+
+The library is the product; this module only loads it and declares signatures. There is no
+fallback: when the shared object is missing the import fails with a build hint.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libcanopy_fp8.so")
+
+CF_OK, CF_ERR_INVALID_ARG, CF_ERR_UNSUPPORTED, CF_ERR_CUDA, CF_ERR_DEVICE_WAIT, CF_ERR_LIMIT = range(6)
+E4M3_MAX = 448.0
+E5M2_MAX = 57344.0
+
+vp = C.c_void_p
+fp = C.c_void_p      # float* on the device
+ip = C.c_void_p      # int* on the device
+sz = C.c_size_t
+ci = C.c_int
+cf = C.c_float
+
+
+class GemmEpilogue(C.Structure):
+    _fields_ = [("d_bias", vp), ("bias_mode", ci), ("d_a_row_descale", fp), ("d_b_col_descale", fp)]
+
+
+class ActSlotStruct(C.Structure):
+    _fields_ = [("amax", fp), ("scale", fp), ("descale", fp), ("history", fp), ("history_cursor", ip),
+                ("history_count", ip), ("scale_snapshot", fp), ("descale_snapshot", fp), ("fp8_max", cf),
+                ("init", ci), ("calib_remaining", ci), ("calib_commit_pending", ci), ("calib_min", fp),
+                ("calib_max", fp)]
+
+
+class Fp8WeightStruct(C.Structure):
+    _fields_ = [("w", vp), ("fwd8", vp), ("bwd8", vp), ("amax", fp), ("scale", fp), ("descale", fp),
+                ("in_dim", ci), ("out_dim", ci), ("stored_out_major", ci)]
+
+
+# name -> (restype, argtypes); every symbol include/canopy_fp8.h declares
+SIGNATURES = {
+    "cf_last_error": (C.c_char_p, []),
+    "cf_abi_version": (ci, []),
+    "cf_launch_count": (C.c_uint64, []),
+    "cf_fp8_amax_bf16": (ci, [vp, sz, fp, vp]),
+    "cf_fp8_scale_from_amax": (ci, [fp, cf, fp, fp, vp]),
+    "cf_fp8_quantize_e4m3": (ci, [vp, vp, fp, sz, vp]),
+    "cf_fp8_quantize_e5m2": (ci, [vp, vp, fp, sz, vp]),
+    "cf_fp8_quantize_e4m3_record": (ci, [vp, vp, fp, fp, sz, vp]),
+    "cf_fp8_quantize_e5m2_record": (ci, [vp, vp, fp, fp, sz, vp]),
+    "cf_fp8_update_delayed_scale": (ci, [fp, cf, fp, fp, fp, ci, ip, ip, vp]),
+    "cf_fp8_quantize_transpose_e4m3": (ci, [vp, vp, fp, ci, ci, vp]),
+    "cf_fp8_quant_and_transpose_e4m3": (ci, [vp, vp, vp, fp, ci, ci, vp]),
+    "cf_transpose_u8": (ci, [vp, vp, ci, ci, vp]),
+    "cf_fp8_clip_probe": (ci, [fp, fp, cf, fp, vp]),
+    "cf_fp8_elem_clip_count": (ci, [vp, fp, cf, sz, fp, vp]),
+    "cf_fp8_pack_bf16_e4m3_raw": (ci, [vp, vp, fp, fp, fp, ip, sz, vp]),
+    "cf_fp8_pack_bf16_e4m3_raw_and_dequant": (ci, [vp, vp, vp, fp, fp, fp, ip, sz, vp]),
+    "cf_fp8_unpack_e4m3_raw_bf16": (ci, [vp, fp, vp, sz, vp]),
+    "cf_fp8_calib_minmax_update": (ci, [fp, fp, fp, vp]),
+    "cf_ctx_create": (ci, [C.POINTER(vp), sz]),
+    "cf_ctx_destroy": (ci, [vp]),
+    "cf_ctx_act8": (vp, [vp]),
+    "cf_ctx_poll_status": (ci, [vp, vp]),
+    "cf_ctx_reserve_workspace": (ci, [vp, sz]),
+    "cf_gemm_fp8_nt": (ci, [vp, ci, ci, ci, vp, ci, ci, fp, vp, fp, vp, ci, C.POINTER(GemmEpilogue), vp]),
+    "cf_gemm_fp8_tn_accum_f32": (ci, [vp, ci, ci, ci, vp, fp, vp, fp, vp, ci, vp]),
+    "cf_gemm_fp8_tn_accum_bf16": (ci, [vp, ci, ci, ci, vp, fp, vp, fp, vp, ci, vp]),
+    "cf_gemm_fp8_nt_grouped": (ci, [vp, ci, ci, ci, ci, ip, ip, vp, ci, ci, fp, ci, vp, fp, vp, ci, vp]),
+    "cf_act_slot_init": (ci, [vp, C.POINTER(ActSlotStruct), cf, ci, vp]),
+    "cf_fp8_quant_act": (ci, [vp, C.POINTER(ActSlotStruct), vp, sz, vp, vp, ci]),
+    "cf_refresh_fp8_weight": (ci, [C.POINTER(Fp8WeightStruct), ci, vp]),
+    "cf_fp8_linear_forward": (ci, [vp, C.POINTER(ActSlotStruct), vp, ci, ci, vp, fp, ci, vp, ci, vp, ci, vp]),
+    "cf_bias_add_strided_bf16": (ci, [vp, vp, ci, ci, ci, ci, vp]),
+    "cf_swiglu_forward": (ci, [vp, vp, vp, ci, vp]),
+    "cf_gelu_forward": (ci, [vp, vp, sz, vp]),
+    "cf_moe_topk_route_f32": (ci, [fp, ci, ci, ci, vp, fp, fp, ci]),
+    "cf_moe_build_expert_row_lists": (ci, [fp, ip, ip, ci, ci, vp]),
+    "cf_moe_expert_offsets_from_counts": (ci, [ip, ip, ci, vp]),
+    "cf_moe_gather_rows_u8": (ci, [vp, vp, ip, ci, ci, vp]),
+    "cf_moe_gather_rows_bf16": (ci, [vp, vp, ip, ci, ci, vp]),
+    "cf_moe_scatter_accumulate_rows_bf16": (ci, [vp, vp, fp, ip, ci, ci, ci, ci, vp]),
+    "cf_moe_scale_accumulate_bf16": (ci, [vp, vp, fp, ci, ci, ci, ci, vp]),
+    "cf_moe_gather_all_u8": (ci, [vp, vp, ip, ip, ip, ci, ci, ci, vp]),
+    "cf_moe_combine_all_bf16": (ci, [vp, vp, fp, ip, ip, ip, ci, ci, ci, vp]),
+    "cf_moe_grouped_expert_forward_fp8": (ci, [vp, vp, fp, ci, fp, ip, ip, ip, vp, fp, vp, fp, vp, ci, ci, ci, ci, ci, vp]),
+}
+
+
+class CanopyError(RuntimeError):
+    """Raised when a C-ABI call returns a non-zero status (the reference's operators throw
+    std::runtime_error in the same situations)."""
+
+    def __init__(self, code, message):
+        super().__init__(f"libcanopy_fp8 status {code}: {message}")
+        self.code = code
+
+
+def load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+            "or `make -C canopy-foundry_b200/csrc`. There is no fallback path.")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)      # AttributeError here means the header and the library disagree
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = load()
+    return _lib
+
+
+def check(code):
+    if code != CF_OK:
+        raise CanopyError(code, lib().cf_last_error().decode("utf-8", "replace"))

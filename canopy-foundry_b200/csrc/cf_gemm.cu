@@ -1,0 +1,493 @@
+// FP8 NT GEMM for sm_100a: TMA -> 128B-swizzled shared-memory ring -> tcgen05.mma
+// (kind::f8f6f4, fp32 accumulators in TMEM, double-buffered) -> fused dequant / bias epilogue.
+//
+//   C[m,n] = (dA * dB) * sum_k A8[m,k] * B8[n,k]          (src/trainer.cu:4498-4534)
+//
+// One persistent CTA per SM, 192 threads:
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      TMEM allocator + MMA issuer (one elected lane)
+//   warps 2..5  epilogue: tcgen05.ld the accumulator, scale, bias, convert, store
+// The same kernel serves the dense call, the beta=1 weight-gradient forms and the ragged
+// per-expert (grouped) schedule: a tile is (expert, 128-row block of that expert, 256-column block).
+//
+// Every wait on an mbarrier is bounded by a wall-clock deadline; a wait that gives up raises an
+// abort flag, records a code in the context's status word, drains the CTA's own copies and MMAs,
+// frees TMEM and returns, so a faulty launch cannot hang the GPU.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "cf_common.cuh"
+#include "cf_gemm.cuh"
+
+namespace cf {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 128;                 // bytes == FP8 elements per k-block (one 128B swizzle row)
+constexpr int UMMA_K = 32;              // FP8 elements per tcgen05.mma
+constexpr int STAGES = 4;
+constexpr int A_STAGE = BM * BK;        // 16 KiB
+constexpr int B_STAGE = BN * BK;        // 32 KiB
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;          // two 128x256 fp32 accumulators
+constexpr int SMEM_BYTES = STAGES * (A_STAGE + B_STAGE) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr unsigned long long WAIT_NS = 1500ull * 1000ull * 1000ull;   // per-wait deadline
+constexpr unsigned long long DRAIN_NS = 20ull * 1000ull * 1000ull;
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ unsigned long long gtime_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait. Returns false when the deadline passed or another role of this CTA aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* s_abort,
+                                          unsigned long long limit_ns = WAIT_NS) {
+    for (int i = 0; i < 64; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = gtime_ns();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*s_abort) return false;
+        if (gtime_ns() - t0 > limit_ns) return false;
+        __nanosleep(64);
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile in shared memory, rows of 128 bytes, 128B swizzle (what the TMA box writes):
+// start address >> 4 in bits [0,14), leading byte offset (unused for swizzled K-major) = 1 in [16,30),
+// stride byte offset = 8 rows * 128 B = 1024 B >> 4 in [32,46), descriptor version 1 in [46,48),
+// layout type 2 (SWIZZLE_128B) in [61,64).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3ffffu) >> 4);
+    d |= static_cast<uint64_t>(1) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+// kind::f8f6f4 instruction descriptor: D fp32 (bits 4-5 = 1), A format bits 7-9, B format bits 10-12
+// (0 = E4M3, 1 = E5M2), both operands K-major (bits 15,16 = 0), N>>3 in bits 17-22, M>>4 in bits 24-28.
+__device__ __forceinline__ uint32_t make_idesc(int a_e5m2, int b_e5m2) {
+    return (1u << 4) | (static_cast<uint32_t>(a_e5m2) << 7) | (static_cast<uint32_t>(b_e5m2) << 10) |
+           (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+}
+
+struct TileCoord {
+    int row0;        // first global row of A / C for this tile
+    int valid_rows;  // rows of the tile that belong to the expert (<= BM)
+    int n0;          // first output column
+    int b_row0;      // first row of the stacked [E*N, K] weight block
+    int group;
+};
+
+// Maps a linear tile index to coordinates. Dense: one group of p.M rows. Grouped: the m-blocks of
+// all experts are concatenated in expert order; counts/offsets are read from device memory.
+__device__ __forceinline__ int total_m_blocks(const GemmParams& p) {
+    if (p.groups <= 1 && p.d_counts == nullptr) return (p.M + BM - 1) / BM;
+    int t = 0;
+    for (int e = 0; e < p.groups; ++e) t += (max(p.d_counts[e], 0) + BM - 1) / BM;
+    return t;
+}
+__device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, int m_blocks) {
+    TileCoord c;
+    const int nb = tile / m_blocks;
+    int mb = tile - nb * m_blocks;
+    c.n0 = nb * BN;
+    if (p.groups <= 1 && p.d_counts == nullptr) {
+        c.group = 0;
+        c.row0 = mb * BM;
+        c.valid_rows = min(BM, p.M - c.row0);
+        c.b_row0 = c.n0;
+        return c;
+    }
+    int e = 0, cnt = 0;
+    for (; e < p.groups; ++e) {
+        cnt = max(p.d_counts[e], 0);
+        const int blocks = (cnt + BM - 1) / BM;
+        if (mb < blocks) break;
+        mb -= blocks;
+    }
+    c.group = e;
+    c.row0 = p.d_offsets[e] + mb * BM;
+    c.valid_rows = min(BM, cnt - mb * BM);
+    c.b_row0 = e * p.N + c.n0;
+    return c;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ uint16_t to_bf16_bits(float v) { return __bfloat16_as_ushort(__float2bfloat16_rn(v)); }
+
+// One output value through the epilogue contract (used by the scalar store paths and by the SIMT kernel).
+__device__ __forceinline__ void store_one(const GemmParams& p, long long grow, int col, float acc, float da, float db) {
+    float v = acc * (da * db);
+    if (p.out_kind == 0) {
+        uint16_t* c = static_cast<uint16_t*>(p.C) + grow * p.ldc + col;
+        if (p.bias && p.bias_mode == 1) v += bf16_bits_to_f32(p.bias[col]);
+        uint16_t r = to_bf16_bits(v);
+        if (p.bias && p.bias_mode == 2) r = to_bf16_bits(bf16_bits_to_f32(r) + bf16_bits_to_f32(p.bias[col]));
+        *c = r;
+    } else if (p.out_kind == 1) {
+        static_cast<float*>(p.C)[grow * p.ldc + col] = v;
+    } else if (p.out_kind == 2) {
+        float* c = static_cast<float*>(p.C) + grow * p.ldc + col;
+        *c = *c + v;
+    } else {
+        uint16_t* c = static_cast<uint16_t*>(p.C) + grow * p.ldc + col;
+        *c = to_bf16_bits(bf16_bits_to_f32(*c) + v);
+    }
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;           // swizzle atoms need 1024-byte alignment
+    const uint32_t smem_a = base;
+    const uint32_t smem_b = base + STAGES * A_STAGE;
+    const uint32_t bars = smem_b + STAGES * B_STAGE;         // 8-byte mbarriers
+    const uint32_t full_bar = bars, empty_bar = bars + 8 * STAGES;
+    const uint32_t tfull_bar = bars + 16 * STAGES, tempty_bar = tfull_bar + 16, drain_bar = tempty_bar + 16;
+    uint8_t* gen = smem_raw + (base - raw);
+    volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(gen + STAGES * (A_STAGE + B_STAGE) + 16 * STAGES + 48);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(const_cast<uint32_t*>(s_tmem) + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar + 8 * a, 1);
+            mbar_init(tempty_bar + 8 * a, 4);
+        }
+        mbar_init(drain_bar, 1);
+        s_abort[0] = 0;
+        s_abort[1] = 0;                                      // stays 0: abort source for the drain waits
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t*>(s_tmem))), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+
+    const int m_blocks = total_m_blocks(p);
+    const int n_blocks = (p.N + BN - 1) / BN;
+    const int total_tiles = m_blocks * n_blocks;
+    const int k_iters = (p.K + BK - 1) / BK;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const TileCoord tc = tile_coord(p, tile, m_blocks);
+                for (int kb = 0; kb < k_iters; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(empty_bar + 8 * s, ph ^ 1, s_abort)) { ok = false; break; }
+                    mbar_expect_tx(full_bar + 8 * s, A_STAGE + B_STAGE);
+                    tma_load_2d(smem_a + s * A_STAGE, &map_a, full_bar + 8 * s, kb * BK, tc.row0);
+                    tma_load_2d(smem_b + s * B_STAGE, &map_b, full_bar + 8 * s, kb * BK, tc.b_row0);
+                }
+            }
+            if (!ok && !*s_abort) { *s_abort = 1; atomicExch(p.d_status, 0x100 | 1); }
+            if (*s_abort || !ok) {
+                // wait (bounded) for this CTA's copies still in flight
+                for (int j = max(0, it - STAGES); j < it; ++j)
+                    mbar_wait(full_bar + 8 * (j % STAGES), (j / STAGES) & 1, s_abort + 1 /*never set*/, DRAIN_NS);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(p.a_e5m2, p.b_e5m2);
+            int it = 0, local_tile = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local_tile) {
+                const int acc = local_tile & 1;
+                if (!mbar_wait(tempty_bar + 8 * acc, ((local_tile >> 1) & 1) ^ 1, s_abort)) { ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                for (int kb = 0; kb < k_iters; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(full_bar + 8 * s, (it / STAGES) & 1, s_abort)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint64_t adesc = make_smem_desc(smem_a + s * A_STAGE);
+                    const uint64_t bdesc = make_smem_desc(smem_b + s * B_STAGE);
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        // advancing 32 bytes inside the 128B swizzle atom = +2 in the (addr >> 4) field
+                        umma_f8(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                    }
+                    tcgen05_commit(empty_bar + 8 * s);     // frees the stage once these MMAs have read it
+                }
+                if (!ok) break;
+                tcgen05_commit(tfull_bar + 8 * acc);       // accumulator complete
+            }
+            if (!ok && !*s_abort) { *s_abort = 1; atomicExch(p.d_status, 0x200 | 1); }
+            if (*s_abort || !ok) {
+                tcgen05_commit(drain_bar);                 // all MMAs issued so far
+                mbar_wait(drain_bar, 0, s_abort + 1, DRAIN_NS);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue warps
+        const int quarter = warp & 3;                      // TMEM lanes this warp may read
+        const int trow = quarter * 32 + lane;
+        int local_tile = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local_tile) {
+            const int acc = local_tile & 1;
+            const TileCoord tc = tile_coord(p, tile, m_blocks);
+            if (!mbar_wait(tfull_bar + 8 * acc, (local_tile >> 1) & 1, s_abort)) { ok = false; break; }
+            tcgen05_fence_after();
+            const long long grow = static_cast<long long>(tc.row0) + trow;
+            const bool row_ok = trow < tc.valid_rows;
+            float da = 1.0f;
+            if (row_ok) {
+                if (p.d_a_row_descale) da = p.d_a_row_descale[grow];
+                else da = p.d_a_descale[p.a_descale_per_group ? tc.group : 0];
+            }
+            const float db_t = p.d_b_col_descale ? 1.0f : *p.d_b_descale;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int ch = 0; ch < BN / 32; ++ch) {
+                const int col0 = tc.n0 + ch * 32;
+                if (col0 >= p.N) break;                    // warp-uniform
+                uint32_t v[32];
+                tmem_ld32(taddr + ch * 32, v);
+                tmem_ld_wait();
+                if (!row_ok) continue;
+                const bool full = col0 + 32 <= p.N;
+                if (p.out_kind == 0 && p.c_vec && full) {
+                    uint16_t* crow = static_cast<uint16_t*>(p.C) + grow * p.ldc + col0;
+                    uint32_t w[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
+                        const float db0 = p.d_b_col_descale ? p.d_b_col_descale[col0 + 2 * j] : db_t;
+                        const float db1 = p.d_b_col_descale ? p.d_b_col_descale[col0 + 2 * j + 1] : db_t;
+                        x0 *= da * db0;
+                        x1 *= da * db1;
+                        if (p.bias_mode == 1) {
+                            const uint32_t bb = *reinterpret_cast<const uint32_t*>(p.bias + col0 + 2 * j);
+                            x0 += __uint_as_float(bb << 16);
+                            x1 += __uint_as_float(bb & 0xffff0000u);
+                            w[j] = pack_bf16x2(x0, x1);
+                        } else if (p.bias_mode == 2) {
+                            const uint32_t bb = *reinterpret_cast<const uint32_t*>(p.bias + col0 + 2 * j);
+                            const uint32_t r = pack_bf16x2(x0, x1);
+                            w[j] = pack_bf16x2(__uint_as_float(r << 16) + __uint_as_float(bb << 16),
+                                               __uint_as_float(r & 0xffff0000u) + __uint_as_float(bb & 0xffff0000u));
+                        } else {
+                            w[j] = pack_bf16x2(x0, x1);
+                        }
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(crow);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int col = col0 + j;
+                        if (col < p.N) {
+                            const float db = p.d_b_col_descale ? p.d_b_col_descale[col] : db_t;
+                            store_one(p, grow, col, __uint_as_float(v[j]), da, db);
+                        }
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar + 8 * acc);
+        }
+        if (!ok && lane == 0 && !*s_abort) { *s_abort = 1; atomicExch(p.d_status, 0x300 | 1); }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ SIMT form
+// Serves shapes the TMA path cannot address (K or lda not a multiple of 16, operands not 16-byte
+// aligned) with identical epilogue semantics. One thread per output element; correctness path only.
+__global__ void __launch_bounds__(256) k_gemm_fp8_nt_simt(const uint8_t* __restrict__ A, long long lda,
+                                                          const uint8_t* __restrict__ B, const GemmParams p) {
+    const int groups = (p.d_counts == nullptr) ? 1 : p.groups;
+    for (int g = 0; g < groups; ++g) {
+        const int rows = p.d_counts ? max(p.d_counts[g], 0) : p.M;
+        const long long row_base = p.d_counts ? p.d_offsets[g] : 0;
+        const long long total = static_cast<long long>(rows) * p.N;
+        for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+             idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+            const long long m = idx / p.N;
+            const int n = static_cast<int>(idx - m * p.N);
+            const uint8_t* a = A + (row_base + m) * lda;
+            const uint8_t* b = B + (static_cast<long long>(g) * p.N + n) * p.K;
+            float acc = 0.0f;
+            for (int k = 0; k < p.K; ++k) {
+                const float av = p.a_e5m2 ? fp8_to_f32<true>(a[k]) : fp8_to_f32<false>(a[k]);
+                const float bv = p.b_e5m2 ? fp8_to_f32<true>(b[k]) : fp8_to_f32<false>(b[k]);
+                acc = fmaf(av, bv, acc);
+            }
+            const long long grow = row_base + m;
+            const float da = p.d_a_row_descale ? p.d_a_row_descale[grow] : p.d_a_descale[p.a_descale_per_group ? g : 0];
+            const float db = p.d_b_col_descale ? p.d_b_col_descale[n] : *p.d_b_descale;
+            store_one(p, grow, n, acc, da, db);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ host side
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// 2-D byte tensor [rows, K] with row pitch `pitch`, box {BK, box_rows}, 128B swizzle, zero fill out of bounds.
+int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, long long pitch, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { set_error("cuTensorMapEncodeTiled entry point not available"); return CF_ERR_CUDA; }
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r)); return CF_ERR_CUDA; }
+    return CF_OK;
+}
+
+}  // namespace
+
+int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const void* d_B, long long b_rows,
+                       GemmParams p, int tile_upper_bound, cudaStream_t st) {
+    if (p.N <= 0 || p.K <= 0 || tile_upper_bound <= 0) return CF_OK;
+    const int rc = require_sm100();
+    if (rc != CF_OK) return rc;
+    const uintptr_t aa = reinterpret_cast<uintptr_t>(d_A), ba = reinterpret_cast<uintptr_t>(d_B);
+    const bool tma_ok = (aa % 16 == 0) && (ba % 16 == 0) && (lda % 16 == 0) && (p.K % 16 == 0);
+    const uintptr_t ca = reinterpret_cast<uintptr_t>(p.C);
+    p.c_vec = (p.out_kind == 0) && (ca % 16 == 0) && (p.ldc % 8 == 0) &&
+              (p.bias == nullptr || reinterpret_cast<uintptr_t>(p.bias) % 4 == 0);
+    if (!p.bias) p.bias_mode = 0;
+    if (!tma_ok) {
+        const int grid = sm_count() * 4;
+        k_gemm_fp8_nt_simt<<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(d_A), lda, static_cast<const uint8_t*>(d_B), p);
+        CF_LAUNCH_CHECK("gemm_fp8_nt_simt");
+        return CF_OK;
+    }
+    CUtensorMap map_a, map_b;
+    int r = make_map(&map_a, d_A, a_rows, p.K, lda, BM);
+    if (r != CF_OK) return r;
+    r = make_map(&map_b, d_B, b_rows, p.K, p.K, BN);
+    if (r != CF_OK) return r;
+    static std::once_flag attr_once[64];
+    int dev = 0;
+    CF_CUDA(cudaGetDevice(&dev));
+    cudaError_t attr_err = cudaSuccess;
+    std::call_once(attr_once[dev & 63], [&] {
+        attr_err = cudaFuncSetAttribute(k_gemm_fp8_nt, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    });
+    if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(k_gemm_fp8_nt)");
+    const int sms = sm_count();
+    const int grid = tile_upper_bound < sms ? tile_upper_bound : sms;
+    k_gemm_fp8_nt<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+    CF_LAUNCH_CHECK("gemm_fp8_nt");
+    return CF_OK;
+}
+
+int gemm_tile_m() { return BM; }
+int gemm_tile_n() { return BN; }
+
+}  // namespace cf

@@ -1,0 +1,39 @@
+// Internal launch interface of the tcgen05 FP8 GEMM (shared by the API and MoE translation units).
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace cf {
+
+struct GemmParams {
+    int groups = 1;                 // experts stacked along the rows of B; 1 = dense
+    int M = 0;                      // dense row count (ignored when d_counts is set)
+    int N = 0;                      // output columns (per expert)
+    int K = 0;
+    const int* d_counts = nullptr;  // grouped: rows per expert (device)
+    const int* d_offsets = nullptr; // grouped: first compact row per expert (device)
+    const float* d_a_descale = nullptr;
+    int a_descale_per_group = 0;
+    const float* d_b_descale = nullptr;
+    const float* d_a_row_descale = nullptr;
+    const float* d_b_col_descale = nullptr;
+    void* C = nullptr;
+    long long ldc = 0;
+    int out_kind = 0;               // 0 bf16 store, 1 f32 store, 2 f32 +=, 3 bf16 +=
+    const uint16_t* bias = nullptr;
+    int bias_mode = 0;
+    int c_vec = 0;                  // filled by the launcher
+    int a_e5m2 = 0;
+    int b_e5m2 = 0;
+    int* d_status = nullptr;        // context status word (bounded-wait failures)
+};
+
+// a_rows / b_rows: row extents of the two byte matrices as the tensor maps should see them.
+// tile_upper_bound: number of (128 x 256) tiles at most (sizes the persistent grid).
+int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const void* d_B, long long b_rows,
+                       GemmParams p, int tile_upper_bound, cudaStream_t st);
+int gemm_tile_m();
+int gemm_tile_n();
+
+struct Ctx;
+}  // namespace cf

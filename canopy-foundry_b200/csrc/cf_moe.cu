@@ -1,0 +1,473 @@
+// Elementwise neighbours of the FP8 GEMMs and the MoE routing / permute / combine kernels,
+// plus the tensor-core grouped expert forward that strings them together.
+#include "cf_common.cuh"
+#include "cf_gemm.cuh"
+
+namespace cf {
+
+struct Ctx;
+// accessors implemented in cf_api.cu
+int* ctx_status(cf_ctx* c);
+void* ctx_workspace(cf_ctx* c, size_t* bytes);
+
+namespace {
+
+constexpr int kT = 256;
+
+__device__ __forceinline__ uint16_t f2bf(float v) { return __bfloat16_as_ushort(__float2bfloat16_rn(v)); }
+
+// kernels/activations.cu:11-21
+__device__ __forceinline__ float stable_sigmoid(float x) {
+    if (x >= 0.0f) return __fdiv_rn(1.0f, 1.0f + expf(-x));
+    const float e = expf(x);
+    return __fdiv_rn(e, 1.0f + e);
+}
+// kernels/moe.cu:513-514
+__device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + erff(v * 0.7071067811865476f)); }
+
+unsigned grid_for(size_t work_items, int per_block) {
+    const size_t b = (work_items + per_block - 1) / per_block;
+    const size_t cap = static_cast<size_t>(sm_count()) * 16;
+    return static_cast<unsigned>(b < 1 ? 1 : (b < cap ? b : cap));
+}
+
+// ---- bias ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kT) k_bias_add(uint16_t* __restrict__ io, const uint16_t* __restrict__ bias, int rows,
+                                                 int cols, long long stride, int base) {
+    const long long total = static_cast<long long>(rows) * cols;
+    for (long long i = static_cast<long long>(blockIdx.x) * kT + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * kT) {
+        const long long r = i / cols;
+        const int c = static_cast<int>(i - r * cols);
+        uint16_t* p = io + r * stride + base + c;
+        *p = f2bf(bf16_bits_to_f32(*p) + bf16_bits_to_f32(bias[c]));
+    }
+}
+
+// ---- SwiGLU / GELU: 8 elements (16 bytes) per thread where alignment allows ---------------------
+template <int OP>   // 0 = swiglu(gate, up), 1 = gelu(x)
+__global__ void __launch_bounds__(kT) k_act(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b,
+                                            uint16_t* __restrict__ out, size_t n, int vec) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * kT;
+    size_t i = static_cast<size_t>(blockIdx.x) * kT + threadIdx.x;
+    const size_t nvec = vec ? n / 8 : 0;
+    for (; i < nvec; i += stride) {
+        const uint4 va = *reinterpret_cast<const uint4*>(a + i * 8);
+        uint4 vb = make_uint4(0, 0, 0, 0);
+        if (OP == 0) vb = *reinterpret_cast<const uint4*>(b + i * 8);
+        const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+        uint32_t wo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float a0 = __uint_as_float(wa[j] << 16), a1 = __uint_as_float(wa[j] & 0xffff0000u);
+            float r0, r1;
+            if (OP == 0) {
+                const float b0 = __uint_as_float(wb[j] << 16), b1 = __uint_as_float(wb[j] & 0xffff0000u);
+                r0 = a0 * stable_sigmoid(a0) * b0;
+                r1 = a1 * stable_sigmoid(a1) * b1;
+            } else {
+                r0 = gelu_erf(a0);
+                r1 = gelu_erf(a1);
+            }
+            wo[j] = static_cast<uint32_t>(f2bf(r0)) | (static_cast<uint32_t>(f2bf(r1)) << 16);
+        }
+        *reinterpret_cast<uint4*>(out + i * 8) = make_uint4(wo[0], wo[1], wo[2], wo[3]);
+    }
+    for (size_t e = nvec * 8 + static_cast<size_t>(blockIdx.x) * kT + threadIdx.x; e < n; e += stride) {
+        const float x = bf16_bits_to_f32(a[e]);
+        out[e] = f2bf(OP == 0 ? x * stable_sigmoid(x) * bf16_bits_to_f32(b[e]) : gelu_erf(x));
+    }
+}
+
+// ---- routing: softmax -> hard top-k -> renormalise; one thread per row ---------------------------
+// kernels/cross_entropy.cu:167-191 (max-subtract, expf, * 1/sum) then kernels/moe.cu:374-407.
+__global__ void __launch_bounds__(128) k_topk_route(float* __restrict__ scores, float* __restrict__ row_sum_save,
+                                                    float* __restrict__ scores_save, int rows, int E, int top_k,
+                                                    int normalize) {
+    const int row = blockIdx.x * 128 + threadIdx.x;
+    if (row >= rows) return;
+    float* s = scores + static_cast<size_t>(row) * E;
+    float mx = -3.402823466e+38f;
+    for (int e = 0; e < E; ++e) mx = fmaxf(mx, s[e]);
+    float sum = 0.0f;
+    for (int e = 0; e < E; ++e) sum += expf(s[e] - mx);
+    const float inv = __fdiv_rn(1.0f, sum);
+    for (int e = 0; e < E; ++e) {
+        const float pr = expf(s[e] - mx) * inv;
+        s[e] = pr;
+        if (scores_save) scores_save[static_cast<size_t>(row) * E + e] = pr;
+    }
+    unsigned long long kept = 0;       // E <= 64
+    const int k = top_k < E ? top_k : E;
+    for (int pick = 0; pick < k; ++pick) {
+        int best = -1;
+        float best_v = -1.0f;
+        for (int e = 0; e < E; ++e)
+            if (!((kept >> e) & 1ull) && s[e] > best_v) { best_v = s[e]; best = e; }
+        if (best < 0) break;
+        kept |= 1ull << best;
+    }
+    float ks = 0.0f;
+    for (int e = 0; e < E; ++e) if ((kept >> e) & 1ull) ks += s[e];
+    if (row_sum_save) row_sum_save[row] = ks;
+    const float invk = (normalize && ks > 0.0f) ? __fdiv_rn(1.0f, ks) : 1.0f;
+    for (int e = 0; e < E; ++e) s[e] = ((kept >> e) & 1ull) ? s[e] * invk : 0.0f;
+}
+
+// ---- dispatch lists: one block per expert, ordered compaction (ascending rows) -------------------
+__global__ void __launch_bounds__(1024) k_build_row_lists(const float* __restrict__ rw, int* __restrict__ counts,
+                                                          int* __restrict__ row_indices, int rows, int E) {
+    __shared__ int s_warp[32];
+    __shared__ int s_base;
+    const int e = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) s_base = 0;
+    __syncthreads();
+    for (int r0 = 0; r0 < rows; r0 += 1024) {
+        const int r = r0 + threadIdx.x;
+        const bool sel = r < rows && rw[static_cast<size_t>(r) * E + e] > 0.0f;
+        const unsigned m = __ballot_sync(0xffffffffu, sel);
+        const int before = __popc(m & ((1u << lane) - 1u));
+        if (lane == 0) s_warp[warp] = __popc(m);
+        __syncthreads();
+        int wbase = 0;
+        for (int w = 0; w < warp; ++w) wbase += s_warp[w];
+        const int base = s_base;
+        if (sel) row_indices[static_cast<size_t>(e) * rows + base + wbase + before] = r;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int t = 0;
+            for (int w = 0; w < 32; ++w) t += s_warp[w];
+            s_base = base + t;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) counts[e] = s_base;
+}
+
+__global__ void k_offsets(const int* counts, int* offsets, int E) {
+    int acc = 0;
+    for (int e = 0; e < E; ++e) { offsets[e] = acc; acc += counts[e]; }
+}
+
+// ---- row gather (permute). blockIdx.y = expert for the all-experts form --------------------------
+// Copies rows of `width_bytes`; 16-byte chunks when vec, bytes otherwise.
+__global__ void __launch_bounds__(kT) k_gather_rows(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                                    const int* __restrict__ row_indices, const int* __restrict__ counts,
+                                                    const int* __restrict__ offsets, int n_rows_host, int rows_stride,
+                                                    long long width_bytes, int vec) {
+    const int e = blockIdx.y;
+    const int n_rows = counts ? counts[e] : n_rows_host;
+    const long long dst_row0 = offsets ? offsets[e] : 0;
+    const int* idx = row_indices + static_cast<size_t>(e) * rows_stride;
+    if (vec) {
+        const long long cpr = width_bytes / 16;
+        const long long total = static_cast<long long>(n_rows) * cpr;
+        for (long long i = static_cast<long long>(blockIdx.x) * kT + threadIdx.x; i < total;
+             i += static_cast<long long>(gridDim.x) * kT) {
+            const long long r = i / cpr, c = i - r * cpr;
+            const uint4 v = *reinterpret_cast<const uint4*>(src + static_cast<long long>(idx[r]) * width_bytes + c * 16);
+            *reinterpret_cast<uint4*>(dst + (dst_row0 + r) * width_bytes + c * 16) = v;
+        }
+    } else {
+        const long long total = static_cast<long long>(n_rows) * width_bytes;
+        for (long long i = static_cast<long long>(blockIdx.x) * kT + threadIdx.x; i < total;
+             i += static_cast<long long>(gridDim.x) * kT) {
+            const long long r = i / width_bytes, c = i - r * width_bytes;
+            dst[(dst_row0 + r) * width_bytes + c] = src[static_cast<long long>(idx[r]) * width_bytes + c];
+        }
+    }
+}
+
+// ---- unpermute + weighted combine for one expert: mixed[row] = bf16(mixed[row] + w * compact[i]) ----
+__global__ void __launch_bounds__(kT) k_scatter_acc(uint16_t* __restrict__ mixed, const uint16_t* __restrict__ compact,
+                                                    const float* __restrict__ rw, const int* __restrict__ row_indices,
+                                                    const int* __restrict__ counts, const int* __restrict__ offsets,
+                                                    int n_rows_host, int expert, int E, int H, int vec) {
+    const int n_rows = counts ? counts[expert] : n_rows_host;
+    const long long c_row0 = offsets ? offsets[expert] : 0;
+    if (vec) {
+        const int cpr = H / 8;
+        const long long total = static_cast<long long>(n_rows) * cpr;
+        for (long long i = static_cast<long long>(blockIdx.x) * kT + threadIdx.x; i < total;
+             i += static_cast<long long>(gridDim.x) * kT) {
+            const long long r = i / cpr;
+            const int c = static_cast<int>(i - r * cpr);
+            const long long row = row_indices[r];
+            const float w = rw[row * E + expert];
+            const uint4 t = *reinterpret_cast<const uint4*>(compact + (c_row0 + r) * H + c * 8);
+            uint4* mp = reinterpret_cast<uint4*>(mixed + row * H + c * 8);
+            const uint4 m = *mp;
+            const uint32_t tw[4] = {t.x, t.y, t.z, t.w}, mw[4] = {m.x, m.y, m.z, m.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float r0 = __uint_as_float(mw[j] << 16) + w * __uint_as_float(tw[j] << 16);
+                const float r1 = __uint_as_float(mw[j] & 0xffff0000u) + w * __uint_as_float(tw[j] & 0xffff0000u);
+                o[j] = static_cast<uint32_t>(f2bf(r0)) | (static_cast<uint32_t>(f2bf(r1)) << 16);
+            }
+            *mp = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    } else {
+        const long long total = static_cast<long long>(n_rows) * H;
+        for (long long i = static_cast<long long>(blockIdx.x) * kT + threadIdx.x; i < total;
+             i += static_cast<long long>(gridDim.x) * kT) {
+            const long long r = i / H;
+            const int h = static_cast<int>(i - r * H);
+            const long long row = row_indices[r];
+            const float w = rw[row * E + expert];
+            uint16_t* d = mixed + row * H + h;
+            *d = f2bf(bf16_bits_to_f32(*d) + w * bf16_bits_to_f32(compact[(c_row0 + r) * H + h]));
+        }
+    }
+}
+
+// ---- dense combine: mixed[row,:] += rw[row,e] * term[row,:] -----------------------------------------
+__global__ void __launch_bounds__(kT) k_scale_acc(uint16_t* __restrict__ mixed, const uint16_t* __restrict__ term,
+                                                  const float* __restrict__ rw, long long rows, int expert, int E, int H) {
+    const long long total = rows * H;
+    for (long long i = static_cast<long long>(blockIdx.x) * kT + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * kT) {
+        const long long r = i / H;
+        const float w = rw[r * E + expert];
+        mixed[i] = f2bf(bf16_bits_to_f32(mixed[i]) + w * bf16_bits_to_f32(term[i]));
+    }
+}
+
+// ---- GELU of the fc_in output over the valid compact rows: amax pass and two-term E4M3 split --------
+// g = gelu(h) is represented as hi + lo with hi = e4m3(g*s), lo = e4m3((g*s - dec(hi))): both terms use
+// the same scale, so one accumulating GEMM over [hi | lo] reproduces g to ~2^-8 relative.
+__device__ __forceinline__ long long valid_elems(const int* counts, int E, int width) {
+    long long t = 0;
+    for (int e = 0; e < E; ++e) t += max(counts[e], 0);
+    return t * width;
+}
+__global__ void __launch_bounds__(kT) k_gelu_amax(const uint16_t* __restrict__ h, const int* __restrict__ counts, int E,
+                                                  int width, float* __restrict__ amax) {
+    const long long n = valid_elems(counts, E, width);
+    float local = 0.0f;
+    for (long long i = static_cast<long long>(blockIdx.x) * kT + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * kT)
+        local = fmaxf(local, fabsf(gelu_erf(bf16_bits_to_f32(h[i]))));
+    block_amax_commit(local, amax);
+}
+__global__ void __launch_bounds__(kT) k_gelu_split(const uint16_t* __restrict__ h, const int* __restrict__ counts, int E,
+                                                   int width, const float* __restrict__ scale, uint8_t* __restrict__ hi,
+                                                   uint8_t* __restrict__ lo) {
+    const long long n = valid_elems(counts, E, width);
+    const float s = *scale;
+    for (long long i = static_cast<long long>(blockIdx.x) * kT + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * kT) {
+        const float g = gelu_erf(bf16_bits_to_f32(h[i])) * s;
+        const uint8_t c = cvt_fp8<false>(g);
+        hi[i] = c;
+        lo[i] = cvt_fp8<false>(g - fp8_to_f32<false>(c));
+    }
+}
+__global__ void k_mul_scalars(const float* a, const float* b, float* out) { *out = *a * *b; }
+
+}  // namespace
+}  // namespace cf
+
+using namespace cf;
+
+#define CF_TRY(call)                    \
+    do {                                \
+        const int rc__ = (call);        \
+        if (rc__ != CF_OK) return rc__; \
+    } while (0)
+
+extern "C" {
+
+int cf_bias_add_strided_bf16(void* d_inout, const void* d_bias, int rows, int cols, int row_stride, int base, void* stream) {
+    CF_REQUIRE(rows >= 0 && cols >= 0 && base >= 0 && row_stride >= 0, "cf_bias_add_strided_bf16: negative argument");
+    if (rows == 0 || cols == 0) return CF_OK;
+    CF_REQUIRE(d_inout && d_bias, "cf_bias_add_strided_bf16: null pointer");
+    k_bias_add<<<grid_for(static_cast<size_t>(rows) * cols, kT * 4), kT, 0, as_stream(stream)>>>(
+        static_cast<uint16_t*>(d_inout), static_cast<const uint16_t*>(d_bias), rows, cols, row_stride, base);
+    CF_LAUNCH_CHECK("bias_add_strided_bf16");
+    return CF_OK;
+}
+
+int cf_swiglu_forward(const void* d_gate, const void* d_up, void* d_out, int n, void* stream) {
+    // kernels/activations.cu:61-72: negative count and null tensors are argument errors
+    CF_REQUIRE(n >= 0, "swiglu element count must be non-negative");
+    if (n == 0) return CF_OK;
+    CF_REQUIRE(d_gate && d_up && d_out, "swiglu received a null tensor pointer");
+    const int vec = ((reinterpret_cast<uintptr_t>(d_gate) | reinterpret_cast<uintptr_t>(d_up) |
+                      reinterpret_cast<uintptr_t>(d_out)) % 16) == 0;
+    k_act<0><<<grid_for(static_cast<size_t>(n), kT * 16), kT, 0, as_stream(stream)>>>(
+        static_cast<const uint16_t*>(d_gate), static_cast<const uint16_t*>(d_up), static_cast<uint16_t*>(d_out),
+        static_cast<size_t>(n), vec);
+    CF_LAUNCH_CHECK("swiglu_forward");
+    return CF_OK;
+}
+
+int cf_gelu_forward(const void* d_x, void* d_out, size_t n, void* stream) {
+    if (n == 0) return CF_OK;
+    CF_REQUIRE(d_x && d_out, "cf_gelu_forward: null pointer");
+    const int vec = ((reinterpret_cast<uintptr_t>(d_x) | reinterpret_cast<uintptr_t>(d_out)) % 16) == 0;
+    k_act<1><<<grid_for(n, kT * 16), kT, 0, as_stream(stream)>>>(static_cast<const uint16_t*>(d_x), nullptr,
+                                                                 static_cast<uint16_t*>(d_out), n, vec);
+    CF_LAUNCH_CHECK("gelu_forward");
+    return CF_OK;
+}
+
+int cf_moe_topk_route_f32(float* d_scores, int rows, int num_experts, int top_k, void* stream, float* d_row_sum_save,
+                          float* d_scores_save, int normalize_topk) {
+    CF_REQUIRE(rows >= 0 && num_experts >= 1 && num_experts <= 64 && top_k >= 0, "cf_moe_topk_route_f32: bad shape (1 <= experts <= 64)");
+    if (rows == 0) return CF_OK;
+    CF_REQUIRE(d_scores, "cf_moe_topk_route_f32: null pointer");
+    k_topk_route<<<(rows + 127) / 128, 128, 0, as_stream(stream)>>>(d_scores, d_row_sum_save, d_scores_save, rows,
+                                                                   num_experts, top_k, normalize_topk);
+    CF_LAUNCH_CHECK("moe_topk_route_f32");
+    return CF_OK;
+}
+
+int cf_moe_build_expert_row_lists(const float* d_route_weights, int* d_counts, int* d_row_indices, int rows,
+                                  int num_experts, void* stream) {
+    CF_REQUIRE(rows >= 0 && num_experts >= 1, "cf_moe_build_expert_row_lists: bad shape");
+    CF_REQUIRE(d_counts && (rows == 0 || (d_route_weights && d_row_indices)), "cf_moe_build_expert_row_lists: null pointer");
+    k_build_row_lists<<<num_experts, 1024, 0, as_stream(stream)>>>(d_route_weights, d_counts, d_row_indices, rows, num_experts);
+    CF_LAUNCH_CHECK("moe_build_expert_row_lists");
+    return CF_OK;
+}
+
+int cf_moe_expert_offsets_from_counts(const int* d_counts, int* d_offsets, int num_experts, void* stream) {
+    CF_REQUIRE(d_counts && d_offsets && num_experts >= 1, "cf_moe_expert_offsets_from_counts: bad argument");
+    k_offsets<<<1, 1, 0, as_stream(stream)>>>(d_counts, d_offsets, num_experts);
+    CF_LAUNCH_CHECK("moe_expert_offsets_from_counts");
+    return CF_OK;
+}
+
+static int gather_rows(const void* src, void* dst, const int* idx, const int* counts, const int* offsets, int n_rows,
+                       int rows_stride, int experts, long long width_bytes, cudaStream_t st) {
+    if (n_rows == 0 || width_bytes == 0) return CF_OK;
+    const int vec = (width_bytes % 16 == 0) && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) % 16 == 0);
+    const size_t items = static_cast<size_t>(n_rows) * (vec ? width_bytes / 16 : width_bytes);
+    dim3 grid(grid_for(items, kT * 4), experts);
+    k_gather_rows<<<grid, kT, 0, st>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), idx, counts, offsets,
+                                      n_rows, rows_stride, width_bytes, vec);
+    CF_LAUNCH_CHECK("moe_gather_rows");
+    return CF_OK;
+}
+
+int cf_moe_gather_rows_u8(const uint8_t* d_src, uint8_t* d_dst, const int* d_row_indices, int n_rows, int width, void* stream) {
+    CF_REQUIRE(n_rows >= 0 && width >= 0, "cf_moe_gather_rows_u8: negative shape");
+    CF_REQUIRE(n_rows == 0 || width == 0 || (d_src && d_dst && d_row_indices), "cf_moe_gather_rows_u8: null pointer");
+    return gather_rows(d_src, d_dst, d_row_indices, nullptr, nullptr, n_rows, 0, 1, width, as_stream(stream));
+}
+int cf_moe_gather_rows_bf16(const void* d_src, void* d_dst, const int* d_row_indices, int n_rows, int width, void* stream) {
+    CF_REQUIRE(n_rows >= 0 && width >= 0, "cf_moe_gather_rows_bf16: negative shape");
+    CF_REQUIRE(n_rows == 0 || width == 0 || (d_src && d_dst && d_row_indices), "cf_moe_gather_rows_bf16: null pointer");
+    return gather_rows(d_src, d_dst, d_row_indices, nullptr, nullptr, n_rows, 0, 1, 2ll * width, as_stream(stream));
+}
+int cf_moe_gather_all_u8(const uint8_t* d_src, uint8_t* d_dst, const int* d_row_indices, const int* d_counts,
+                         const int* d_offsets, int rows, int num_experts, int width, void* stream) {
+    CF_REQUIRE(rows >= 0 && width >= 0 && num_experts >= 1, "cf_moe_gather_all_u8: bad shape");
+    if (rows == 0 || width == 0) return CF_OK;
+    CF_REQUIRE(d_src && d_dst && d_row_indices && d_counts && d_offsets, "cf_moe_gather_all_u8: null pointer");
+    return gather_rows(d_src, d_dst, d_row_indices, d_counts, d_offsets, rows, rows, num_experts, width, as_stream(stream));
+}
+
+static int scatter_acc(void* mixed, const void* compact, const float* rw, const int* idx, const int* counts,
+                       const int* offsets, int n_rows, int expert, int E, int H, cudaStream_t st) {
+    if (n_rows == 0 || H == 0) return CF_OK;
+    const int vec = (H % 8 == 0) && ((reinterpret_cast<uintptr_t>(mixed) | reinterpret_cast<uintptr_t>(compact)) % 16 == 0);
+    const size_t items = static_cast<size_t>(n_rows) * (vec ? H / 8 : H);
+    k_scatter_acc<<<grid_for(items, kT * 2), kT, 0, st>>>(static_cast<uint16_t*>(mixed), static_cast<const uint16_t*>(compact),
+                                                         rw, idx, counts, offsets, n_rows, expert, E, H, vec);
+    CF_LAUNCH_CHECK("moe_scatter_accumulate_rows_bf16");
+    return CF_OK;
+}
+
+int cf_moe_scatter_accumulate_rows_bf16(void* d_mixed, const void* d_compact, const float* d_route_weights,
+                                        const int* d_row_indices, int n_rows, int expert_idx, int num_experts, int H,
+                                        void* stream) {
+    CF_REQUIRE(n_rows >= 0 && H >= 0 && expert_idx >= 0 && expert_idx < num_experts, "cf_moe_scatter_accumulate_rows_bf16: bad argument");
+    CF_REQUIRE(n_rows == 0 || H == 0 || (d_mixed && d_compact && d_route_weights && d_row_indices), "cf_moe_scatter_accumulate_rows_bf16: null pointer");
+    return scatter_acc(d_mixed, d_compact, d_route_weights, d_row_indices, nullptr, nullptr, n_rows, expert_idx, num_experts, H, as_stream(stream));
+}
+
+int cf_moe_combine_all_bf16(void* d_mixed, const void* d_compact, const float* d_route_weights, const int* d_row_indices,
+                            const int* d_counts, const int* d_offsets, int rows, int num_experts, int H, void* stream) {
+    CF_REQUIRE(rows >= 0 && H >= 0 && num_experts >= 1, "cf_moe_combine_all_bf16: bad shape");
+    if (rows == 0 || H == 0) return CF_OK;
+    CF_REQUIRE(d_mixed && d_compact && d_route_weights && d_row_indices && d_counts && d_offsets, "cf_moe_combine_all_bf16: null pointer");
+    for (int e = 0; e < num_experts; ++e)
+        CF_TRY(scatter_acc(d_mixed, d_compact, d_route_weights, d_row_indices + static_cast<size_t>(e) * rows, d_counts,
+                           d_offsets, rows, e, num_experts, H, as_stream(stream)));
+    return CF_OK;
+}
+
+int cf_moe_scale_accumulate_bf16(void* d_mixed, const void* d_term, const float* d_route_weights, int rows, int expert_idx,
+                                 int num_experts, int H, void* stream) {
+    CF_REQUIRE(rows >= 0 && H >= 0 && expert_idx >= 0 && expert_idx < num_experts, "cf_moe_scale_accumulate_bf16: bad argument");
+    if (rows == 0 || H == 0) return CF_OK;
+    CF_REQUIRE(d_mixed && d_term && d_route_weights, "cf_moe_scale_accumulate_bf16: null pointer");
+    k_scale_acc<<<grid_for(static_cast<size_t>(rows) * H, kT * 4), kT, 0, as_stream(stream)>>>(
+        static_cast<uint16_t*>(d_mixed), static_cast<const uint16_t*>(d_term), d_route_weights, rows, expert_idx, num_experts, H);
+    CF_LAUNCH_CHECK("moe_scale_accumulate_bf16");
+    return CF_OK;
+}
+
+int cf_moe_grouped_expert_forward_fp8(cf_ctx* ctx, const void* d_hidden, const float* d_fcin_descale, int fcin_is_e5m2,
+                                      const float* d_route_weights, const int* d_counts, const int* d_offsets,
+                                      const int* d_row_indices, const void* d_fc_in_w, const float* d_fc_in_descale,
+                                      const void* d_fc_out_w, const float* d_fc_out_descale, void* d_mixed, int rows,
+                                      int H, int Ie, int num_experts, int total_selected_rows, void* stream) {
+    CF_REQUIRE(ctx != nullptr, "cf_moe_grouped_expert_forward_fp8: null context");
+    CF_REQUIRE(rows >= 0 && H > 0 && Ie > 0 && num_experts >= 1 && total_selected_rows >= 0, "cf_moe_grouped_expert_forward_fp8: bad shape");
+    if (rows == 0 || total_selected_rows == 0) return CF_OK;
+    CF_REQUIRE(d_hidden && d_fcin_descale && d_route_weights && d_counts && d_offsets && d_row_indices && d_fc_in_w &&
+               d_fc_in_descale && d_fc_out_w && d_fc_out_descale && d_mixed, "cf_moe_grouped_expert_forward_fp8: null pointer");
+    CF_REQUIRE(H % 16 == 0 && Ie % 16 == 0, "cf_moe_grouped_expert_forward_fp8: H and Ie must be multiples of 16");
+    const size_t T = static_cast<size_t>(total_selected_rows);
+    // workspace carve-up (256-byte aligned pieces)
+    auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
+    const size_t b_xc = up(T * H), b_hc = up(T * Ie * 2), b_g = up(T * Ie * 2), b_yc = up(T * H * 2), b_sc = 256;
+    size_t have = 0;
+    uint8_t* ws = static_cast<uint8_t*>(ctx_workspace(ctx, &have));
+    if (have < b_xc + b_hc + b_g + b_yc + b_sc) {
+        set_error("cf_moe_grouped_expert_forward_fp8: needs %zu bytes of context workspace, %zu reserved",
+                  b_xc + b_hc + b_g + b_yc + b_sc, have);
+        return CF_ERR_LIMIT;
+    }
+    uint8_t* xc = ws;
+    uint16_t* hc = reinterpret_cast<uint16_t*>(ws + b_xc);
+    uint8_t* g8 = ws + b_xc + b_hc;                 // [T, 2*Ie]: rows of hi | lo halves are stored as two planes
+    uint16_t* yc = reinterpret_cast<uint16_t*>(ws + b_xc + b_hc + b_g);
+    float* sc = reinterpret_cast<float*>(ws + b_xc + b_hc + b_g + b_yc);   // [0] amax [4] scale [8] descale [12] descale*wout
+    cudaStream_t st = as_stream(stream);
+
+    CF_TRY(cf_moe_gather_all_u8(static_cast<const uint8_t*>(d_hidden), xc, d_row_indices, d_counts, d_offsets, rows,
+                                num_experts, H, stream));
+    CF_TRY(cf_gemm_fp8_nt_grouped(ctx, num_experts, total_selected_rows, Ie, H, d_counts, d_offsets, xc, H, fcin_is_e5m2,
+                                  d_fcin_descale, 0, d_fc_in_w, d_fc_in_descale, hc, Ie, stream));
+    CF_CUDA(cudaMemsetAsync(sc, 0, sizeof(float), st));
+    const unsigned eg = grid_for(T * Ie, kT * 8);
+    k_gelu_amax<<<eg, kT, 0, st>>>(hc, d_counts, num_experts, Ie, sc);
+    CF_LAUNCH_CHECK("moe_gelu_amax");
+    CF_TRY(cf_fp8_scale_from_amax(sc, CF_E4M3_MAX, sc + 4, sc + 8, stream));
+    uint8_t* g_hi = g8;
+    uint8_t* g_lo = g8 + T * Ie;
+    k_gelu_split<<<eg, kT, 0, st>>>(hc, d_counts, num_experts, Ie, sc + 4, g_hi, g_lo);
+    CF_LAUNCH_CHECK("moe_gelu_split");
+    // y = dG*dWout * (hi . W^T + lo . W^T): the second launch accumulates into the first one's bf16 result
+    CF_TRY(cf_gemm_fp8_nt_grouped(ctx, num_experts, total_selected_rows, H, Ie, d_counts, d_offsets, g_hi, Ie, 0, sc + 8, 0,
+                                  d_fc_out_w, d_fc_out_descale, yc, H, stream));
+    {
+        GemmParams p;
+        p.groups = num_experts; p.N = H; p.K = Ie;
+        p.d_counts = d_counts; p.d_offsets = d_offsets;
+        p.d_a_descale = sc + 8; p.d_b_descale = d_fc_out_descale;
+        p.C = yc; p.ldc = H; p.out_kind = 3;
+        p.d_status = ctx_status(ctx);
+        const int m_blocks = (total_selected_rows + gemm_tile_m() - 1) / gemm_tile_m() + num_experts;
+        CF_TRY(launch_gemm_fp8_nt(g_lo, Ie, total_selected_rows, d_fc_out_w, static_cast<long long>(num_experts) * H, p,
+                                  m_blocks * ((H + gemm_tile_n() - 1) / gemm_tile_n()), st));
+    }
+    return cf_moe_combine_all_bf16(d_mixed, yc, d_route_weights, d_row_indices, d_counts, d_offsets, rows, num_experts, H, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,319 @@
+"""Operator mirror of the reference's FP8 / MoE interface on torch CUDA tensors.
+
+Function names, argument order and meaning follow include/ida_native/kernels.hpp:983-1052 (FP8),
+:313-423 (MoE) and the file-static helpers of src/trainer.cu (lt_gemm_fp8_nt :4498, fp8_quant_act
+:4732, refresh_fp8_weights :4694). torch supplies device memory and streams only; every operator
+runs in libcanopy_fp8.so on the current torch stream. A failing call raises CanopyError, where the
+reference throws std::runtime_error.
+"""
+import ctypes as C
+
+import torch
+
+from . import _capi
+from ._capi import E4M3_MAX, E5M2_MAX, CanopyError, check
+
+__all__ = [
+    "E4M3_MAX", "E5M2_MAX", "CanopyError", "Fp8Ctx", "ActSlot", "Fp8Weight",
+    "fp8_amax_bf16", "fp8_scale_from_amax", "fp8_quantize_e4m3", "fp8_quantize_e5m2",
+    "fp8_quantize_e4m3_record", "fp8_quantize_e5m2_record", "fp8_update_delayed_scale",
+    "fp8_quantize_transpose_e4m3", "fp8_quant_and_transpose_e4m3", "transpose_u8", "fp8_clip_probe",
+    "fp8_elem_clip_count", "fp8_pack_bf16_e4m3_raw", "fp8_pack_bf16_e4m3_raw_and_dequant",
+    "fp8_unpack_e4m3_raw_bf16", "lt_gemm_fp8_nt", "lt_gemm_fp8_tn_accum_f32", "gemm_fp8_nt_grouped",
+    "fp8_quant_act", "refresh_fp8_weight", "fp8_linear_forward", "bias_add_strided_bf16", "swiglu_forward",
+    "gelu_forward", "moe_topk_route_f32", "moe_build_expert_row_lists", "moe_expert_offsets_from_counts",
+    "moe_gather_rows_u8", "moe_gather_rows_bf16", "moe_scatter_accumulate_rows_bf16",
+    "moe_scale_accumulate_bf16", "moe_gather_all_u8", "moe_combine_all_bf16",
+    "moe_grouped_expert_forward_fp8", "launch_count",
+]
+
+
+def _s():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t):
+    if t is None:
+        return None
+    assert t.is_cuda, "device tensor expected"
+    return C.c_void_p(t.data_ptr())
+
+
+def _L():
+    return _capi.lib()
+
+
+_rt = None
+
+
+def _cudart():
+    """The CUDA runtime torch already loaded (used only for debug read-backs of slot scalars)."""
+    global _rt
+    if _rt is None:
+        for name in ("libcudart.so.12", "libcudart.so.13", "libcudart.so"):
+            try:
+                _rt = C.CDLL(name)
+                break
+            except OSError:
+                continue
+        if _rt is None:
+            raise ImportError("libcudart not found")
+        _rt.cudaMemcpy.restype = C.c_int
+    return _rt
+
+
+def launch_count():
+    return int(_L().cf_launch_count())
+
+
+# ---------------------------------------------------------------- quantize / cast
+def fp8_amax_bf16(x, amax):
+    check(_L().cf_fp8_amax_bf16(_p(x), x.numel(), _p(amax), _s()))
+
+
+def fp8_scale_from_amax(amax, fp8_max, scale, descale):
+    check(_L().cf_fp8_scale_from_amax(_p(amax), fp8_max, _p(scale), _p(descale), _s()))
+
+
+def fp8_quantize_e4m3(x, out, scale, n=None):
+    check(_L().cf_fp8_quantize_e4m3(_p(x), _p(out), _p(scale), x.numel() if n is None else n, _s()))
+
+
+def fp8_quantize_e5m2(x, out, scale, n=None):
+    check(_L().cf_fp8_quantize_e5m2(_p(x), _p(out), _p(scale), x.numel() if n is None else n, _s()))
+
+
+def fp8_quantize_e4m3_record(x, out, scale, amax, n=None):
+    check(_L().cf_fp8_quantize_e4m3_record(_p(x), _p(out), _p(scale), _p(amax), x.numel() if n is None else n, _s()))
+
+
+def fp8_quantize_e5m2_record(x, out, scale, amax, n=None):
+    check(_L().cf_fp8_quantize_e5m2_record(_p(x), _p(out), _p(scale), _p(amax), x.numel() if n is None else n, _s()))
+
+
+def fp8_update_delayed_scale(amax, fp8_max, scale, descale, history, history_len, cursor, count):
+    check(_L().cf_fp8_update_delayed_scale(_p(amax), fp8_max, _p(scale), _p(descale), _p(history), history_len,
+                                           _p(cursor), _p(count), _s()))
+
+
+def fp8_quantize_transpose_e4m3(w, out, scale, K, N):
+    check(_L().cf_fp8_quantize_transpose_e4m3(_p(w), _p(out), _p(scale), K, N, _s()))
+
+
+def fp8_quant_and_transpose_e4m3(x, act8, snap, scale, K, N):
+    check(_L().cf_fp8_quant_and_transpose_e4m3(_p(x), _p(act8), _p(snap), _p(scale), K, N, _s()))
+
+
+def transpose_u8(src, dst, rows, cols):
+    check(_L().cf_transpose_u8(_p(src), _p(dst), rows, cols, _s()))
+
+
+def fp8_clip_probe(amax, scale, fp8_max, stats):
+    check(_L().cf_fp8_clip_probe(_p(amax), _p(scale), fp8_max, _p(stats), _s()))
+
+
+def fp8_elem_clip_count(x, scale, fp8_max, out):
+    check(_L().cf_fp8_elem_clip_count(_p(x), _p(scale), fp8_max, x.numel(), _p(out), _s()))
+
+
+def fp8_pack_bf16_e4m3_raw(x, out, amax, scale, descale, bad_count):
+    check(_L().cf_fp8_pack_bf16_e4m3_raw(_p(x), _p(out), _p(amax), _p(scale), _p(descale), _p(bad_count), x.numel(), _s()))
+
+
+def fp8_pack_bf16_e4m3_raw_and_dequant(x, out, dequant, amax, scale, descale, bad_count):
+    check(_L().cf_fp8_pack_bf16_e4m3_raw_and_dequant(_p(x), _p(out), _p(dequant), _p(amax), _p(scale), _p(descale),
+                                                     _p(bad_count), x.numel(), _s()))
+
+
+def fp8_unpack_e4m3_raw_bf16(codes, descale, out):
+    check(_L().cf_fp8_unpack_e4m3_raw_bf16(_p(codes), _p(descale), _p(out), codes.numel(), _s()))
+
+
+# ---------------------------------------------------------------- context, slots
+class Fp8Ctx:
+    """Counterpart of the reference's Fp8Ctx (src/trainer.cu:3296-3345): owns the shared act8 scratch,
+    the scalar pool ActSlots live in and the status word of the tensor-core kernels."""
+
+    def __init__(self, act8_bytes=0):
+        h = C.c_void_p()
+        check(_L().cf_ctx_create(C.byref(h), act8_bytes))
+        self.handle = h
+        self.act8_bytes = act8_bytes
+
+    def act8_ptr(self):
+        return _L().cf_ctx_act8(self.handle)
+
+    def reserve_workspace(self, nbytes):
+        check(_L().cf_ctx_reserve_workspace(self.handle, nbytes))
+
+    def poll_status(self):
+        """Synchronises the current stream; raises CanopyError(CF_ERR_DEVICE_WAIT) if a kernel gave up a wait."""
+        check(_L().cf_ctx_poll_status(self.handle, _s()))
+
+    def close(self):
+        if self.handle:
+            _L().cf_ctx_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class ActSlot:
+    """Delayed-scaling state of one activation/gradient call site (ActSlot, src/trainer.cu:3248-3279)."""
+
+    def __init__(self, ctx, fp8_max=E4M3_MAX, calib_calls=0):
+        self.ctx = ctx
+        self.c = _capi.ActSlotStruct()
+        check(_L().cf_act_slot_init(ctx.handle, C.byref(self.c), fp8_max, calib_calls, _s()))
+
+    def _read(self, ptr, dtype=torch.float32, n=1):
+        """Debug read-back of slot scalars (device pointers owned by the context's pool)."""
+        torch.cuda.current_stream().synchronize()
+        host = torch.empty(n, dtype=dtype)
+        rc = _cudart().cudaMemcpy(C.c_void_p(host.data_ptr()), C.c_void_p(ptr), C.c_size_t(n * host.element_size()),
+                                  C.c_int(2))
+        if rc != 0:
+            raise CanopyError(_capi.CF_ERR_CUDA, f"cudaMemcpy device->host failed with {rc}")
+        return host
+
+    def scalars(self):
+        c = self.c
+        return {
+            "amax": self._read(c.amax).item(), "scale": self._read(c.scale).item(),
+            "descale": self._read(c.descale).item(), "scale_snapshot": self._read(c.scale_snapshot).item(),
+            "descale_snapshot": self._read(c.descale_snapshot).item(),
+            "history": self._read(c.history, n=8).tolist(),
+            "cursor": self._read(c.history_cursor, torch.int32).item(),
+            "count": self._read(c.history_count, torch.int32).item(),
+            "fp8_max": c.fp8_max, "init": c.init, "calib_remaining": c.calib_remaining,
+        }
+
+
+class Fp8Weight:
+    """One FP8-cached weight (Fp8Slot, src/trainer.cu:3284-3294): bf16 master plus both E4M3 layouts."""
+
+    def __init__(self, w, stored_out_major):
+        assert w.dtype == torch.bfloat16 and w.dim() == 2 and w.is_contiguous()
+        self.w = w
+        if stored_out_major:
+            self.out_dim, self.in_dim = w.shape
+        else:
+            self.in_dim, self.out_dim = w.shape
+        self.fwd8 = torch.empty(self.out_dim, self.in_dim, dtype=torch.uint8, device=w.device)
+        self.bwd8 = torch.empty(self.in_dim, self.out_dim, dtype=torch.uint8, device=w.device)
+        self.scalars = torch.zeros(12, dtype=torch.float32, device=w.device)   # 16-byte aligned amax/scale/descale
+        self.amax, self.scale, self.descale = self.scalars[0:1], self.scalars[4:5], self.scalars[8:9]
+        self.c = _capi.Fp8WeightStruct(w.data_ptr(), self.fwd8.data_ptr(), self.bwd8.data_ptr(), self.amax.data_ptr(),
+                                       self.scale.data_ptr(), self.descale.data_ptr(), self.in_dim, self.out_dim,
+                                       int(stored_out_major))
+
+
+def refresh_fp8_weight(weight, recompute_amax=True):
+    check(_L().cf_refresh_fp8_weight(C.byref(weight.c), int(recompute_amax), _s()))
+
+
+def fp8_quant_act(ctx, slot, x, out8=None, is_recompute=False, n=None):
+    dst = C.c_void_p(ctx.act8_ptr()) if out8 is None else _p(out8)
+    check(_L().cf_fp8_quant_act(ctx.handle, C.byref(slot.c), _p(x), x.numel() if n is None else n, dst, _s(),
+                                int(is_recompute)))
+
+
+# ---------------------------------------------------------------- GEMMs
+def _epi(bias, bias_mode, a_row_descale, b_col_descale):
+    if bias is None and a_row_descale is None and b_col_descale is None:
+        return None
+    return C.byref(_capi.GemmEpilogue(bias.data_ptr() if bias is not None else None, bias_mode,
+                                      a_row_descale.data_ptr() if a_row_descale is not None else None,
+                                      b_col_descale.data_ptr() if b_col_descale is not None else None))
+
+
+def lt_gemm_fp8_nt(ctx, M, N, K, A, lda, a_is_e5m2, a_descale, B, b_descale, Cout, ldc, bias=None, bias_mode=0,
+                   a_row_descale=None, b_col_descale=None):
+    """C[M,N] bf16 = (dA*dB) * A8[M,K] . B8[N,K]^T  (src/trainer.cu:4498-4534)."""
+    check(_L().cf_gemm_fp8_nt(ctx.handle, M, N, K, _p(A), lda, int(a_is_e5m2), _p(a_descale), _p(B), _p(b_descale),
+                              _p(Cout), ldc, _epi(bias, bias_mode, a_row_descale, b_col_descale), _s()))
+
+
+def lt_gemm_fp8_tn_accum_f32(ctx, M, N, K, Xt, ds_x, dYt, ds_dy, dW, ldc):
+    """dW[M,N] += (dsx*dsdy) * Xt[M,K] . dYt[N,K]^T; dW fp32 or bf16 (src/trainer.cu:4596-4691)."""
+    fn = _L().cf_gemm_fp8_tn_accum_f32 if dW.dtype == torch.float32 else _L().cf_gemm_fp8_tn_accum_bf16
+    check(fn(ctx.handle, M, N, K, _p(Xt), _p(ds_x), _p(dYt), _p(ds_dy), _p(dW), ldc, _s()))
+
+
+def gemm_fp8_nt_grouped(ctx, num_experts, max_total_rows, N, K, counts, offsets, A, lda, a_is_e5m2, a_descale,
+                        per_expert_a_descale, B, b_descale, Cout, ldc):
+    check(_L().cf_gemm_fp8_nt_grouped(ctx.handle, num_experts, max_total_rows, N, K, _p(counts), _p(offsets), _p(A),
+                                      lda, int(a_is_e5m2), _p(a_descale), int(per_expert_a_descale), _p(B),
+                                      _p(b_descale), _p(Cout), ldc, _s()))
+
+
+def fp8_linear_forward(ctx, slot, x, w8, w_descale, y, bias=None, bias_mode=2):
+    M, K = x.shape
+    N = w8.shape[0]
+    check(_L().cf_fp8_linear_forward(ctx.handle, C.byref(slot.c), _p(x), M, K, _p(w8), _p(w_descale), N, _p(bias),
+                                     bias_mode if bias is not None else 0, _p(y), y.stride(0), _s()))
+
+
+# ---------------------------------------------------------------- elementwise + MoE
+def bias_add_strided_bf16(inout, bias, rows, cols, row_stride, base):
+    check(_L().cf_bias_add_strided_bf16(_p(inout), _p(bias), rows, cols, row_stride, base, _s()))
+
+
+def swiglu_forward(gate, up, out, n=None):
+    check(_L().cf_swiglu_forward(_p(gate), _p(up), _p(out), gate.numel() if n is None else n, _s()))
+
+
+def gelu_forward(x, out):
+    check(_L().cf_gelu_forward(_p(x), _p(out), x.numel(), _s()))
+
+
+def moe_topk_route_f32(scores, rows, num_experts, top_k, row_sum_save=None, scores_save=None, normalize_topk=True):
+    check(_L().cf_moe_topk_route_f32(_p(scores), rows, num_experts, top_k, _s(), _p(row_sum_save), _p(scores_save),
+                                     int(normalize_topk)))
+
+
+def moe_build_expert_row_lists(route_weights, counts, row_indices, rows, num_experts):
+    check(_L().cf_moe_build_expert_row_lists(_p(route_weights), _p(counts), _p(row_indices), rows, num_experts, _s()))
+
+
+def moe_expert_offsets_from_counts(counts, offsets, num_experts):
+    check(_L().cf_moe_expert_offsets_from_counts(_p(counts), _p(offsets), num_experts, _s()))
+
+
+def moe_gather_rows_u8(src, dst, row_indices, n_rows, width):
+    check(_L().cf_moe_gather_rows_u8(_p(src), _p(dst), _p(row_indices), n_rows, width, _s()))
+
+
+def moe_gather_rows_bf16(src, dst, row_indices, n_rows, width):
+    check(_L().cf_moe_gather_rows_bf16(_p(src), _p(dst), _p(row_indices), n_rows, width, _s()))
+
+
+def moe_scatter_accumulate_rows_bf16(mixed, compact, route_weights, row_indices, n_rows, expert_idx, num_experts, H):
+    check(_L().cf_moe_scatter_accumulate_rows_bf16(_p(mixed), _p(compact), _p(route_weights), _p(row_indices), n_rows,
+                                                   expert_idx, num_experts, H, _s()))
+
+
+def moe_scale_accumulate_bf16(mixed, term, route_weights, rows, expert_idx, num_experts, H):
+    check(_L().cf_moe_scale_accumulate_bf16(_p(mixed), _p(term), _p(route_weights), rows, expert_idx, num_experts, H, _s()))
+
+
+def moe_gather_all_u8(src, dst, row_indices, counts, offsets, rows, num_experts, width):
+    check(_L().cf_moe_gather_all_u8(_p(src), _p(dst), _p(row_indices), _p(counts), _p(offsets), rows, num_experts, width, _s()))
+
+
+def moe_combine_all_bf16(mixed, compact, route_weights, row_indices, counts, offsets, rows, num_experts, H):
+    check(_L().cf_moe_combine_all_bf16(_p(mixed), _p(compact), _p(route_weights), _p(row_indices), _p(counts),
+                                       _p(offsets), rows, num_experts, H, _s()))
+
+
+def moe_grouped_expert_forward_fp8(ctx, hidden, fcin_descale, fcin_is_e5m2, route_weights, counts, offsets, row_indices,
+                                   fc_in_w, fc_in_descale, fc_out_w, fc_out_descale, mixed, rows, H, Ie, num_experts,
+                                   total_selected_rows):
+    check(_L().cf_moe_grouped_expert_forward_fp8(ctx.handle, _p(hidden), _p(fcin_descale), int(fcin_is_e5m2),
+                                                 _p(route_weights), _p(counts), _p(offsets), _p(row_indices),
+                                                 _p(fc_in_w), _p(fc_in_descale), _p(fc_out_w), _p(fc_out_descale),
+                                                 _p(mixed), rows, H, Ie, num_experts, total_selected_rows, _s()))

@@ -1,0 +1,269 @@
+/*
+ * canopy_fp8.h — C ABI of libcanopy_fp8.so, the sm_100a implementation of
+ * Canopy-Foundry's FP8 quantize-and-GEMM hot path.
+ *
+ * Conventions (they follow the reference's operator layer, include/ida_native/kernels.hpp):
+ *   - every pointer named d_* is a DEVICE pointer; scalars such as scales, amax and ring
+ *     cursors live on the device and are read at kernel time;
+ *   - `stream` is a cudaStream_t passed as void*; all work is stream-ordered, no entry
+ *     point synchronises the host unless its comment says so;
+ *   - operators allocate nothing: buffers come from the caller, workspace from a cf_ctx;
+ *   - bf16 tensors are passed as const void* / void* (2-byte elements, __nv_bfloat16 bits),
+ *     FP8 tensors as 1-byte codes (E4M3 "fn" or E5M2);
+ *   - return value: CF_OK or a CF_ERR_* code; cf_last_error() gives the text for the calling
+ *     thread. The reference's functions return void and throw std::runtime_error; the C++
+ *     shim (canopy-foundry_b200/shim) converts a non-zero status into that exception.
+ *   - the library runs on compute capability 10.x only and has no CPU or library fallback.
+ *
+ * Each declaration cites the reference interface it replaces (path:line inside the
+ * reference project).
+ */
+#ifndef CANOPY_FP8_H
+#define CANOPY_FP8_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    CF_OK = 0,
+    CF_ERR_INVALID_ARG = 1,   /* null pointer, negative size, misaligned scale pointer, ... */
+    CF_ERR_UNSUPPORTED = 2,   /* shape or device this build cannot serve */
+    CF_ERR_CUDA = 3,          /* a CUDA runtime / driver call failed; see cf_last_error() */
+    CF_ERR_DEVICE_WAIT = 4,   /* a bounded device-side wait gave up (reported by cf_ctx_poll_status) */
+    CF_ERR_LIMIT = 5          /* size beyond a documented fixed limit */
+};
+
+#define CF_E4M3_MAX 448.0f     /* src/trainer.cu:3179 */
+#define CF_E5M2_MAX 57344.0f   /* src/trainer.cu:3212 */
+
+const char* cf_last_error(void);
+/* ABI version of this header; bumped when a signature changes. */
+int cf_abi_version(void);
+
+/* ------------------------------------------------------------------ quantize / cast */
+
+/* kernels/fp8.cu:250-253, include/ida_native/kernels.hpp:983.
+ * *d_amax = max |x[i]| over n bf16 values (NaN ignored, +Inf propagates). Zeroes d_amax itself. */
+int cf_fp8_amax_bf16(const void* d_x, size_t n, float* d_amax, void* stream);
+
+/* kernels/fp8.cu:255-259, kernels.hpp:1003-1004.
+ * a = max(*d_amax, 1e-12); *d_scale = fp8_max / a; *d_descale = a / fp8_max (IEEE divides). */
+int cf_fp8_scale_from_amax(const float* d_amax, float fp8_max, float* d_scale, float* d_descale, void* stream);
+
+/* kernels/fp8.cu:261-279, kernels.hpp:1005-1008.
+ * out[i] = fp8(float(x[i]) * *d_scale), round-to-nearest-even, saturate to finite. */
+int cf_fp8_quantize_e4m3(const void* d_x, void* d_out, const float* d_scale, size_t n, void* stream);
+int cf_fp8_quantize_e5m2(const void* d_x, void* d_out, const float* d_scale, size_t n, void* stream);
+
+/* kernels/fp8.cu:310-330, kernels.hpp:1021-1026.
+ * As above and, in the same pass, *d_amax = max(*d_amax, max|x|) of the UNSCALED input
+ * (integer atomicMax on the float bits; the caller zeroes d_amax first). */
+int cf_fp8_quantize_e4m3_record(const void* d_x, void* d_out, const float* d_scale, float* d_amax, size_t n, void* stream);
+int cf_fp8_quantize_e5m2_record(const void* d_x, void* d_out, const float* d_scale, float* d_amax, size_t n, void* stream);
+
+/* kernels/fp8.cu:396-417, kernels.hpp:1042-1052.
+ * Ring of the last history_len clamped amaxes; scale = fp8_max / max(ring). history_len <= 0
+ * behaves like cf_fp8_scale_from_amax. Cursor outside [0,len) restarts at 0. */
+int cf_fp8_update_delayed_scale(const float* d_amax, float fp8_max, float* d_scale, float* d_descale,
+                                float* d_history, int history_len, int* d_history_cursor,
+                                int* d_history_count, void* stream);
+
+/* kernels/fp8.cu:281-290, kernels.hpp:1010-1011.  w[K,N] bf16 -> out[N,K] E4M3. */
+int cf_fp8_quantize_transpose_e4m3(const void* d_w, void* d_out, const float* d_scale, int K, int N, void* stream);
+
+/* kernels/fp8.cu:292-308, kernels.hpp:1016-1018.  in[K,N] bf16 -> act8[K,N] and snap[N,K] E4M3.
+ * Either output pointer may be NULL to skip that layout (src/trainer.cu:8225-8228 uses snap only). */
+int cf_fp8_quant_and_transpose_e4m3(const void* d_in, void* d_act8_out, void* d_snap_out,
+                                    const float* d_scale, int K, int N, void* stream);
+
+/* src/trainer.cu:1441-1448 (file-static transpose_u8).  in[rows,cols] bytes -> out[cols,rows]. */
+int cf_transpose_u8(const void* d_in, void* d_out, int rows, int cols, void* stream);
+
+/* kernels/fp8.cu:358-363, kernels.hpp:1029-1032.  stats = [clipped_calls, max_ratio, total_calls]. */
+int cf_fp8_clip_probe(const float* d_amax, const float* d_scale, float fp8_max, float* d_stats, void* stream);
+/* kernels/fp8.cu:389-394, kernels.hpp:1034-1037.  out[0] += clipped elements, out[1] += n. */
+int cf_fp8_elem_clip_count(const void* d_x, const float* d_scale, float fp8_max, size_t n, float* d_out, void* stream);
+
+/* kernels/fp8.cu:491-528, kernels.hpp:988-1002: raw-byte E4M3 storage path. Encoder semantics are those
+ * of include/ida_native/fp8_e4m3.hpp (non-finite products become sign|0x7f and are counted in d_bad_count). */
+int cf_fp8_pack_bf16_e4m3_raw(const void* d_x, uint8_t* d_out, float* d_amax, float* d_scale, float* d_descale,
+                              int* d_bad_count, size_t n, void* stream);
+int cf_fp8_pack_bf16_e4m3_raw_and_dequant(const void* d_x, uint8_t* d_out, void* d_dequant, float* d_amax,
+                                          float* d_scale, float* d_descale, int* d_bad_count, size_t n, void* stream);
+int cf_fp8_unpack_e4m3_raw_bf16(const uint8_t* d_in, const float* d_descale, void* d_out, size_t n, void* stream);
+
+/* src/trainer.cu:3789-3795 (k_calib_minmax_update): running min/max of the clamped amax. */
+int cf_fp8_calib_minmax_update(const float* d_amax, float* d_calib_min, float* d_calib_max, void* stream);
+
+/* ------------------------------------------------------------------ context */
+
+/* Replaces the reference's Fp8Ctx (src/trainer.cu:3296-3345) as far as this path needs it: it owns the
+ * device status word the tensor-core kernels report bounded-wait failures into, the shared act8 scratch
+ * and the scalar pool ActSlots are carved from. Created once per device; creation allocates, calls on
+ * the hot path do not. act8_bytes may be 0 when cf_fp8_quant_act is not used. */
+typedef struct cf_ctx cf_ctx;
+int cf_ctx_create(cf_ctx** out, size_t act8_bytes);
+int cf_ctx_destroy(cf_ctx* ctx);
+/* Device pointer of the shared quantised-activation scratch (Fp8Ctx::act8, src/trainer.cu:3339-3340). */
+void* cf_ctx_act8(cf_ctx* ctx);
+/* Synchronises `stream`, then returns CF_OK or CF_ERR_DEVICE_WAIT if any kernel launched through this
+ * context since the last poll abandoned a bounded wait (its output is then invalid). Clears the word. */
+int cf_ctx_poll_status(cf_ctx* ctx, void* stream);
+/* Number of kernels this library launched through any entry point since load (process-wide counter). */
+uint64_t cf_launch_count(void);
+
+/* ------------------------------------------------------------------ FP8 GEMM */
+
+/* Epilogue description shared by the GEMM entry points. Zero-initialise for the reference behaviour. */
+typedef struct cf_gemm_epilogue {
+    const void* d_bias;          /* bf16[N] or NULL */
+    int bias_mode;               /* 0 none; 1 add in fp32 before the single bf16 rounding (fused);
+                                    2 reference order: round to bf16, then bf16(float(c)+float(bias))
+                                      as kernels/moe.cu:325-336 does after the GEMM */
+    const float* d_a_row_descale; /* NULL, or float[M]: per-row (per-token) scales replace *d_a_descale */
+    const float* d_b_col_descale; /* NULL, or float[N]: per-output-channel scales replace *d_b_descale */
+} cf_gemm_epilogue;
+
+/* src/trainer.cu:4498-4534 (file-static lt_gemm_fp8_nt, the cuBLASLt call).
+ * C[M,N] bf16 (row stride ldc) = (*d_a_descale * *d_b_descale) * sum_k A8[m,k] * B8[n,k], fp32 accumulate.
+ * A8: row-major [M,K], row stride lda bytes, E4M3 (a_is_e5m2 = 0) or E5M2 (1).
+ * B8: row-major [N,K] contiguous, E4M3.   epi may be NULL. */
+int cf_gemm_fp8_nt(cf_ctx* ctx, int M, int N, int K, const void* d_A, int lda, int a_is_e5m2,
+                   const float* d_a_descale, const void* d_B, const float* d_b_descale, void* d_C, int ldc,
+                   const cf_gemm_epilogue* epi, void* stream);
+
+/* src/trainer.cu:4596-4625 and :4670-4691 (lt_gemm_fp8_tn_accum_f32, fp32 and bf16 accumulators).
+ * dW[M,N] += (*d_ds_x * *d_ds_dy) * sum_k Xt[m,k] * dYt[n,k]; Xt E4M3 [M,K], dYt E5M2 [N,K], both
+ * contiguous with leading dimension K. */
+int cf_gemm_fp8_tn_accum_f32(cf_ctx* ctx, int M, int N, int K, const void* d_Xt_e4m3, const float* d_ds_x,
+                             const void* d_dYt_e5m2, const float* d_ds_dy, float* d_dW, int ldc, void* stream);
+int cf_gemm_fp8_tn_accum_bf16(cf_ctx* ctx, int M, int N, int K, const void* d_Xt_e4m3, const float* d_ds_x,
+                              const void* d_dYt_e5m2, const float* d_ds_dy, void* d_dW, int ldc, void* stream);
+
+/* The ragged per-expert GEMMs of src/trainer.cu:6893-6927 as ONE launch with a device-side schedule:
+ * for every expert e, rows [d_offsets[e], d_offsets[e]+d_counts[e]) of the compact A8 [total_rows,K]
+ * are multiplied with B8[e] ([N,K] slice of a [E,N,K] block) into the same rows of compact C [.,ldc].
+ * No host synchronisation; max_total_rows bounds sum(counts) (tile budget only). d_a_descale / d_b_descale
+ * are one per-tensor scalar each unless per_expert_a_descale != 0, in which case d_a_descale is float[E]. */
+int cf_gemm_fp8_nt_grouped(cf_ctx* ctx, int num_experts, int max_total_rows, int N, int K, const int* d_counts,
+                           const int* d_offsets, const void* d_A, int lda, int a_is_e5m2, const float* d_a_descale,
+                           int per_expert_a_descale, const void* d_B, const float* d_b_descale, void* d_C, int ldc,
+                           void* stream);
+
+/* ------------------------------------------------------------------ delayed-scaling slot + fused linear */
+
+/* Mirror of ActSlot (src/trainer.cu:3248-3279). All pointer members are device scalars; cf_act_slot_init
+ * carves them from the context's scalar pool (16-byte aligned, src/trainer.cu:4239-4242). */
+typedef struct cf_act_slot {
+    float* amax;
+    float* scale;
+    float* descale;
+    float* history;          /* float[8] (kActHistoryLen, src/trainer.cu:3213) */
+    int* history_cursor;
+    int* history_count;
+    float* scale_snapshot;
+    float* descale_snapshot;
+    float fp8_max;           /* CF_E4M3_MAX or CF_E5M2_MAX */
+    int init;
+    int calib_remaining;
+    int calib_commit_pending;
+    float* calib_min;
+    float* calib_max;
+} cf_act_slot;
+
+int cf_act_slot_init(cf_ctx* ctx, cf_act_slot* slot, float fp8_max, int calib_calls, void* stream);
+
+/* src/trainer.cu:4732-4851 (file-static fp8_quant_act): quantise x into d_out8 (the reference always
+ * writes Fp8Ctx::act8; pass cf_ctx_act8(ctx) for that) following the slot's state machine — recompute,
+ * calibration, first use, steady state (snapshot, record-quantise, ring update). A pending calibration
+ * commit synchronises the stream and reads two floats back, exactly like the reference (:4750-4752). */
+int cf_fp8_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, size_t n, void* d_out8, void* stream,
+                     int is_recompute);
+
+/* One FP8-cached weight (Fp8Slot, src/trainer.cu:3284-3294) and its refresh (:4694-4712): [amax] -> scale ->
+ * quantise into the native layout cache -> quantise-transpose into the other one. */
+typedef struct cf_fp8_weight {
+    const void* w;      /* bf16 master */
+    void* fwd8;         /* [out,in] E4M3 */
+    void* bwd8;         /* [in,out] E4M3 */
+    float* amax;
+    float* scale;
+    float* descale;
+    int in_dim;
+    int out_dim;
+    int stored_out_major;
+} cf_fp8_weight;
+int cf_refresh_fp8_weight(const cf_fp8_weight* slot, int recompute_amax, void* stream);
+
+/* The forward FP8 linear of src/trainer.cu:6114-6132 as one call: fp8_quant_act(x) into the context's act8
+ * scratch, then lt_gemm_fp8_nt against the cached weight with the slot's snapshot descale, then the bias
+ * step. y[M,N] bf16. */
+int cf_fp8_linear_forward(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, int M, int K, const void* d_w8,
+                          const float* d_w_descale, int N, const void* d_bias, int bias_mode, void* d_y, int ldy,
+                          void* stream);
+
+/* ------------------------------------------------------------------ elementwise neighbours of the GEMMs */
+
+/* kernels/moe.cu:338-345, kernels.hpp:243-247. */
+int cf_bias_add_strided_bf16(void* d_inout, const void* d_bias, int rows, int cols, int row_stride, int base, void* stream);
+/* kernels/activations.cu:76-87, kernels.hpp:159-165.  out = bf16(silu(gate) * up). */
+int cf_swiglu_forward(const void* d_gate, const void* d_up, void* d_out, int n, void* stream);
+/* kernels/moe.cu:519-521, kernels.hpp:334.  exact-erf GELU. */
+int cf_gelu_forward(const void* d_x, void* d_out, size_t n, void* stream);
+
+/* ------------------------------------------------------------------ MoE routing, permute, combine */
+
+/* kernels/moe.cu:410-422, kernels.hpp:313-317: softmax in place, hard top-k (lowest index wins ties),
+ * zero the rest, renormalise kept. Save pointers may be NULL. */
+int cf_moe_topk_route_f32(float* d_scores, int rows, int num_experts, int top_k, void* stream,
+                          float* d_row_sum_save, float* d_scores_save, int normalize_topk);
+/* kernels/moe.cu:702-710, kernels.hpp:361-364. Zeroes d_counts itself (the reference relies on the caller);
+ * row order inside one expert is ascending (the reference's is atomic-order dependent). */
+int cf_moe_build_expert_row_lists(const float* d_route_weights, int* d_counts, int* d_row_indices, int rows,
+                                  int num_experts, void* stream);
+/* kernels/moe.cu:859-863, kernels.hpp:396-398. */
+int cf_moe_expert_offsets_from_counts(const int* d_counts, int* d_offsets, int num_experts, void* stream);
+/* kernels/moe.cu:712-728, kernels.hpp:365-372. */
+int cf_moe_gather_rows_u8(const uint8_t* d_src, uint8_t* d_dst, const int* d_row_indices, int n_rows, int width, void* stream);
+int cf_moe_gather_rows_bf16(const void* d_src, void* d_dst, const int* d_row_indices, int n_rows, int width, void* stream);
+/* kernels/moe.cu:730-738, kernels.hpp:373-377. */
+int cf_moe_scatter_accumulate_rows_bf16(void* d_mixed, const void* d_compact, const float* d_route_weights,
+                                        const int* d_row_indices, int n_rows, int expert_idx, int num_experts, int H,
+                                        void* stream);
+/* kernels/moe.cu:677-683, kernels.hpp:341-344. */
+int cf_moe_scale_accumulate_bf16(void* d_mixed, const void* d_term, const float* d_route_weights, int rows,
+                                 int expert_idx, int num_experts, int H, void* stream);
+
+/* Device-scheduled forms of the two passes above for all experts at once (no host copy of the counts):
+ * gather every expert's rows into one compact [sum(counts), width] buffer at d_offsets[e], and combine
+ * every expert's compact output back, one expert after the other per row in expert order (same rounding
+ * sequence as running cf_moe_scatter_accumulate_rows_bf16 for e = 0..E-1). */
+int cf_moe_gather_all_u8(const uint8_t* d_src, uint8_t* d_dst, const int* d_row_indices, const int* d_counts,
+                         const int* d_offsets, int rows, int num_experts, int width, void* stream);
+int cf_moe_combine_all_bf16(void* d_mixed, const void* d_compact, const float* d_route_weights,
+                            const int* d_row_indices, const int* d_counts, const int* d_offsets, int rows,
+                            int num_experts, int H, void* stream);
+
+/* kernels/moe.cu:1062-1127, kernels.hpp:414-423: grouped selected-expert FP8 forward with exact-erf GELU,
+ * accumulating rw*y into d_mixed. The tensor-core implementation needs workspace, which the reference
+ * signature has no room for, hence the ctx parameter: it uses about
+ *   total_selected_rows * (3*H + 4*Ie) + 2 KiB bytes of ctx workspace (cf_ctx_reserve_workspace, done once
+ * outside the hot path; the call fails with CF_ERR_LIMIT when too little is reserved). The fc_in output is
+ * rounded to bf16 and the GELU output is carried into fc_out as a two-term E4M3 split (hi + lo, ~2^-8
+ * relative) where the reference keeps it in fp32: outputs agree within the path's 1e-2 relative-Frobenius
+ * tolerance, not bit for bit. */
+int cf_ctx_reserve_workspace(cf_ctx* ctx, size_t bytes);
+int cf_moe_grouped_expert_forward_fp8(cf_ctx* ctx, const void* d_hidden, const float* d_fcin_descale, int fcin_is_e5m2,
+                                      const float* d_route_weights, const int* d_counts, const int* d_offsets,
+                                      const int* d_row_indices, const void* d_fc_in_w, const float* d_fc_in_descale,
+                                      const void* d_fc_out_w, const float* d_fc_out_descale, void* d_mixed, int rows,
+                                      int H, int Ie, int num_experts, int total_selected_rows, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CANOPY_FP8_H */

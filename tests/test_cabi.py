@@ -1,0 +1,37 @@
+"""CPU-side checks of the boundary: the shared library loads without a GPU and exports every symbol
+include/canopy_fp8.h declares; argument validation that needs no device works."""
+import ctypes as C
+import os
+import re
+
+from gpu_util import ROOT, package
+
+
+def test_library_exports_every_declared_symbol():
+    cfb = package()
+    lib = cfb._capi.lib()
+    hdr = open(os.path.join(ROOT, "include", "canopy_fp8.h")).read()
+    declared = set(re.findall(r"\b(cf_[a-z0-9_]+)\s*\(", hdr))
+    assert declared, "no declarations parsed"
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} is declared in include/canopy_fp8.h but not exported"
+    assert declared == set(cfb._capi.SIGNATURES), "ctypes table and header disagree"
+    assert lib.cf_abi_version() == 1
+
+
+def test_struct_layouts_match_the_header():
+    cfb = package()
+    # pointer-sized and 4-byte members only; sizes follow the C layout rules on LP64
+    assert C.sizeof(cfb._capi.GemmEpilogue) == 32
+    assert C.sizeof(cfb._capi.ActSlotStruct) == 8 * 8 + 4 * 4 + 2 * 8
+    assert C.sizeof(cfb._capi.Fp8WeightStruct) == 6 * 8 + 3 * 4 + 4
+
+
+def test_argument_validation_without_a_device():
+    cfb = package()
+    lib = cfb._capi.lib()
+    assert lib.cf_fp8_quantize_e4m3(None, None, None, 16, None) == cfb._capi.CF_ERR_INVALID_ARG
+    assert b"null pointer" in lib.cf_last_error()
+    assert lib.cf_swiglu_forward(None, None, None, -1, None) == cfb._capi.CF_ERR_INVALID_ARG
+    assert lib.cf_fp8_quantize_e4m3(None, None, C.c_void_p(16), 0, None) == cfb._capi.CF_OK     # n == 0 is a no-op
+    assert lib.cf_moe_topk_route_f32(None, 4, 100, 2, None, None, None, 1) == cfb._capi.CF_ERR_INVALID_ARG

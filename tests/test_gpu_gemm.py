@@ -1,0 +1,225 @@
+"""GPU parity of the tcgen05 FP8 GEMM: relative Frobenius error <= 1e-2 against the CPU oracle (the
+tolerance BASELINE states for GEMM outputs), plus a cross-check against cuBLASLt (torch._scaled_mm), the
+library the reference itself calls (src/trainer.cu:4516-4533)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+from gpu_util import bf16_to_u16, f32_scalar, package, randn_bf16, rel_fro, u16_to_bf16  # noqa: E402
+
+TOL = 1e-2        # relative Frobenius, as stated for GEMM outputs
+TIGHT = 5e-3      # what bf16 output rounding alone allows (2^-9 per element)
+
+
+@pytest.fixture(scope="module")
+def cfb():
+    assert torch.cuda.is_available()
+    return package()
+
+
+@pytest.fixture(scope="module")
+def ctx(cfb):
+    c = cfb.Fp8Ctx(act8_bytes=64 << 20)
+    yield c
+    c.close()
+
+
+def _quant(cfb, x, e5m2=False):
+    am, sc, de = f32_scalar(), f32_scalar(), f32_scalar()
+    cfb.fp8_amax_bf16(x, am)
+    cfb.fp8_scale_from_amax(am, cfb.E5M2_MAX if e5m2 else cfb.E4M3_MAX, sc, de)
+    q = torch.empty(x.shape, dtype=torch.uint8, device="cuda")
+    (cfb.fp8_quantize_e5m2 if e5m2 else cfb.fp8_quantize_e4m3)(x, q, sc)
+    return q, de
+
+
+def _oracle_gemm(oracle, a8, b8, da, db, **kw):
+    return oracle.gemm_fp8_nt(a8.cpu().numpy(), b8.cpu().numpy(), da[0].item(), db[0].item(), **kw)
+
+
+@pytest.mark.parametrize("M,N,K", [
+    (128, 256, 128), (128, 256, 512), (256, 512, 1024), (1, 16, 16), (5, 48, 64), (130, 260, 144),
+    (300, 1000, 2064), (64, 4096, 512), (1024, 1024, 4096), (129, 257, 4096 + 16), (777, 333, 48),
+])
+def test_dense_nt_vs_oracle(cfb, ctx, oracle, M, N, K):
+    a = randn_bf16((M, K), seed=M + N, outlier_frac=0.001)
+    w = randn_bf16((N, K), std=0.02, seed=K)
+    a8, da = _quant(cfb, a)
+    w8, dw = _quant(cfb, w)
+    c = torch.full((M + 2, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    cfb.lt_gemm_fp8_nt(ctx, M, N, K, a8, K, False, da, w8, dw, c, N)
+    ctx.poll_status()
+    want = _oracle_gemm(oracle, a8, w8, da, dw)
+    got = bf16_to_u16(c)
+    err = rel_fro(oracle.bf16_to_f32(got[:M]), oracle.bf16_to_f32(want))
+    assert err < TIGHT, err
+    assert (c[M:] == 7.0).all()          # rows past M untouched
+
+
+def test_e5m2_activation_and_strides(cfb, ctx, oracle):
+    """dgrad form: E5M2 A read as a column slice (lda = 3H) and C written as a column slice (ldc = 3H)
+    (src/trainer.cu:6127-6132, :8527-8533)."""
+    M, H = 384, 256
+    g = randn_bf16((M, 3 * H), std=1e-3, seed=1)
+    g8, dg = _quant(cfb, g, e5m2=True)
+    w = randn_bf16((H, H), std=0.02, seed=2)
+    w8, dw = _quant(cfb, w)
+    out = torch.zeros((M, 3 * H), dtype=torch.bfloat16, device="cuda")
+    for j in range(3):
+        a_slice = g8.view(-1)[j * H:]
+        c_slice = out.view(-1)[j * H:]
+        cfb.lt_gemm_fp8_nt(ctx, M, H, H, a_slice, 3 * H, True, dg, w8, dw, c_slice, 3 * H)
+    ctx.poll_status()
+    g8n, w8n = g8.cpu().numpy(), w8.cpu().numpy()
+    for j in range(3):
+        want = oracle.gemm_fp8_nt(np.ascontiguousarray(g8n[:, j * H:(j + 1) * H]), w8n, dg[0].item(), dw[0].item(),
+                                  a_is_e5m2=True)
+        got = bf16_to_u16(out[:, j * H:(j + 1) * H])
+        assert rel_fro(oracle.bf16_to_f32(got), oracle.bf16_to_f32(want)) < TIGHT
+
+
+def test_unaligned_operands_take_the_simt_form(cfb, ctx, oracle):
+    M, N, K = 33, 20, 40            # K not a multiple of 16
+    a8 = torch.randint(0, 0x78, (M, K), dtype=torch.uint8, device="cuda")
+    w8 = torch.randint(0, 0x78, (N, K), dtype=torch.uint8, device="cuda")
+    da, dw = f32_scalar(0.01), f32_scalar(0.02)
+    c = torch.zeros((M, N), dtype=torch.bfloat16, device="cuda")
+    cfb.lt_gemm_fp8_nt(ctx, M, N, K, a8, K, False, da, w8, dw, c, N)
+    want = _oracle_gemm(oracle, a8, w8, da, dw)
+    assert rel_fro(oracle.bf16_to_f32(bf16_to_u16(c)), oracle.bf16_to_f32(want)) < TIGHT
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_bias_epilogue(cfb, ctx, oracle, mode):
+    M, N, K = 200, 512, 256
+    a8, da = _quant(cfb, randn_bf16((M, K), seed=11))
+    w8, dw = _quant(cfb, randn_bf16((N, K), std=0.02, seed=12))
+    bias = randn_bf16((N,), std=0.01, seed=13)
+    c = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    cfb.lt_gemm_fp8_nt(ctx, M, N, K, a8, K, False, da, w8, dw, c, N, bias=bias, bias_mode=mode)
+    want = _oracle_gemm(oracle, a8, w8, da, dw, bias=bf16_to_u16(bias), bias_mode=mode)
+    assert rel_fro(oracle.bf16_to_f32(bf16_to_u16(c)), oracle.bf16_to_f32(want)) < TIGHT
+    if mode == 2:
+        # reference order = GEMM then the separate bias kernel: must agree bit for bit with our own two-step
+        c2 = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+        cfb.lt_gemm_fp8_nt(ctx, M, N, K, a8, K, False, da, w8, dw, c2, N)
+        cfb.bias_add_strided_bf16(c2, bias, M, N, N, 0)
+        assert torch.equal(c, c2)
+
+
+def test_per_token_and_per_channel_scales(cfb, ctx, oracle):
+    """Configuration 3's scaling granularity (no reference code): C[m,n] = dA[m] * dW[n] * acc."""
+    M, N, K = 160, 384, 512
+    rng = np.random.default_rng(0)
+    a8 = torch.randint(0, 0x70, (M, K), dtype=torch.uint8, device="cuda")
+    w8 = torch.randint(0, 0x70, (N, K), dtype=torch.uint8, device="cuda")
+    dr = torch.from_numpy(rng.uniform(1e-3, 1e-2, M).astype(np.float32)).cuda()
+    dc = torch.from_numpy(rng.uniform(1e-4, 1e-3, N).astype(np.float32)).cuda()
+    one = f32_scalar(1.0)
+    c = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    cfb.lt_gemm_fp8_nt(ctx, M, N, K, a8, K, False, one, w8, one, c, N, a_row_descale=dr, b_col_descale=dc)
+    want = oracle.gemm_fp8_nt(a8.cpu().numpy(), w8.cpu().numpy(), dr.cpu().numpy(), dc.cpu().numpy())
+    assert rel_fro(oracle.bf16_to_f32(bf16_to_u16(c)), oracle.bf16_to_f32(want)) < TIGHT
+
+
+@pytest.mark.parametrize("out_dtype", ["f32", "bf16"])
+def test_tn_weight_gradient_accumulate(cfb, ctx, oracle, out_dtype):
+    """dW[M,N] += Xt[M,K] . dYt[N,K]^T with E4M3 x E5M2 operands (src/trainer.cu:4596-4691)."""
+    M, N, K = 256, 320, 1024
+    xt8, dx = _quant(cfb, randn_bf16((M, K), seed=21))
+    dy8, dd = _quant(cfb, randn_bf16((N, K), std=1e-3, seed=22), e5m2=True)
+    init = torch.randn((M, N), device="cuda") * 1e-2
+    if out_dtype == "f32":
+        dw = init.clone()
+        cfb.lt_gemm_fp8_tn_accum_f32(ctx, M, N, K, xt8, dx, dy8, dd, dw, N)
+        want = oracle.gemm_fp8_nt(xt8.cpu().numpy(), dy8.cpu().numpy(), dx[0].item(), dd[0].item(), b_is_e5m2=True,
+                                  out_kind=2, C_init=init.cpu().numpy())
+        assert rel_fro(dw.cpu().numpy(), want) < 1e-5
+    else:
+        dw = init.to(torch.bfloat16)
+        w0 = bf16_to_u16(dw).copy()
+        cfb.lt_gemm_fp8_tn_accum_f32(ctx, M, N, K, xt8, dx, dy8, dd, dw, N)
+        want = oracle.gemm_fp8_nt(xt8.cpu().numpy(), dy8.cpu().numpy(), dx[0].item(), dd[0].item(), b_is_e5m2=True,
+                                  out_kind=3, C_init=w0)
+        assert rel_fro(oracle.bf16_to_f32(bf16_to_u16(dw)), oracle.bf16_to_f32(want)) < TIGHT
+    ctx.poll_status()
+
+
+def test_against_cublaslt(cfb, ctx):
+    """Same FP8 bytes through torch._scaled_mm (cuBLASLt) — the incumbent kernel the reference calls."""
+    if not hasattr(torch, "_scaled_mm"):
+        pytest.skip("torch._scaled_mm not available")
+    M, N, K = 512, 768, 1024
+    a8, da = _quant(cfb, randn_bf16((M, K), seed=31))
+    w8, dw = _quant(cfb, randn_bf16((N, K), std=0.02, seed=32))
+    c = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    cfb.lt_gemm_fp8_nt(ctx, M, N, K, a8, K, False, da, w8, dw, c, N)
+    ref = torch._scaled_mm(a8.view(torch.float8_e4m3fn), w8.view(torch.float8_e4m3fn).t(), scale_a=da[0:1],
+                           scale_b=dw[0:1], out_dtype=torch.bfloat16)
+    assert rel_fro(c.float().cpu().numpy(), ref.float().cpu().numpy()) < TIGHT
+
+
+def test_full_size_properties(cfb, ctx, oracle):
+    """BASELINE configuration 2 at full size (8192 x 4096 x 4096): linearity in the scale, row-slab
+    consistency (a row block computed alone equals the same rows of the full product, bit for bit) and a
+    sampled comparison with the oracle."""
+    M, N, K = 8192, 4096, 4096
+    x = randn_bf16((M, K), seed=0, outlier_frac=0.001)
+    w = randn_bf16((N, K), std=0.02, seed=1)
+    x8, dx = _quant(cfb, x)
+    w8, dw = _quant(cfb, w)
+    c = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    cfb.lt_gemm_fp8_nt(ctx, M, N, K, x8, K, False, dx, w8, dw, c, N)
+    ctx.poll_status()
+    # sampled rows against the oracle
+    rows = [0, 1, 127, 128, 4095, 4096, 8191, 5000]
+    sub = x8[rows].contiguous()
+    want = _oracle_gemm(oracle, sub, w8, dx, dw)
+    assert rel_fro(oracle.bf16_to_f32(bf16_to_u16(c[rows])), oracle.bf16_to_f32(want)) < TIGHT
+    # row slab alone == same rows of the full product
+    c_slab = torch.empty((256, N), dtype=torch.bfloat16, device="cuda")
+    cfb.lt_gemm_fp8_nt(ctx, 256, N, K, x8[1024:1280], K, False, dx, w8, dw, c_slab, N)
+    assert torch.equal(c_slab, c[1024:1280])
+    # doubling the activation descale doubles every output exactly (power of two)
+    dx2 = f32_scalar(dx[0].item() * 2.0)
+    c2 = torch.empty((512, N), dtype=torch.bfloat16, device="cuda")
+    cfb.lt_gemm_fp8_nt(ctx, 512, N, K, x8[:512], K, False, dx2, w8, dw, c2, N)
+    assert torch.equal(c2.float(), c[:512].float() * 2.0)
+    ctx.poll_status()
+
+
+def test_fp8_linear_forward_delayed_scaling(cfb, ctx, oracle):
+    """quant_act -> GEMM -> bias in one call, two steps so the second uses the delayed (previous) scale."""
+    M, K, N = 512, 1024, 768
+    w = randn_bf16((N, K), std=0.02, seed=41)
+    fw = cfb.Fp8Weight(w, stored_out_major=True)
+    cfb.refresh_fp8_weight(fw)
+    bias = randn_bf16((N,), std=0.01, seed=42)
+    slot = cfb.ActSlot(ctx, cfb.E4M3_MAX, calib_calls=0)
+    y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    prev = None
+    for step in range(3):
+        x = randn_bf16((M, K), std=1.0 + 0.5 * step, seed=50 + step, outlier_frac=0.001)
+        cfb.fp8_linear_forward(ctx, slot, x, fw.fwd8, fw.descale, y, bias=bias, bias_mode=2)
+        xs = bf16_to_u16(x)
+        a = oracle.amax_bf16(xs)
+        s_used, d_used = oracle.scale_from_amax(a, 448.0) if prev is None else prev
+        x8 = oracle.quantize_bf16(xs, s_used)
+        want = oracle.gemm_fp8_nt(x8, fw.fwd8.cpu().numpy(), d_used, fw.descale.item(), bias=bf16_to_u16(bias), bias_mode=2)
+        assert rel_fro(oracle.bf16_to_f32(bf16_to_u16(y)), oracle.bf16_to_f32(want)) < TIGHT, step
+        sc = slot.scalars()
+        prev = (np.float32(sc["scale"]), np.float32(sc["descale"]))
+    ctx.poll_status()
+
+
+def test_gemm_argument_errors(cfb, ctx):
+    a8 = torch.zeros((16, 16), dtype=torch.uint8, device="cuda")
+    d = f32_scalar(1.0)
+    c = torch.zeros((16, 16), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(cfb.CanopyError):
+        cfb.lt_gemm_fp8_nt(ctx, 16, 16, 16, a8, 8, False, d, a8, d, c, 16)      # lda < K
+    with pytest.raises(cfb.CanopyError):
+        cfb.lt_gemm_fp8_nt(ctx, 16, 16, 16, None, 16, False, d, a8, d, c, 16)   # null A
+    cfb.lt_gemm_fp8_nt(ctx, 0, 16, 16, a8, 16, False, d, a8, d, c, 16)          # empty M is a no-op

@@ -1,0 +1,284 @@
+"""GPU parity of the MoE routing / permute / grouped GEMM / combine path and the elementwise neighbours."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+from gpu_util import (bf16_to_u16, f32_scalar, package, randn_bf16, ref_gpu_or_none, rel_fro, stream_ptr,  # noqa: E402
+                      u16_to_bf16)
+
+TOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def cfb():
+    assert torch.cuda.is_available()
+    return package()
+
+
+@pytest.fixture(scope="module")
+def ctx(cfb):
+    c = cfb.Fp8Ctx(act8_bytes=16 << 20)
+    yield c
+    c.close()
+
+
+@pytest.fixture(scope="module")
+def refgpu():
+    return ref_gpu_or_none()
+
+
+def _quant(cfb, x, e5m2=False):
+    am, sc, de = f32_scalar(), f32_scalar(), f32_scalar()
+    cfb.fp8_amax_bf16(x, am)
+    cfb.fp8_scale_from_amax(am, cfb.E5M2_MAX if e5m2 else cfb.E4M3_MAX, sc, de)
+    q = torch.empty(x.shape, dtype=torch.uint8, device="cuda")
+    (cfb.fp8_quantize_e5m2 if e5m2 else cfb.fp8_quantize_e4m3)(x, q, sc)
+    return q, de
+
+
+def _zipf_logits(rows, E, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    p = torch.arange(1, E + 1, device="cuda", dtype=torch.float32) ** -1.1
+    return torch.randn((rows, E), generator=g, device="cuda") + torch.log(p / p.sum())
+
+
+def _route(cfb, rows, E, k, seed):
+    rw = _zipf_logits(rows, E, seed).contiguous()
+    cfb.moe_topk_route_f32(rw, rows, E, k)
+    counts = torch.zeros(E, dtype=torch.int32, device="cuda")
+    idx = torch.full((E, rows), -1, dtype=torch.int32, device="cuda")
+    cfb.moe_build_expert_row_lists(rw, counts, idx, rows, E)
+    offs = torch.empty(E, dtype=torch.int32, device="cuda")
+    cfb.moe_expert_offsets_from_counts(counts, offs, E)
+    return rw, counts, idx, offs
+
+
+def test_elementwise(cfb, oracle, refgpu):
+    for n in [1, 9, 4096, 100003]:
+        g, u = randn_bf16((n,), std=3.0, seed=n), randn_bf16((n,), seed=n + 1)
+        out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+        cfb.swiglu_forward(g, u, out)
+        want = oracle.swiglu_forward(bf16_to_u16(g), bf16_to_u16(u))
+        # expf differs by an ulp between libm and the device: allow one bf16 ulp
+        diff = np.abs(bf16_to_u16(out).astype(np.int32) - want.astype(np.int32))
+        assert diff.max() <= 1, diff.max()
+        cfb.gelu_forward(g, out)
+        diff = np.abs(bf16_to_u16(out).astype(np.int32) - oracle.gelu_forward(bf16_to_u16(g)).astype(np.int32))
+        assert diff.max() <= 1
+        if refgpu is not None:       # same device maths as the reference kernels: bit for bit
+            r = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+            refgpu.call("ref_swiglu_forward", g, u, r, n, stream_ptr())
+            torch.cuda.synchronize()
+            cfb.swiglu_forward(g, u, out)
+            assert torch.equal(r.view(torch.int16), out.view(torch.int16))
+            refgpu.call("ref_gelu_forward", g, r, C.c_size_t(n), stream_ptr())
+            torch.cuda.synchronize()
+            cfb.gelu_forward(g, out)
+            assert torch.equal(r.view(torch.int16), out.view(torch.int16))
+    # strided bias
+    rows, H = 37, 48
+    x = randn_bf16((rows, 3 * H), seed=3)
+    b = randn_bf16((H,), std=0.1, seed=4)
+    xs = bf16_to_u16(x).copy()
+    cfb.bias_add_strided_bf16(x, b, rows, H, 3 * H, H)
+    oracle.bias_add_strided_bf16(xs, bf16_to_u16(b), rows, H, 3 * H, H)
+    assert np.array_equal(bf16_to_u16(x), xs)
+
+
+@pytest.mark.parametrize("rows,E,k", [(1, 3, 2), (257, 8, 2), (4096, 8, 2), (1000, 11, 3), (64, 4, 4)])
+def test_routing_and_dispatch_lists(cfb, oracle, refgpu, rows, E, k):
+    logits = _zipf_logits(rows, E, rows).contiguous()
+    rw = logits.clone()
+    cfb.moe_topk_route_f32(rw, rows, E, k)
+    want = oracle.moe_topk_route(logits.cpu().numpy(), k)
+    got = rw.cpu().numpy()
+    np.testing.assert_allclose(got, want, rtol=0, atol=3e-7)
+    # selection may differ only on rows whose k-th and (k+1)-th probabilities are within rounding
+    mism = np.any((got > 0) != (want > 0), axis=1)
+    assert mism.mean() < 1e-3
+    if refgpu is not None:
+        r = logits.clone()
+        refgpu.call("ref_moe_topk_route_f32", r, rows, E, k, stream_ptr())
+        torch.cuda.synchronize()
+        np.testing.assert_allclose(r.cpu().numpy(), got, rtol=0, atol=3e-7)
+        assert np.array_equal(r.cpu().numpy() > 0, got > 0)
+    counts = torch.full((E,), 123, dtype=torch.int32, device="cuda")
+    idx = torch.full((E, rows), -1, dtype=torch.int32, device="cuda")
+    cfb.moe_build_expert_row_lists(rw, counts, idx, rows, E)
+    c_o, i_o = oracle.moe_build_expert_row_lists(got)
+    assert np.array_equal(counts.cpu().numpy(), c_o) and np.array_equal(idx.cpu().numpy(), i_o)
+    offs = torch.empty(E, dtype=torch.int32, device="cuda")
+    cfb.moe_expert_offsets_from_counts(counts, offs, E)
+    assert np.array_equal(offs.cpu().numpy(), oracle.moe_offsets(c_o))
+    if refgpu is not None:      # the reference's list order is atomic-dependent: compare as sets
+        rc = torch.zeros(E, dtype=torch.int32, device="cuda")
+        ri = torch.full((E, rows), -1, dtype=torch.int32, device="cuda")
+        refgpu.call("ref_moe_build_expert_row_lists", rw, rc, ri, rows, E, stream_ptr())
+        torch.cuda.synchronize()
+        assert np.array_equal(rc.cpu().numpy(), c_o)
+        for e in range(E):
+            assert sorted(ri[e, :c_o[e]].cpu().tolist()) == i_o[e, :c_o[e]].tolist()
+
+
+def test_ties_pick_lowest_index(cfb):
+    s = torch.zeros((2, 5), dtype=torch.float32, device="cuda")
+    cfb.moe_topk_route_f32(s, 2, 5, 2)
+    assert s.cpu().tolist() == [[0.5, 0.5, 0, 0, 0]] * 2
+
+
+@pytest.mark.parametrize("width", [16, 64, 100, 4096])
+def test_permute_and_combine(cfb, oracle, width):
+    rows, E, k = 300, 6, 2
+    rw, counts, idx, offs = _route(cfb, rows, E, k, 7)
+    c_n, i_n, o_n = counts.cpu().numpy(), idx.cpu().numpy(), offs.cpu().numpy()
+    total = int(c_n.sum())
+    src8 = torch.randint(0, 255, (rows, width), dtype=torch.uint8, device="cuda")
+    compact = torch.zeros((total, width), dtype=torch.uint8, device="cuda")
+    cfb.moe_gather_all_u8(src8, compact, idx, counts, offs, rows, E, width)
+    for e in range(E):
+        sel = i_n[e, :c_n[e]]
+        assert np.array_equal(compact[o_n[e]:o_n[e] + c_n[e]].cpu().numpy(), src8.cpu().numpy()[sel])
+        one = torch.empty((max(int(c_n[e]), 1), width), dtype=torch.uint8, device="cuda")
+        cfb.moe_gather_rows_u8(src8, one, idx[e], int(c_n[e]), width)
+        assert np.array_equal(one[:c_n[e]].cpu().numpy(), src8.cpu().numpy()[sel])
+    srcb = randn_bf16((rows, width), seed=8)
+    e0 = int(np.argmax(c_n))
+    gb = torch.empty((int(c_n[e0]), width), dtype=torch.bfloat16, device="cuda")
+    cfb.moe_gather_rows_bf16(srcb, gb, idx[e0], int(c_n[e0]), width)
+    assert torch.equal(gb, srcb[idx[e0, :c_n[e0]].long()])
+    # combine: per-expert scatter calls, the all-experts form and the dense form agree bit for bit with the oracle
+    y = randn_bf16((total, width), seed=9)
+    mixed_a = randn_bf16((rows, width), seed=10)
+    mixed_b = mixed_a.clone()
+    m_o = bf16_to_u16(mixed_a).copy()
+    rw_n, y_n = rw.cpu().numpy(), bf16_to_u16(y)
+    for e in range(E):
+        if c_n[e] == 0:
+            continue
+        cfb.moe_scatter_accumulate_rows_bf16(mixed_a, y[o_n[e]:o_n[e] + c_n[e]], rw, idx[e], int(c_n[e]), e, E, width)
+        oracle.moe_scatter_accumulate_rows_bf16(m_o, np.ascontiguousarray(y_n[o_n[e]:o_n[e] + c_n[e]]), rw_n,
+                                                i_n[e, :c_n[e]], e)
+    cfb.moe_combine_all_bf16(mixed_b, y, rw, idx, counts, offs, rows, E, width)
+    assert np.array_equal(bf16_to_u16(mixed_a), m_o) and torch.equal(mixed_a, mixed_b)
+    term = randn_bf16((rows, width), seed=11)
+    mixed_c = randn_bf16((rows, width), seed=12)
+    m2 = bf16_to_u16(mixed_c).copy()
+    cfb.moe_scale_accumulate_bf16(mixed_c, term, rw, rows, 1, E, width)
+    oracle.moe_scale_accumulate_bf16(m2, bf16_to_u16(term), rw_n, 1)
+    assert np.array_equal(bf16_to_u16(mixed_c), m2)
+
+
+@pytest.mark.parametrize("rows,E,N,K", [(64, 2, 256, 128), (500, 8, 384, 256), (1000, 5, 272, 528), (2048, 8, 1024, 1024)])
+def test_grouped_gemm_vs_oracle(cfb, ctx, oracle, rows, E, N, K):
+    """Ragged per-expert GEMM in one launch, including empty experts and one expert holding most rows."""
+    rw, counts, idx, offs = _route(cfb, rows, E, 2, rows + E)
+    c_n, o_n = counts.cpu().numpy(), offs.cpu().numpy()
+    total = int(c_n.sum())
+    x8, dx = _quant(cfb, randn_bf16((rows, K), seed=1))
+    xc = torch.zeros((total, K), dtype=torch.uint8, device="cuda")
+    cfb.moe_gather_all_u8(x8, xc, idx, counts, offs, rows, E, K)
+    w8, dw = _quant(cfb, randn_bf16((E, N, K), std=0.02, seed=2))
+    out = torch.full((total + 3, N), 5.0, dtype=torch.bfloat16, device="cuda")
+    cfb.gemm_fp8_nt_grouped(ctx, E, total, N, K, counts, offs, xc, K, False, dx, False, w8, dw, out, N)
+    ctx.poll_status()
+    xcn, w8n = xc.cpu().numpy(), w8.cpu().numpy()
+    for e in range(E):
+        if c_n[e] == 0:
+            continue
+        want = oracle.gemm_fp8_nt(np.ascontiguousarray(xcn[o_n[e]:o_n[e] + c_n[e]]), w8n[e], dx[0].item(), dw[0].item())
+        got = bf16_to_u16(out[o_n[e]:o_n[e] + c_n[e]])
+        assert rel_fro(oracle.bf16_to_f32(got), oracle.bf16_to_f32(want)) < 5e-3, e
+    assert (out[total:] == 5.0).all()
+
+
+def test_grouped_gemm_skewed_and_empty(cfb, ctx, oracle):
+    E, N, K = 4, 256, 256
+    counts = torch.tensor([0, 700, 0, 1], dtype=torch.int32, device="cuda")
+    offs = torch.tensor([0, 0, 700, 700], dtype=torch.int32, device="cuda")
+    total = 701
+    xc = torch.randint(0, 0x70, (total, K), dtype=torch.uint8, device="cuda")
+    w8 = torch.randint(0, 0x70, (E, N, K), dtype=torch.uint8, device="cuda")
+    d = f32_scalar(1e-3)
+    out = torch.zeros((total, N), dtype=torch.bfloat16, device="cuda")
+    cfb.gemm_fp8_nt_grouped(ctx, E, total, N, K, counts, offs, xc, K, False, d, False, w8, d, out, N)
+    ctx.poll_status()
+    xcn, w8n = xc.cpu().numpy(), w8.cpu().numpy()
+    want1 = oracle.gemm_fp8_nt(np.ascontiguousarray(xcn[:700]), w8n[1], 1e-3, 1e-3)
+    want3 = oracle.gemm_fp8_nt(np.ascontiguousarray(xcn[700:]), w8n[3], 1e-3, 1e-3)
+    assert rel_fro(oracle.bf16_to_f32(bf16_to_u16(out[:700])), oracle.bf16_to_f32(want1)) < 5e-3
+    assert rel_fro(oracle.bf16_to_f32(bf16_to_u16(out[700:])), oracle.bf16_to_f32(want3)) < 5e-3
+
+
+@pytest.mark.parametrize("rows,H,Ie,E", [(96, 64, 128, 3), (512, 256, 512, 8)])
+def test_grouped_expert_forward_fp8(cfb, ctx, oracle, refgpu, rows, H, Ie, E):
+    """moe_grouped_expert_forward_fp8 (kernels/moe.cu:1062-1127): GELU experts, rw-weighted accumulate."""
+    rw, counts, idx, offs = _route(cfb, rows, E, 2, 77)
+    total = int(counts.sum().item())
+    x8, dx = _quant(cfb, randn_bf16((rows, H), seed=1))
+    win8, dwin = _quant(cfb, randn_bf16((E, Ie, H), std=0.05, seed=2))
+    wout8, dwout = _quant(cfb, randn_bf16((E, H, Ie), std=0.05, seed=3))
+    mixed = randn_bf16((rows, H), std=0.1, seed=4)
+    m_o = bf16_to_u16(mixed).copy()
+    ctx.reserve_workspace(total * (3 * H + 4 * Ie) + 4096)
+    cfb.moe_grouped_expert_forward_fp8(ctx, x8, dx, False, rw, counts, offs, idx, win8, dwin, wout8, dwout, mixed, rows,
+                                       H, Ie, E, total)
+    ctx.poll_status()
+    oracle.moe_grouped_expert_forward_fp8(x8.cpu().numpy(), dx[0].item(), rw.cpu().numpy(), counts.cpu().numpy(),
+                                          idx.cpu().numpy(), win8.cpu().numpy(), dwin[0].item(), wout8.cpu().numpy(),
+                                          dwout[0].item(), m_o)
+    err = rel_fro(oracle.bf16_to_f32(bf16_to_u16(mixed)), oracle.bf16_to_f32(m_o))
+    assert err < TOL, err
+    if refgpu is not None:
+        m_r = randn_bf16((rows, H), std=0.1, seed=4)
+        refgpu.call("ref_moe_grouped_expert_forward_fp8", x8, dx, 0, rw, counts, offs, idx, win8, dwin, wout8, dwout,
+                    m_r, rows, H, Ie, E, total, stream_ptr())
+        torch.cuda.synchronize()
+        assert rel_fro(mixed.float().cpu().numpy(), m_r.float().cpu().numpy()) < TOL
+
+
+def test_ragged_expert_sequence(cfb, ctx, oracle):
+    """The selected-row FP8 branch of moe_expert_bank_forward (src/trainer.cu:6886-6934): per expert gather ->
+    fc_in GEMM -> GELU -> re-quantise -> fc_out GEMM -> scatter-accumulate, here with device-side scheduling."""
+    rows, H, Ie, E = 400, 128, 256, 4
+    rw, counts, idx, offs = _route(cfb, rows, E, 2, 5)
+    c_n, i_n, o_n = counts.cpu().numpy(), idx.cpu().numpy(), offs.cpu().numpy()
+    total = int(c_n.sum())
+    x8, dx = _quant(cfb, randn_bf16((rows, H), seed=1))
+    win8, dwin = _quant(cfb, randn_bf16((E, Ie, H), std=0.05, seed=2))
+    wout8, dwout = _quant(cfb, randn_bf16((E, H, Ie), std=0.05, seed=3))
+    xc = torch.empty((total, H), dtype=torch.uint8, device="cuda")
+    cfb.moe_gather_all_u8(x8, xc, idx, counts, offs, rows, E, H)
+    h = torch.empty((total, Ie), dtype=torch.bfloat16, device="cuda")
+    cfb.gemm_fp8_nt_grouped(ctx, E, total, Ie, H, counts, offs, xc, H, False, dx, False, win8, dwin, h, Ie)
+    cfb.gelu_forward(h, h)
+    # per-expert activation slots (first use = exact amax), as the reference's fcout ActSlots
+    g8 = torch.empty((total, Ie), dtype=torch.uint8, device="cuda")
+    dg = torch.zeros(E * 4, dtype=torch.float32, device="cuda")
+    for e in range(E):
+        if c_n[e] == 0:
+            continue
+        q, d = _quant(cfb, h[o_n[e]:o_n[e] + c_n[e]])
+        g8[o_n[e]:o_n[e] + c_n[e]] = q
+        dg[e] = d[0]
+    y = torch.empty((total, H), dtype=torch.bfloat16, device="cuda")
+    cfb.gemm_fp8_nt_grouped(ctx, E, total, H, Ie, counts, offs, g8, Ie, False, dg, True, wout8, dwout, y, H)
+    mixed = torch.zeros((rows, H), dtype=torch.bfloat16, device="cuda")
+    cfb.moe_combine_all_bf16(mixed, y, rw, idx, counts, offs, rows, E, H)
+    ctx.poll_status()
+    # oracle: same sequence on the host
+    m_o = np.zeros((rows, H), dtype=np.uint16)
+    x8n, rw_n = x8.cpu().numpy(), rw.cpu().numpy()
+    for e in range(E):
+        if c_n[e] == 0:
+            continue
+        sel = i_n[e, :c_n[e]]
+        xe = oracle.moe_gather_rows(x8n, sel)
+        he = oracle.gelu_forward(oracle.gemm_fp8_nt(xe, win8[e].cpu().numpy(), dx[0].item(), dwin[0].item()))
+        s_e, d_e = oracle.scale_from_amax(oracle.amax_bf16(he), 448.0)
+        ye = oracle.gemm_fp8_nt(oracle.quantize_bf16(he, s_e), wout8[e].cpu().numpy(), d_e, dwout[0].item())
+        oracle.moe_scatter_accumulate_rows_bf16(m_o, ye, rw_n, sel, e)
+    assert rel_fro(oracle.bf16_to_f32(bf16_to_u16(mixed)), oracle.bf16_to_f32(m_o)) < TOL

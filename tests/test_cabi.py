@@ -35,3 +35,21 @@ def test_argument_validation_without_a_device():
     assert lib.cf_swiglu_forward(None, None, None, -1, None) == cfb._capi.CF_ERR_INVALID_ARG
     assert lib.cf_fp8_quantize_e4m3(None, None, C.c_void_p(16), 0, None) == cfb._capi.CF_OK     # n == 0 is a no-op
     assert lib.cf_moe_topk_route_f32(None, 4, 100, 2, None, None, None, 1) == cfb._capi.CF_ERR_INVALID_ARG
+
+
+def test_shim_compiles_against_the_reference_headers(tmp_path):
+    """The C++ drop-in (namespace ida_native definitions) must match the reference's declarations: compile it
+    against include/ida_native/kernels.hpp where the reference tree is available (this container only)."""
+    import shutil
+    import subprocess
+
+    import pytest
+    ref = "/root/reference"
+    if not os.path.isdir(os.path.join(ref, "include", "ida_native")) or shutil.which("nvcc") is None:
+        pytest.skip("reference tree or nvcc not present")
+    src = os.path.join(ROOT, "canopy-foundry_b200", "shim", "ida_native_kernels.cu")
+    out = tmp_path / "shim.o"
+    r = subprocess.run(["nvcc", "-std=c++20", "-gencode", "arch=compute_100a,code=sm_100a", f"-I{ref}/include",
+                        f"-I{ref}/include-public", f"-I{ROOT}/include", "-c", src, "-o", str(out)],
+                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    assert r.returncode == 0, r.stdout[-3000:]

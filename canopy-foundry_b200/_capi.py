@@ -71,6 +71,7 @@ SIGNATURES = {
     "cf_fp8_quant_act": (ci, [vp, C.POINTER(ActSlotStruct), vp, sz, vp, vp, ci]),
     "cf_refresh_fp8_weight": (ci, [C.POINTER(Fp8WeightStruct), ci, vp]),
     "cf_fp8_linear_forward": (ci, [vp, C.POINTER(ActSlotStruct), vp, ci, ci, vp, fp, ci, vp, ci, vp, ci, vp]),
+    "cf_fp8_linear_static_scratch": (ci, [vp, ci, ci, fp, fp, vp, fp, ci, vp, ci, vp, ci, ip, vp]),
     "cf_bias_add_strided_bf16": (ci, [vp, vp, ci, ci, ci, ci, vp]),
     "cf_swiglu_forward": (ci, [vp, vp, vp, ci, vp]),
     "cf_gelu_forward": (ci, [vp, vp, sz, vp]),

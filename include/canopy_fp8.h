@@ -206,6 +206,23 @@ int cf_fp8_linear_forward(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, int M
                           const float* d_w_descale, int N, const void* d_bias, int bias_mode, void* d_y, int ldy,
                           void* stream);
 
+/* No counterpart in the reference. The same computation as the quantise + GEMM + bias part of
+ * cf_fp8_linear_forward, for callers that may not allocate device memory and therefore cannot create a
+ * cf_ctx: a trainer whose arena already owns the device-memory budget, or a latency-critical thread that
+ * cannot afford the device-wide stall of cudaMalloc / cudaFree. The E4M3 copy of the activation is kept in
+ * a 4 MiB array that is part of the library image (every GPU that loads the library holds it until exit),
+ * so M*K must not exceed 4 MiB (4,194,304 elements); larger calls return CF_ERR_LIMIT. The caller passes
+ * the scale pair to quantise with (for delayed scaling: an ActSlot's snapshot pair) and all inputs and
+ * outputs; the call itself uses no cudaMalloc, cudaFree or other allocating routine.
+ *   y[M,N] bf16 (row stride ldy) = (*d_x_descale * *d_w_descale) * e4m3(x * *d_x_scale) . w8^T  [+ bias]
+ * d_status_or_null: optional device int that receives a non-zero code if a bounded device-side wait gave up.
+ * The first call on each device looks up the array's device address; make that first call outside any
+ * stream capture. All calls share the one array and it keeps the previous call's contents (the call clears
+ * the word it needs zeroed): two calls that overlap on the GPU, e.g. on different streams, race on it. */
+int cf_fp8_linear_static_scratch(const void* d_x, int M, int K, const float* d_x_scale, const float* d_x_descale,
+                                 const void* d_w8, const float* d_w_descale, int N, const void* d_bias, int bias_mode,
+                                 void* d_y, int ldy, int* d_status_or_null, void* stream);
+
 /* ------------------------------------------------------------------ elementwise neighbours of the GEMMs */
 
 /* kernels/moe.cu:338-345, kernels.hpp:243-247. */

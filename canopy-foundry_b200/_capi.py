@@ -29,7 +29,7 @@ class ActSlotStruct(C.Structure):
     _fields_ = [("amax", fp), ("scale", fp), ("descale", fp), ("history", fp), ("history_cursor", ip),
                 ("history_count", ip), ("scale_snapshot", fp), ("descale_snapshot", fp), ("fp8_max", cf),
                 ("init", ci), ("calib_remaining", ci), ("calib_commit_pending", ci), ("calib_min", fp),
-                ("calib_max", fp)]
+                ("calib_max", fp), ("ticket", vp)]
 
 
 class Fp8WeightStruct(C.Structure):

@@ -5,6 +5,7 @@
 
 #include "cf_common.cuh"
 #include "cf_gemm.cuh"
+#include "cf_internal.cuh"
 
 namespace cf {
 
@@ -262,6 +263,7 @@ int cf_act_slot_init(cf_ctx* ctx, cf_act_slot* slot, float fp8_max, int calib_ca
     slot->history_count = reinterpret_cast<int*>(base + 18);
     slot->calib_min = base + 19;
     slot->calib_max = base + 20;
+    slot->ticket = reinterpret_cast<unsigned*>(base + 21);
     slot->history = nullptr;
     slot->fp8_max = fp8_max;
     slot->init = 0;
@@ -333,9 +335,16 @@ int cf_fp8_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, size_t n, 
     }
 
     // steady state: snapshot, record-quantise with the previous scale, advance the ring
-    CF_CUDA(cudaMemsetAsync(slot->amax, 0, sizeof(float), st));
-    CF_CUDA(cudaMemcpyAsync(slot->scale_snapshot, slot->scale, sizeof(float), cudaMemcpyDeviceToDevice, st));
-    CF_CUDA(cudaMemcpyAsync(slot->descale_snapshot, slot->descale, sizeof(float), cudaMemcpyDeviceToDevice, st));
+    CF_TRY(slot_begin(slot->scale, slot->descale, slot->scale_snapshot, slot->descale_snapshot, slot->amax, st));
+    if (slot->ticket) {
+        // two launches in all: the last block of the record pass runs the ring update
+        RingTail tail;
+        tail.fp8_max = slot->fp8_max; tail.scale = slot->scale; tail.descale = slot->descale;
+        tail.history = slot->history; tail.history_len = kHistoryLen;
+        tail.history_cursor = slot->history_cursor; tail.history_count = slot->history_count;
+        tail.ticket = slot->ticket;
+        return quantize_record_fused(d_x, d_out8, slot->scale, slot->amax, n, slot->fp8_max == CF_E5M2_MAX, tail, st);
+    }
     if (slot->fp8_max == CF_E5M2_MAX)
         CF_TRY(cf_fp8_quantize_e5m2_record(d_x, d_out8, slot->scale, slot->amax, n, stream));
     else
@@ -350,11 +359,13 @@ int cf_refresh_fp8_weight(const cf_fp8_weight* w, int recompute_amax, void* stre
     CF_REQUIRE(w->in_dim > 0 && w->out_dim > 0, "cf_refresh_fp8_weight: bad dims");
     const size_t n = static_cast<size_t>(w->in_dim) * w->out_dim;
     if (recompute_amax) CF_TRY(cf_fp8_amax_bf16(w->w, n, w->amax, stream));
-    CF_TRY(cf_fp8_scale_from_amax(w->amax, CF_E4M3_MAX, w->scale, w->descale, stream));
-    // one read of the bf16 master produces both layouts (the reference reads it twice: :4701-4709)
+    // One launch: the scale is derived from the amax inside the kernel (and published), and one read of the
+    // bf16 master produces both layouts (the reference runs scale + two quantise passes: :4700-4709).
+    ScaleFromAmax sfa;
+    sfa.amax = w->amax; sfa.fp8_max = CF_E4M3_MAX; sfa.scale_out = w->scale; sfa.descale_out = w->descale;
     if (w->stored_out_major)
-        return cf_fp8_quant_and_transpose_e4m3(w->w, w->fwd8, w->bwd8, w->scale, w->out_dim, w->in_dim, stream);
-    return cf_fp8_quant_and_transpose_e4m3(w->w, w->bwd8, w->fwd8, w->scale, w->in_dim, w->out_dim, stream);
+        return quant_dual_from_amax(w->w, w->fwd8, w->bwd8, sfa, w->out_dim, w->in_dim, as_stream(stream));
+    return quant_dual_from_amax(w->w, w->bwd8, w->fwd8, sfa, w->in_dim, w->out_dim, as_stream(stream));
 }
 
 int cf_fp8_linear_forward(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, int M, int K, const void* d_w8,

@@ -15,6 +15,7 @@
 // frees TMEM and returns, so a faulty launch cannot hang the GPU.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "cf_common.cuh"
@@ -23,18 +24,33 @@
 namespace cf {
 namespace {
 
-constexpr int BM = 128;
-constexpr int BN = 256;
+constexpr int BM = 128;                 // rows of A / C per CTA (TMEM lanes)
+constexpr int BN = 256;                 // output columns per tile
 constexpr int BK = 128;                 // bytes == FP8 elements per k-block (one 128B swizzle row)
 constexpr int UMMA_K = 32;              // FP8 elements per tcgen05.mma
-constexpr int STAGES = 4;
-constexpr int A_STAGE = BM * BK;        // 16 KiB
-constexpr int B_STAGE = BN * BK;        // 32 KiB
 constexpr int NUM_THREADS = 192;
-constexpr int TMEM_COLS = 512;          // two 128x256 fp32 accumulators
-constexpr int SMEM_BYTES = STAGES * (A_STAGE + B_STAGE) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int TMEM_COLS = 512;          // two 128x256 fp32 accumulators per CTA
 constexpr unsigned long long WAIT_NS = 1500ull * 1000ull * 1000ull;   // per-wait deadline
 constexpr unsigned long long DRAIN_NS = 20ull * 1000ull * 1000ull;
+
+// Output staging for the TMA-store epilogue: per epilogue warp two 32-row x 128-byte (64 bf16) boxes.
+constexpr int C_BOX_COLS = 64;
+constexpr int C_BOX_BYTES = 32 * C_BOX_COLS * 2;           // 4 KiB
+constexpr int C_STAGING = 4 * 2 * C_BOX_BYTES;             // 32 KiB
+
+// Shape of the shared-memory ring. Single CTA: the CTA loads all 256 rows of the B tile. CTA pair
+// (cta_group::2, one 256x256 tile per pair): each CTA loads its own 128 rows of A and HALF of the B tile,
+// which halves the L2 -> shared-memory traffic per SM; the smaller stage buys two more stages.
+template <bool PAIR>
+struct Cfg {
+    static constexpr int B_ROWS = PAIR ? 128 : 256;       // rows of B this CTA loads per stage
+    static constexpr int STAGES = PAIR ? 6 : 4;
+    static constexpr int A_STAGE = BM * BK;               // 16 KiB
+    static constexpr int B_STAGE = B_ROWS * BK;           // 16 / 32 KiB
+    static constexpr int TILE_M = PAIR ? 256 : 128;       // rows of C per tile (pair: 128 per CTA)
+    static constexpr int RING = STAGES * (A_STAGE + B_STAGE);
+    static constexpr int SMEM_BYTES = RING + C_STAGING + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -82,8 +98,58 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 __device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// Pair form: the arrive is delivered to the barrier at the same offset in both CTAs of the pair.
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of `local_addr` in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t mapa(uint32_t local_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Pair form of the TMA load: the data lands in this CTA's shared memory, the byte count is credited to a
+// barrier that may live in the other CTA of the pair (no multicast: every CTA fetches its own box).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void umma_f8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
 }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -125,14 +191,15 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
 
 // kind::f8f6f4 instruction descriptor: D fp32 (bits 4-5 = 1), A format bits 7-9, B format bits 10-12
 // (0 = E4M3, 1 = E5M2), both operands K-major (bits 15,16 = 0), N>>3 in bits 17-22, M>>4 in bits 24-28.
-__device__ __forceinline__ uint32_t make_idesc(int a_e5m2, int b_e5m2) {
+__device__ __forceinline__ uint32_t make_idesc(int a_e5m2, int b_e5m2, int mma_m) {
     return (1u << 4) | (static_cast<uint32_t>(a_e5m2) << 7) | (static_cast<uint32_t>(b_e5m2) << 10) |
-           (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+           (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(mma_m >> 4) << 24);
 }
+
 
 struct TileCoord {
     int row0;        // first global row of A / C for this tile
-    int valid_rows;  // rows of the tile that belong to the expert (<= BM)
+    int valid_rows;  // rows of the tile that belong to the expert (<= tile rows)
     int n0;          // first output column
     int b_row0;      // first row of the stacked [E*N, K] weight block
     int group;
@@ -140,34 +207,43 @@ struct TileCoord {
 
 // Maps a linear tile index to coordinates. Dense: one group of p.M rows. Grouped: the m-blocks of
 // all experts are concatenated in expert order; counts/offsets are read from device memory.
-__device__ __forceinline__ int total_m_blocks(const GemmParams& p) {
-    if (p.groups <= 1 && p.d_counts == nullptr) return (p.M + BM - 1) / BM;
+__device__ __forceinline__ int total_m_blocks(const GemmParams& p, int TM) {
+    if (p.groups <= 1 && p.d_counts == nullptr) return (p.M + TM - 1) / TM;
     int t = 0;
-    for (int e = 0; e < p.groups; ++e) t += (max(p.d_counts[e], 0) + BM - 1) / BM;
+    for (int e = 0; e < p.groups; ++e) t += (max(p.d_counts[e], 0) + TM - 1) / TM;
     return t;
 }
-__device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, int m_blocks) {
+__device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, int m_blocks, int TM) {
     TileCoord c;
-    const int nb = tile / m_blocks;
-    int mb = tile - nb * m_blocks;
+    // Band rasterisation: consecutive tile indices walk RASTER_M row blocks down, then one column block
+    // right, so the tiles in flight at any time share few A and B slabs (L2 reuse).
+    const int n_blocks = (p.N + BN - 1) / BN;
+    const int RASTER_M = p.raster_m;
+    const int band_tiles = RASTER_M * n_blocks;
+    const int band = tile / band_tiles;
+    const int first_m = band * RASTER_M;
+    const int band_m = min(RASTER_M, m_blocks - first_m);
+    const int r = tile - band * band_tiles;
+    const int nb = r / band_m;
+    int mb = first_m + (r - nb * band_m);
     c.n0 = nb * BN;
     if (p.groups <= 1 && p.d_counts == nullptr) {
         c.group = 0;
-        c.row0 = mb * BM;
-        c.valid_rows = min(BM, p.M - c.row0);
+        c.row0 = mb * TM;
+        c.valid_rows = min(TM, p.M - c.row0);
         c.b_row0 = c.n0;
         return c;
     }
     int e = 0, cnt = 0;
     for (; e < p.groups; ++e) {
         cnt = max(p.d_counts[e], 0);
-        const int blocks = (cnt + BM - 1) / BM;
+        const int blocks = (cnt + TM - 1) / TM;
         if (mb < blocks) break;
         mb -= blocks;
     }
     c.group = e;
-    c.row0 = p.d_offsets[e] + mb * BM;
-    c.valid_rows = min(BM, cnt - mb * BM);
+    c.row0 = p.d_offsets[e] + mb * TM;
+    c.valid_rows = min(TM, cnt - mb * TM);
     c.b_row0 = e * p.N + c.n0;
     return c;
 }
@@ -199,30 +275,39 @@ __device__ __forceinline__ void store_one(const GemmParams& p, long long grow, i
     }
 }
 
+template <bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+              const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
+    using C = Cfg<PAIR>;
+    constexpr int STAGES = C::STAGES, A_STAGE = C::A_STAGE, B_STAGE = C::B_STAGE, TM = C::TILE_M;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;           // swizzle atoms need 1024-byte alignment
     const uint32_t smem_a = base;
     const uint32_t smem_b = base + STAGES * A_STAGE;
-    const uint32_t bars = smem_b + STAGES * B_STAGE;         // 8-byte mbarriers
+    const uint32_t smem_c = smem_b + STAGES * B_STAGE;       // output staging (1024-byte aligned)
+    const uint32_t bars = smem_c + C_STAGING;                // 8-byte mbarriers
     const uint32_t full_bar = bars, empty_bar = bars + 8 * STAGES;
     const uint32_t tfull_bar = bars + 16 * STAGES, tempty_bar = tfull_bar + 16, drain_bar = tempty_bar + 16;
     uint8_t* gen = smem_raw + (base - raw);
-    volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(gen + STAGES * (A_STAGE + B_STAGE) + 16 * STAGES + 48);
+    volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(gen + C::RING + C_STAGING + 16 * STAGES + 48);
     volatile int* s_abort = reinterpret_cast<volatile int*>(const_cast<uint32_t*>(s_tmem) + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;       // 0 = leader of the pair
+    const bool leader = cta_rank == 0;
+    const int unit = PAIR ? (blockIdx.x >> 1) : blockIdx.x;        // persistent scheduling unit (CTA or pair)
+    const int n_units = PAIR ? (gridDim.x >> 1) : gridDim.x;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(full_bar + 8 * s, 1);
-            mbar_init(empty_bar + 8 * s, 1);
+            mbar_init(full_bar + 8 * s, 1);                  // one arrive.expect_tx by the (leader's) producer
+            mbar_init(empty_bar + 8 * s, 1);                 // one tcgen05.commit
         }
         for (int a = 0; a < 2; ++a) {
-            mbar_init(tfull_bar + 8 * a, 1);
-            mbar_init(tempty_bar + 8 * a, 4);
+            mbar_init(tfull_bar + 8 * a, 1);                 // one tcgen05.commit
+            mbar_init(tempty_bar + 8 * a, PAIR ? 8 : 4);     // one arrive per epilogue warp (of both CTAs)
         }
         mbar_init(drain_bar, 1);
         s_abort[0] = 0;
@@ -231,51 +316,75 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+        if (p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t*>(s_tmem))), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t*>(s_tmem))), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t*>(s_tmem))), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();                            // peer barriers are initialised before any remote signal
     tcgen05_fence_after();
     const uint32_t tmem_base = *s_tmem;
 
-    const int m_blocks = total_m_blocks(p);
+    const int m_blocks = total_m_blocks(p, TM);
     const int n_blocks = (p.N + BN - 1) / BN;
     const int total_tiles = m_blocks * n_blocks;
     const int k_iters = (p.K + BK - 1) / BK;
 
     if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer
+        // ------------------------------------------------------------ TMA producer (both CTAs of a pair)
         if (lane == 0) {
             int it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const TileCoord tc = tile_coord(p, tile, m_blocks);
+            // the byte count of a stage is credited to the leader's barrier
+            const uint32_t full_dst = PAIR ? mapa(full_bar, 0) : full_bar;
+            for (int tile = unit; ok && tile < total_tiles; tile += n_units) {
+                const TileCoord tc = tile_coord(p, tile, m_blocks, TM);
+                const int a_row = tc.row0 + static_cast<int>(cta_rank) * BM;
+                const int b_row = tc.b_row0 + static_cast<int>(cta_rank) * C::B_ROWS;
                 for (int kb = 0; kb < k_iters; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(empty_bar + 8 * s, ph ^ 1, s_abort)) { ok = false; break; }
-                    mbar_expect_tx(full_bar + 8 * s, A_STAGE + B_STAGE);
-                    tma_load_2d(smem_a + s * A_STAGE, &map_a, full_bar + 8 * s, kb * BK, tc.row0);
-                    tma_load_2d(smem_b + s * B_STAGE, &map_b, full_bar + 8 * s, kb * BK, tc.b_row0);
+#ifdef CF_GEMM_EXPERIMENT
+                    if ((p.experiment & 1) && it >= STAGES) {      // no operand traffic after the first ring fill
+                        if (leader) mbar_arrive(full_bar + 8 * s);
+                        continue;
+                    }
+#endif
+                    if (PAIR) {
+                        if (leader) mbar_expect_tx(full_bar + 8 * s, 2 * (A_STAGE + B_STAGE));
+                        tma_load_2d_pair(smem_a + s * A_STAGE, &map_a, full_dst + 8 * s, kb * BK, a_row);
+                        tma_load_2d_pair(smem_b + s * B_STAGE, &map_b, full_dst + 8 * s, kb * BK, b_row);
+                    } else {
+                        mbar_expect_tx(full_bar + 8 * s, A_STAGE + B_STAGE);
+                        tma_load_2d(smem_a + s * A_STAGE, &map_a, full_bar + 8 * s, kb * BK, a_row);
+                        tma_load_2d(smem_b + s * B_STAGE, &map_b, full_bar + 8 * s, kb * BK, b_row);
+                    }
                 }
             }
             if (!ok && !*s_abort) { *s_abort = 1; atomicExch(p.d_status, 0x100 | 1); }
-            if (*s_abort || !ok) {
-                // wait (bounded) for this CTA's copies still in flight
+            if ((*s_abort || !ok) && leader) {
+                // wait (bounded) for the copies still in flight into this stage ring (for a pair the leader's
+                // barriers also count the peer's copies; the peer meets the leader at the closing cluster barrier)
                 for (int j = max(0, it - STAGES); j < it; ++j)
                     mbar_wait(full_bar + 8 * (j % STAGES), (j / STAGES) & 1, s_abort + 1 /*never set*/, DRAIN_NS);
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc(p.a_e5m2, p.b_e5m2);
+        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && leader) {
+            const uint32_t idesc = make_idesc(p.a_e5m2, p.b_e5m2, TM);
             int it = 0, local_tile = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local_tile) {
+            for (int tile = unit; ok && tile < total_tiles; tile += n_units, ++local_tile) {
                 const int acc = local_tile & 1;
                 if (!mbar_wait(tempty_bar + 8 * acc, ((local_tile >> 1) & 1) ^ 1, s_abort)) { ok = false; break; }
                 tcgen05_fence_after();
@@ -289,32 +398,39 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
 #pragma unroll
                     for (int kk = 0; kk < BK / UMMA_K; ++kk) {
                         // advancing 32 bytes inside the 128B swizzle atom = +2 in the (addr >> 4) field
-                        umma_f8(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        if (PAIR) umma_f8_pair(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        else umma_f8(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
                     }
-                    tcgen05_commit(empty_bar + 8 * s);     // frees the stage once these MMAs have read it
+                    // frees the stage (in both CTAs of a pair) once these MMAs have read it
+                    if (PAIR) tcgen05_commit_pair(empty_bar + 8 * s); else tcgen05_commit(empty_bar + 8 * s);
                 }
                 if (!ok) break;
-                tcgen05_commit(tfull_bar + 8 * acc);       // accumulator complete
+                if (PAIR) tcgen05_commit_pair(tfull_bar + 8 * acc); else tcgen05_commit(tfull_bar + 8 * acc);
             }
             if (!ok && !*s_abort) { *s_abort = 1; atomicExch(p.d_status, 0x200 | 1); }
             if (*s_abort || !ok) {
-                tcgen05_commit(drain_bar);                 // all MMAs issued so far
+                // all MMAs issued so far
+                if (PAIR) asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(drain_bar) : "memory");
+                else tcgen05_commit(drain_bar);
                 mbar_wait(drain_bar, 0, s_abort + 1, DRAIN_NS);
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue warps
+        // ------------------------------------------------------------ epilogue warps (both CTAs of a pair)
         const int quarter = warp & 3;                      // TMEM lanes this warp may read
         const int trow = quarter * 32 + lane;
+        const uint32_t tempty_dst = PAIR ? mapa(tempty_bar, 0) : tempty_bar;
         int local_tile = 0;
+        uint32_t store_seq = 0;                            // alternates this warp's two staging boxes
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local_tile) {
+        for (int tile = unit; ok && tile < total_tiles; tile += n_units, ++local_tile) {
             const int acc = local_tile & 1;
-            const TileCoord tc = tile_coord(p, tile, m_blocks);
+            const TileCoord tc = tile_coord(p, tile, m_blocks, TM);
             if (!mbar_wait(tfull_bar + 8 * acc, (local_tile >> 1) & 1, s_abort)) { ok = false; break; }
             tcgen05_fence_after();
-            const long long grow = static_cast<long long>(tc.row0) + trow;
-            const bool row_ok = trow < tc.valid_rows;
+            const int row_in_tile = static_cast<int>(cta_rank) * BM + trow;
+            const long long grow = static_cast<long long>(tc.row0) + row_in_tile;
+            const bool row_ok = row_in_tile < tc.valid_rows;
             float da = 1.0f;
             if (row_ok) {
                 if (p.d_a_row_descale) da = p.d_a_row_descale[grow];
@@ -322,30 +438,36 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             }
             const float db_t = p.d_b_col_descale ? 1.0f : *p.d_b_descale;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+            // Full boxes of bf16 output go through shared memory and TMA stores (whole 128-byte lines per row);
+            // ragged rows of a grouped tile, column tails and the fp32 / accumulate forms use direct stores.
+            const int warp_row0 = static_cast<int>(cta_rank) * BM + quarter * 32;
+            const bool warp_rows_full = (p.d_counts == nullptr) || (warp_row0 + 32 <= tc.valid_rows);
+            if (p.tma_store && warp_rows_full && warp_row0 < tc.valid_rows) {
+                const uint32_t stage0 = smem_c + static_cast<uint32_t>(warp - 2) * 2 * C_BOX_BYTES;
+                const uint32_t row_off = static_cast<uint32_t>(lane) * 128u;
+                const uint32_t sw = static_cast<uint32_t>(lane & 7);
+                int ch64 = 0;
 #pragma unroll 1
-            for (int ch = 0; ch < BN / 32; ++ch) {
-                const int col0 = tc.n0 + ch * 32;
-                if (col0 >= p.N) break;                    // warp-uniform
-                uint32_t v[32];
-                tmem_ld32(taddr + ch * 32, v);
-                tmem_ld_wait();
-                if (!row_ok) continue;
-                const bool full = col0 + 32 <= p.N;
-                if (p.out_kind == 0 && p.c_vec && full) {
-                    uint16_t* crow = static_cast<uint16_t*>(p.C) + grow * p.ldc + col0;
-                    uint32_t w[16];
+                for (; ch64 < BN / C_BOX_COLS; ++ch64) {
+                    const int col0 = tc.n0 + ch64 * C_BOX_COLS;
+                    if (col0 + C_BOX_COLS > p.N) break;    // warp-uniform; the tail takes the direct path below
+                    uint32_t v0[32], v1[32];
+                    tmem_ld32(taddr + ch64 * C_BOX_COLS, v0);
+                    tmem_ld32(taddr + ch64 * C_BOX_COLS + 32, v1);
+                    tmem_ld_wait();
+                    uint32_t w[32];
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
+                    for (int j = 0; j < 32; ++j) {
+                        const uint32_t r0 = j < 16 ? v0[2 * j] : v1[2 * j - 32];
+                        const uint32_t r1 = j < 16 ? v0[2 * j + 1] : v1[2 * j - 31];
+                        float x0 = __uint_as_float(r0), x1 = __uint_as_float(r1);
                         const float db0 = p.d_b_col_descale ? p.d_b_col_descale[col0 + 2 * j] : db_t;
                         const float db1 = p.d_b_col_descale ? p.d_b_col_descale[col0 + 2 * j + 1] : db_t;
                         x0 *= da * db0;
                         x1 *= da * db1;
                         if (p.bias_mode == 1) {
                             const uint32_t bb = *reinterpret_cast<const uint32_t*>(p.bias + col0 + 2 * j);
-                            x0 += __uint_as_float(bb << 16);
-                            x1 += __uint_as_float(bb & 0xffff0000u);
-                            w[j] = pack_bf16x2(x0, x1);
+                            w[j] = pack_bf16x2(x0 + __uint_as_float(bb << 16), x1 + __uint_as_float(bb & 0xffff0000u));
                         } else if (p.bias_mode == 2) {
                             const uint32_t bb = *reinterpret_cast<const uint32_t*>(p.bias + col0 + 2 * j);
                             const uint32_t r = pack_bf16x2(x0, x1);
@@ -355,10 +477,28 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                             w[j] = pack_bf16x2(x0, x1);
                         }
                     }
-                    uint4* dst = reinterpret_cast<uint4*>(crow);
+                    const uint32_t buf = stage0 + (store_seq++ & 1u) * C_BOX_BYTES;
+                    if (lane == 0) bulk_wait_read_1();     // the store that last read this buffer has drained it
+                    __syncwarp();
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
-                } else {
+                    for (int q = 0; q < 8; ++q)            // 16-byte chunk q of this row sits at (q ^ row%8): 128B swizzle
+                        st_shared_v4(buf + row_off + ((static_cast<uint32_t>(q) ^ sw) << 4), w[4 * q], w[4 * q + 1],
+                                     w[4 * q + 2], w[4 * q + 3]);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&map_c, buf, col0, tc.row0 + warp_row0);
+                        bulk_commit();
+                    }
+                }
+                // column tail (N not a multiple of 64): direct stores
+                for (int ch = ch64 * 2; ch < BN / 32; ++ch) {
+                    const int col0 = tc.n0 + ch * 32;
+                    if (col0 >= p.N) break;
+                    uint32_t v[32];
+                    tmem_ld32(taddr + ch * 32, v);
+                    tmem_ld_wait();
+                    if (!row_ok) continue;
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const int col = col0 + j;
@@ -368,20 +508,79 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                         }
                     }
                 }
-            }
+            } else {
+#pragma unroll 1
+                for (int ch = 0; ch < BN / 32; ++ch) {
+                    const int col0 = tc.n0 + ch * 32;
+                    if (col0 >= p.N) break;                    // warp-uniform
+    #ifdef CF_GEMM_EXPERIMENT
+                    if (p.experiment & 2) break;               // no accumulator read-out, no stores
+    #endif
+                    uint32_t v[32];
+                    tmem_ld32(taddr + ch * 32, v);
+                    tmem_ld_wait();
+                    if (!row_ok) continue;
+    #ifdef CF_GEMM_EXPERIMENT
+                    if (p.experiment & 4) continue;            // accumulator read-out but no stores
+    #endif
+                    const bool full = col0 + 32 <= p.N;
+                    if (p.out_kind == 0 && p.c_vec && full) {
+                        uint16_t* crow = static_cast<uint16_t*>(p.C) + grow * p.ldc + col0;
+                        uint32_t w[16];
+    #pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
+                            const float db0 = p.d_b_col_descale ? p.d_b_col_descale[col0 + 2 * j] : db_t;
+                            const float db1 = p.d_b_col_descale ? p.d_b_col_descale[col0 + 2 * j + 1] : db_t;
+                            x0 *= da * db0;
+                            x1 *= da * db1;
+                            if (p.bias_mode == 1) {
+                                const uint32_t bb = *reinterpret_cast<const uint32_t*>(p.bias + col0 + 2 * j);
+                                x0 += __uint_as_float(bb << 16);
+                                x1 += __uint_as_float(bb & 0xffff0000u);
+                                w[j] = pack_bf16x2(x0, x1);
+                            } else if (p.bias_mode == 2) {
+                                const uint32_t bb = *reinterpret_cast<const uint32_t*>(p.bias + col0 + 2 * j);
+                                const uint32_t r = pack_bf16x2(x0, x1);
+                                w[j] = pack_bf16x2(__uint_as_float(r << 16) + __uint_as_float(bb << 16),
+                                                   __uint_as_float(r & 0xffff0000u) + __uint_as_float(bb & 0xffff0000u));
+                            } else {
+                                w[j] = pack_bf16x2(x0, x1);
+                            }
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(crow);
+    #pragma unroll
+                        for (int q = 0; q < 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+                    } else {
+    #pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int col = col0 + j;
+                            if (col < p.N) {
+                                const float db = p.d_b_col_descale ? p.d_b_col_descale[col] : db_t;
+                                store_one(p, grow, col, __uint_as_float(v[j]), da, db);
+                            }
+                        }
+                    }
+                }
+    }
             tcgen05_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar + 8 * acc);
+            if (lane == 0) {
+                if (PAIR) mbar_arrive_cluster(tempty_dst + 8 * acc); else mbar_arrive(tempty_bar + 8 * acc);
+            }
         }
+        if (lane == 0) bulk_wait_all();                    // this warp's TMA stores have completed
         if (!ok && lane == 0 && !*s_abort) { *s_abort = 1; atomicExch(p.d_status, 0x300 | 1); }
     }
 
     tcgen05_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();          // the peer may still read this CTA's operands / signal its barriers
     if (warp == 1) {
         __syncwarp();
         tcgen05_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -448,6 +647,47 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, lon
     return CF_OK;
 }
 
+// Number of CTA pairs the device can keep resident at once (cached per device); 0 = pairs unusable.
+int max_resident_pairs() {
+    static int cached[64];
+    static std::once_flag once[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    std::call_once(once[dev & 63], [&] {
+        int n = 0;
+        if (cudaFuncSetAttribute(k_gemm_fp8_nt<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true>::SMEM_BYTES) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(2 * sm_count());
+            cfg.blockDim = dim3(NUM_THREADS);
+            cfg.dynamicSmemBytes = Cfg<true>::SMEM_BYTES;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+            cfg.attrs = at;
+            cfg.numAttrs = 1;
+            if (cudaOccupancyMaxActiveClusters(&n, k_gemm_fp8_nt<true>, &cfg) != cudaSuccess) n = 0;
+        }
+        (void)cudaGetLastError();
+        cached[dev & 63] = n;
+    });
+    return cached[dev & 63];
+}
+
+// bf16 output tensor [rows, N] with row pitch ldc elements, box {64 columns, 32 rows}, 128B swizzle.
+int make_map_c(CUtensorMap* map, const void* ptr, long long rows, long long N, long long ldc) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { set_error("cuTensorMapEncodeTiled entry point not available"); return CF_ERR_CUDA; }
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldc) * 2};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(C_BOX_COLS), 32};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (output) failed with CUresult %d", static_cast<int>(r)); return CF_ERR_CUDA; }
+    return CF_OK;
+}
+
 }  // namespace
 
 int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const void* d_B, long long b_rows,
@@ -461,28 +701,70 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     p.c_vec = (p.out_kind == 0) && (ca % 16 == 0) && (p.ldc % 8 == 0) &&
               (p.bias == nullptr || reinterpret_cast<uintptr_t>(p.bias) % 4 == 0);
     if (!p.bias) p.bias_mode = 0;
+#ifdef CF_GEMM_EXPERIMENT
+    { const char* e = std::getenv("CF_GEMM_EXPERIMENT"); p.experiment = e ? std::atoi(e) : 0; }
+    { const char* e = std::getenv("CF_GEMM_RASTER"); if (e && std::atoi(e) > 0) p.raster_m = std::atoi(e); }
+#endif
     if (!tma_ok) {
         const int grid = sm_count() * 4;
         k_gemm_fp8_nt_simt<<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(d_A), lda, static_cast<const uint8_t*>(d_B), p);
         CF_LAUNCH_CHECK("gemm_fp8_nt_simt");
         return CF_OK;
     }
-    CUtensorMap map_a, map_b;
+    // Paired CTAs (256-row tiles) pay off when the row blocks are mostly full; small or very ragged problems
+    // keep the 128-row single-CTA tiles. CF_GEMM_TILE=1|2 forces a form (A/B measurements, tests).
+    static const int forced = [] { const char* e = std::getenv("CF_GEMM_TILE"); return e ? std::atoi(e) : 0; }();
+    const long long rows_per_group = (p.d_counts ? a_rows / (p.groups > 0 ? p.groups : 1) : p.M);
+    bool pair = forced == 2 || (forced != 1 && rows_per_group >= 512);
+    const int pairs = pair ? max_resident_pairs() : 0;
+    if (pairs <= 0) pair = false;
+
+    CUtensorMap map_a, map_b, map_c;
     int r = make_map(&map_a, d_A, a_rows, p.K, lda, BM);
     if (r != CF_OK) return r;
-    r = make_map(&map_b, d_B, b_rows, p.K, p.K, BN);
+    r = make_map(&map_b, d_B, b_rows, p.K, p.K, pair ? Cfg<true>::B_ROWS : Cfg<false>::B_ROWS);
     if (r != CF_OK) return r;
-    static std::once_flag attr_once[64];
+    p.c_rows = p.d_counts ? a_rows : p.M;
+    p.tma_store = (p.c_vec && p.N >= C_BOX_COLS) ? 1 : 0;
+    static const bool no_tma_store = [] { const char* e = std::getenv("CF_GEMM_DIRECT_STORE"); return e && e[0] == '1'; }();
+    if (no_tma_store) p.tma_store = 0;
+    if (p.tma_store) {
+        r = make_map_c(&map_c, p.C, p.c_rows, p.N, p.ldc);
+        if (r != CF_OK) return r;
+    } else {
+        map_c = map_a;   // never dereferenced by the kernel when tma_store == 0
+    }
     int dev = 0;
     CF_CUDA(cudaGetDevice(&dev));
+    if (pair) {
+        // tile_upper_bound counts 128-row blocks; a pair tile covers two of them
+        const int n_blocks = (p.N + BN - 1) / BN;
+        const int m128 = tile_upper_bound / (n_blocks > 0 ? n_blocks : 1);
+        const int pair_tiles = ((m128 + 1) / 2 + (p.d_counts ? p.groups : 0)) * n_blocks;
+        const int units = pair_tiles < pairs ? pair_tiles : pairs;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * units);
+        cfg.blockDim = dim3(NUM_THREADS);
+        cfg.dynamicSmemBytes = Cfg<true>::SMEM_BYTES;
+        cfg.stream = st;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        CF_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_fp8_nt<true>, map_a, map_b, map_c, p));
+        CF_LAUNCH_CHECK("gemm_fp8_nt<pair>");
+        return CF_OK;
+    }
+    static std::once_flag attr_once[64];
     cudaError_t attr_err = cudaSuccess;
     std::call_once(attr_once[dev & 63], [&] {
-        attr_err = cudaFuncSetAttribute(k_gemm_fp8_nt, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        attr_err = cudaFuncSetAttribute(k_gemm_fp8_nt<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<false>::SMEM_BYTES);
     });
     if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(k_gemm_fp8_nt)");
     const int sms = sm_count();
     const int grid = tile_upper_bound < sms ? tile_upper_bound : sms;
-    k_gemm_fp8_nt<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+    k_gemm_fp8_nt<false><<<grid, NUM_THREADS, Cfg<false>::SMEM_BYTES, st>>>(map_a, map_b, map_c, p);
     CF_LAUNCH_CHECK("gemm_fp8_nt");
     return CF_OK;
 }

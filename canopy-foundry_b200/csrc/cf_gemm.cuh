@@ -23,9 +23,13 @@ struct GemmParams {
     const uint16_t* bias = nullptr;
     int bias_mode = 0;
     int c_vec = 0;                  // filled by the launcher
+    int tma_store = 0;              // filled by the launcher: bf16 output goes through shared memory + TMA stores
+    long long c_rows = 0;           // filled by the launcher: row extent of C for the store tensor map
     int a_e5m2 = 0;
     int b_e5m2 = 0;
     int* d_status = nullptr;        // context status word (bounded-wait failures)
+    int raster_m = 8;               // row blocks per rasterisation band
+    int experiment = 0;             // measurement builds only (-DCF_GEMM_EXPERIMENT): 1 no operand loads, 2 no epilogue, 4 no stores
 };
 
 // a_rows / b_rows: row extents of the two byte matrices as the tensor maps should see them.

@@ -5,11 +5,52 @@
 //   amax = integer atomicMax over fmaxf(|x|) partials           (fp8.cu:27-31)
 // max() is order-free, so wider threads/vectors change no bit of the result.
 #include "cf_common.cuh"
+#include "cf_internal.cuh"
 
 namespace cf {
 namespace {
 
 constexpr int kThreads = 256;
+
+// Delayed-scale ring update (kernels/fp8.cu:105-142), shared by the stand-alone kernel and the fused tail.
+__device__ __forceinline__ void ring_update(float amax, float fp8_max, float* scale, float* descale, float* history,
+                                            int history_len, int* history_cursor, int* history_count) {
+    const float a = fmaxf(amax, 1e-12f);
+    if (history_len <= 0) {
+        *scale = __fdiv_rn(fp8_max, a);
+        *descale = __fdiv_rn(a, fp8_max);
+        return;
+    }
+    int cursor = *history_cursor;
+    int count = *history_count;
+    if (cursor < 0 || cursor >= history_len) cursor = 0;
+    history[cursor] = a;
+    cursor = (cursor + 1) % history_len;
+    if (count < history_len) ++count;
+    float m = history[0];
+    for (int i = 1; i < count; ++i) m = fmaxf(m, history[i]);
+    m = fmaxf(m, 1e-12f);
+    *history_cursor = cursor;
+    *history_count = count;
+    *scale = __fdiv_rn(fp8_max, m);
+    *descale = __fdiv_rn(m, fp8_max);
+}
+
+// After the block's amax has been committed: the last block of the grid to get here runs the ring update,
+// so the record pass and the scale update are one launch.
+__device__ __forceinline__ void fused_tail(const RingTail& t, float* amax) {
+    if (t.ticket == nullptr) return;
+    if (threadIdx.x == 0) {
+        __threadfence();                                    // this block's atomicMax is visible before its ticket
+        const unsigned prev = atomicAdd(t.ticket, 1u);
+        if (prev == gridDim.x - 1) {
+            __threadfence();
+            const float a = __int_as_float(atomicMax(reinterpret_cast<int*>(amax), 0));   // coherent read
+            ring_update(a, t.fp8_max, t.scale, t.descale, t.history, t.history_len, t.history_cursor, t.history_count);
+            *t.ticket = 0;                                  // ready for the next call
+        }
+    }
+}
 
 __device__ __forceinline__ uint4 ldg_stream16(const void* p) {
     uint4 v;
@@ -44,7 +85,7 @@ __device__ __forceinline__ float amax8(float local, const float (&f)[8]) {
 template <bool E5M2, bool QUANT, bool RECORD>
 __global__ void __launch_bounds__(kThreads) k_stream(const uint16_t* __restrict__ x, uint8_t* __restrict__ out,
                                                      const float* __restrict__ scale, float* __restrict__ amax,
-                                                     size_t n, size_t head, size_t nvec) {
+                                                     size_t n, size_t head, size_t nvec, const RingTail tail) {
     const float s = QUANT ? *scale : 0.0f;
     float local = 0.0f;
     const uint16_t* xv = x + head;
@@ -89,14 +130,17 @@ __global__ void __launch_bounds__(kThreads) k_stream(const uint16_t* __restrict_
             if (QUANT) out[idx] = cvt_fp8<E5M2>(v * s);
         }
     }
-    if (RECORD) block_amax_commit(local, amax);
+    if (RECORD) {
+        block_amax_commit(local, amax);
+        fused_tail(tail, amax);
+    }
 }
 
 // Fully scalar form for pointers whose relative alignment rules out 16-byte accesses.
 template <bool E5M2, bool QUANT, bool RECORD>
 __global__ void __launch_bounds__(kThreads) k_stream_scalar(const uint16_t* __restrict__ x, uint8_t* __restrict__ out,
                                                             const float* __restrict__ scale,
-                                                            float* __restrict__ amax, size_t n) {
+                                                            float* __restrict__ amax, size_t n, const RingTail tail) {
     const float s = QUANT ? *scale : 0.0f;
     float local = 0.0f;
     for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n;
@@ -105,13 +149,26 @@ __global__ void __launch_bounds__(kThreads) k_stream_scalar(const uint16_t* __re
         if (RECORD) local = fmaxf(local, fabsf(v));
         if (QUANT) out[i] = cvt_fp8<E5M2>(v * s);
     }
-    if (RECORD) block_amax_commit(local, amax);
+    if (RECORD) {
+        block_amax_commit(local, amax);
+        fused_tail(tail, amax);
+    }
+}
+
+__global__ void k_ring_update_only(const float* amax, const RingTail t) {
+    ring_update(*amax, t.fp8_max, t.scale, t.descale, t.history, t.history_len, t.history_cursor, t.history_count);
 }
 
 template <bool E5M2, bool QUANT, bool RECORD>
 int launch_stream(const void* d_x, void* d_out, const float* d_scale, float* d_amax, size_t n, cudaStream_t st,
-                  const char* name) {
-    if (n == 0) return CF_OK;
+                  const char* name, const RingTail tail = RingTail()) {
+    if (n == 0) {
+        if (tail.ticket) {     // nothing to scan: the ring still advances with the caller-zeroed amax
+            k_ring_update_only<<<1, 1, 0, st>>>(d_amax, tail);
+            CF_LAUNCH_CHECK(name);
+        }
+        return CF_OK;
+    }
     const uintptr_t xa = reinterpret_cast<uintptr_t>(d_x);
     const uintptr_t oa = reinterpret_cast<uintptr_t>(d_out);
     // Peel `head` elements so that the input is 16-byte aligned; the vector path also needs the
@@ -128,7 +185,7 @@ int launch_stream(const void* d_x, void* d_out, const float* d_scale, float* d_a
         const size_t blocks = (n + kThreads - 1) / kThreads;
         const unsigned grid = static_cast<unsigned>(blocks < static_cast<size_t>(sms) * 16 ? blocks : static_cast<size_t>(sms) * 16);
         k_stream_scalar<E5M2, QUANT, RECORD><<<grid, kThreads, 0, st>>>(
-            static_cast<const uint16_t*>(d_x), static_cast<uint8_t*>(d_out), d_scale, d_amax, n);
+            static_cast<const uint16_t*>(d_x), static_cast<uint8_t*>(d_out), d_scale, d_amax, n, tail);
     } else {
         const size_t nvec = (n - head) / 16;
         size_t blocks = (nvec + 2 * kThreads - 1) / (2 * kThreads);
@@ -136,7 +193,7 @@ int launch_stream(const void* d_x, void* d_out, const float* d_scale, float* d_a
         const size_t cap = static_cast<size_t>(sms) * 8;
         const unsigned grid = static_cast<unsigned>(blocks < cap ? blocks : cap);
         k_stream<E5M2, QUANT, RECORD><<<grid, kThreads, 0, st>>>(
-            static_cast<const uint16_t*>(d_x), static_cast<uint8_t*>(d_out), d_scale, d_amax, n, head, nvec);
+            static_cast<const uint16_t*>(d_x), static_cast<uint8_t*>(d_out), d_scale, d_amax, n, head, nvec, tail);
     }
     CF_LAUNCH_CHECK(name);
     return CF_OK;
@@ -151,25 +208,15 @@ __global__ void k_scale_from_amax(const float* amax, float fp8_max, float* scale
 
 __global__ void k_update_delayed_scale(const float* amax, float fp8_max, float* scale, float* descale, float* history,
                                        int history_len, int* history_cursor, int* history_count) {
-    const float a = fmaxf(*amax, 1e-12f);
-    if (history_len <= 0) {
-        *scale = __fdiv_rn(fp8_max, a);
-        *descale = __fdiv_rn(a, fp8_max);
-        return;
-    }
-    int cursor = *history_cursor;
-    int count = *history_count;
-    if (cursor < 0 || cursor >= history_len) cursor = 0;
-    history[cursor] = a;
-    cursor = (cursor + 1) % history_len;
-    if (count < history_len) ++count;
-    float m = history[0];
-    for (int i = 1; i < count; ++i) m = fmaxf(m, history[i]);
-    m = fmaxf(m, 1e-12f);
-    *history_cursor = cursor;
-    *history_count = count;
-    *scale = __fdiv_rn(fp8_max, m);
-    *descale = __fdiv_rn(m, fp8_max);
+    ring_update(*amax, fp8_max, scale, descale, history, history_len, history_cursor, history_count);
+}
+
+// Start of a steady-state fp8_quant_act call: snapshot the pair the forward pass is about to use and zero the
+// amax slot (src/trainer.cu:4823-4827 does this with two scalar copies and a memset).
+__global__ void k_slot_begin(const float* scale, const float* descale, float* snap_scale, float* snap_descale, float* amax) {
+    *snap_scale = *scale;
+    *snap_descale = *descale;
+    *amax = 0.0f;
 }
 
 __global__ void k_calib_minmax(const float* amax, float* cmin, float* cmax) {
@@ -279,11 +326,25 @@ template <bool SRC_BF16>
 __global__ void __launch_bounds__(kThreads) k_tile_transpose(const void* __restrict__ src, uint8_t* __restrict__ direct,
                                                              uint8_t* __restrict__ transposed,
                                                              const float* __restrict__ scale, int R, int Ccols,
-                                                             int src_vec, int direct_vec, int trans_vec) {
+                                                             int src_vec, int direct_vec, int trans_vec,
+                                                             const ScaleFromAmax sfa) {
     __shared__ uint32_t tile[kTR * kPitchW];
     const int r0 = blockIdx.y * kTR, c0 = blockIdx.x * kTC;
     const int tid = threadIdx.x;
-    const float s = SRC_BF16 ? *scale : 0.0f;
+    float s = 0.0f;
+    if (SRC_BF16) {
+        if (sfa.amax) {
+            // every block derives the same scale from the amax (kernels/fp8.cu:34-40); one thread publishes it
+            const float a = fmaxf(*sfa.amax, 1e-12f);
+            s = __fdiv_rn(sfa.fp8_max, a);
+            if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) {
+                *sfa.scale_out = s;
+                *sfa.descale_out = __fdiv_rn(a, sfa.fp8_max);
+            }
+        } else {
+            s = *scale;
+        }
+    }
 
     if (SRC_BF16) {
         // 8 threads x 8 columns per source row, 32 rows per pass, 8 passes
@@ -379,7 +440,7 @@ __global__ void __launch_bounds__(kThreads) k_tile_transpose(const void* __restr
 
 template <bool SRC_BF16>
 int launch_tile_transpose(const void* src, void* direct, void* transposed, const float* scale, int R, int Ccols,
-                          cudaStream_t st, const char* name) {
+                          cudaStream_t st, const char* name, const ScaleFromAmax sfa = ScaleFromAmax()) {
     if (R == 0 || Ccols == 0) return CF_OK;
     const uintptr_t sa = reinterpret_cast<uintptr_t>(src), da = reinterpret_cast<uintptr_t>(direct),
                     ta = reinterpret_cast<uintptr_t>(transposed);
@@ -390,12 +451,31 @@ int launch_tile_transpose(const void* src, void* direct, void* transposed, const
     dim3 grid((Ccols + kTC - 1) / kTC, (R + kTR - 1) / kTR);
     k_tile_transpose<SRC_BF16><<<grid, kThreads, 0, st>>>(src, static_cast<uint8_t*>(direct),
                                                           static_cast<uint8_t*>(transposed), scale, R, Ccols, src_vec,
-                                                          direct_vec, trans_vec);
+                                                          direct_vec, trans_vec, sfa);
     CF_LAUNCH_CHECK(name);
     return CF_OK;
 }
 
 }  // namespace
+
+int slot_begin(const float* scale, const float* descale, float* snap_scale, float* snap_descale, float* amax,
+               cudaStream_t st) {
+    k_slot_begin<<<1, 1, 0, st>>>(scale, descale, snap_scale, snap_descale, amax);
+    CF_LAUNCH_CHECK("slot_begin");
+    return CF_OK;
+}
+
+int quantize_record_fused(const void* d_x, void* d_out, const float* d_scale, float* d_amax, size_t n, bool e5m2,
+                          const RingTail& tail, cudaStream_t st) {
+    return e5m2 ? launch_stream<true, true, true>(d_x, d_out, d_scale, d_amax, n, st, "quantize_e5m2_record_fused", tail)
+                : launch_stream<false, true, true>(d_x, d_out, d_scale, d_amax, n, st, "quantize_e4m3_record_fused", tail);
+}
+
+int quant_dual_from_amax(const void* d_in, void* d_direct, void* d_transposed, const ScaleFromAmax& sfa, int R, int Ccols,
+                         cudaStream_t st) {
+    return launch_tile_transpose<true>(d_in, d_direct, d_transposed, nullptr, R, Ccols, st, "quant_dual_from_amax", sfa);
+}
+
 }  // namespace cf
 
 using namespace cf;

@@ -173,6 +173,8 @@ typedef struct cf_act_slot {
     int calib_commit_pending;
     float* calib_min;
     float* calib_max;
+    unsigned* ticket;        /* optional zero-initialised device word (not in the reference's ActSlot): when set,
+                                steady-state calls fuse the ring update into the record pass; NULL = separate launch */
 } cf_act_slot;
 
 int cf_act_slot_init(cf_ctx* ctx, cf_act_slot* slot, float fp8_max, int calib_calls, void* stream);

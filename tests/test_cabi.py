@@ -23,7 +23,7 @@ def test_struct_layouts_match_the_header():
     cfb = package()
     # pointer-sized and 4-byte members only; sizes follow the C layout rules on LP64
     assert C.sizeof(cfb._capi.GemmEpilogue) == 32
-    assert C.sizeof(cfb._capi.ActSlotStruct) == 8 * 8 + 4 * 4 + 2 * 8
+    assert C.sizeof(cfb._capi.ActSlotStruct) == 8 * 8 + 4 * 4 + 3 * 8
     assert C.sizeof(cfb._capi.Fp8WeightStruct) == 6 * 8 + 3 * 4 + 4
 
 

@@ -9,6 +9,7 @@ The directory name contains a hyphen, so import it with importlib:
 """
 from . import _capi
 from . import ops
+from . import parallel
 from .ops import *  # noqa: F401,F403
 
-__all__ = ["_capi", "ops"] + ops.__all__
+__all__ = ["_capi", "ops", "parallel"] + ops.__all__

@@ -67,14 +67,19 @@ SIGNATURES = {
     "cf_gemm_fp8_tn_accum_f32": (ci, [vp, ci, ci, ci, vp, fp, vp, fp, vp, ci, vp]),
     "cf_gemm_fp8_tn_accum_bf16": (ci, [vp, ci, ci, ci, vp, fp, vp, fp, vp, ci, vp]),
     "cf_gemm_fp8_nt_grouped": (ci, [vp, ci, ci, ci, ci, ip, ip, vp, ci, ci, fp, ci, vp, fp, vp, ci, vp]),
+    "cf_gemm_fp8_nt_segments": (ci, [vp, ci, ci, ip, ci, ci, ci, ip, ip, vp, ci, ci, fp, ci, vp, fp, vp, ci, vp]),
     "cf_act_slot_init": (ci, [vp, C.POINTER(ActSlotStruct), cf, ci, vp]),
     "cf_fp8_quant_act": (ci, [vp, C.POINTER(ActSlotStruct), vp, sz, vp, vp, ci]),
+    "cf_fp8_swiglu_quant_act": (ci, [vp, C.POINTER(ActSlotStruct), vp, vp, ci, ci, ci, vp, vp]),
     "cf_refresh_fp8_weight": (ci, [C.POINTER(Fp8WeightStruct), ci, vp]),
     "cf_fp8_linear_forward": (ci, [vp, C.POINTER(ActSlotStruct), vp, ci, ci, vp, fp, ci, vp, ci, vp, ci, vp]),
     "cf_fp8_linear_static_scratch": (ci, [vp, ci, ci, fp, fp, vp, fp, ci, vp, ci, vp, ci, ip, vp]),
     "cf_bias_add_strided_bf16": (ci, [vp, vp, ci, ci, ci, ci, vp]),
     "cf_swiglu_forward": (ci, [vp, vp, vp, ci, vp]),
     "cf_gelu_forward": (ci, [vp, vp, sz, vp]),
+    "cf_fp8_quantize_rowwise_e4m3": (ci, [vp, ci, vp, ci, fp, fp, ci, ci, vp]),
+    "cf_swiglu_quantize_rowwise_e4m3": (ci, [vp, vp, ci, vp, ci, fp, fp, ci, ci, vp]),
+    "cf_swiglu_quantize_e4m3_record": (ci, [vp, vp, ci, vp, ci, fp, fp, ci, ci, vp]),
     "cf_moe_topk_route_f32": (ci, [fp, ci, ci, ci, vp, fp, fp, ci]),
     "cf_moe_build_expert_row_lists": (ci, [fp, ip, ip, ci, ci, vp]),
     "cf_moe_expert_offsets_from_counts": (ci, [ip, ip, ci, vp]),

@@ -219,6 +219,17 @@ int cf_gemm_fp8_nt_grouped(cf_ctx* ctx, int num_experts, int max_total_rows, int
                            const int* d_offsets, const void* d_A, int lda, int a_is_e5m2, const float* d_a_descale,
                            int per_expert_a_descale, const void* d_B, const float* d_b_descale, void* d_C, int ldc,
                            void* stream) {
+    return cf_gemm_fp8_nt_segments(ctx, num_experts, num_experts, nullptr, max_total_rows, N, K, d_counts, d_offsets, d_A,
+                                   lda, a_is_e5m2, d_a_descale, per_expert_a_descale, d_B, d_b_descale, d_C, ldc, stream);
+}
+
+int cf_gemm_fp8_nt_segments(cf_ctx* ctx, int num_segments, int num_weights, const int* d_segment_weight,
+                            int max_total_rows, int N, int K, const int* d_counts, const int* d_offsets, const void* d_A,
+                            int lda, int a_is_e5m2, const float* d_a_descale, int per_segment_a_descale, const void* d_B,
+                            const float* d_b_descale, void* d_C, int ldc, void* stream) {
+    const int num_experts = num_segments;
+    const int per_expert_a_descale = per_segment_a_descale;
+    CF_REQUIRE(num_weights >= 1, "cf_gemm_fp8_nt_segments: num_weights must be positive");
     CF_REQUIRE(ctx != nullptr, "cf_gemm_fp8_nt_grouped: null context");
     CF_REQUIRE(num_experts >= 1 && num_experts <= 1024, "cf_gemm_fp8_nt_grouped: num_experts out of range");
     CF_REQUIRE(max_total_rows >= 0 && N >= 0 && K > 0, "cf_gemm_fp8_nt_grouped: bad shape");
@@ -230,6 +241,7 @@ int cf_gemm_fp8_nt_grouped(cf_ctx* ctx, int num_experts, int max_total_rows, int
     p.groups = num_experts;
     p.N = N; p.K = K;
     p.d_counts = d_counts; p.d_offsets = d_offsets;
+    p.d_group_weight = d_segment_weight;
     p.d_a_descale = d_a_descale; p.a_descale_per_group = per_expert_a_descale ? 1 : 0;
     p.d_b_descale = d_b_descale;
     p.C = d_C; p.ldc = ldc; p.out_kind = 0;
@@ -237,7 +249,7 @@ int cf_gemm_fp8_nt_grouped(cf_ctx* ctx, int num_experts, int max_total_rows, int
     p.d_status = reinterpret_cast<Ctx*>(ctx)->d_status;
     const int m_blocks = (max_total_rows + gemm_tile_m() - 1) / gemm_tile_m() + num_experts;
     const int tiles = m_blocks * ((N + gemm_tile_n() - 1) / gemm_tile_n());
-    return launch_gemm_fp8_nt(d_A, lda, max_total_rows, d_B, static_cast<long long>(num_experts) * N, p, tiles,
+    return launch_gemm_fp8_nt(d_A, lda, max_total_rows, d_B, static_cast<long long>(num_weights) * N, p, tiles,
                               as_stream(stream));
 }
 
@@ -351,6 +363,43 @@ int cf_fp8_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, size_t n, 
         CF_TRY(cf_fp8_quantize_e4m3_record(d_x, d_out8, slot->scale, slot->amax, n, stream));
     CF_TRY(cf_fp8_update_delayed_scale(slot->amax, slot->fp8_max, slot->scale, slot->descale, slot->history, kHistoryLen,
                                        slot->history_cursor, slot->history_count, stream));
+    return CF_OK;
+}
+
+int cf_fp8_swiglu_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_gate, const void* d_up, int ld_in, int rows,
+                            int cols, void* d_out8, void* stream) {
+    CF_REQUIRE(ctx && slot && slot->amax, "cf_fp8_swiglu_quant_act: null or uninitialised slot");
+    CF_REQUIRE(rows >= 0 && cols >= 0 && ld_in >= cols, "cf_fp8_swiglu_quant_act: bad shape");
+    CF_REQUIRE(slot->fp8_max == CF_E4M3_MAX, "cf_fp8_swiglu_quant_act: E4M3 slots only");
+    CF_REQUIRE(rows == 0 || cols == 0 || (d_gate && d_up && d_out8), "cf_fp8_swiglu_quant_act: null tensor pointer");
+    cudaStream_t st = as_stream(stream);
+    if (!slot->init) {
+        // first use: exact amax of the product (a record pass whose codes are overwritten below), then the
+        // same sequence as fp8_quant_act's first call (src/trainer.cu:4793-4815)
+        CF_CUDA(cudaMemsetAsync(slot->amax, 0, sizeof(float), st));
+        CF_CUDA(cudaMemsetAsync(slot->scale, 0, sizeof(float), st));
+        CF_TRY(swiglu_record_launch(d_gate, d_up, ld_in, d_out8, cols, slot->scale, slot->amax, rows, cols, RingTail(), st));
+        CF_TRY(cf_fp8_scale_from_amax(slot->amax, slot->fp8_max, slot->scale, slot->descale, stream));
+        CF_CUDA(cudaMemcpyAsync(slot->scale_snapshot, slot->scale, sizeof(float), cudaMemcpyDeviceToDevice, st));
+        CF_CUDA(cudaMemcpyAsync(slot->descale_snapshot, slot->descale, sizeof(float), cudaMemcpyDeviceToDevice, st));
+        CF_TRY(swiglu_record_launch(d_gate, d_up, ld_in, d_out8, cols, slot->scale, slot->amax, rows, cols, RingTail(), st));
+        CF_TRY(cf_fp8_update_delayed_scale(slot->amax, slot->fp8_max, slot->scale, slot->descale, slot->history,
+                                           kHistoryLen, slot->history_cursor, slot->history_count, stream));
+        slot->init = 1;
+        return CF_OK;
+    }
+    CF_TRY(slot_begin(slot->scale, slot->descale, slot->scale_snapshot, slot->descale_snapshot, slot->amax, st));
+    RingTail tail;
+    if (slot->ticket) {
+        tail.fp8_max = slot->fp8_max; tail.scale = slot->scale; tail.descale = slot->descale;
+        tail.history = slot->history; tail.history_len = kHistoryLen;
+        tail.history_cursor = slot->history_cursor; tail.history_count = slot->history_count;
+        tail.ticket = slot->ticket;
+    }
+    CF_TRY(swiglu_record_launch(d_gate, d_up, ld_in, d_out8, cols, slot->scale, slot->amax, rows, cols, tail, st));
+    if (!slot->ticket)
+        CF_TRY(cf_fp8_update_delayed_scale(slot->amax, slot->fp8_max, slot->scale, slot->descale, slot->history,
+                                           kHistoryLen, slot->history_cursor, slot->history_count, stream));
     return CF_OK;
 }
 

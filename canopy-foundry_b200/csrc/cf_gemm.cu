@@ -244,7 +244,7 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, i
     c.group = e;
     c.row0 = p.d_offsets[e] + mb * TM;
     c.valid_rows = min(TM, cnt - mb * TM);
-    c.b_row0 = e * p.N + c.n0;
+    c.b_row0 = (p.d_group_weight ? p.d_group_weight[e] : e) * p.N + c.n0;
     return c;
 }
 
@@ -599,7 +599,7 @@ __global__ void __launch_bounds__(256) k_gemm_fp8_nt_simt(const uint8_t* __restr
             const long long m = idx / p.N;
             const int n = static_cast<int>(idx - m * p.N);
             const uint8_t* a = A + (row_base + m) * lda;
-            const uint8_t* b = B + (static_cast<long long>(g) * p.N + n) * p.K;
+            const uint8_t* b = B + (static_cast<long long>(p.d_group_weight ? p.d_group_weight[g] : g) * p.N + n) * p.K;
             float acc = 0.0f;
             for (int k = 0; k < p.K; ++k) {
                 const float av = p.a_e5m2 ? fp8_to_f32<true>(a[k]) : fp8_to_f32<false>(a[k]);

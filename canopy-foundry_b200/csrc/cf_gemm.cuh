@@ -12,6 +12,7 @@ struct GemmParams {
     int K = 0;
     const int* d_counts = nullptr;  // grouped: rows per expert (device)
     const int* d_offsets = nullptr; // grouped: first compact row per expert (device)
+    const int* d_group_weight = nullptr; // grouped: weight-block index per group (device); null = group index
     const float* d_a_descale = nullptr;
     int a_descale_per_group = 0;
     const float* d_b_descale = nullptr;

@@ -32,4 +32,7 @@ int quantize_record_fused(const void* d_x, void* d_out, const float* d_scale, fl
 int quant_dual_from_amax(const void* d_in, void* d_direct, void* d_transposed, const ScaleFromAmax& sfa, int R, int Ccols,
                          cudaStream_t st);
 
+int swiglu_record_launch(const void* d_gate, const void* d_up, int ld_in, void* d_out, int ld_out, const float* d_scale,
+                         float* d_amax, int rows, int cols, const RingTail& tail, cudaStream_t st);
+
 }  // namespace cf

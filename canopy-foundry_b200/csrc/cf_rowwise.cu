@@ -1,0 +1,230 @@
+// Per-token (row-wise) E4M3 quantisation and the SwiGLU -> re-quantise fusions that feed the down projection.
+//
+// Row-wise scaling has no counterpart in the reference (it scales per tensor); it generalises
+// kernels/fp8.cu:34-49 per row:  a_r = max(amax_r, 1e-12), scale_r = 448 / a_r, descale_r = a_r / 448,
+// code = e4m3(x * scale_r). The SwiGLU arithmetic and its bf16 rounding point are those of
+// kernels/activations.cu:11-40 (the product is rounded to bf16 before it is quantised, exactly as if
+// swiglu_forward had written it to memory first).
+#include "cf_common.cuh"
+#include "cf_internal.cuh"
+
+namespace cf {
+namespace {
+
+constexpr int kRT = 256;          // threads per row
+constexpr int kMaxVec = 8;        // 16-byte vectors (8 elements each) a thread keeps in registers: K <= 16384
+
+__device__ __forceinline__ float stable_sigmoid(float x) {
+    if (x >= 0.0f) return __fdiv_rn(1.0f, 1.0f + expf(-x));
+    const float e = expf(x);
+    return __fdiv_rn(e, 1.0f + e);
+}
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+    f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xffff0000u);
+    f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
+}
+
+__device__ __forceinline__ float block_max_bcast(float v) {
+    __shared__ float s_part[kRT / 32];
+    __shared__ float s_res;
+    v = warp_max(v);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = threadIdx.x < kRT / 32 ? s_part[threadIdx.x] : 0.0f;
+        t = warp_max(t);
+        if (threadIdx.x == 0) s_res = t;
+    }
+    __syncthreads();
+    return s_res;
+}
+
+// One block per row. SWIGLU: the row is silu(gate)*up rounded to bf16; otherwise the bf16 input itself.
+// The row lives in registers between the amax pass and the quantise pass (one read of HBM).
+template <bool SWIGLU>
+__global__ void __launch_bounds__(kRT) k_rowwise(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b, long long ld_in,
+                                                 uint8_t* __restrict__ out, long long ld_out, float* __restrict__ row_scale,
+                                                 float* __restrict__ row_descale, int cols, int vec) {
+    const long long row = blockIdx.x;
+    const uint16_t* ar = a + row * ld_in;
+    const uint16_t* br = SWIGLU ? b + row * ld_in : nullptr;
+    uint8_t* orow = out + row * ld_out;
+    float vals[kMaxVec][8];
+    float local = 0.0f;
+    const int nvec = vec ? cols / 8 : 0;
+#pragma unroll
+    for (int j = 0; j < kMaxVec; ++j) {
+        const int v = threadIdx.x + j * kRT;
+        if (v < nvec) {
+            unpack8(*reinterpret_cast<const uint4*>(ar + v * 8), vals[j]);
+            if (SWIGLU) {
+                float u[8];
+                unpack8(*reinterpret_cast<const uint4*>(br + v * 8), u);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) vals[j][e] = bf16_round(vals[j][e] * stable_sigmoid(vals[j][e]) * u[e]);
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) local = fmaxf(local, fabsf(vals[j][e]));
+        }
+    }
+    // columns the vector path does not cover (cols % 8, or everything when unaligned): recomputed in pass 2
+    for (int c = nvec * 8 + threadIdx.x; c < cols; c += kRT) {
+        float x = bf16_bits_to_f32(ar[c]);
+        if (SWIGLU) x = bf16_round(x * stable_sigmoid(x) * bf16_bits_to_f32(br[c]));
+        local = fmaxf(local, fabsf(x));
+    }
+    const float amax = fmaxf(block_max_bcast(local), 1e-12f);
+    const float s = __fdiv_rn(448.0f, amax);
+    if (threadIdx.x == 0) {
+        if (row_scale) row_scale[row] = s;
+        row_descale[row] = __fdiv_rn(amax, 448.0f);
+    }
+#pragma unroll
+    for (int j = 0; j < kMaxVec; ++j) {
+        const int v = threadIdx.x + j * kRT;
+        if (v < nvec) {
+            uint2 q;
+            q.x = cvt_fp8x4<false>(vals[j][0] * s, vals[j][1] * s, vals[j][2] * s, vals[j][3] * s);
+            q.y = cvt_fp8x4<false>(vals[j][4] * s, vals[j][5] * s, vals[j][6] * s, vals[j][7] * s);
+            *reinterpret_cast<uint2*>(orow + v * 8) = q;
+        }
+    }
+    for (int c = nvec * 8 + threadIdx.x; c < cols; c += kRT) {
+        float x = bf16_bits_to_f32(ar[c]);
+        if (SWIGLU) x = bf16_round(x * stable_sigmoid(x) * bf16_bits_to_f32(br[c]));
+        orow[c] = cvt_fp8<false>(x * s);
+    }
+}
+
+// Per-tensor delayed-scaling form: out = e4m3(bf16(silu(g)*u) * *scale), amax of the bf16 product recorded.
+// Fuses swiglu_forward (kernels/activations.cu) with fp8_quantize_e4m3_record (kernels/fp8.cu:67-84):
+// the 2-byte intermediate never goes to HBM.
+__global__ void __launch_bounds__(kRT) k_swiglu_record(const uint16_t* __restrict__ g, const uint16_t* __restrict__ u,
+                                                       long long ld_in, uint8_t* __restrict__ out, long long ld_out,
+                                                       const float* __restrict__ scale, float* __restrict__ amax,
+                                                       long long rows, int cols, int vec, const RingTail tail) {
+    const float s = *scale;
+    float local = 0.0f;
+    const int vpr = vec ? cols / 8 : 0;                       // vectors per row
+    const long long total = rows * vpr;
+    for (long long i = static_cast<long long>(blockIdx.x) * kRT + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * kRT) {
+        const long long r = i / vpr;
+        const int v = static_cast<int>(i - r * vpr);
+        float a[8], b[8];
+        unpack8(*reinterpret_cast<const uint4*>(g + r * ld_in + v * 8), a);
+        unpack8(*reinterpret_cast<const uint4*>(u + r * ld_in + v * 8), b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            a[e] = bf16_round(a[e] * stable_sigmoid(a[e]) * b[e]);
+            local = fmaxf(local, fabsf(a[e]));
+        }
+        uint2 q;
+        q.x = cvt_fp8x4<false>(a[0] * s, a[1] * s, a[2] * s, a[3] * s);
+        q.y = cvt_fp8x4<false>(a[4] * s, a[5] * s, a[6] * s, a[7] * s);
+        *reinterpret_cast<uint2*>(out + r * ld_out + v * 8) = q;
+    }
+    const int tail0 = vpr * 8, tailn = cols - tail0;
+    const long long ttotal = rows * tailn;
+    for (long long i = static_cast<long long>(blockIdx.x) * kRT + threadIdx.x; i < ttotal;
+         i += static_cast<long long>(gridDim.x) * kRT) {
+        const long long r = i / tailn;
+        const int c = tail0 + static_cast<int>(i - r * tailn);
+        float x = bf16_bits_to_f32(g[r * ld_in + c]);
+        x = bf16_round(x * stable_sigmoid(x) * bf16_bits_to_f32(u[r * ld_in + c]));
+        local = fmaxf(local, fabsf(x));
+        out[r * ld_out + c] = cvt_fp8<false>(x * s);
+    }
+    block_amax_commit(local, amax);
+    if (tail.ticket != nullptr && threadIdx.x == 0) {
+        // last block to finish runs the delayed-scale ring update (kernels/fp8.cu:105-142)
+        __threadfence();
+        if (atomicAdd(tail.ticket, 1u) == gridDim.x - 1) {
+            __threadfence();
+            const float a = fmaxf(__int_as_float(atomicMax(reinterpret_cast<int*>(amax), 0)), 1e-12f);
+            int cursor = *tail.history_cursor, count = *tail.history_count;
+            if (cursor < 0 || cursor >= tail.history_len) cursor = 0;
+            tail.history[cursor] = a;
+            cursor = (cursor + 1) % tail.history_len;
+            if (count < tail.history_len) ++count;
+            float m = tail.history[0];
+            for (int i = 1; i < count; ++i) m = fmaxf(m, tail.history[i]);
+            m = fmaxf(m, 1e-12f);
+            *tail.history_cursor = cursor;
+            *tail.history_count = count;
+            *tail.scale = __fdiv_rn(tail.fp8_max, m);
+            *tail.descale = __fdiv_rn(m, tail.fp8_max);
+            *tail.ticket = 0;
+        }
+    }
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+int swiglu_record_launch(const void* d_gate, const void* d_up, int ld_in, void* d_out, int ld_out, const float* d_scale,
+                         float* d_amax, int rows, int cols, const RingTail& tail, cudaStream_t st) {
+    const int vec = aligned16(d_gate) && aligned16(d_up) && (ld_in % 8 == 0) &&
+                    ((reinterpret_cast<uintptr_t>(d_out) & 7) == 0) && (ld_out % 8 == 0);
+    const size_t items = static_cast<size_t>(rows) * (vec ? cols / 8 : cols);
+    size_t blocks = (items + kRT * 2 - 1) / (kRT * 2);
+    const size_t cap = static_cast<size_t>(sm_count()) * 8;
+    if (blocks < 1) blocks = 1;
+    if (blocks > cap) blocks = cap;
+    k_swiglu_record<<<static_cast<unsigned>(blocks), kRT, 0, st>>>(
+        static_cast<const uint16_t*>(d_gate), static_cast<const uint16_t*>(d_up), ld_in, static_cast<uint8_t*>(d_out), ld_out,
+        d_scale, d_amax, rows, cols, vec, tail);
+    CF_LAUNCH_CHECK("swiglu_quantize_e4m3_record");
+    return CF_OK;
+}
+
+}  // namespace cf
+
+using namespace cf;
+
+extern "C" {
+
+int cf_fp8_quantize_rowwise_e4m3(const void* d_x, int ld_x, void* d_out, int ld_out, float* d_row_scale,
+                                 float* d_row_descale, int rows, int cols, void* stream) {
+    CF_REQUIRE(rows >= 0 && cols >= 0 && ld_x >= cols && ld_out >= cols, "cf_fp8_quantize_rowwise_e4m3: bad shape");
+    if (rows == 0 || cols == 0) return CF_OK;
+    CF_REQUIRE(d_x && d_out && d_row_descale, "cf_fp8_quantize_rowwise_e4m3: null pointer");
+    if (cols > kRT * kMaxVec * 8) { set_error("cf_fp8_quantize_rowwise_e4m3: at most %d columns", kRT * kMaxVec * 8); return CF_ERR_LIMIT; }
+    const int vec = aligned16(d_x) && (ld_x % 8 == 0) && ((reinterpret_cast<uintptr_t>(d_out) & 7) == 0) && (ld_out % 8 == 0);
+    k_rowwise<false><<<rows, kRT, 0, as_stream(stream)>>>(static_cast<const uint16_t*>(d_x), nullptr, ld_x,
+                                                          static_cast<uint8_t*>(d_out), ld_out, d_row_scale, d_row_descale,
+                                                          cols, vec);
+    CF_LAUNCH_CHECK("quantize_rowwise_e4m3");
+    return CF_OK;
+}
+
+int cf_swiglu_quantize_rowwise_e4m3(const void* d_gate, const void* d_up, int ld_in, void* d_out, int ld_out,
+                                    float* d_row_scale, float* d_row_descale, int rows, int cols, void* stream) {
+    CF_REQUIRE(rows >= 0 && cols >= 0 && ld_in >= cols && ld_out >= cols, "cf_swiglu_quantize_rowwise_e4m3: bad shape");
+    if (rows == 0 || cols == 0) return CF_OK;
+    CF_REQUIRE(d_gate && d_up && d_out && d_row_descale, "cf_swiglu_quantize_rowwise_e4m3: null pointer");
+    if (cols > kRT * kMaxVec * 8) { set_error("cf_swiglu_quantize_rowwise_e4m3: at most %d columns", kRT * kMaxVec * 8); return CF_ERR_LIMIT; }
+    const int vec = aligned16(d_gate) && aligned16(d_up) && (ld_in % 8 == 0) &&
+                    ((reinterpret_cast<uintptr_t>(d_out) & 7) == 0) && (ld_out % 8 == 0);
+    k_rowwise<true><<<rows, kRT, 0, as_stream(stream)>>>(static_cast<const uint16_t*>(d_gate), static_cast<const uint16_t*>(d_up),
+                                                         ld_in, static_cast<uint8_t*>(d_out), ld_out, d_row_scale,
+                                                         d_row_descale, cols, vec);
+    CF_LAUNCH_CHECK("swiglu_quantize_rowwise_e4m3");
+    return CF_OK;
+}
+
+int cf_swiglu_quantize_e4m3_record(const void* d_gate, const void* d_up, int ld_in, void* d_out, int ld_out,
+                                   const float* d_scale, float* d_amax, int rows, int cols, void* stream) {
+    CF_REQUIRE(rows >= 0 && cols >= 0 && ld_in >= cols && ld_out >= cols, "cf_swiglu_quantize_e4m3_record: bad shape");
+    CF_REQUIRE(d_scale && d_amax, "cf_swiglu_quantize_e4m3_record: null scalar pointer");
+    if (rows == 0 || cols == 0) return CF_OK;
+    CF_REQUIRE(d_gate && d_up && d_out, "cf_swiglu_quantize_e4m3_record: null pointer");
+    return swiglu_record_launch(d_gate, d_up, ld_in, d_out, ld_out, d_scale, d_amax, rows, cols, RingTail(), as_stream(stream));
+}
+
+}  // extern "C"

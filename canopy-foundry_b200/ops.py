@@ -19,12 +19,13 @@ __all__ = [
     "fp8_quantize_e4m3_record", "fp8_quantize_e5m2_record", "fp8_update_delayed_scale",
     "fp8_quantize_transpose_e4m3", "fp8_quant_and_transpose_e4m3", "transpose_u8", "fp8_clip_probe",
     "fp8_elem_clip_count", "fp8_pack_bf16_e4m3_raw", "fp8_pack_bf16_e4m3_raw_and_dequant",
-    "fp8_unpack_e4m3_raw_bf16", "lt_gemm_fp8_nt", "lt_gemm_fp8_tn_accum_f32", "gemm_fp8_nt_grouped",
-    "fp8_quant_act", "refresh_fp8_weight", "fp8_linear_forward", "bias_add_strided_bf16", "swiglu_forward",
-    "gelu_forward", "moe_topk_route_f32", "moe_build_expert_row_lists", "moe_expert_offsets_from_counts",
+    "fp8_unpack_e4m3_raw_bf16", "lt_gemm_fp8_nt", "lt_gemm_fp8_tn_accum_f32", "gemm_fp8_nt_grouped", "gemm_fp8_nt_segments",
+    "fp8_quant_act", "fp8_swiglu_quant_act", "refresh_fp8_weight", "fp8_linear_forward", "bias_add_strided_bf16", "swiglu_forward",
+    "gelu_forward", "fp8_quantize_rowwise_e4m3", "swiglu_quantize_rowwise_e4m3", "swiglu_quantize_e4m3_record",
+    "moe_topk_route_f32", "moe_build_expert_row_lists", "moe_expert_offsets_from_counts",
     "moe_gather_rows_u8", "moe_gather_rows_bf16", "moe_scatter_accumulate_rows_bf16",
     "moe_scale_accumulate_bf16", "moe_gather_all_u8", "moe_combine_all_bf16",
-    "moe_grouped_expert_forward_fp8", "launch_count",
+    "moe_grouped_expert_forward_fp8", "launch_count", "swiglu_mlp_fp8_rowwise", "MoeSwigluFp8",
 ]
 
 
@@ -222,6 +223,10 @@ def fp8_quant_act(ctx, slot, x, out8=None, is_recompute=False, n=None):
                                 int(is_recompute)))
 
 
+def fp8_swiglu_quant_act(ctx, slot, gate, up, ld_in, rows, cols, out8):
+    check(_L().cf_fp8_swiglu_quant_act(ctx.handle, C.byref(slot.c), _p(gate), _p(up), ld_in, rows, cols, _p(out8), _s()))
+
+
 # ---------------------------------------------------------------- GEMMs
 def _epi(bias, bias_mode, a_row_descale, b_col_descale):
     if bias is None and a_row_descale is None and b_col_descale is None:
@@ -251,6 +256,13 @@ def gemm_fp8_nt_grouped(ctx, num_experts, max_total_rows, N, K, counts, offsets,
                                       _p(b_descale), _p(Cout), ldc, _s()))
 
 
+def gemm_fp8_nt_segments(ctx, num_segments, num_weights, segment_weight, max_total_rows, N, K, counts, offsets, A, lda,
+                         a_is_e5m2, a_descale, per_segment_a_descale, B, b_descale, Cout, ldc):
+    check(_L().cf_gemm_fp8_nt_segments(ctx.handle, num_segments, num_weights, _p(segment_weight), max_total_rows, N, K,
+                                       _p(counts), _p(offsets), _p(A), lda, int(a_is_e5m2), _p(a_descale),
+                                       int(per_segment_a_descale), _p(B), _p(b_descale), _p(Cout), ldc, _s()))
+
+
 def fp8_linear_forward(ctx, slot, x, w8, w_descale, y, bias=None, bias_mode=2):
     M, K = x.shape
     N = w8.shape[0]
@@ -269,6 +281,24 @@ def swiglu_forward(gate, up, out, n=None):
 
 def gelu_forward(x, out):
     check(_L().cf_gelu_forward(_p(x), _p(out), x.numel(), _s()))
+
+
+def fp8_quantize_rowwise_e4m3(x, out, row_descale, row_scale=None, rows=None, cols=None, ld_x=None, ld_out=None):
+    rows = x.shape[0] if rows is None else rows
+    cols = x.shape[1] if cols is None else cols
+    check(_L().cf_fp8_quantize_rowwise_e4m3(_p(x), x.stride(0) if ld_x is None else ld_x, _p(out),
+                                            out.stride(0) if ld_out is None else ld_out, _p(row_scale), _p(row_descale),
+                                            rows, cols, _s()))
+
+
+def swiglu_quantize_rowwise_e4m3(gate, up, out, row_descale, rows, cols, ld_in, ld_out=None, row_scale=None):
+    check(_L().cf_swiglu_quantize_rowwise_e4m3(_p(gate), _p(up), ld_in, _p(out), cols if ld_out is None else ld_out,
+                                               _p(row_scale), _p(row_descale), rows, cols, _s()))
+
+
+def swiglu_quantize_e4m3_record(gate, up, out, scale, amax, rows, cols, ld_in, ld_out=None):
+    check(_L().cf_swiglu_quantize_e4m3_record(_p(gate), _p(up), ld_in, _p(out), cols if ld_out is None else ld_out,
+                                              _p(scale), _p(amax), rows, cols, _s()))
 
 
 def moe_topk_route_f32(scores, rows, num_experts, top_k, row_sum_save=None, scores_save=None, normalize_topk=True):
@@ -317,3 +347,84 @@ def moe_grouped_expert_forward_fp8(ctx, hidden, fcin_descale, fcin_is_e5m2, rout
                                                  _p(route_weights), _p(counts), _p(offsets), _p(row_indices),
                                                  _p(fc_in_w), _p(fc_in_descale), _p(fc_out_w), _p(fc_out_descale),
                                                  _p(mixed), rows, H, Ie, num_experts, total_selected_rows, _s()))
+
+
+# ---------------------------------------------------------------- composites for BASELINE configurations 3 and 4
+def swiglu_mlp_fp8_rowwise(ctx, x, w_gateup8, w_gateup_descale, w_down8, w_down_descale, y, work=None):
+    """Llama-style SwiGLU MLP in FP8 with per-token activation scales and per-output-channel weight scales
+    (configuration 3; the reference has per-tensor scales only, so this follows the documented generalisation
+    C[m,n] = dA[m] * dW[n] * acc):
+        x8, dx   = rowwise_quant(x)                      [M,H]
+        gu       = x8 . w_gateup8^T  (scales dx, dWgu)   [M,2F]  gate = gu[:, :F], up = gu[:, F:]
+        h8, dh   = rowwise_quant(bf16(silu(gate) * up))  [M,F]
+        y        = h8 . w_down8^T    (scales dh, dWd)    [M,H]
+    w_gateup8 is [2F,H] (gate rows first), w_down8 is [H,F]; descales are float[2F] / float[H]."""
+    M, H = x.shape
+    F2 = w_gateup8.shape[0]
+    F = F2 // 2
+    dev = x.device
+    if work is None:
+        work = {}
+    x8 = work.setdefault("x8", torch.empty((M, H), dtype=torch.uint8, device=dev))
+    dx = work.setdefault("dx", torch.empty(M, dtype=torch.float32, device=dev))
+    gu = work.setdefault("gu", torch.empty((M, F2), dtype=torch.bfloat16, device=dev))
+    h8 = work.setdefault("h8", torch.empty((M, F), dtype=torch.uint8, device=dev))
+    dh = work.setdefault("dh", torch.empty(M, dtype=torch.float32, device=dev))
+    one = work.setdefault("one", torch.ones(4, dtype=torch.float32, device=dev))
+    fp8_quantize_rowwise_e4m3(x, x8, dx)
+    lt_gemm_fp8_nt(ctx, M, F2, H, x8, H, False, one, w_gateup8, one, gu, F2, a_row_descale=dx,
+                   b_col_descale=w_gateup_descale)
+    swiglu_quantize_rowwise_e4m3(gu, gu.view(-1)[F:], h8, dh, M, F, F2)
+    lt_gemm_fp8_nt(ctx, M, y.shape[1], F, h8, F, False, one, w_down8, one, y, y.stride(0), a_row_descale=dh,
+                   b_col_descale=w_down_descale)
+    return work
+
+
+class MoeSwigluFp8:
+    """Top-k routed SwiGLU experts in FP8 (configuration 4): route -> dispatch lists -> per-tensor delayed-scale
+    quantise of x -> permute -> ragged gate/up GEMM -> SwiGLU + delayed-scale re-quantise -> ragged down GEMM ->
+    unpermute + weighted combine. Everything is scheduled on the device (no host copy of the counts); the
+    rounding points are those of the reference's SwiGLU expert maths (src/trainer.cu:6510-6529) combined with its
+    FP8 quantise / GEMM semantics. Weights: w_gateup8 [E,2F,H] and w_down8 [E,H,F] with one per-tensor descale each."""
+
+    def __init__(self, ctx, rows, H, F, E, top_k, device="cuda"):
+        self.ctx, self.rows, self.H, self.F, self.E, self.k = ctx, rows, H, F, E, top_k
+        T = rows * top_k
+        self.T = T
+        self.counts = torch.zeros(E, dtype=torch.int32, device=device)
+        self.offsets = torch.zeros(E, dtype=torch.int32, device=device)
+        self.idx = torch.zeros((E, rows), dtype=torch.int32, device=device)
+        self.x8 = torch.empty((rows, H), dtype=torch.uint8, device=device)
+        self.xc = torch.empty((T, H), dtype=torch.uint8, device=device)
+        self.gu = torch.empty((T, 2 * F), dtype=torch.bfloat16, device=device)
+        self.h8 = torch.empty((T, F), dtype=torch.uint8, device=device)
+        self.yc = torch.empty((T, H), dtype=torch.bfloat16, device=device)
+        self.slot_x = ActSlot(ctx, E4M3_MAX)
+        self.slot_h = ActSlot(ctx, E4M3_MAX)
+
+    def forward(self, x, route_weights, w_gateup8, w_gateup_descale, w_down8, w_down_descale, mixed):
+        """route_weights: float32 [rows,E] router logits, overwritten in place by the sparse route weights."""
+        rows, H, F, E, T = self.rows, self.H, self.F, self.E, self.T
+        moe_topk_route_f32(route_weights, rows, E, self.k)
+        moe_build_expert_row_lists(route_weights, self.counts, self.idx, rows, E)
+        moe_expert_offsets_from_counts(self.counts, self.offsets, E)
+        fp8_quant_act(self.ctx, self.slot_x, x, self.x8)
+        moe_gather_all_u8(self.x8, self.xc, self.idx, self.counts, self.offsets, rows, E, H)
+        gemm_fp8_nt_grouped(self.ctx, E, T, 2 * F, H, self.counts, self.offsets, self.xc, H, False,
+                            _DevPtr(self.slot_x.c.descale_snapshot), False, w_gateup8, w_gateup_descale, self.gu, 2 * F)
+        fp8_swiglu_quant_act(self.ctx, self.slot_h, self.gu, self.gu.view(-1)[F:], 2 * F, T, F, self.h8)
+        gemm_fp8_nt_grouped(self.ctx, E, T, H, F, self.counts, self.offsets, self.h8, F, False,
+                            _DevPtr(self.slot_h.c.descale_snapshot), False, w_down8, w_down_descale, self.yc, H)
+        moe_combine_all_bf16(mixed, self.yc, route_weights, self.idx, self.counts, self.offsets, rows, E, H)
+
+
+class _DevPtr:
+    """Wraps a raw device address so that it can be passed where a tensor is expected."""
+
+    is_cuda = True
+
+    def __init__(self, addr):
+        self._addr = addr
+
+    def data_ptr(self):
+        return self._addr

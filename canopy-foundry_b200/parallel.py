@@ -1,0 +1,222 @@
+"""Sharding of the FP8 path across the GPUs of one box (one process per GPU, torch.distributed).
+
+The reference has no multi-GPU form of this path (no NCCL, MPI or Gloo anywhere in its tree; its only transport
+is a two-device layer pipeline, include/ida_native/arena.hpp:24-26), so single-GPU output is the parity target
+and the partitioning below is new work:
+
+  * dense GEMMs: weights sharded by output columns (gate/up, forward GEMMs) or by the contraction dimension
+    (down projection, dgrad). A per-tensor weight scale needs the amax of the WHOLE tensor: one max-all-reduce of
+    one float keeps the scale bit-identical to the single-GPU one. Row-parallel partial products are summed in
+    fp32 by an all-reduce.
+  * MoE: experts are sharded (expert parallelism), tokens stay data-parallel. Rows travel as E4M3 bytes
+    (1 byte per element on the wire) with one all-to-all out and one bf16 all-to-all back.
+
+The planning code is pure host logic and runs on CPU tensors with the gloo backend too (tests use that).
+"""
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def shard_range(n, world, rank, multiple=1):
+    """Contiguous balanced shard [start, stop) of range(n) for `rank`; shard sizes are multiples of `multiple`
+    except possibly the last one."""
+    units = (n + multiple - 1) // multiple
+    base, extra = divmod(units, world)
+    start_u = rank * base + min(rank, extra)
+    stop_u = start_u + base + (1 if rank < extra else 0)
+    return min(start_u * multiple, n), min(stop_u * multiple, n)
+
+
+def allreduce_max_(t, group=None):
+    """In-place max over ranks (weight amax of a sharded tensor, float32). max() is exact in any order, so every
+    rank ends with the value a single GPU would have computed."""
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return t
+
+
+def allreduce_sum_(t, group=None):
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+    return t
+
+
+def all_to_all_rows(send, send_splits, recv_splits, group=None):
+    """Variable-size all-to-all of the rows of a 2-D tensor. NCCL: one all_to_all_single; gloo (CPU tests) has no
+    all-to-all, so the same exchange is issued as paired isend/irecv."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    recv = send.new_empty((int(sum(recv_splits)),) + tuple(send.shape[1:]))
+    if dist.get_backend(group) == "nccl":
+        dist.all_to_all_single(recv, send, output_split_sizes=list(recv_splits), input_split_sizes=list(send_splits),
+                               group=group)
+        return recv
+    s_off = [0]
+    for c in send_splits:
+        s_off.append(s_off[-1] + int(c))
+    r_off = [0]
+    for c in recv_splits:
+        r_off.append(r_off[-1] + int(c))
+    recv[r_off[rank]:r_off[rank + 1]] = send[s_off[rank]:s_off[rank + 1]]
+    reqs = []
+    for peer in range(world):
+        if peer == rank:
+            continue
+        if send_splits[peer]:
+            reqs.append(dist.isend(send[s_off[peer]:s_off[peer + 1]].contiguous(), dst=peer, group=group))
+        if recv_splits[peer]:
+            reqs.append(dist.irecv(recv[r_off[peer]:r_off[peer + 1]], src=peer, group=group))
+    for r in reqs:
+        r.wait()
+    return recv
+
+
+@dataclass
+class EpPlan:
+    """Who sends how many rows to whom for one expert-parallel MoE layer.
+
+    Experts are sharded contiguously: rank r owns experts [e_lo(r), e_hi(r)). Every rank's compact send buffer is
+    ordered by expert (so by destination rank). On the receiving side the rows arrive grouped by source rank and,
+    inside each source, by local expert: each (source, local expert) run is one GEMM segment."""
+    world: int
+    rank: int
+    num_experts: int
+    counts_all: List[List[int]]          # [world][num_experts] rows each rank routes to each expert
+    send_splits: List[int]               # rows this rank sends to each rank
+    recv_splits: List[int]               # rows this rank receives from each rank
+    seg_counts: List[int]                # per (source, local expert) segment, source-major
+    seg_offsets: List[int]
+    seg_weight: List[int]                # local expert index of each segment
+    seg_source: List[int]                # source rank of each segment
+    total_recv: int
+
+    @staticmethod
+    def expert_range(num_experts, world, rank):
+        return shard_range(num_experts, world, rank)
+
+    @classmethod
+    def build(cls, counts_all, rank):
+        world = len(counts_all)
+        num_experts = len(counts_all[0])
+        ranges = [cls.expert_range(num_experts, world, r) for r in range(world)]
+        send_splits = [int(sum(counts_all[rank][lo:hi])) for lo, hi in ranges]
+        lo, hi = ranges[rank]
+        recv_splits = [int(sum(counts_all[src][lo:hi])) for src in range(world)]
+        seg_counts, seg_offsets, seg_weight, seg_source = [], [], [], []
+        off = 0
+        for src in range(world):
+            for e in range(lo, hi):
+                c = int(counts_all[src][e])
+                seg_counts.append(c)
+                seg_offsets.append(off)
+                seg_weight.append(e - lo)
+                seg_source.append(src)
+                off += c
+        return cls(world, rank, num_experts, [list(map(int, c)) for c in counts_all], send_splits, recv_splits,
+                   seg_counts, seg_offsets, seg_weight, seg_source, off)
+
+
+def gather_counts(local_counts, group=None):
+    """All ranks' per-expert row counts as a host table [world][E] (one small all-gather and one device->host copy:
+    the split sizes of an all-to-all have to be known on the host)."""
+    world = dist.get_world_size(group)
+    buf = [torch.empty_like(local_counts) for _ in range(world)]
+    dist.all_gather(buf, local_counts, group=group)
+    return [b.cpu().tolist() for b in buf]
+
+
+class ShardedFp8Weight:
+    """A logical [N_total, K] weight sharded by output columns: this rank holds rows [n_lo, n_hi). The per-tensor
+    scale comes from the amax of the whole tensor (local amax, then max-all-reduce), so the E4M3 bytes of the shard
+    equal the same rows of the single-GPU cache."""
+
+    def __init__(self, cfb, w_shard, group=None):
+        self.cfb = cfb
+        self.w = w_shard
+        self.group = group
+        self.fw = cfb.Fp8Weight(w_shard, stored_out_major=True)
+
+    def refresh(self):
+        cfb = self.cfb
+        cfb.fp8_amax_bf16(self.w, self.fw.amax)
+        allreduce_max_(self.fw.amax, self.group)
+        cfb.refresh_fp8_weight(self.fw, recompute_amax=False)
+        return self.fw
+
+
+class EpMoeSwigluFp8:
+    """Expert-parallel form of ops.MoeSwigluFp8: tokens are data-parallel (this rank holds `rows` of them), experts
+    are sharded over the ranks. Per layer: route locally -> counts all-gather -> E4M3 rows all-to-all -> ragged
+    gate/up GEMM over (source, expert) segments with the source's activation scale -> SwiGLU + delayed-scale
+    re-quantise -> ragged down GEMM -> bf16 all-to-all back -> local weighted combine."""
+
+    def __init__(self, cfb, ctx, rows, H, F, num_experts, top_k, group=None, device="cuda", recv_capacity=None):
+        self.cfb, self.ctx, self.group = cfb, ctx, group
+        self.rows, self.H, self.F, self.E, self.k = rows, H, F, num_experts, top_k
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.e_lo, self.e_hi = EpPlan.expert_range(num_experts, self.world, self.rank)
+        self.T = rows * top_k
+        # worst case every token of every rank picks this rank's experts
+        self.cap = recv_capacity or self.T * self.world
+        dev = device
+        self.counts = torch.zeros(num_experts, dtype=torch.int32, device=dev)
+        self.offsets = torch.zeros(num_experts, dtype=torch.int32, device=dev)
+        self.idx = torch.zeros((num_experts, rows), dtype=torch.int32, device=dev)
+        self.x8 = torch.empty((rows, H), dtype=torch.uint8, device=dev)
+        self.xc = torch.empty((self.T, H), dtype=torch.uint8, device=dev)
+        self.slot_x = cfb.ActSlot(ctx, cfb.E4M3_MAX)
+        self.slot_h = cfb.ActSlot(ctx, cfb.E4M3_MAX)
+        self.device = dev
+        self.plan: Optional[EpPlan] = None
+
+    def forward(self, x, route_weights, w_gateup8_local, w_gateup_descale, w_down8_local, w_down_descale, mixed):
+        cfb, ctx = self.cfb, self.ctx
+        rows, H, F, E = self.rows, self.H, self.F, self.E
+        cfb.moe_topk_route_f32(route_weights, rows, E, self.k)
+        cfb.moe_build_expert_row_lists(route_weights, self.counts, self.idx, rows, E)
+        cfb.moe_expert_offsets_from_counts(self.counts, self.offsets, E)
+        cfb.fp8_quant_act(ctx, self.slot_x, x, self.x8)
+        cfb.moe_gather_all_u8(self.x8, self.xc, self.idx, self.counts, self.offsets, rows, E, H)
+        # exchange: counts (host-visible), every rank's activation descale, then the rows
+        plan = EpPlan.build(gather_counts(self.counts, self.group), self.rank)
+        self.plan = plan
+        dx_local = torch.empty(1, dtype=torch.float32, device=self.device)
+        _copy_device_scalar(cfb, dx_local, self.slot_x.c.descale_snapshot)
+        dx_all = [torch.empty(1, dtype=torch.float32, device=self.device) for _ in range(self.world)]
+        dist.all_gather(dx_all, dx_local, group=self.group)
+        recv8 = all_to_all_rows(self.xc, plan.send_splits, plan.recv_splits, self.group)
+        R = plan.total_recv
+        nseg = len(plan.seg_counts)
+        dev = self.device
+        seg_counts = torch.tensor(plan.seg_counts, dtype=torch.int32, device=dev)
+        seg_offsets = torch.tensor(plan.seg_offsets, dtype=torch.int32, device=dev)
+        seg_weight = torch.tensor(plan.seg_weight, dtype=torch.int32, device=dev)
+        seg_dx = torch.cat(dx_all)[torch.tensor(plan.seg_source, device=dev)].contiguous()
+        e_local = self.e_hi - self.e_lo
+        yc = torch.empty((max(R, 1), H), dtype=torch.bfloat16, device=dev)
+        if R > 0:
+            gu = torch.empty((R, 2 * F), dtype=torch.bfloat16, device=dev)
+            h8 = torch.empty((R, F), dtype=torch.uint8, device=dev)
+            cfb.gemm_fp8_nt_segments(ctx, nseg, e_local, seg_weight, R, 2 * F, H, seg_counts, seg_offsets, recv8, H, False,
+                                     seg_dx, True, w_gateup8_local, w_gateup_descale, gu, 2 * F)
+            cfb.fp8_swiglu_quant_act(ctx, self.slot_h, gu, gu.view(-1)[F:], 2 * F, R, F, h8)
+            cfb.gemm_fp8_nt_segments(ctx, nseg, e_local, seg_weight, R, H, F, seg_counts, seg_offsets, h8, F, False,
+                                     cfb.ops._DevPtr(self.slot_h.c.descale_snapshot), False, w_down8_local,
+                                     w_down_descale, yc, H)
+        back = all_to_all_rows(yc[:R], plan.recv_splits, plan.send_splits, self.group)
+        cfb.moe_combine_all_bf16(mixed, back, route_weights, self.idx, self.counts, self.offsets, rows, E, H)
+
+
+def _copy_device_scalar(cfb, dst_tensor, src_addr):
+    """dst_tensor[0] = *(float*)src_addr, stream-ordered on the current stream (device-to-device)."""
+    import ctypes as C
+    rt = cfb.ops._cudart()
+    rt.cudaMemcpyAsync.restype = C.c_int
+    rc = rt.cudaMemcpyAsync(C.c_void_p(dst_tensor.data_ptr()), C.c_void_p(src_addr), C.c_size_t(4), C.c_int(3),
+                            C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    if rc != 0:
+        raise RuntimeError(f"cudaMemcpyAsync failed with {rc}")

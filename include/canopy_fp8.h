@@ -154,6 +154,16 @@ int cf_gemm_fp8_nt_grouped(cf_ctx* ctx, int num_experts, int max_total_rows, int
                            int per_expert_a_descale, const void* d_B, const float* d_b_descale, void* d_C, int ldc,
                            void* stream);
 
+/* The same launch over arbitrary row segments: segment g multiplies rows [d_offsets[g], +d_counts[g]) with weight block
+ * d_segment_weight[g] (0 <= index < num_weights; NULL = g) of the stacked [num_weights, N, K] tensor, optionally with
+ * its own activation descale (per_segment_a_descale: d_a_descale is float[num_segments]). Expert parallelism uses it:
+ * rows received from different ranks for the same local expert are separate segments with that rank's scale. No
+ * counterpart in the reference (it has no expert parallelism, include/ida_native/arena.hpp:24-26). */
+int cf_gemm_fp8_nt_segments(cf_ctx* ctx, int num_segments, int num_weights, const int* d_segment_weight,
+                            int max_total_rows, int N, int K, const int* d_counts, const int* d_offsets, const void* d_A,
+                            int lda, int a_is_e5m2, const float* d_a_descale, int per_segment_a_descale, const void* d_B,
+                            const float* d_b_descale, void* d_C, int ldc, void* stream);
+
 /* ------------------------------------------------------------------ delayed-scaling slot + fused linear */
 
 /* Mirror of ActSlot (src/trainer.cu:3248-3279). All pointer members are device scalars; cf_act_slot_init
@@ -185,6 +195,13 @@ int cf_act_slot_init(cf_ctx* ctx, cf_act_slot* slot, float fp8_max, int calib_ca
  * commit synchronises the stream and reads two floats back, exactly like the reference (:4750-4752). */
 int cf_fp8_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, size_t n, void* d_out8, void* stream,
                      int is_recompute);
+
+/* swiglu_forward (src/trainer.cu:6322) followed by fp8_quant_act on its output (:7138-7140) as one pass over gate and
+ * up: the bf16 SwiGLU product is rounded exactly as swiglu_forward would write it, quantised with the slot's
+ * delayed scale, its amax recorded and the ring advanced. E4M3 slots without calibration; the first call takes an
+ * exact amax first. gate/up are [rows, cols] views with row stride ld_in; d_out8 is [rows, cols] contiguous. */
+int cf_fp8_swiglu_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_gate, const void* d_up, int ld_in, int rows,
+                            int cols, void* d_out8, void* stream);
 
 /* One FP8-cached weight (Fp8Slot, src/trainer.cu:3284-3294) and its refresh (:4694-4712): [amax] -> scale ->
  * quantise into the native layout cache -> quantise-transpose into the other one. */
@@ -233,6 +250,21 @@ int cf_bias_add_strided_bf16(void* d_inout, const void* d_bias, int rows, int co
 int cf_swiglu_forward(const void* d_gate, const void* d_up, void* d_out, int n, void* stream);
 /* kernels/moe.cu:519-521, kernels.hpp:334.  exact-erf GELU. */
 int cf_gelu_forward(const void* d_x, void* d_out, size_t n, void* stream);
+
+/* Per-token (row-wise) scaling — BASELINE configuration 3's granularity; the reference scales per tensor only, so
+ * these generalise kernels/fp8.cu:34-49 per row: a_r = max(amax_r, 1e-12), scale_r = 448/a_r, descale_r = a_r/448,
+ * out[r,c] = e4m3(x[r,c] * scale_r). d_row_scale may be NULL. At most 16384 columns. The GEMM consumes d_row_descale
+ * through cf_gemm_epilogue.d_a_row_descale. */
+int cf_fp8_quantize_rowwise_e4m3(const void* d_x, int ld_x, void* d_out, int ld_out, float* d_row_scale,
+                                 float* d_row_descale, int rows, int cols, void* stream);
+/* The same on bf16(silu(gate) * up): swiglu_forward (kernels/activations.cu:28-40) and the re-quantisation before the
+ * down projection (src/trainer.cu:7138-7146) in one pass; gate and up are [rows, cols] views with row stride ld_in. */
+int cf_swiglu_quantize_rowwise_e4m3(const void* d_gate, const void* d_up, int ld_in, void* d_out, int ld_out,
+                                    float* d_row_scale, float* d_row_descale, int rows, int cols, void* stream);
+/* Per-tensor delayed-scaling form of the same fusion: swiglu_forward + fp8_quantize_e4m3_record
+ * (kernels/fp8.cu:310-319) without the bf16 intermediate in HBM. The caller zeroes d_amax. */
+int cf_swiglu_quantize_e4m3_record(const void* d_gate, const void* d_up, int ld_in, void* d_out, int ld_out,
+                                   const float* d_scale, float* d_amax, int rows, int cols, void* stream);
 
 /* ------------------------------------------------------------------ MoE routing, permute, combine */
 

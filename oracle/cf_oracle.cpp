@@ -416,6 +416,27 @@ void orc_swiglu_forward(const uint16_t* gate, const uint16_t* up, uint16_t* out,
     }
 }
 
+// ---- row-wise (per-token) scaling: kernels/fp8.cu:34-49 applied per row (no reference code; documented
+// generalisation for configuration 3). swiglu != 0 quantises bf16(silu(gate)*up) (kernels/activations.cu:28-40).
+void orc_quantize_rowwise_e4m3(const uint16_t* a, const uint16_t* b_or_null, int64_t ld_in, uint8_t* out, int64_t ld_out,
+                               float* row_scale, float* row_descale, int rows, int cols) {
+    std::vector<float> v(cols);
+    for (int64_t r = 0; r < rows; ++r) {
+        float amax = 0.0f;
+        for (int c = 0; c < cols; ++c) {
+            float x = bf16_to_f32(a[r * ld_in + c]);
+            if (b_or_null) x = bf16_to_f32(f32_to_bf16(x * stable_sigmoid(x) * bf16_to_f32(b_or_null[r * ld_in + c])));
+            v[c] = x;
+            amax = amax_step(amax, x);
+        }
+        const float am = std::fmax(amax, 1e-12f);
+        const float s = 448.0f / am;
+        if (row_scale) row_scale[r] = s;
+        row_descale[r] = am / 448.0f;
+        for (int c = 0; c < cols; ++c) out[r * ld_out + c] = e4m3_sat(v[c] * s);
+    }
+}
+
 // ---- kernels/moe.cu:510-516  k_gelu_fwd -------------------------------------
 void orc_gelu_forward(const uint16_t* x, uint16_t* out, int64_t n) {
     for (int64_t i = 0; i < n; ++i) out[i] = f32_to_bf16(gelu_erf(bf16_to_f32(x[i])));

@@ -174,6 +174,16 @@ class Oracle:
         self.lib.orc_swiglu_forward(_ptr(gate), _ptr(up), _ptr(out), c_i64(gate.size))
         return out
 
+    def quantize_rowwise_e4m3(self, a, b=None):
+        """a (and optional b for the SwiGLU form): uint16 [rows, cols] contiguous."""
+        rows, cols = a.shape
+        out = np.empty((rows, cols), dtype=np.uint8)
+        sc = np.empty(rows, dtype=np.float32)
+        de = np.empty(rows, dtype=np.float32)
+        self.lib.orc_quantize_rowwise_e4m3(_ptr(a), _ptr(b), c_i64(cols), _ptr(out), c_i64(cols), _ptr(sc), _ptr(de),
+                                           c_i(rows), c_i(cols))
+        return out, sc, de
+
     def gelu_forward(self, x):
         out = np.empty(x.shape, dtype=np.uint16)
         self.lib.orc_gelu_forward(_ptr(x), _ptr(out), c_i64(x.size))

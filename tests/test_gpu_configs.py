@@ -1,0 +1,268 @@
+"""BASELINE configurations 3 (SwiGLU MLP, per-token / per-channel scales), 4 (MoE SwiGLU experts) and 5
+(large-shape E4M3 forward / E5M2 dgrad) as parity cases: reduced sizes against the oracle, full sizes through
+sampled rows and size-independent properties."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+from gpu_util import bf16_to_u16, f32_scalar, package, randn_bf16, rel_fro, u16_to_bf16  # noqa: E402
+
+TOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def cfb():
+    assert torch.cuda.is_available()
+    return package()
+
+
+@pytest.fixture(scope="module")
+def ctx(cfb):
+    c = cfb.Fp8Ctx(act8_bytes=1 << 20)
+    yield c
+    c.close()
+
+
+def _rowquant(cfb, w):
+    w8 = torch.empty(w.shape, dtype=torch.uint8, device="cuda")
+    d = torch.empty(w.shape[0], dtype=torch.float32, device="cuda")
+    cfb.fp8_quantize_rowwise_e4m3(w, w8, d)
+    return w8, d
+
+
+def _tensorquant(cfb, x, e5m2=False):
+    am, sc, de = f32_scalar(), f32_scalar(), f32_scalar()
+    cfb.fp8_amax_bf16(x, am)
+    cfb.fp8_scale_from_amax(am, cfb.E5M2_MAX if e5m2 else cfb.E4M3_MAX, sc, de)
+    q = torch.empty(x.shape, dtype=torch.uint8, device="cuda")
+    (cfb.fp8_quantize_e5m2 if e5m2 else cfb.fp8_quantize_e4m3)(x, q, sc)
+    return q, de
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1), (3, 7), (17, 64), (64, 4096), (33, 14336), (5, 1000), (8, 16384)])
+def test_rowwise_quantize_bit_exact(cfb, oracle, rows, cols):
+    x = randn_bf16((rows, cols), seed=rows * cols, outlier_frac=0.01)
+    x[0] = 0                                      # an all-zero row: amax clamps to 1e-12
+    out = torch.full((rows, cols + 8), 0xAB, dtype=torch.uint8, device="cuda")
+    sc = torch.empty(rows, dtype=torch.float32, device="cuda")
+    de = torch.empty(rows, dtype=torch.float32, device="cuda")
+    cfb.fp8_quantize_rowwise_e4m3(x, out, de, row_scale=sc, ld_out=cols + 8)
+    w, s_o, d_o = oracle.quantize_rowwise_e4m3(bf16_to_u16(x))
+    got = out.cpu().numpy()
+    assert np.array_equal(got[:, :cols], w) and (got[:, cols:] == 0xAB).all()
+    assert np.array_equal(sc.cpu().numpy(), s_o) and np.array_equal(de.cpu().numpy(), d_o)
+    # a strided 2-byte-aligned view (row stride cols, first column dropped) takes the scalar path
+    if cols > 1:
+        xv = x.view(-1)[1:]
+        out2 = torch.empty((rows - 1 if rows > 1 else 1, cols), dtype=torch.uint8, device="cuda")
+        if rows > 1:
+            de2 = torch.empty(rows - 1, dtype=torch.float32, device="cuda")
+            cfb.fp8_quantize_rowwise_e4m3(xv, out2, de2, rows=rows - 1, cols=cols - 1, ld_x=cols, ld_out=cols)
+            ref = np.ascontiguousarray(bf16_to_u16(x).reshape(-1)[1:1 + (rows - 1) * cols].reshape(rows - 1, cols)[:, :cols - 1])
+            w2, _, d2 = oracle.quantize_rowwise_e4m3(ref)
+            assert np.array_equal(out2.cpu().numpy()[:, :cols - 1], w2) and np.array_equal(de2.cpu().numpy(), d2)
+
+
+@pytest.mark.parametrize("rows,F", [(9, 40), (64, 1024), (32, 14336)])
+def test_swiglu_fusions_match_the_two_step_sequence(cfb, ctx, oracle, rows, F):
+    """The fused kernels must produce the bytes of swiglu_forward followed by the quantise kernel (both verified
+    against the reference's own kernels elsewhere); against the CPU oracle libm's expf allows rare one-step differences."""
+    gu = randn_bf16((rows, 2 * F), std=2.0, seed=F)
+    gate, up = gu.view(-1), gu.view(-1)[F:]
+    # two-step sequence on the device
+    g_c, u_c = gu[:, :F].contiguous(), gu[:, F:].contiguous()
+    h = torch.empty((rows, F), dtype=torch.bfloat16, device="cuda")
+    cfb.swiglu_forward(g_c, u_c, h)
+    want8 = torch.empty((rows, F), dtype=torch.uint8, device="cuda")
+    want_d = torch.empty(rows, dtype=torch.float32, device="cuda")
+    cfb.fp8_quantize_rowwise_e4m3(h, want8, want_d)
+    got8 = torch.empty((rows, F), dtype=torch.uint8, device="cuda")
+    got_d = torch.empty(rows, dtype=torch.float32, device="cuda")
+    cfb.swiglu_quantize_rowwise_e4m3(gate, up, got8, got_d, rows, F, 2 * F)
+    assert torch.equal(got8, want8) and torch.equal(got_d, want_d)
+    o8, _, o_d = oracle.quantize_rowwise_e4m3(bf16_to_u16(g_c), bf16_to_u16(u_c))
+    assert (got8.cpu().numpy() != o8).mean() < 2e-3
+    np.testing.assert_allclose(got_d.cpu().numpy(), o_d, rtol=2 ** -7)
+    # per-tensor record form
+    sc = f32_scalar(37.0)
+    am_w, am_g = f32_scalar(), f32_scalar()
+    w8 = torch.empty((rows, F), dtype=torch.uint8, device="cuda")
+    g8 = torch.empty((rows, F), dtype=torch.uint8, device="cuda")
+    cfb.fp8_quantize_e4m3_record(h, w8, sc, am_w)
+    cfb.swiglu_quantize_e4m3_record(gate, up, g8, sc, am_g, rows, F, 2 * F)
+    assert torch.equal(g8, w8) and am_g[0].item() == am_w[0].item()
+    # slot form over three steps: identical bytes and slot scalars as swiglu_forward + fp8_quant_act
+    s_a, s_b = cfb.ActSlot(ctx, cfb.E4M3_MAX), cfb.ActSlot(ctx, cfb.E4M3_MAX)
+    for step in range(3):
+        gu2 = randn_bf16((rows, 2 * F), std=1.0 + step, seed=100 + step)
+        cfb.swiglu_forward(gu2[:, :F].contiguous(), gu2[:, F:].contiguous(), h)
+        cfb.fp8_quant_act(ctx, s_a, h, w8)
+        cfb.fp8_swiglu_quant_act(ctx, s_b, gu2, gu2.view(-1)[F:], 2 * F, rows, F, g8)
+        assert torch.equal(g8, w8), step
+        a, b = s_a.scalars(), s_b.scalars()
+        for k in ("amax", "scale", "descale", "scale_snapshot", "descale_snapshot", "history", "cursor", "count"):
+            assert a[k] == b[k], (step, k)
+
+
+def _mlp_oracle(oracle, x_u16, wgu8, dgu, wd8, dd):
+    x8, _, dx = oracle.quantize_rowwise_e4m3(x_u16)
+    gu = oracle.gemm_fp8_nt(x8, wgu8, dx, dgu)
+    F = wgu8.shape[0] // 2
+    h8, _, dh = oracle.quantize_rowwise_e4m3(np.ascontiguousarray(gu[:, :F]), np.ascontiguousarray(gu[:, F:]))
+    return oracle.gemm_fp8_nt(h8, wd8, dh, dd)
+
+
+def test_config3_swiglu_mlp_reduced(cfb, ctx, oracle):
+    M, H, F = 384, 256, 640
+    x = randn_bf16((M, H), seed=1)
+    wgu8, dgu = _rowquant(cfb, randn_bf16((2 * F, H), std=0.02, seed=2))
+    wd8, dd = _rowquant(cfb, randn_bf16((H, F), std=0.02, seed=3))
+    y = torch.empty((M, H), dtype=torch.bfloat16, device="cuda")
+    cfb.swiglu_mlp_fp8_rowwise(ctx, x, wgu8, dgu, wd8, dd, y)
+    ctx.poll_status()
+    want = _mlp_oracle(oracle, bf16_to_u16(x), wgu8.cpu().numpy(), dgu.cpu().numpy(), wd8.cpu().numpy(), dd.cpu().numpy())
+    assert rel_fro(y.float().cpu().numpy(), oracle.bf16_to_f32(want)) < TOL
+    # column-sharded gate/up (N split in two, outputs concatenated) and row-sharded down (K split, partial sums
+    # added in fp32) reproduce the unsharded result: what each of 2 GPUs would compute
+    one = torch.ones(4, dtype=torch.float32, device="cuda")
+    x8 = torch.empty((M, H), dtype=torch.uint8, device="cuda"); dx = torch.empty(M, dtype=torch.float32, device="cuda")
+    cfb.fp8_quantize_rowwise_e4m3(x, x8, dx)
+    gu_full = torch.empty((M, 2 * F), dtype=torch.bfloat16, device="cuda")
+    cfb.lt_gemm_fp8_nt(ctx, M, 2 * F, H, x8, H, False, one, wgu8, one, gu_full, 2 * F, a_row_descale=dx, b_col_descale=dgu)
+    gu_sh = torch.empty_like(gu_full)
+    for r in range(2):
+        # rank r owns gate rows [r*F/2, (r+1)*F/2) and the matching up rows
+        for base in (0, F):
+            lo = base + r * (F // 2)
+            cfb.lt_gemm_fp8_nt(ctx, M, F // 2, H, x8, H, False, one, wgu8[lo:lo + F // 2], one, gu_sh.view(-1)[lo:], 2 * F,
+                               a_row_descale=dx, b_col_descale=dgu[lo:lo + F // 2])
+    assert torch.equal(gu_sh, gu_full)
+    ctx.poll_status()
+
+
+def test_config3_full_size_sampled(cfb, ctx, oracle):
+    """M=16384, hidden 4096, ffn 14336 at full size; sampled token rows against the oracle."""
+    M, H, F = 16384, 4096, 14336
+    x = randn_bf16((M, H), seed=1)
+    wgu8, dgu = _rowquant(cfb, randn_bf16((2 * F, H), std=0.02, seed=2))
+    wd8, dd = _rowquant(cfb, randn_bf16((H, F), std=0.02, seed=3))
+    y = torch.empty((M, H), dtype=torch.bfloat16, device="cuda")
+    work = cfb.swiglu_mlp_fp8_rowwise(ctx, x, wgu8, dgu, wd8, dd, y)
+    ctx.poll_status()
+    rows = [0, 127, 128, 255, 256, 8191, 16383]
+    want = _mlp_oracle(oracle, bf16_to_u16(x[rows]), wgu8.cpu().numpy(), dgu.cpu().numpy(), wd8.cpu().numpy(), dd.cpu().numpy())
+    assert rel_fro(y[rows].float().cpu().numpy(), oracle.bf16_to_f32(want)) < TOL
+    # per-token scaling makes rows independent: a slab computed alone reproduces the same rows bit for bit
+    y2 = torch.empty((512, H), dtype=torch.bfloat16, device="cuda")
+    cfb.swiglu_mlp_fp8_rowwise(ctx, x[4096:4608], wgu8, dgu, wd8, dd, y2)
+    assert torch.equal(y2, y[4096:4608])
+    del work
+
+
+def _zipf_logits(rows, E, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    p = torch.arange(1, E + 1, device="cuda", dtype=torch.float32) ** -1.1
+    return (torch.randn((rows, E), generator=g, device="cuda") + torch.log(p / p.sum())).contiguous()
+
+
+def _moe_oracle_rows(oracle, cfb, moe, x, rw, wgu8, dgu, wd8, dd, sample_rows):
+    """Recomputes mixed[r] for a few token rows on the host from the quantised tensors and slot snapshots."""
+    F, H, E = moe.F, moe.H, moe.E
+    dx = np.float32(moe.slot_x.scalars()["descale_snapshot"])
+    sh = np.float32(moe.slot_h.scalars()["scale_snapshot"])
+    dh = np.float32(moe.slot_h.scalars()["descale_snapshot"])
+    x8 = moe.x8.cpu().numpy()
+    rw_n = rw.cpu().numpy()
+    out = np.zeros((len(sample_rows), H), dtype=np.uint16)
+    for i, r in enumerate(sample_rows):
+        for e in range(E):
+            w = rw_n[r, e]
+            if w <= 0:
+                continue
+            gu = oracle.gemm_fp8_nt(x8[r:r + 1], wgu8[e].cpu().numpy(), dx, dgu[0].item())
+            h = oracle.swiglu_forward(np.ascontiguousarray(gu[:, :F]), np.ascontiguousarray(gu[:, F:]))
+            h8 = oracle.quantize_bf16(h, sh)
+            ye = oracle.gemm_fp8_nt(h8, wd8[e].cpu().numpy(), dh, dd[0].item())
+            acc = oracle.bf16_to_f32(out[i:i + 1]) + w * oracle.bf16_to_f32(ye)
+            out[i] = oracle.to_bf16(acc)[0]
+    return out
+
+
+@pytest.mark.parametrize("rows,H,F,E,k", [(300, 128, 256, 4, 2), (1024, 256, 512, 8, 2)])
+def test_config4_moe_swiglu_reduced(cfb, ctx, oracle, rows, H, F, E, k):
+    x = randn_bf16((rows, H), seed=1)
+    rw = _zipf_logits(rows, E, 3)
+    wgu8, dgu = _tensorquant(cfb, randn_bf16((E, 2 * F, H), std=0.05, seed=4))
+    wd8, dd = _tensorquant(cfb, randn_bf16((E, H, F), std=0.05, seed=5))
+    moe = cfb.MoeSwigluFp8(ctx, rows, H, F, E, k)
+    mixed = torch.zeros((rows, H), dtype=torch.bfloat16, device="cuda")
+    moe.forward(x, rw, wgu8, dgu, wd8, dd, mixed)
+    ctx.poll_status()
+    assert int(moe.counts.sum().item()) == rows * k
+    sample = list(range(0, rows, max(1, rows // 40)))
+    want = _moe_oracle_rows(oracle, cfb, moe, x, rw, wgu8, dgu, wd8, dd, sample)
+    assert rel_fro(mixed[sample].float().cpu().numpy(), oracle.bf16_to_f32(want)) < TOL
+    # second step: delayed scales now come from the first step's amax; result stays within tolerance of the oracle
+    x2 = randn_bf16((rows, H), std=1.5, seed=7)
+    rw2 = _zipf_logits(rows, E, 9)
+    mixed2 = torch.zeros((rows, H), dtype=torch.bfloat16, device="cuda")
+    moe.forward(x2, rw2, wgu8, dgu, wd8, dd, mixed2)
+    ctx.poll_status()
+    want2 = _moe_oracle_rows(oracle, cfb, moe, x2, rw2, wgu8, dgu, wd8, dd, sample)
+    assert rel_fro(mixed2[sample].float().cpu().numpy(), oracle.bf16_to_f32(want2)) < TOL
+
+
+def test_config4_full_size_sampled(cfb, ctx, oracle):
+    """32768 tokens, hidden 4096, 8 experts of ffn 14336, top-2, Zipf(1.1)-skewed load: sampled tokens against the
+    oracle, conservation of the dispatch (every token lands in exactly two experts) and combine linearity."""
+    rows, H, F, E, k = 32768, 4096, 14336, 8, 2
+    x = randn_bf16((rows, H), seed=1)
+    rw = _zipf_logits(rows, E, 3)
+    wgu8, dgu = _tensorquant(cfb, randn_bf16((E, 2 * F, H), std=0.02, seed=4))
+    wd8, dd = _tensorquant(cfb, randn_bf16((E, H, F), std=0.02, seed=5))
+    moe = cfb.MoeSwigluFp8(ctx, rows, H, F, E, k)
+    mixed = torch.zeros((rows, H), dtype=torch.bfloat16, device="cuda")
+    moe.forward(x, rw, wgu8, dgu, wd8, dd, mixed)
+    ctx.poll_status()
+    counts = moe.counts.cpu().numpy()
+    assert counts.sum() == rows * k and counts[0] > counts[-1]          # skewed load, nothing dropped
+    flat = torch.cat([moe.idx[e, :counts[e]] for e in range(E)]).cpu().numpy()
+    assert np.array_equal(np.bincount(flat, minlength=rows), np.full(rows, k))
+    sample = [0, 1, 777, 16384, 32767]
+    want = _moe_oracle_rows(oracle, cfb, moe, x, rw, wgu8, dgu, wd8, dd, sample)
+    assert rel_fro(mixed[sample].float().cpu().numpy(), oracle.bf16_to_f32(want)) < TOL
+    del moe
+
+
+def test_config5_large_shape_forward_and_dgrad(cfb, ctx, oracle):
+    """M=32768, K=8192, N=28672 E4M3 forward and the E5M2-gradient x E4M3-weight dgrad of matching shape
+    (dX[32768x8192] = dY[32768x28672] . W^T with W cached [8192x28672]); sampled rows against the oracle."""
+    M, K, N = 32768, 8192, 28672
+    a8, da = _tensorquant(cfb, randn_bf16((M, K), seed=1))
+    w = randn_bf16((N, K), std=0.02, seed=2)
+    fw = cfb.Fp8Weight(w, stored_out_major=True)        # fwd8 = [N,K], bwd8 = [K,N]
+    cfb.refresh_fp8_weight(fw)
+    c = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    cfb.lt_gemm_fp8_nt(ctx, M, N, K, a8, K, False, da, fw.fwd8, fw.descale, c, N)
+    ctx.poll_status()
+    rows = [0, 255, 256, 20000, 32767]
+    want = oracle.gemm_fp8_nt(a8[rows].cpu().numpy(), fw.fwd8.cpu().numpy(), da[0].item(), fw.descale.item())
+    assert rel_fro(c[rows].float().cpu().numpy(), oracle.bf16_to_f32(want)) < 5e-3
+    del c
+    dy = (randn_bf16((M, N), seed=3).float() * 1e-3).to(torch.bfloat16)
+    dy8, ddy = _tensorquant(cfb, dy, e5m2=True)
+    del dy
+    dxo = torch.empty((M, K), dtype=torch.bfloat16, device="cuda")
+    cfb.lt_gemm_fp8_nt(ctx, M, K, N, dy8, N, True, ddy, fw.bwd8, fw.descale, dxo, K)
+    ctx.poll_status()
+    want = oracle.gemm_fp8_nt(dy8[rows].cpu().numpy(), fw.bwd8.cpu().numpy(), ddy[0].item(), fw.descale.item(), a_is_e5m2=True)
+    assert rel_fro(dxo[rows].float().cpu().numpy(), oracle.bf16_to_f32(want)) < 5e-3
+    # N-sharding over 8 GPUs: each shard's forward slice equals the same columns of the full product
+    c_sh = torch.empty((1024, N // 8), dtype=torch.bfloat16, device="cuda")
+    cfb.lt_gemm_fp8_nt(ctx, 1024, N // 8, K, a8, K, False, da, fw.fwd8[3 * (N // 8):4 * (N // 8)], fw.descale, c_sh, N // 8)
+    c_full = torch.empty((1024, N), dtype=torch.bfloat16, device="cuda")
+    cfb.lt_gemm_fp8_nt(ctx, 1024, N, K, a8, K, False, da, fw.fwd8, fw.descale, c_full, N)
+    assert torch.equal(c_sh, c_full[:, 3 * (N // 8):4 * (N // 8)])
+    ctx.poll_status()

@@ -1,0 +1,136 @@
+"""Host-side logic of the multi-GPU path on CPU ranks (gloo, world size 2 and 3): shard ranges, the weight-amax
+max-all-reduce, the expert-parallel plan and the row exchange out and back."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from gpu_util import package
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, fn_name, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        globals()[fn_name](rank, world)
+        ret[rank] = "ok"
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = traceback.format_exc()
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(fn_name, world):
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = _free_port()
+    procs = [mp.get_context("spawn").Process(target=_worker, args=(r, world, port, fn_name, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert not p.is_alive(), "rank did not finish"
+    for r in range(world):
+        assert ret.get(r) == "ok", ret.get(r)
+
+
+def test_shard_range_partitions():
+    par = package().parallel
+    for n, world, mult in [(28672, 8, 1), (14336, 8, 128), (4096, 3, 256), (10, 4, 1), (5, 8, 1), (0, 2, 1)]:
+        cover = []
+        for r in range(world):
+            lo, hi = par.shard_range(n, world, r, mult)
+            assert 0 <= lo <= hi <= n
+            if hi < n:
+                assert (hi - lo) % mult == 0
+            cover += list(range(lo, hi))
+        assert cover == list(range(n))
+    assert par.shard_range(28672, 8, 3) == (3 * 3584, 4 * 3584)
+
+
+def _amax_case(rank, world):
+    par = package().parallel
+    torch.manual_seed(0)
+    w = torch.randn(64, 32) * 0.02                     # the whole logical weight, same on every rank
+    lo, hi = par.shard_range(64, world, rank)
+    local = w[lo:hi].abs().max().reshape(1).clone()
+    par.allreduce_max_(local)
+    assert local.item() == w.abs().max().item()        # bit-identical to the single-GPU amax
+    part = torch.full((4,), float(rank + 1))
+    par.allreduce_sum_(part)
+    assert part[0].item() == sum(range(1, world + 1))
+
+
+def test_weight_amax_allreduce_world2():
+    _run("_amax_case", 2)
+
+
+def _ep_case(rank, world):
+    par = package().parallel
+    E, rows, k, width = 6, 40, 2, 8
+    g = torch.Generator().manual_seed(100 + rank)
+    # each row picks k distinct experts
+    picks = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(rows)])
+    counts = torch.zeros(E, dtype=torch.int32)
+    for e in picks.flatten().tolist():
+        counts[e] += 1
+    table = par.gather_counts(counts)
+    assert table[rank] == counts.tolist() and len(table) == world
+    plan = par.EpPlan.build(table, rank)
+    assert sum(plan.send_splits) == rows * k
+    # compact send buffer ordered by expert; every row tagged (source rank, expert, running index)
+    send = torch.zeros((rows * k, width), dtype=torch.int32)
+    pos = 0
+    for e in range(E):
+        for i in range(counts[e]):
+            send[pos, 0], send[pos, 1], send[pos, 2] = rank, e, i
+            pos += 1
+    recv = par.all_to_all_rows(send, plan.send_splits, plan.recv_splits)
+    assert recv.shape[0] == plan.total_recv == sum(plan.recv_splits)
+    lo, hi = par.EpPlan.expert_range(E, world, rank)
+    for c, off, w_idx, src in zip(plan.seg_counts, plan.seg_offsets, plan.seg_weight, plan.seg_source):
+        seg = recv[off:off + c]
+        assert c == table[src][lo + w_idx]
+        if c:
+            assert (seg[:, 0] == src).all() and (seg[:, 1] == lo + w_idx).all()
+            assert seg[:, 2].tolist() == list(range(c))
+    # the way back restores the sender's order exactly
+    back = par.all_to_all_rows(recv * 2, plan.recv_splits, plan.send_splits)
+    assert torch.equal(back, send * 2)
+    # uint8 rows (what actually travels) and a rank that receives nothing
+    send8 = (send[:, :4] % 251).to(torch.uint8)
+    back8 = par.all_to_all_rows(par.all_to_all_rows(send8, plan.send_splits, plan.recv_splits), plan.recv_splits, plan.send_splits)
+    assert torch.equal(back8, send8)
+
+
+def test_expert_parallel_plan_and_exchange_world2():
+    _run("_ep_case", 2)
+
+
+def test_expert_parallel_plan_and_exchange_world3():
+    _run("_ep_case", 3)
+
+
+def test_plan_is_consistent_across_ranks():
+    par = package().parallel
+    rng = np.random.default_rng(0)
+    table = rng.integers(0, 50, size=(4, 8)).tolist()
+    plans = [par.EpPlan.build(table, r) for r in range(4)]
+    for a in range(4):
+        for b in range(4):
+            assert plans[a].send_splits[b] == plans[b].recv_splits[a]
+    assert sum(p.total_recv for p in plans) == int(np.sum(table))

@@ -172,6 +172,119 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_moe(args):
+    """BASELINE configuration 4: 32768 tokens, hidden 4096, 8 SwiGLU experts of ffn 14336, top-2 routing with a
+    Zipf(1.1)-skewed load. One step = route + dispatch lists + quantise + permute + ragged gate/up GEMM + SwiGLU
+    re-quantise + ragged down GEMM + unpermute/combine. N > 1: expert parallel (E/N experts and 32768/N tokens per
+    rank, E4M3 all-to-all out, bf16 all-to-all back): strong scaling, value = tokens of all ranks per second."""
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    cfb = importlib.import_module("canopy-foundry_b200")
+    par = cfb.parallel
+    TOK, H, F, E, TOPK = 32768, 4096, 14336, 8, 2
+    rows = TOK // world
+    use_ep = world > 1 and args.moe_mode == "ep"
+    e_lo, e_hi = par.EpPlan.expert_range(E, world, rank) if use_ep else (0, E)
+    ctx = cfb.Fp8Ctx(act8_bytes=0)
+    g = torch.Generator(device=dev).manual_seed(1000 + rank)
+    x = torch.randn((rows, H), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    pz = [(e + 1) ** -1.1 for e in range(E)]
+    # Expert placement by expected load (longest-processing-time greedy over the Zipf popularity): expert ids are
+    # renamed so that every rank owns a contiguous range of about equal total popularity. Renaming experts changes
+    # nothing in the maths; with one expert per rank (N = 8) no placement can balance a skewed load.
+    order = sorted(range(E), key=lambda e: -pz[e])
+    bins = [[] for _ in range(world if use_ep else 1)]
+    per = E // len(bins)
+    for e in order:
+        cand = [b for b in range(len(bins)) if len(bins[b]) < per]
+        tgt = min(cand, key=lambda b: sum(pz[i] for i in bins[b]))
+        bins[tgt].append(e)
+    perm = [e for b in bins for e in b]                  # new id -> popularity rank
+    p = torch.tensor([pz[e] for e in perm], device=dev, dtype=torch.float32)
+    logits = (torch.randn((rows, E), generator=g, device=dev) + torch.log(p / p.sum())).contiguous()
+
+    def quant_experts(shape, std, seed):
+        gw = torch.Generator(device=dev).manual_seed(seed)
+        amax = torch.zeros(4, dtype=torch.float32, device=dev)
+        sc, de = torch.zeros_like(amax), torch.zeros_like(amax)
+        w8 = torch.empty(shape, dtype=torch.uint8, device=dev)
+        ws = []
+        for e in range(shape[0]):                       # one expert at a time keeps the bf16 staging small
+            w = (torch.randn(shape[1:], generator=gw, device=dev, dtype=torch.float32) * std).to(torch.bfloat16)
+            ws.append(w)
+        wall = torch.stack(ws)
+        cfb.fp8_amax_bf16(wall, amax)
+        par.allreduce_max_(amax)                        # one per-tensor scale over all experts of all ranks
+        cfb.fp8_scale_from_amax(amax, cfb.E4M3_MAX, sc, de)
+        cfb.fp8_quantize_e4m3(wall, w8, sc)
+        return w8, de
+
+    n_local = e_hi - e_lo
+    wgu8, dgu = quant_experts((n_local, 2 * F, H), 0.02, 50 + rank)
+    wd8, dd = quant_experts((n_local, H, F), 0.02, 70 + rank)
+    mixed = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
+    layer = par.EpMoeSwigluFp8(cfb, ctx, rows, H, F, E, TOPK, device=dev) if use_ep else \
+        cfb.MoeSwigluFp8(ctx, rows, H, F, E, TOPK, device=dev)
+
+    def step():
+        rw = logits.clone()
+        mixed.zero_()
+        layer.forward(x, rw, wgu8, dgu, wd8, dd, mixed)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    ctx.poll_status()
+    sampler = ClockSampler(local)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    l0 = cfb.launch_count()
+    sampler.start()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    launches = cfb.launch_count() - l0
+    ctx.poll_status()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    loads = torch.tensor([float(layer.plan.total_recv) if use_ep else float(rows * TOPK)], dtype=torch.float64, device=dev)
+    lmax = loads.clone()
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(lmax, op=dist.ReduceOp.MAX)
+    ms = t.item() / args.steps
+    if rank == 0:
+        flop = 2.0 * TOK * TOPK * 3 * H * F
+        print(json.dumps({
+            "metric": "moe_fp8_tokens_per_s", "value": TOK / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": "moe_swiglu_fp8_32768tok_H4096_E8_F14336_top2_zipf1.1 (BASELINE config 4)",
+                       "parallelism": (f"ep{world} (all-to-all, experts placed by load)" if use_ep else
+                                       f"dp{world} (experts replicated, tokens sharded, no collective)") if world > 1 else "single GPU",
+                       "max_rows_on_one_rank": int(lmax.item()), "mean_rows_per_rank": TOK * TOPK / world,
+                       "l2": "inputs larger than L2 (1.4 GB of expert weights per step)"},
+            "tflops": flop / (ms * 1e-3) / 1e12, "gpu_launches": int(launches), "clocks": clocks}), flush=True)
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -182,10 +295,17 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--bias-mode", type=int, default=2, help="2 = reference rounding order, 1 = single rounding")
+    ap.add_argument("--moe-mode", default="ep", choices=["ep", "dp"],
+                    help="N > 1: ep = expert parallel with all-to-all (experts placed by load), dp = experts replicated, tokens sharded")
+    ap.add_argument("--workload", default="linear", choices=["linear", "moe"],
+                    help="linear = BASELINE configuration 2 (the headline line); moe = configuration 4 tokens/s")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.workload == "moe":
+        run_moe(args)
         return
 
     import torch

@@ -47,8 +47,33 @@ int require_sm100();
 
 inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 
+// Launch with programmatic dependent launch: the grid may be scheduled while its predecessor in the stream is
+// still draining; the kernel itself orders its memory accesses with pdl_wait() (griddepcontrol.wait), so only
+// launch latency and the kernel's prologue overlap with the predecessor's tail.
+template <class... KArgs, class... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- device helpers -----------------------------------------------------------------
 #ifdef __CUDACC__
+
+// Waits until the grids this one depends on have completed and their writes are visible, then lets the next
+// grid of the stream be scheduled behind this one. No-ops for launches without the attribute.
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t bits16) { return __uint_as_float(bits16 << 16); }
 

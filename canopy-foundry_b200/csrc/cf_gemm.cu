@@ -98,9 +98,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-                 ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+// The output is written once and not read again by this kernel: evict-first keeps it from pushing the operand
+// slabs (which every tile re-reads) out of L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y, uint64_t policy) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y), "l"(policy) : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
@@ -332,6 +339,9 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     if (PAIR) cluster_sync_all();                            // peer barriers are initialised before any remote signal
     tcgen05_fence_after();
     const uint32_t tmem_base = *s_tmem;
+    // Everything above touched only this CTA's shared memory, TMEM and kernel parameters; from here on the kernel
+    // reads what earlier kernels of the stream wrote (operands, scales, counts).
+    pdl_wait();
 
     const int m_blocks = total_m_blocks(p, TM);
     const int n_blocks = (p.N + BN - 1) / BN;
@@ -422,6 +432,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         const uint32_t tempty_dst = PAIR ? mapa(tempty_bar, 0) : tempty_bar;
         int local_tile = 0;
         uint32_t store_seq = 0;                            // alternates this warp's two staging boxes
+        const uint64_t store_policy = l2_policy_evict_first();
         bool ok = true;
         for (int tile = unit; ok && tile < total_tiles; tile += n_units, ++local_tile) {
             const int acc = local_tile & 1;
@@ -451,43 +462,63 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 for (; ch64 < BN / C_BOX_COLS; ++ch64) {
                     const int col0 = tc.n0 + ch64 * C_BOX_COLS;
                     if (col0 + C_BOX_COLS > p.N) break;    // warp-uniform; the tail takes the direct path below
-                    uint32_t v0[32], v1[32];
-                    tmem_ld32(taddr + ch64 * C_BOX_COLS, v0);
-                    tmem_ld32(taddr + ch64 * C_BOX_COLS + 32, v1);
-                    tmem_ld_wait();
-                    uint32_t w[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const uint32_t r0 = j < 16 ? v0[2 * j] : v1[2 * j - 32];
-                        const uint32_t r1 = j < 16 ? v0[2 * j + 1] : v1[2 * j - 31];
-                        float x0 = __uint_as_float(r0), x1 = __uint_as_float(r1);
-                        const float db0 = p.d_b_col_descale ? p.d_b_col_descale[col0 + 2 * j] : db_t;
-                        const float db1 = p.d_b_col_descale ? p.d_b_col_descale[col0 + 2 * j + 1] : db_t;
-                        x0 *= da * db0;
-                        x1 *= da * db1;
-                        if (p.bias_mode == 1) {
-                            const uint32_t bb = *reinterpret_cast<const uint32_t*>(p.bias + col0 + 2 * j);
-                            w[j] = pack_bf16x2(x0 + __uint_as_float(bb << 16), x1 + __uint_as_float(bb & 0xffff0000u));
-                        } else if (p.bias_mode == 2) {
-                            const uint32_t bb = *reinterpret_cast<const uint32_t*>(p.bias + col0 + 2 * j);
-                            const uint32_t r = pack_bf16x2(x0, x1);
-                            w[j] = pack_bf16x2(__uint_as_float(r << 16) + __uint_as_float(bb << 16),
-                                               __uint_as_float(r & 0xffff0000u) + __uint_as_float(bb & 0xffff0000u));
-                        } else {
-                            w[j] = pack_bf16x2(x0, x1);
-                        }
-                    }
                     const uint32_t buf = stage0 + (store_seq++ & 1u) * C_BOX_BYTES;
                     if (lane == 0) bulk_wait_read_1();     // the store that last read this buffer has drained it
                     __syncwarp();
 #pragma unroll
-                    for (int q = 0; q < 8; ++q)            // 16-byte chunk q of this row sits at (q ^ row%8): 128B swizzle
-                        st_shared_v4(buf + row_off + ((static_cast<uint32_t>(q) ^ sw) << 4), w[4 * q], w[4 * q + 1],
-                                     w[4 * q + 2], w[4 * q + 3]);
+                    for (int half = 0; half < 2; ++half) {
+                        const int col = col0 + half * 32;
+                        // bias and per-column scales of these 32 columns: a few 16-byte loads of addresses that are
+                        // the same in every lane (L1 broadcast), issued before the accumulator read-out
+                        uint4 bq[4];
+                        float4 cq[8];
+                        if (p.bias_mode != 0) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) bq[q] = __ldg(reinterpret_cast<const uint4*>(p.bias + col) + q);
+                        }
+                        if (p.d_b_col_descale) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) cq[q] = __ldg(reinterpret_cast<const float4*>(p.d_b_col_descale + col) + q);
+                        }
+                        uint32_t v[32];
+                        tmem_ld32(taddr + ch64 * C_BOX_COLS + half * 32, v);
+                        tmem_ld_wait();
+                        uint32_t w[16];
+                        const float dab = da * db_t;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
+                            if (p.d_b_col_descale) {
+                                const float4 c4 = cq[j >> 1];
+                                x0 *= da * ((j & 1) ? c4.z : c4.x);
+                                x1 *= da * ((j & 1) ? c4.w : c4.y);
+                            } else {
+                                x0 *= dab;
+                                x1 *= dab;
+                            }
+                            if (p.bias_mode != 0) {
+                                const uint4 b4 = bq[j >> 2];
+                                const uint32_t bb = (j & 3) == 0 ? b4.x : (j & 3) == 1 ? b4.y : (j & 3) == 2 ? b4.z : b4.w;
+                                const float b0 = __uint_as_float(bb << 16), b1 = __uint_as_float(bb & 0xffff0000u);
+                                if (p.bias_mode == 1) {
+                                    w[j] = pack_bf16x2(x0 + b0, x1 + b1);
+                                } else {
+                                    const uint32_t r = pack_bf16x2(x0, x1);
+                                    w[j] = pack_bf16x2(__uint_as_float(r << 16) + b0, __uint_as_float(r & 0xffff0000u) + b1);
+                                }
+                            } else {
+                                w[j] = pack_bf16x2(x0, x1);
+                            }
+                        }
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)        // 16-byte chunk c of this row sits at (c ^ row%8): 128B swizzle
+                            st_shared_v4(buf + row_off + ((static_cast<uint32_t>(half * 4 + q) ^ sw) << 4), w[4 * q],
+                                         w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+                    }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {
-                        tma_store_2d(&map_c, buf, col0, tc.row0 + warp_row0);
+                        tma_store_2d(&map_c, buf, col0, tc.row0 + warp_row0, store_policy);
                         bulk_commit();
                     }
                 }
@@ -725,7 +756,9 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     r = make_map(&map_b, d_B, b_rows, p.K, p.K, pair ? Cfg<true>::B_ROWS : Cfg<false>::B_ROWS);
     if (r != CF_OK) return r;
     p.c_rows = p.d_counts ? a_rows : p.M;
-    p.tma_store = (p.c_vec && p.N >= C_BOX_COLS) ? 1 : 0;
+    p.tma_store = (p.c_vec && p.N >= C_BOX_COLS &&
+                   (p.bias == nullptr || reinterpret_cast<uintptr_t>(p.bias) % 16 == 0) &&
+                   (p.d_b_col_descale == nullptr || reinterpret_cast<uintptr_t>(p.d_b_col_descale) % 16 == 0)) ? 1 : 0;
     static const bool no_tma_store = [] { const char* e = std::getenv("CF_GEMM_DIRECT_STORE"); return e && e[0] == '1'; }();
     if (no_tma_store) p.tma_store = 0;
     if (p.tma_store) {
@@ -747,11 +780,13 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
         cfg.blockDim = dim3(NUM_THREADS);
         cfg.dynamicSmemBytes = Cfg<true>::SMEM_BYTES;
         cfg.stream = st;
-        cudaLaunchAttribute at[1];
+        cudaLaunchAttribute at[2];
         at[0].id = cudaLaunchAttributeClusterDimension;
         at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = at;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = 2;
         CF_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_fp8_nt<true>, map_a, map_b, map_c, p));
         CF_LAUNCH_CHECK("gemm_fp8_nt<pair>");
         return CF_OK;
@@ -764,7 +799,7 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(k_gemm_fp8_nt)");
     const int sms = sm_count();
     const int grid = tile_upper_bound < sms ? tile_upper_bound : sms;
-    k_gemm_fp8_nt<false><<<grid, NUM_THREADS, Cfg<false>::SMEM_BYTES, st>>>(map_a, map_b, map_c, p);
+    CF_CUDA(launch_pdl(k_gemm_fp8_nt<false>, dim3(grid), dim3(NUM_THREADS), Cfg<false>::SMEM_BYTES, st, map_a, map_b, map_c, p));
     CF_LAUNCH_CHECK("gemm_fp8_nt");
     return CF_OK;
 }

@@ -86,6 +86,7 @@ template <bool E5M2, bool QUANT, bool RECORD>
 __global__ void __launch_bounds__(kThreads) k_stream(const uint16_t* __restrict__ x, uint8_t* __restrict__ out,
                                                      const float* __restrict__ scale, float* __restrict__ amax,
                                                      size_t n, size_t head, size_t nvec, const RingTail tail) {
+    pdl_wait();
     const float s = QUANT ? *scale : 0.0f;
     float local = 0.0f;
     const uint16_t* xv = x + head;
@@ -141,6 +142,7 @@ template <bool E5M2, bool QUANT, bool RECORD>
 __global__ void __launch_bounds__(kThreads) k_stream_scalar(const uint16_t* __restrict__ x, uint8_t* __restrict__ out,
                                                             const float* __restrict__ scale,
                                                             float* __restrict__ amax, size_t n, const RingTail tail) {
+    pdl_wait();
     const float s = QUANT ? *scale : 0.0f;
     float local = 0.0f;
     for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n;
@@ -184,16 +186,16 @@ int launch_stream(const void* d_x, void* d_out, const float* d_scale, float* d_a
     if (!vec_ok) {
         const size_t blocks = (n + kThreads - 1) / kThreads;
         const unsigned grid = static_cast<unsigned>(blocks < static_cast<size_t>(sms) * 16 ? blocks : static_cast<size_t>(sms) * 16);
-        k_stream_scalar<E5M2, QUANT, RECORD><<<grid, kThreads, 0, st>>>(
-            static_cast<const uint16_t*>(d_x), static_cast<uint8_t*>(d_out), d_scale, d_amax, n, tail);
+        CF_CUDA(launch_pdl(k_stream_scalar<E5M2, QUANT, RECORD>, dim3(grid), dim3(kThreads), 0, st,
+                           static_cast<const uint16_t*>(d_x), static_cast<uint8_t*>(d_out), d_scale, d_amax, n, tail));
     } else {
         const size_t nvec = (n - head) / 16;
         size_t blocks = (nvec + 2 * kThreads - 1) / (2 * kThreads);
         if (blocks < 1) blocks = 1;
         const size_t cap = static_cast<size_t>(sms) * 8;
         const unsigned grid = static_cast<unsigned>(blocks < cap ? blocks : cap);
-        k_stream<E5M2, QUANT, RECORD><<<grid, kThreads, 0, st>>>(
-            static_cast<const uint16_t*>(d_x), static_cast<uint8_t*>(d_out), d_scale, d_amax, n, head, nvec, tail);
+        CF_CUDA(launch_pdl(k_stream<E5M2, QUANT, RECORD>, dim3(grid), dim3(kThreads), 0, st,
+                           static_cast<const uint16_t*>(d_x), static_cast<uint8_t*>(d_out), d_scale, d_amax, n, head, nvec, tail));
     }
     CF_LAUNCH_CHECK(name);
     return CF_OK;
@@ -214,6 +216,7 @@ __global__ void k_update_delayed_scale(const float* amax, float fp8_max, float* 
 // Start of a steady-state fp8_quant_act call: snapshot the pair the forward pass is about to use and zero the
 // amax slot (src/trainer.cu:4823-4827 does this with two scalar copies and a memset).
 __global__ void k_slot_begin(const float* scale, const float* descale, float* snap_scale, float* snap_descale, float* amax) {
+    pdl_wait();
     *snap_scale = *scale;
     *snap_descale = *descale;
     *amax = 0.0f;
@@ -315,12 +318,19 @@ unsigned flat_grid(size_t n, int per_block) {
 }
 
 // ---- tiled transpose family ----------------------------------------------------------------
-// One block moves a tile of TR source rows x 64 source columns through shared memory and writes
-// it transposed: 64 output rows x TR contiguous bytes. Source is bf16 (quantised on the way in,
-// optionally also written un-transposed) or bytes (plain transpose).
+// One block moves a tile of 256 source rows x 64 source columns through shared memory and writes it
+// transposed: 64 output rows x 256 contiguous bytes, each output row written by one warp-wide store
+// instruction (32 lanes x 8 bytes). Source is bf16 (quantised on the way in, optionally also written
+// un-transposed) or bytes (plain transpose).
 constexpr int kTR = 256;          // source rows per tile  -> 256 contiguous output bytes per row
-constexpr int kTC = 64;           // source columns per tile
-constexpr int kPitchW = 17;       // shared row pitch in 32-bit words (64 bytes + 4 pad): conflict-free column reads
+constexpr int kTC = 64;           // source columns per tile (16 words of quantised bytes per source row)
+
+// Shared-memory word index of (source row k, word column wc). Rows are 16 words with no padding; the word
+// column is XOR-swizzled by the 8-row group and the two halves of the tile are offset by one row, which makes
+// the column-wise reads of the write-out phase hit 32 different banks.
+__device__ __forceinline__ int tile_word(int k, int wc) {
+    return ((k ^ ((k >> 7) & 1)) << 4) + (wc ^ ((k >> 3) & 15));
+}
 
 template <bool SRC_BF16>
 __global__ void __launch_bounds__(kThreads) k_tile_transpose(const void* __restrict__ src, uint8_t* __restrict__ direct,
@@ -328,9 +338,10 @@ __global__ void __launch_bounds__(kThreads) k_tile_transpose(const void* __restr
                                                              const float* __restrict__ scale, int R, int Ccols,
                                                              int src_vec, int direct_vec, int trans_vec,
                                                              const ScaleFromAmax sfa) {
-    __shared__ uint32_t tile[kTR * kPitchW];
+    __shared__ uint32_t tile[kTR * 16];
     const int r0 = blockIdx.y * kTR, c0 = blockIdx.x * kTC;
     const int tid = threadIdx.x;
+    pdl_wait();
     float s = 0.0f;
     if (SRC_BF16) {
         if (sfa.amax) {
@@ -347,37 +358,47 @@ __global__ void __launch_bounds__(kThreads) k_tile_transpose(const void* __restr
     }
 
     if (SRC_BF16) {
-        // 8 threads x 8 columns per source row, 32 rows per pass, 8 passes
+        // 8 threads x 8 columns per source row, 32 rows per pass, 8 passes; all loads of a thread issued first
         const uint16_t* in = static_cast<const uint16_t*>(src);
         const int cg = (tid & 7) * 8, rl = tid >> 3;
+        uint4 raw[kTR / 32];
 #pragma unroll
         for (int p = 0; p < kTR / 32; ++p) {
             const int r = r0 + p * 32 + rl, c = c0 + cg;
-            uint2 q = make_uint2(0u, 0u);
+            raw[p] = make_uint4(0u, 0u, 0u, 0u);
             if (r < R && c < Ccols) {
                 const size_t off = static_cast<size_t>(r) * Ccols + c;
-                float f[8];
                 if (src_vec && c + 8 <= Ccols) {
-                    unpack8(ldg_stream16(in + off), f);
+                    raw[p] = ldg_stream16(in + off);
                 } else {
+                    uint32_t w[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-                    for (int b = 0; b < 8; ++b) f[b] = (c + b < Ccols) ? bf16_bits_to_f32(in[off + b]) : 0.0f;
-                }
-                q = quant8<false>(f, s);
-                if (direct) {
-                    if (direct_vec && c + 8 <= Ccols) {
-                        *reinterpret_cast<uint2*>(direct + off) = q;
-                    } else {
-                        const uint64_t qq = (static_cast<uint64_t>(q.y) << 32) | q.x;
-#pragma unroll
-                        for (int b = 0; b < 8; ++b)
-                            if (c + b < Ccols) direct[off + b] = static_cast<uint8_t>(qq >> (8 * b));
-                    }
+                    for (int b = 0; b < 8; ++b)
+                        if (c + b < Ccols) w[b >> 1] |= static_cast<uint32_t>(in[off + b]) << (16 * (b & 1));
+                    raw[p] = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
-            uint32_t* w = tile + (p * 32 + rl) * kPitchW + (cg >> 2);
-            w[0] = q.x;
-            w[1] = q.y;
+        }
+#pragma unroll
+        for (int p = 0; p < kTR / 32; ++p) {
+            const int k = p * 32 + rl;
+            const int r = r0 + k, c = c0 + cg;
+            float f[8];
+            unpack8(raw[p], f);
+            const uint2 q = quant8<false>(f, s);
+            if (direct && r < R && c < Ccols) {
+                const size_t off = static_cast<size_t>(r) * Ccols + c;
+                if (direct_vec && c + 8 <= Ccols) {
+                    *reinterpret_cast<uint2*>(direct + off) = q;
+                } else {
+                    const uint64_t qq = (static_cast<uint64_t>(q.y) << 32) | q.x;
+#pragma unroll
+                    for (int b = 0; b < 8; ++b)
+                        if (c + b < Ccols) direct[off + b] = static_cast<uint8_t>(qq >> (8 * b));
+                }
+            }
+            tile[tile_word(k, cg >> 2)] = q.x;
+            tile[tile_word(k, (cg >> 2) + 1)] = q.y;
         }
     } else {
         // 4 threads x 16 bytes per source row, 64 rows per pass, 4 passes
@@ -385,7 +406,8 @@ __global__ void __launch_bounds__(kThreads) k_tile_transpose(const void* __restr
         const int cg = (tid & 3) * 16, rl = tid >> 2;
 #pragma unroll
         for (int p = 0; p < kTR / 64; ++p) {
-            const int r = r0 + p * 64 + rl, c = c0 + cg;
+            const int k = p * 64 + rl;
+            const int r = r0 + k, c = c0 + cg;
             uint4 q = make_uint4(0u, 0u, 0u, 0u);
             if (r < R && c < Ccols) {
                 const size_t off = static_cast<size_t>(r) * Ccols + c;
@@ -399,41 +421,49 @@ __global__ void __launch_bounds__(kThreads) k_tile_transpose(const void* __restr
                     q = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
-            uint32_t* w = tile + (p * 64 + rl) * kPitchW + (cg >> 2);
-            w[0] = q.x; w[1] = q.y; w[2] = q.z; w[3] = q.w;
+            const int wc = cg >> 2;
+            tile[tile_word(k, wc)] = q.x;
+            tile[tile_word(k, wc + 1)] = q.y;
+            tile[tile_word(k, wc + 2)] = q.z;
+            tile[tile_word(k, wc + 3)] = q.w;
         }
     }
     __syncthreads();
     if (!transposed) return;
 
-    // Each thread owns 4 source columns x 16 source rows: 16 word reads, four 4x4 byte transposes,
-    // four 16-byte stores (one per output row).
-    const int ng = tid & 15, kc = tid >> 4;
-    uint32_t o[4][4];
+    // Lane = 8 consecutive source rows (kc8), warp = two word columns (ng): 8 word reads, two 4x4 byte
+    // transposes, four 8-byte stores; the 32 lanes of one store cover one whole 256-byte output row.
+    const int kc8 = tid & 31, warp = tid >> 5;
 #pragma unroll
-    for (int blk = 0; blk < 4; ++blk) {
-        const uint32_t* w = tile + (kc * 16 + blk * 4) * kPitchW + ng;
-        const uint32_t w0 = w[0], w1 = w[kPitchW], w2 = w[2 * kPitchW], w3 = w[3 * kPitchW];
-        const uint32_t a = __byte_perm(w0, w1, 0x5140), b = __byte_perm(w2, w3, 0x5140);
-        const uint32_t c = __byte_perm(w0, w1, 0x7362), d = __byte_perm(w2, w3, 0x7362);
-        o[0][blk] = __byte_perm(a, b, 0x5410);
-        o[1][blk] = __byte_perm(a, b, 0x7632);
-        o[2][blk] = __byte_perm(c, d, 0x5410);
-        o[3][blk] = __byte_perm(c, d, 0x7632);
-    }
-    const int orow0 = c0 + ng * 4;          // output row = source column
-    const int ocol = r0 + kc * 16;          // output column = source row
+    for (int half = 0; half < 2; ++half) {
+        const int ng = warp * 2 + half;
+        uint32_t w[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int orow = orow0 + j;
-        if (orow >= Ccols || ocol >= R) continue;
-        uint8_t* dst = transposed + static_cast<size_t>(orow) * R + ocol;
-        if (trans_vec && ocol + 16 <= R) {
-            *reinterpret_cast<uint4*>(dst) = make_uint4(o[j][0], o[j][1], o[j][2], o[j][3]);
-        } else {
+        for (int r = 0; r < 8; ++r) w[r] = tile[tile_word(kc8 * 8 + r, ng)];
+        uint32_t o[4][2];
 #pragma unroll
-            for (int b = 0; b < 16; ++b)
-                if (ocol + b < R) dst[b] = static_cast<uint8_t>(o[j][b >> 2] >> (8 * (b & 3)));
+        for (int blk = 0; blk < 2; ++blk) {
+            const uint32_t w0 = w[blk * 4], w1 = w[blk * 4 + 1], w2 = w[blk * 4 + 2], w3 = w[blk * 4 + 3];
+            const uint32_t a = __byte_perm(w0, w1, 0x5140), b = __byte_perm(w2, w3, 0x5140);
+            const uint32_t c = __byte_perm(w0, w1, 0x7362), d = __byte_perm(w2, w3, 0x7362);
+            o[0][blk] = __byte_perm(a, b, 0x5410);
+            o[1][blk] = __byte_perm(a, b, 0x7632);
+            o[2][blk] = __byte_perm(c, d, 0x5410);
+            o[3][blk] = __byte_perm(c, d, 0x7632);
+        }
+        const int ocol = r0 + kc8 * 8;           // output column = source row
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int orow = c0 + ng * 4 + j;    // output row = source column
+            if (orow >= Ccols || ocol >= R) continue;
+            uint8_t* dst = transposed + static_cast<size_t>(orow) * R + ocol;
+            if (trans_vec && ocol + 8 <= R) {
+                *reinterpret_cast<uint2*>(dst) = make_uint2(o[j][0], o[j][1]);
+            } else {
+#pragma unroll
+                for (int b = 0; b < 8; ++b)
+                    if (ocol + b < R) dst[b] = static_cast<uint8_t>(o[j][b >> 2] >> (8 * (b & 3)));
+            }
         }
     }
 }
@@ -447,11 +477,10 @@ int launch_tile_transpose(const void* src, void* direct, void* transposed, const
     const int esz = SRC_BF16 ? 2 : 1;
     const int src_vec = (sa % 16 == 0) && ((static_cast<size_t>(Ccols) * esz) % 16 == 0);
     const int direct_vec = direct && (da % 8 == 0) && (Ccols % 8 == 0);
-    const int trans_vec = transposed && (ta % 16 == 0) && (R % 16 == 0);
+    const int trans_vec = transposed && (ta % 8 == 0) && (R % 8 == 0);
     dim3 grid((Ccols + kTC - 1) / kTC, (R + kTR - 1) / kTR);
-    k_tile_transpose<SRC_BF16><<<grid, kThreads, 0, st>>>(src, static_cast<uint8_t*>(direct),
-                                                          static_cast<uint8_t*>(transposed), scale, R, Ccols, src_vec,
-                                                          direct_vec, trans_vec, sfa);
+    CF_CUDA(launch_pdl(k_tile_transpose<SRC_BF16>, grid, dim3(kThreads), 0, st, src, static_cast<uint8_t*>(direct),
+                       static_cast<uint8_t*>(transposed), scale, R, Ccols, src_vec, direct_vec, trans_vec, sfa));
     CF_LAUNCH_CHECK(name);
     return CF_OK;
 }
@@ -460,7 +489,7 @@ int launch_tile_transpose(const void* src, void* direct, void* transposed, const
 
 int slot_begin(const float* scale, const float* descale, float* snap_scale, float* snap_descale, float* amax,
                cudaStream_t st) {
-    k_slot_begin<<<1, 1, 0, st>>>(scale, descale, snap_scale, snap_descale, amax);
+    CF_CUDA(launch_pdl(k_slot_begin, dim3(1), dim3(1), 0, st, scale, descale, snap_scale, snap_descale, amax));
     CF_LAUNCH_CHECK("slot_begin");
     return CF_OK;
 }

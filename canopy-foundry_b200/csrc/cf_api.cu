@@ -347,16 +347,20 @@ int cf_fp8_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, size_t n, 
     }
 
     // steady state: snapshot, record-quantise with the previous scale, advance the ring
-    CF_TRY(slot_begin(slot->scale, slot->descale, slot->scale_snapshot, slot->descale_snapshot, slot->amax, st));
     if (slot->ticket) {
-        // two launches in all: the last block of the record pass runs the ring update
+        // ONE launch: block 0 snapshots the pair, every block accumulates its amax into the work word next to
+        // the ticket, the last block publishes the amax and runs the ring update (src/trainer.cu:4823-4850 takes
+        // two scalar copies, a memset and two kernels for the same effect)
         RingTail tail;
         tail.fp8_max = slot->fp8_max; tail.scale = slot->scale; tail.descale = slot->descale;
         tail.history = slot->history; tail.history_len = kHistoryLen;
         tail.history_cursor = slot->history_cursor; tail.history_count = slot->history_count;
         tail.ticket = slot->ticket;
+        tail.work_amax = reinterpret_cast<float*>(slot->ticket + 1);
+        tail.snap_scale = slot->scale_snapshot; tail.snap_descale = slot->descale_snapshot;
         return quantize_record_fused(d_x, d_out8, slot->scale, slot->amax, n, slot->fp8_max == CF_E5M2_MAX, tail, st);
     }
+    CF_TRY(slot_begin(slot->scale, slot->descale, slot->scale_snapshot, slot->descale_snapshot, slot->amax, st));
     if (slot->fp8_max == CF_E5M2_MAX)
         CF_TRY(cf_fp8_quantize_e5m2_record(d_x, d_out8, slot->scale, slot->amax, n, stream));
     else

@@ -15,6 +15,11 @@ struct RingTail {
     int* history_cursor = nullptr;
     int* history_count = nullptr;
     unsigned* ticket = nullptr;      // zero-initialised device word owned by the slot
+    // single-launch form (all three set): amax accumulates in *work_amax (zero between calls), the kernel
+    // snapshots the pair it quantises with, and the tail publishes the amax
+    float* work_amax = nullptr;
+    float* snap_scale = nullptr;
+    float* snap_descale = nullptr;
 };
 
 // Scale derived inside the quantise kernel from a device amax (amax != nullptr enables it).

@@ -45,7 +45,15 @@ __device__ __forceinline__ void fused_tail(const RingTail& t, float* amax) {
         const unsigned prev = atomicAdd(t.ticket, 1u);
         if (prev == gridDim.x - 1) {
             __threadfence();
-            const float a = __int_as_float(atomicMax(reinterpret_cast<int*>(amax), 0));   // coherent read
+            float a;
+            if (t.work_amax) {
+                // single-launch form: the blocks accumulated into the slot's work word; publish it as the call's
+                // amax and leave the work word zero for the next call
+                a = __int_as_float(atomicExch(reinterpret_cast<int*>(t.work_amax), 0));
+                *amax = a;
+            } else {
+                a = __int_as_float(atomicMax(reinterpret_cast<int*>(amax), 0));   // coherent read
+            }
             ring_update(a, t.fp8_max, t.scale, t.descale, t.history, t.history_len, t.history_cursor, t.history_count);
             *t.ticket = 0;                                  // ready for the next call
         }
@@ -88,6 +96,12 @@ __global__ void __launch_bounds__(kThreads) k_stream(const uint16_t* __restrict_
                                                      size_t n, size_t head, size_t nvec, const RingTail tail) {
     pdl_wait();
     const float s = QUANT ? *scale : 0.0f;
+    if (RECORD && tail.snap_scale && blockIdx.x == 0 && threadIdx.x == 0) {
+        // single-launch form: the pair this call quantises with is snapshotted here (nobody reads the snapshot
+        // words during this kernel; the live pair is rewritten only by the last block's tail)
+        *tail.snap_scale = s;
+        *tail.snap_descale = *tail.descale;
+    }
     float local = 0.0f;
     const uint16_t* xv = x + head;
     uint8_t* ov = out + head;
@@ -132,7 +146,7 @@ __global__ void __launch_bounds__(kThreads) k_stream(const uint16_t* __restrict_
         }
     }
     if (RECORD) {
-        block_amax_commit(local, amax);
+        block_amax_commit(local, tail.work_amax ? tail.work_amax : amax);
         fused_tail(tail, amax);
     }
 }
@@ -144,6 +158,10 @@ __global__ void __launch_bounds__(kThreads) k_stream_scalar(const uint16_t* __re
                                                             float* __restrict__ amax, size_t n, const RingTail tail) {
     pdl_wait();
     const float s = QUANT ? *scale : 0.0f;
+    if (RECORD && tail.snap_scale && blockIdx.x == 0 && threadIdx.x == 0) {
+        *tail.snap_scale = s;
+        *tail.snap_descale = *tail.descale;
+    }
     float local = 0.0f;
     for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n;
          i += static_cast<size_t>(gridDim.x) * kThreads) {
@@ -152,12 +170,17 @@ __global__ void __launch_bounds__(kThreads) k_stream_scalar(const uint16_t* __re
         if (QUANT) out[i] = cvt_fp8<E5M2>(v * s);
     }
     if (RECORD) {
-        block_amax_commit(local, amax);
+        block_amax_commit(local, tail.work_amax ? tail.work_amax : amax);
         fused_tail(tail, amax);
     }
 }
 
-__global__ void k_ring_update_only(const float* amax, const RingTail t) {
+__global__ void k_ring_update_only(float* amax, const RingTail t) {
+    if (t.snap_scale) {                 // empty tensor in the single-launch form: snapshot, amax = 0, ring update
+        *t.snap_scale = *t.scale;
+        *t.snap_descale = *t.descale;
+        *amax = 0.0f;
+    }
     ring_update(*amax, t.fp8_max, t.scale, t.descale, t.history, t.history_len, t.history_cursor, t.history_count);
 }
 

@@ -183,8 +183,9 @@ typedef struct cf_act_slot {
     int calib_commit_pending;
     float* calib_min;
     float* calib_max;
-    unsigned* ticket;        /* optional zero-initialised device word (not in the reference's ActSlot): when set,
-                                steady-state calls fuse the ring update into the record pass; NULL = separate launch */
+    unsigned* ticket;        /* optional pair of zero-initialised device words, 8 bytes (not in the reference's ActSlot):
+                                when set, a steady-state cf_fp8_quant_act is ONE launch (snapshot, record-quantise and
+                                ring update fused); NULL = the reference's sequence of small launches */
 } cf_act_slot;
 
 int cf_act_slot_init(cf_ctx* ctx, cf_act_slot* slot, float fp8_max, int calib_calls, void* stream);

@@ -22,7 +22,7 @@ cf = C.c_float
 
 
 class GemmEpilogue(C.Structure):
-    _fields_ = [("d_bias", vp), ("bias_mode", ci), ("d_a_row_descale", fp), ("d_b_col_descale", fp)]
+    _fields_ = [("d_bias", vp), ("bias_mode", ci), ("d_a_row_descale", fp), ("d_b_col_descale", fp), ("out_fp32", ci)]
 
 
 class ActSlotStruct(C.Structure):

@@ -86,7 +86,7 @@ using namespace cf;
 extern "C" {
 
 const char* cf_last_error(void) { return t_error; }
-int cf_abi_version(void) { return 1; }
+int cf_abi_version(void) { return 2; }
 uint64_t cf_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int cf_ctx_create(cf_ctx** out, size_t act8_bytes) {
@@ -181,6 +181,10 @@ int cf_gemm_fp8_nt(cf_ctx* ctx, int M, int N, int K, const void* d_A, int lda, i
         p.bias_mode = epi->d_bias ? epi->bias_mode : 0;
         p.d_a_row_descale = epi->d_a_row_descale;
         p.d_b_col_descale = epi->d_b_col_descale;
+        if (epi->out_fp32) {
+            CF_REQUIRE(epi->d_bias == nullptr, "cf_gemm_fp8_nt: out_fp32 takes no bias");
+            p.out_kind = 1;
+        }
     }
     p.d_status = reinterpret_cast<Ctx*>(ctx)->d_status;
     if (K == 0) {   // empty contraction: the product is zero, the epilogue still applies

@@ -228,19 +228,21 @@ def fp8_swiglu_quant_act(ctx, slot, gate, up, ld_in, rows, cols, out8):
 
 
 # ---------------------------------------------------------------- GEMMs
-def _epi(bias, bias_mode, a_row_descale, b_col_descale):
-    if bias is None and a_row_descale is None and b_col_descale is None:
+def _epi(bias, bias_mode, a_row_descale, b_col_descale, out_fp32=False):
+    if bias is None and a_row_descale is None and b_col_descale is None and not out_fp32:
         return None
     return C.byref(_capi.GemmEpilogue(bias.data_ptr() if bias is not None else None, bias_mode,
                                       a_row_descale.data_ptr() if a_row_descale is not None else None,
-                                      b_col_descale.data_ptr() if b_col_descale is not None else None))
+                                      b_col_descale.data_ptr() if b_col_descale is not None else None, int(out_fp32)))
 
 
 def lt_gemm_fp8_nt(ctx, M, N, K, A, lda, a_is_e5m2, a_descale, B, b_descale, Cout, ldc, bias=None, bias_mode=0,
                    a_row_descale=None, b_col_descale=None):
-    """C[M,N] bf16 = (dA*dB) * A8[M,K] . B8[N,K]^T  (src/trainer.cu:4498-4534)."""
+    """C[M,N] = (dA*dB) * A8[M,K] . B8[N,K]^T  (src/trainer.cu:4498-4534). C is bf16 like the reference's output;
+    a float32 C selects the fp32 partial-product form used by row-parallel (K-sharded) GEMMs."""
+    out_fp32 = Cout.dtype == torch.float32
     check(_L().cf_gemm_fp8_nt(ctx.handle, M, N, K, _p(A), lda, int(a_is_e5m2), _p(a_descale), _p(B), _p(b_descale),
-                              _p(Cout), ldc, _epi(bias, bias_mode, a_row_descale, b_col_descale), _s()))
+                              _p(Cout), ldc, _epi(bias, bias_mode, a_row_descale, b_col_descale, out_fp32), _s()))
 
 
 def lt_gemm_fp8_tn_accum_f32(ctx, M, N, K, Xt, ds_x, dYt, ds_dy, dW, ldc):

@@ -147,6 +147,20 @@ class ShardedFp8Weight:
         return self.fw
 
 
+def row_parallel_gemm_fp8(cfb, ctx, M, N, K_local, a8_local, a_descale, w8_local, w_descale, out_bf16, group=None,
+                          a_row_descale=None, b_col_descale=None, partial=None):
+    """K-sharded (row-parallel) NT GEMM: every rank multiplies its K slice — A8[:, k_lo:k_hi] against W8[:, k_lo:k_hi] —
+    into an fp32 partial product, the partials are summed by an all-reduce and rounded to bf16 once. With per-tensor
+    scales the result differs from the single-GPU GEMM only by the fp32 summation order."""
+    if partial is None:
+        partial = torch.empty((M, N), dtype=torch.float32, device=out_bf16.device)
+    cfb.lt_gemm_fp8_nt(ctx, M, N, K_local, a8_local, a8_local.stride(0), False, a_descale, w8_local, w_descale, partial, N,
+                       a_row_descale=a_row_descale, b_col_descale=b_col_descale)
+    allreduce_sum_(partial, group)
+    out_bf16.copy_(partial)
+    return out_bf16
+
+
 class EpMoeSwigluFp8:
     """Expert-parallel form of ops.MoeSwigluFp8: tokens are data-parallel (this rank holds `rows` of them), experts
     are sharded over the ranks. Per layer: route locally -> counts all-gather -> E4M3 rows all-to-all -> ragged

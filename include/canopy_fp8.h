@@ -126,6 +126,9 @@ typedef struct cf_gemm_epilogue {
                                       as kernels/moe.cu:325-336 does after the GEMM */
     const float* d_a_row_descale; /* NULL, or float[M]: per-row (per-token) scales replace *d_a_descale */
     const float* d_b_col_descale; /* NULL, or float[N]: per-output-channel scales replace *d_b_descale */
+    int out_fp32;                /* 0: C is bf16 (the reference's output type); 1: C is float[M, ldc] and no bias is
+                                    applied — the partial product of a K-sharded (row-parallel) GEMM, to be summed
+                                    across ranks in fp32 */
 } cf_gemm_epilogue;
 
 /* src/trainer.cu:4498-4534 (file-static lt_gemm_fp8_nt, the cuBLASLt call).

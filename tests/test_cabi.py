@@ -16,13 +16,13 @@ def test_library_exports_every_declared_symbol():
     for name in sorted(declared):
         assert hasattr(lib, name), f"{name} is declared in include/canopy_fp8.h but not exported"
     assert declared == set(cfb._capi.SIGNATURES), "ctypes table and header disagree"
-    assert lib.cf_abi_version() == 1
+    assert lib.cf_abi_version() == 2
 
 
 def test_struct_layouts_match_the_header():
     cfb = package()
     # pointer-sized and 4-byte members only; sizes follow the C layout rules on LP64
-    assert C.sizeof(cfb._capi.GemmEpilogue) == 32
+    assert C.sizeof(cfb._capi.GemmEpilogue) == 40
     assert C.sizeof(cfb._capi.ActSlotStruct) == 8 * 8 + 4 * 4 + 3 * 8
     assert C.sizeof(cfb._capi.Fp8WeightStruct) == 6 * 8 + 3 * 4 + 4
 

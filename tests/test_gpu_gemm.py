@@ -223,3 +223,23 @@ def test_gemm_argument_errors(cfb, ctx):
     with pytest.raises(cfb.CanopyError):
         cfb.lt_gemm_fp8_nt(ctx, 16, 16, 16, None, 16, False, d, a8, d, c, 16)   # null A
     cfb.lt_gemm_fp8_nt(ctx, 0, 16, 16, a8, 16, False, d, a8, d, c, 16)          # empty M is a no-op
+
+
+def test_fp32_partial_product_and_k_sharding(cfb, ctx, oracle):
+    """Row-parallel form: fp32 output of K slices, summed, equals the unsharded product (fp32 summation order only)."""
+    M, N, K = 300, 512, 2048
+    a8, da = _quant(cfb, randn_bf16((M, K), seed=61))
+    w8, dw = _quant(cfb, randn_bf16((N, K), std=0.02, seed=62))
+    full = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    cfb.lt_gemm_fp8_nt(ctx, M, N, K, a8, K, False, da, w8, dw, full, N)
+    want = _oracle_gemm(oracle, a8, w8, da, dw, out_kind=1)
+    assert rel_fro(full.cpu().numpy(), want) < 1e-5
+    acc = torch.zeros((M, N), dtype=torch.float32, device="cuda")
+    part = torch.empty_like(acc)
+    for r in range(4):
+        lo = r * (K // 4)
+        # a K slice of both operands: A as a strided view (lda = K), W as a contiguous copy of its columns
+        cfb.lt_gemm_fp8_nt(ctx, M, N, K // 4, a8.view(-1)[lo:], K, False, da, w8[:, lo:lo + K // 4].contiguous(), dw, part, N)
+        acc += part
+    assert rel_fro(acc.cpu().numpy(), full.cpu().numpy()) < 1e-5
+    ctx.poll_status()

@@ -60,6 +60,18 @@ def _worker(rank, world, port, ret):
         full = cfb.Fp8Weight(w, stored_out_major=True)
         cfb.refresh_fp8_weight(full)
         assert torch.equal(fw.fwd8, full.fwd8[lo:hi]) and fw.scale.item() == full.scale.item()
+        # ---- row-parallel (K-sharded) GEMM with the fp32 all-reduce vs the unsharded GEMM
+        Mr, Nr, Kr = 256, 384, 1024
+        a_full = randn_bf16((Mr, Kr), seed=5, device=dev)
+        w_full = randn_bf16((Nr, Kr), std=0.02, seed=6, device=dev)
+        a8f, daf = _tensorquant(cfb, a_full)
+        w8f, dwf = _tensorquant(cfb, w_full)
+        klo, khi = par.shard_range(Kr, world, rank, 128)
+        y_ref = torch.empty((Mr, Nr), dtype=torch.bfloat16, device=dev)
+        cfb.lt_gemm_fp8_nt(ctx, Mr, Nr, Kr, a8f, Kr, False, daf, w8f, dwf, y_ref, Nr)
+        y_rp = torch.empty_like(y_ref)
+        par.row_parallel_gemm_fp8(cfb, ctx, Mr, Nr, khi - klo, a8f[:, klo:khi], daf, w8f[:, klo:khi].contiguous(), dwf, y_rp)
+        assert rel_fro(y_rp.float().cpu().numpy(), y_ref.float().cpu().numpy()) < 3e-3
         # ---- expert-parallel MoE vs the single-GPU layer on all tokens
         rows, H, F, E, k = 256, 128, 256, 4, 2
         gw = torch.Generator(device=dev).manual_seed(11)

@@ -264,7 +264,6 @@ __global__ void __launch_bounds__(kT) k_gelu_split(const uint16_t* __restrict__ 
         lo[i] = cvt_fp8<false>(g - fp8_to_f32<false>(c));
     }
 }
-__global__ void k_mul_scalars(const float* a, const float* b, float* out) { *out = *a * *b; }
 
 }  // namespace
 }  // namespace cf

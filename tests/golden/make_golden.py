@@ -1,9 +1,8 @@
 """Regenerates the committed golden fixtures from the reference tree.
 
-Run in a container that has the reference checked out (default /root/reference)
-and oracle/_ref built (make -C oracle):
+Run where the reference tree is checked out and oracle/_ref has been built (make -C oracle):
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 Outputs (all small, committed):
   e4m3_codec_all_bf16.npz   the reference's fp8_e4m3::pack and NVIDIA's host
@@ -27,7 +26,7 @@ from oracle_bindings import RefHost  # noqa: E402
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("CANOPY_REFERENCE", "/root/reference")
     r = RefHost()
     allbf = (np.arange(65536, dtype=np.uint32) << 16).view(np.float32)
     unpack = np.array([r.lib.ref_e4m3_unpack(b) for b in range(256)], dtype=np.float32)

@@ -44,7 +44,7 @@ def test_shim_compiles_against_the_reference_headers(tmp_path):
     import subprocess
 
     import pytest
-    ref = "/root/reference"
+    ref = os.environ.get("CANOPY_REFERENCE", "/root/reference")
     if not os.path.isdir(os.path.join(ref, "include", "ida_native")) or shutil.which("nvcc") is None:
         pytest.skip("reference tree or nvcc not present")
     src = os.path.join(ROOT, "canopy-foundry_b200", "shim", "ida_native_kernels.cu")

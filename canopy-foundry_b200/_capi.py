@@ -63,6 +63,7 @@ SIGNATURES = {
     "cf_ctx_act8": (vp, [vp]),
     "cf_ctx_poll_status": (ci, [vp, vp]),
     "cf_ctx_reserve_workspace": (ci, [vp, sz]),
+    "cf_ctx_selftest_bounded_wait": (ci, [vp, ci, vp]),
     "cf_gemm_fp8_nt": (ci, [vp, ci, ci, ci, vp, ci, ci, fp, vp, fp, vp, ci, C.POINTER(GemmEpilogue), vp]),
     "cf_gemm_fp8_tn_accum_f32": (ci, [vp, ci, ci, ci, vp, fp, vp, fp, vp, ci, vp]),
     "cf_gemm_fp8_tn_accum_bf16": (ci, [vp, ci, ci, ci, vp, fp, vp, fp, vp, ci, vp]),

@@ -153,6 +153,13 @@ int cf_ctx_poll_status(cf_ctx* ctx, void* stream) {
     return CF_OK;
 }
 
+int cf_ctx_selftest_bounded_wait(cf_ctx* ctx, int limit_ms, void* stream) {
+    CF_REQUIRE(ctx != nullptr, "cf_ctx_selftest_bounded_wait: null context");
+    CF_REQUIRE(limit_ms >= 1 && limit_ms <= 1000, "cf_ctx_selftest_bounded_wait: limit must be 1..1000 ms");
+    return launch_wait_selftest(reinterpret_cast<Ctx*>(ctx)->d_status, static_cast<unsigned long long>(limit_ms) * 1000000ull,
+                                as_stream(stream));
+}
+
 // ------------------------------------------------------------------ GEMM entry points
 static int check_gemm_common(const char* fn, cf_ctx* ctx, int M, int N, int K, const void* A, const void* B,
                              const void* C, const float* da, const float* db) {

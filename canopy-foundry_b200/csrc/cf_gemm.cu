@@ -615,6 +615,25 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     }
 }
 
+// ------------------------------------------------------------------ bounded-wait self-test
+// Exercises the failure path of the waits above without any fault: one CTA arms nothing and waits on an
+// mbarrier that nobody signals; the wait gives up after `limit_ns`, the kernel records the same status code a
+// starved producer would and returns normally. The host then sees CF_ERR_DEVICE_WAIT from cf_ctx_poll_status.
+__global__ void k_wait_selftest(int* d_status, unsigned long long limit_ns) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int s_abort[2];
+    if (threadIdx.x == 0) {
+        s_abort[0] = s_abort[1] = 0;
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (!mbar_wait(smem_u32(&bar), 0, s_abort, limit_ns)) atomicExch(d_status, 0x400 | 1);
+    }
+    __syncthreads();
+}
+
 // ------------------------------------------------------------------ SIMT form
 // Serves shapes the TMA path cannot address (K or lda not a multiple of 16, operands not 16-byte
 // aligned) with identical epilogue semantics. One thread per output element; correctness path only.
@@ -801,6 +820,14 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     const int grid = tile_upper_bound < sms ? tile_upper_bound : sms;
     CF_CUDA(launch_pdl(k_gemm_fp8_nt<false>, dim3(grid), dim3(NUM_THREADS), Cfg<false>::SMEM_BYTES, st, map_a, map_b, map_c, p));
     CF_LAUNCH_CHECK("gemm_fp8_nt");
+    return CF_OK;
+}
+
+int launch_wait_selftest(int* d_status, unsigned long long limit_ns, cudaStream_t st) {
+    const int rc = require_sm100();
+    if (rc != CF_OK) return rc;
+    k_wait_selftest<<<1, 32, 0, st>>>(d_status, limit_ns);
+    CF_LAUNCH_CHECK("wait_selftest");
     return CF_OK;
 }
 

@@ -37,6 +37,7 @@ struct GemmParams {
 // tile_upper_bound: number of (128 x 256) tiles at most (sizes the persistent grid).
 int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const void* d_B, long long b_rows,
                        GemmParams p, int tile_upper_bound, cudaStream_t st);
+int launch_wait_selftest(int* d_status, unsigned long long limit_ns, cudaStream_t st);
 int gemm_tile_m();
 int gemm_tile_n();
 

@@ -151,6 +151,10 @@ class Fp8Ctx:
         """Synchronises the current stream; raises CanopyError(CF_ERR_DEVICE_WAIT) if a kernel gave up a wait."""
         check(_L().cf_ctx_poll_status(self.handle, _s()))
 
+    def selftest_bounded_wait(self, limit_ms=5):
+        """Launches the wait that is designed to run out; the following poll_status() raises CF_ERR_DEVICE_WAIT."""
+        check(_L().cf_ctx_selftest_bounded_wait(self.handle, limit_ms, _s()))
+
     def close(self):
         if self.handle:
             _L().cf_ctx_destroy(self.handle)

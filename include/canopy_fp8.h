@@ -113,6 +113,11 @@ void* cf_ctx_act8(cf_ctx* ctx);
 /* Synchronises `stream`, then returns CF_OK or CF_ERR_DEVICE_WAIT if any kernel launched through this
  * context since the last poll abandoned a bounded wait (its output is then invalid). Clears the word. */
 int cf_ctx_poll_status(cf_ctx* ctx, void* stream);
+/* Failure-detection self-test (no counterpart in the reference): launches one small kernel whose only wait is on a
+ * barrier nothing ever signals; the wait gives up after limit_ms (1..1000), the kernel records a status code and
+ * returns normally, and the next cf_ctx_poll_status reports CF_ERR_DEVICE_WAIT. Nothing faults or hangs; the context
+ * stays usable. It checks the path a starved tensor-core pipeline would take. */
+int cf_ctx_selftest_bounded_wait(cf_ctx* ctx, int limit_ms, void* stream);
 /* Number of kernels this library launched through any entry point since load (process-wide counter). */
 uint64_t cf_launch_count(void);
 

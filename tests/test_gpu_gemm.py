@@ -243,3 +243,22 @@ def test_fp32_partial_product_and_k_sharding(cfb, ctx, oracle):
         acc += part
     assert rel_fro(acc.cpu().numpy(), full.cpu().numpy()) < 1e-5
     ctx.poll_status()
+
+
+def test_bounded_wait_reports_a_status_and_leaves_the_context_usable(cfb, ctx, oracle):
+    """Failure detection without a fault: a wait that nothing satisfies gives up after its limit, the kernel returns,
+    the host reads CF_ERR_DEVICE_WAIT once, and the next GEMM through the same context is correct."""
+    ctx.poll_status()
+    ctx.selftest_bounded_wait(limit_ms=5)
+    with pytest.raises(cfb.CanopyError) as ei:
+        ctx.poll_status()
+    assert ei.value.code == cfb._capi.CF_ERR_DEVICE_WAIT
+    ctx.poll_status()                                   # the word was cleared by the failing poll
+    M, N, K = 256, 256, 256
+    a8, da = _quant(cfb, randn_bf16((M, K), seed=71))
+    w8, dw = _quant(cfb, randn_bf16((N, K), std=0.02, seed=72))
+    c = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    cfb.lt_gemm_fp8_nt(ctx, M, N, K, a8, K, False, da, w8, dw, c, N)
+    ctx.poll_status()
+    want = _oracle_gemm(oracle, a8, w8, da, dw)
+    assert rel_fro(oracle.bf16_to_f32(bf16_to_u16(c)), oracle.bf16_to_f32(want)) < TIGHT

@@ -232,7 +232,7 @@ def run_moe(args):
     wgu8, dgu = quant_experts((n_local, 2 * F, H), 0.02, 50 + rank)
     wd8, dd = quant_experts((n_local, H, F), 0.02, 70 + rank)
     mixed = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
-    layer = par.EpMoeSwigluFp8(cfb, ctx, rows, H, F, E, TOPK, device=dev) if use_ep else \
+    layer = par.EpMoeSwigluFp8(cfb, ctx, rows, H, F, E, TOPK, device=dev, fused_return=args.moe_fused_return) if use_ep else \
         cfb.MoeSwigluFp8(ctx, rows, H, F, E, TOPK, device=dev)
 
     def step():
@@ -275,7 +275,7 @@ def run_moe(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
             "config": {"workload": "moe_swiglu_fp8_32768tok_H4096_E8_F14336_top2_zipf1.1 (BASELINE config 4)",
-                       "parallelism": (f"ep{world} (all-to-all, experts placed by load)" if use_ep else
+                       "parallelism": (f"ep{world} (all-to-all, experts placed by load{', GEMM-fused return leg' if args.moe_fused_return else ''})" if use_ep else
                                        f"dp{world} (experts replicated, tokens sharded, no collective)") if world > 1 else "single GPU",
                        "max_rows_on_one_rank": int(lmax.item()), "mean_rows_per_rank": TOK * TOPK / world,
                        "l2": "inputs larger than L2 (1.4 GB of expert weights per step)"},
@@ -295,6 +295,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--bias-mode", type=int, default=2, help="2 = reference rounding order, 1 = single rounding")
+    ap.add_argument("--moe-fused-return", action="store_true",
+                    help="ep mode: the down GEMM stores its rows straight into the owners' buffers over NVLink (no return all-to-all)")
     ap.add_argument("--moe-mode", default="ep", choices=["ep", "dp"],
                     help="N > 1: ep = expert parallel with all-to-all (experts placed by load), dp = experts replicated, tokens sharded")
     ap.add_argument("--workload", default="linear", choices=["linear", "moe"],

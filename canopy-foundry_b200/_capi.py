@@ -69,6 +69,7 @@ SIGNATURES = {
     "cf_gemm_fp8_tn_accum_bf16": (ci, [vp, ci, ci, ci, vp, fp, vp, fp, vp, ci, vp]),
     "cf_gemm_fp8_nt_grouped": (ci, [vp, ci, ci, ci, ci, ip, ip, vp, ci, ci, fp, ci, vp, fp, vp, ci, vp]),
     "cf_gemm_fp8_nt_segments": (ci, [vp, ci, ci, ip, ci, ci, ci, ip, ip, vp, ci, ci, fp, ci, vp, fp, vp, ci, vp]),
+    "cf_gemm_fp8_nt_segments_scatter": (ci, [vp, ci, ci, ip, ci, ci, ci, ip, ip, vp, ci, ci, fp, ci, vp, fp, vp, vp, vp, ci, vp]),
     "cf_act_slot_init": (ci, [vp, C.POINTER(ActSlotStruct), cf, ci, vp]),
     "cf_fp8_quant_act": (ci, [vp, C.POINTER(ActSlotStruct), vp, sz, vp, vp, ci]),
     "cf_fp8_swiglu_quant_act": (ci, [vp, C.POINTER(ActSlotStruct), vp, vp, ci, ci, ci, vp, vp]),

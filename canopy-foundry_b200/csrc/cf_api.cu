@@ -238,6 +238,20 @@ int cf_gemm_fp8_nt_segments(cf_ctx* ctx, int num_segments, int num_weights, cons
                             int max_total_rows, int N, int K, const int* d_counts, const int* d_offsets, const void* d_A,
                             int lda, int a_is_e5m2, const float* d_a_descale, int per_segment_a_descale, const void* d_B,
                             const float* d_b_descale, void* d_C, int ldc, void* stream) {
+    return cf_gemm_fp8_nt_segments_scatter(ctx, num_segments, num_weights, d_segment_weight, max_total_rows, N, K, d_counts,
+                                           d_offsets, d_A, lda, a_is_e5m2, d_a_descale, per_segment_a_descale, d_B,
+                                           d_b_descale, d_C, nullptr, nullptr, ldc, stream);
+}
+
+int cf_gemm_fp8_nt_segments_scatter(cf_ctx* ctx, int num_segments, int num_weights, const int* d_segment_weight,
+                                    int max_total_rows, int N, int K, const int* d_counts, const int* d_offsets,
+                                    const void* d_A, int lda, int a_is_e5m2, const float* d_a_descale,
+                                    int per_segment_a_descale, const void* d_B, const float* d_b_descale, void* d_C,
+                                    void* const* d_segment_out, const long long* d_segment_out_row0, int ldc,
+                                    void* stream) {
+    CF_REQUIRE((d_segment_out == nullptr) == (d_segment_out_row0 == nullptr),
+               "cf_gemm_fp8_nt_segments_scatter: d_segment_out and d_segment_out_row0 go together");
+    if (d_segment_out && d_C == nullptr) d_C = const_cast<void*>(static_cast<const void*>(d_segment_out));   // unused placeholder
     const int num_experts = num_segments;
     const int per_expert_a_descale = per_segment_a_descale;
     CF_REQUIRE(num_weights >= 1, "cf_gemm_fp8_nt_segments: num_weights must be positive");
@@ -253,6 +267,8 @@ int cf_gemm_fp8_nt_segments(cf_ctx* ctx, int num_segments, int num_weights, cons
     p.N = N; p.K = K;
     p.d_counts = d_counts; p.d_offsets = d_offsets;
     p.d_group_weight = d_segment_weight;
+    p.d_group_out = d_segment_out;
+    p.d_group_out_row0 = d_segment_out_row0;
     p.d_a_descale = d_a_descale; p.a_descale_per_group = per_expert_a_descale ? 1 : 0;
     p.d_b_descale = d_b_descale;
     p.C = d_C; p.ldc = ldc; p.out_kind = 0;

@@ -210,6 +210,8 @@ struct TileCoord {
     int n0;          // first output column
     int b_row0;      // first row of the stacked [E*N, K] weight block
     int group;
+    void* out_base;  // where this tile's rows are written (p.C, or a per-segment buffer that may live on a peer GPU)
+    long long out_row0;  // output row of the tile's first row inside out_base
 };
 
 // Maps a linear tile index to coordinates. Dense: one group of p.M rows. Grouped: the m-blocks of
@@ -239,6 +241,8 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, i
         c.row0 = mb * TM;
         c.valid_rows = min(TM, p.M - c.row0);
         c.b_row0 = c.n0;
+        c.out_base = p.C;
+        c.out_row0 = c.row0;
         return c;
     }
     int e = 0, cnt = 0;
@@ -252,6 +256,13 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, i
     c.row0 = p.d_offsets[e] + mb * TM;
     c.valid_rows = min(TM, cnt - mb * TM);
     c.b_row0 = (p.d_group_weight ? p.d_group_weight[e] : e) * p.N + c.n0;
+    if (p.d_group_out) {
+        c.out_base = p.d_group_out[e];
+        c.out_row0 = p.d_group_out_row0[e] + static_cast<long long>(mb) * TM;
+    } else {
+        c.out_base = p.C;
+        c.out_row0 = c.row0;
+    }
     return c;
 }
 
@@ -263,21 +274,21 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 __device__ __forceinline__ uint16_t to_bf16_bits(float v) { return __bfloat16_as_ushort(__float2bfloat16_rn(v)); }
 
 // One output value through the epilogue contract (used by the scalar store paths and by the SIMT kernel).
-__device__ __forceinline__ void store_one(const GemmParams& p, long long grow, int col, float acc, float da, float db) {
+__device__ __forceinline__ void store_one(const GemmParams& p, void* cbase, long long grow, int col, float acc, float da, float db) {
     float v = acc * (da * db);
     if (p.out_kind == 0) {
-        uint16_t* c = static_cast<uint16_t*>(p.C) + grow * p.ldc + col;
+        uint16_t* c = static_cast<uint16_t*>(cbase) + grow * p.ldc + col;
         if (p.bias && p.bias_mode == 1) v += bf16_bits_to_f32(p.bias[col]);
         uint16_t r = to_bf16_bits(v);
         if (p.bias && p.bias_mode == 2) r = to_bf16_bits(bf16_bits_to_f32(r) + bf16_bits_to_f32(p.bias[col]));
         *c = r;
     } else if (p.out_kind == 1) {
-        static_cast<float*>(p.C)[grow * p.ldc + col] = v;
+        static_cast<float*>(cbase)[grow * p.ldc + col] = v;
     } else if (p.out_kind == 2) {
-        float* c = static_cast<float*>(p.C) + grow * p.ldc + col;
+        float* c = static_cast<float*>(cbase) + grow * p.ldc + col;
         *c = *c + v;
     } else {
-        uint16_t* c = static_cast<uint16_t*>(p.C) + grow * p.ldc + col;
+        uint16_t* c = static_cast<uint16_t*>(cbase) + grow * p.ldc + col;
         *c = to_bf16_bits(bf16_bits_to_f32(*c) + v);
     }
 }
@@ -440,11 +451,11 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             if (!mbar_wait(tfull_bar + 8 * acc, (local_tile >> 1) & 1, s_abort)) { ok = false; break; }
             tcgen05_fence_after();
             const int row_in_tile = static_cast<int>(cta_rank) * BM + trow;
-            const long long grow = static_cast<long long>(tc.row0) + row_in_tile;
+            const long long grow = tc.out_row0 + row_in_tile;             // output row
             const bool row_ok = row_in_tile < tc.valid_rows;
             float da = 1.0f;
             if (row_ok) {
-                if (p.d_a_row_descale) da = p.d_a_row_descale[grow];
+                if (p.d_a_row_descale) da = p.d_a_row_descale[static_cast<long long>(tc.row0) + row_in_tile];
                 else da = p.d_a_descale[p.a_descale_per_group ? tc.group : 0];
             }
             const float db_t = p.d_b_col_descale ? 1.0f : *p.d_b_descale;
@@ -535,7 +546,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                         const int col = col0 + j;
                         if (col < p.N) {
                             const float db = p.d_b_col_descale ? p.d_b_col_descale[col] : db_t;
-                            store_one(p, grow, col, __uint_as_float(v[j]), da, db);
+                            store_one(p, tc.out_base, grow, col, __uint_as_float(v[j]), da, db);
                         }
                     }
                 }
@@ -556,7 +567,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     #endif
                     const bool full = col0 + 32 <= p.N;
                     if (p.out_kind == 0 && p.c_vec && full) {
-                        uint16_t* crow = static_cast<uint16_t*>(p.C) + grow * p.ldc + col0;
+                        uint16_t* crow = static_cast<uint16_t*>(tc.out_base) + grow * p.ldc + col0;
                         uint32_t w[16];
     #pragma unroll
                         for (int j = 0; j < 16; ++j) {
@@ -588,7 +599,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                             const int col = col0 + j;
                             if (col < p.N) {
                                 const float db = p.d_b_col_descale ? p.d_b_col_descale[col] : db_t;
-                                store_one(p, grow, col, __uint_as_float(v[j]), da, db);
+                                store_one(p, tc.out_base, grow, col, __uint_as_float(v[j]), da, db);
                             }
                         }
                     }
@@ -659,7 +670,8 @@ __global__ void __launch_bounds__(256) k_gemm_fp8_nt_simt(const uint8_t* __restr
             const long long grow = row_base + m;
             const float da = p.d_a_row_descale ? p.d_a_row_descale[grow] : p.d_a_descale[p.a_descale_per_group ? g : 0];
             const float db = p.d_b_col_descale ? p.d_b_col_descale[n] : *p.d_b_descale;
-            store_one(p, grow, n, acc, da, db);
+            if (p.d_group_out) store_one(p, p.d_group_out[g], p.d_group_out_row0[g] + m, n, acc, da, db);
+            else store_one(p, p.C, grow, n, acc, da, db);
         }
     }
 }
@@ -748,7 +760,8 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     const uintptr_t aa = reinterpret_cast<uintptr_t>(d_A), ba = reinterpret_cast<uintptr_t>(d_B);
     const bool tma_ok = (aa % 16 == 0) && (ba % 16 == 0) && (lda % 16 == 0) && (p.K % 16 == 0);
     const uintptr_t ca = reinterpret_cast<uintptr_t>(p.C);
-    p.c_vec = (p.out_kind == 0) && (ca % 16 == 0) && (p.ldc % 8 == 0) &&
+    // per-segment output buffers: the caller guarantees 16-byte aligned bases (checked at the API boundary)
+    p.c_vec = (p.out_kind == 0) && (p.d_group_out != nullptr || ca % 16 == 0) && (p.ldc % 8 == 0) &&
               (p.bias == nullptr || reinterpret_cast<uintptr_t>(p.bias) % 4 == 0);
     if (!p.bias) p.bias_mode = 0;
 #ifdef CF_GEMM_EXPERIMENT
@@ -775,7 +788,7 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     r = make_map(&map_b, d_B, b_rows, p.K, p.K, pair ? Cfg<true>::B_ROWS : Cfg<false>::B_ROWS);
     if (r != CF_OK) return r;
     p.c_rows = p.d_counts ? a_rows : p.M;
-    p.tma_store = (p.c_vec && p.N >= C_BOX_COLS &&
+    p.tma_store = (p.c_vec && p.d_group_out == nullptr && p.N >= C_BOX_COLS &&
                    (p.bias == nullptr || reinterpret_cast<uintptr_t>(p.bias) % 16 == 0) &&
                    (p.d_b_col_descale == nullptr || reinterpret_cast<uintptr_t>(p.d_b_col_descale) % 16 == 0)) ? 1 : 0;
     static const bool no_tma_store = [] { const char* e = std::getenv("CF_GEMM_DIRECT_STORE"); return e && e[0] == '1'; }();

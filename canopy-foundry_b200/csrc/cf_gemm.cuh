@@ -13,6 +13,8 @@ struct GemmParams {
     const int* d_counts = nullptr;  // grouped: rows per expert (device)
     const int* d_offsets = nullptr; // grouped: first compact row per expert (device)
     const int* d_group_weight = nullptr; // grouped: weight-block index per group (device); null = group index
+    void* const* d_group_out = nullptr;  // grouped: per-group output base (device array; may point into a peer GPU); null = C
+    const long long* d_group_out_row0 = nullptr;  // grouped: first output row of the group inside its base
     const float* d_a_descale = nullptr;
     int a_descale_per_group = 0;
     const float* d_b_descale = nullptr;

@@ -19,7 +19,7 @@ __all__ = [
     "fp8_quantize_e4m3_record", "fp8_quantize_e5m2_record", "fp8_update_delayed_scale",
     "fp8_quantize_transpose_e4m3", "fp8_quant_and_transpose_e4m3", "transpose_u8", "fp8_clip_probe",
     "fp8_elem_clip_count", "fp8_pack_bf16_e4m3_raw", "fp8_pack_bf16_e4m3_raw_and_dequant",
-    "fp8_unpack_e4m3_raw_bf16", "lt_gemm_fp8_nt", "lt_gemm_fp8_tn_accum_f32", "gemm_fp8_nt_grouped", "gemm_fp8_nt_segments",
+    "fp8_unpack_e4m3_raw_bf16", "lt_gemm_fp8_nt", "lt_gemm_fp8_tn_accum_f32", "gemm_fp8_nt_grouped", "gemm_fp8_nt_segments", "gemm_fp8_nt_segments_scatter",
     "fp8_quant_act", "fp8_swiglu_quant_act", "refresh_fp8_weight", "fp8_linear_forward", "bias_add_strided_bf16", "swiglu_forward",
     "gelu_forward", "fp8_quantize_rowwise_e4m3", "swiglu_quantize_rowwise_e4m3", "swiglu_quantize_e4m3_record",
     "moe_topk_route_f32", "moe_build_expert_row_lists", "moe_expert_offsets_from_counts",
@@ -267,6 +267,16 @@ def gemm_fp8_nt_segments(ctx, num_segments, num_weights, segment_weight, max_tot
     check(_L().cf_gemm_fp8_nt_segments(ctx.handle, num_segments, num_weights, _p(segment_weight), max_total_rows, N, K,
                                        _p(counts), _p(offsets), _p(A), lda, int(a_is_e5m2), _p(a_descale),
                                        int(per_segment_a_descale), _p(B), _p(b_descale), _p(Cout), ldc, _s()))
+
+
+def gemm_fp8_nt_segments_scatter(ctx, num_segments, num_weights, segment_weight, max_total_rows, N, K, counts, offsets, A,
+                                 lda, a_is_e5m2, a_descale, per_segment_a_descale, B, b_descale, segment_out,
+                                 segment_out_row0, ldc):
+    """segment_out: int64 device tensor of output base addresses; segment_out_row0: int64 device tensor of first rows."""
+    check(_L().cf_gemm_fp8_nt_segments_scatter(ctx.handle, num_segments, num_weights, _p(segment_weight), max_total_rows, N,
+                                               K, _p(counts), _p(offsets), _p(A), lda, int(a_is_e5m2), _p(a_descale),
+                                               int(per_segment_a_descale), _p(B), _p(b_descale), None, _p(segment_out),
+                                               _p(segment_out_row0), ldc, _s()))
 
 
 def fp8_linear_forward(ctx, slot, x, w8, w_descale, y, bias=None, bias_mode=2):

@@ -167,7 +167,11 @@ class EpMoeSwigluFp8:
     gate/up GEMM over (source, expert) segments with the source's activation scale -> SwiGLU + delayed-scale
     re-quantise -> ragged down GEMM -> bf16 all-to-all back -> local weighted combine."""
 
-    def __init__(self, cfb, ctx, rows, H, F, num_experts, top_k, group=None, device="cuda", recv_capacity=None):
+    def __init__(self, cfb, ctx, rows, H, F, num_experts, top_k, group=None, device="cuda", recv_capacity=None,
+                 fused_return=False):
+        """fused_return: the down-projection GEMM writes every segment's rows straight into the `back` buffer of the
+        rank that owns the tokens (NVLink P2P stores from the GEMM epilogue into symmetric memory), which removes the
+        bf16 all-to-all of the return leg; one tiny all-reduce orders the combine behind all ranks' GEMMs."""
         self.cfb, self.ctx, self.group = cfb, ctx, group
         self.rows, self.H, self.F, self.E, self.k = rows, H, F, num_experts, top_k
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -186,6 +190,15 @@ class EpMoeSwigluFp8:
         self.slot_h = cfb.ActSlot(ctx, cfb.E4M3_MAX)
         self.device = dev
         self.plan: Optional[EpPlan] = None
+        self.fused_return = bool(fused_return) and self.world > 1
+        if self.fused_return:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.back = symm_mem.empty((self.T, H), dtype=torch.bfloat16, device=dev)
+            self._hdl = symm_mem.rendezvous(self.back, group if group is not None else dist.group.WORLD)
+            self.peer_back = [self._hdl.get_buffer(r, (self.T, H), torch.bfloat16) for r in range(self.world)]
+            for t in self.peer_back:
+                assert t.data_ptr() % 16 == 0
+            self._fence = torch.zeros(1, dtype=torch.float32, device=dev)
 
     def forward(self, x, route_weights, w_gateup8_local, w_gateup_descale, w_down8_local, w_down_descale, mixed):
         cfb, ctx = self.cfb, self.ctx
@@ -218,10 +231,25 @@ class EpMoeSwigluFp8:
             cfb.gemm_fp8_nt_segments(ctx, nseg, e_local, seg_weight, R, 2 * F, H, seg_counts, seg_offsets, recv8, H, False,
                                      seg_dx, True, w_gateup8_local, w_gateup_descale, gu, 2 * F)
             cfb.fp8_swiglu_quant_act(ctx, self.slot_h, gu, gu.view(-1)[F:], 2 * F, R, F, h8)
-            cfb.gemm_fp8_nt_segments(ctx, nseg, e_local, seg_weight, R, H, F, seg_counts, seg_offsets, h8, F, False,
-                                     cfb.ops._DevPtr(self.slot_h.c.descale_snapshot), False, w_down8_local,
-                                     w_down_descale, yc, H)
-        back = all_to_all_rows(yc[:R], plan.recv_splits, plan.send_splits, self.group)
+            if self.fused_return:
+                # segment (src, e) returns to rank src at the row where expert e starts in src's compact order
+                row0 = [int(sum(plan.counts_all[src][:self.e_lo + w])) for src, w in zip(plan.seg_source, plan.seg_weight)]
+                for src, w, c, r0 in zip(plan.seg_source, plan.seg_weight, plan.seg_counts, row0):
+                    assert 0 <= r0 and r0 + c <= self.T, "segment would leave the peer's buffer"
+                seg_out = torch.tensor([self.peer_back[src].data_ptr() for src in plan.seg_source], dtype=torch.int64, device=dev)
+                seg_row0 = torch.tensor(row0, dtype=torch.int64, device=dev)
+                cfb.gemm_fp8_nt_segments_scatter(ctx, nseg, e_local, seg_weight, R, H, F, seg_counts, seg_offsets, h8, F,
+                                                 False, cfb.ops._DevPtr(self.slot_h.c.descale_snapshot), False,
+                                                 w_down8_local, w_down_descale, seg_out, seg_row0, H)
+            else:
+                cfb.gemm_fp8_nt_segments(ctx, nseg, e_local, seg_weight, R, H, F, seg_counts, seg_offsets, h8, F, False,
+                                         cfb.ops._DevPtr(self.slot_h.c.descale_snapshot), False, w_down8_local,
+                                         w_down_descale, yc, H)
+        if self.fused_return:
+            dist.all_reduce(self._fence, group=self.group)      # every rank's GEMM (and its peer stores) has completed
+            back = self.back
+        else:
+            back = all_to_all_rows(yc[:R], plan.recv_splits, plan.send_splits, self.group)
         cfb.moe_combine_all_bf16(mixed, back, route_weights, self.idx, self.counts, self.offsets, rows, E, H)
 
 

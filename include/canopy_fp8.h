@@ -172,6 +172,19 @@ int cf_gemm_fp8_nt_segments(cf_ctx* ctx, int num_segments, int num_weights, cons
                             int lda, int a_is_e5m2, const float* d_a_descale, int per_segment_a_descale, const void* d_B,
                             const float* d_b_descale, void* d_C, int ldc, void* stream);
 
+/* GEMM fused with the return leg of an expert-parallel exchange: like cf_gemm_fp8_nt_segments, but the rows of segment g
+ * are written to d_segment_out[g] (a device array of 16-byte aligned bf16 base pointers, row stride ldc) starting at
+ * row d_segment_out_row0[g] of that buffer. The bases may be peer-GPU buffers mapped into this process (NVLink P2P
+ * stores from the epilogue), which replaces the all-to-all that would otherwise carry the expert outputs back to the
+ * ranks that own the tokens; the caller orders the consumers behind the kernel with its own cross-rank barrier.
+ * d_C is unused when d_segment_out is given. No counterpart in the reference. */
+int cf_gemm_fp8_nt_segments_scatter(cf_ctx* ctx, int num_segments, int num_weights, const int* d_segment_weight,
+                                    int max_total_rows, int N, int K, const int* d_counts, const int* d_offsets,
+                                    const void* d_A, int lda, int a_is_e5m2, const float* d_a_descale,
+                                    int per_segment_a_descale, const void* d_B, const float* d_b_descale, void* d_C,
+                                    void* const* d_segment_out, const long long* d_segment_out_row0, int ldc,
+                                    void* stream);
+
 /* ------------------------------------------------------------------ delayed-scaling slot + fused linear */
 
 /* Mirror of ActSlot (src/trainer.cu:3248-3279). All pointer members are device scalars; cf_act_slot_init

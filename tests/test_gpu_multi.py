@@ -90,6 +90,16 @@ def _worker(rank, world, port, ret):
             ep.forward(xs[rank], rw, wgu8[e_lo:e_hi].contiguous(), dgu, wd8[e_lo:e_hi].contiguous(), dd, mixed)
             ctx.poll_status()
         assert sum(ep.plan.send_splits) == rows * k
+        # the GEMM that writes its output straight into the owners' buffers (P2P stores) gives the same bits as the
+        # GEMM followed by the bf16 all-to-all
+        ep2 = par.EpMoeSwigluFp8(cfb, ctx, rows, H, F, E, k, device=dev, fused_return=True)
+        mixed_f = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
+        for step in range(2):
+            rw2 = logits[rank].clone()
+            mixed_f.zero_()
+            ep2.forward(xs[rank], rw2, wgu8[e_lo:e_hi].contiguous(), dgu, wd8[e_lo:e_hi].contiguous(), dd, mixed_f)
+            ctx.poll_status()
+        assert torch.equal(mixed_f.view(torch.int16), mixed.view(torch.int16))
         # Host oracle on sampled tokens with the very scales the distributed layer used: this rank's activation
         # scale for x, and for every expert the SwiGLU slot scale of the rank that owns it.
         import sys

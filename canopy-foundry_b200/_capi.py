@@ -76,6 +76,8 @@ SIGNATURES = {
     "cf_refresh_fp8_weight": (ci, [C.POINTER(Fp8WeightStruct), ci, vp]),
     "cf_fp8_linear_forward": (ci, [vp, C.POINTER(ActSlotStruct), vp, ci, ci, vp, fp, ci, vp, ci, vp, ci, vp]),
     "cf_fp8_linear_static_scratch": (ci, [vp, ci, ci, fp, fp, vp, fp, ci, vp, ci, vp, ci, ip, vp]),
+    "cf_lion_step_f32_state": (ci, [vp, fp, fp, sz, cf, cf, cf, cf, vp, fp, C.c_uint]),
+    "cf_lion_step_bf16_state": (ci, [vp, vp, fp, sz, cf, cf, cf, cf, vp, fp, C.c_uint]),
     "cf_bias_add_strided_bf16": (ci, [vp, vp, ci, ci, ci, ci, vp]),
     "cf_swiglu_forward": (ci, [vp, vp, vp, ci, vp]),
     "cf_gelu_forward": (ci, [vp, vp, sz, vp]),

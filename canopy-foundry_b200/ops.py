@@ -21,7 +21,7 @@ __all__ = [
     "fp8_elem_clip_count", "fp8_pack_bf16_e4m3_raw", "fp8_pack_bf16_e4m3_raw_and_dequant",
     "fp8_unpack_e4m3_raw_bf16", "lt_gemm_fp8_nt", "lt_gemm_fp8_tn_accum_f32", "gemm_fp8_nt_grouped", "gemm_fp8_nt_segments", "gemm_fp8_nt_segments_scatter",
     "fp8_quant_act", "fp8_swiglu_quant_act", "refresh_fp8_weight", "fp8_linear_forward", "bias_add_strided_bf16", "swiglu_forward",
-    "gelu_forward", "fp8_quantize_rowwise_e4m3", "swiglu_quantize_rowwise_e4m3", "swiglu_quantize_e4m3_record",
+    "gelu_forward", "lion_step", "fp8_quantize_rowwise_e4m3", "swiglu_quantize_rowwise_e4m3", "swiglu_quantize_e4m3_record",
     "moe_topk_route_f32", "moe_build_expert_row_lists", "moe_expert_offsets_from_counts",
     "moe_gather_rows_u8", "moe_gather_rows_bf16", "moe_scatter_accumulate_rows_bf16",
     "moe_scale_accumulate_bf16", "moe_gather_all_u8", "moe_combine_all_bf16",
@@ -293,6 +293,12 @@ def bias_add_strided_bf16(inout, bias, rows, cols, row_stride, base):
 
 def swiglu_forward(gate, up, out, n=None):
     check(_L().cf_swiglu_forward(_p(gate), _p(up), _p(out), gate.numel() if n is None else n, _s()))
+
+
+def lion_step(w, m, grad, lr, beta1, beta2, wd, weight_amax=None, sr_seed=0):
+    """lion_step (include/ida_native/kernels.hpp:1089-1108); m float32 or bfloat16 selects the overload."""
+    fn = _L().cf_lion_step_f32_state if m.dtype == torch.float32 else _L().cf_lion_step_bf16_state
+    check(fn(_p(w), _p(m), _p(grad), w.numel(), lr, beta1, beta2, wd, _s(), _p(weight_amax), sr_seed))
 
 
 def gelu_forward(x, out):

@@ -85,6 +85,16 @@ void fp8_unpack_e4m3_raw_bf16(const std::uint8_t* d_in, const float* d_descale, 
     cf_check(cf_fp8_unpack_e4m3_raw_bf16(d_in, d_descale, d_out, n, s), "fp8_unpack_e4m3_raw_bf16");
 }
 
+// kernels/lion.cu:121-144
+void lion_step(__nv_bfloat16* d_w, float* d_m, const float* d_grad, std::size_t n, float lr, float beta1, float beta2,
+               float wd, cudaStream_t stream, float* d_weight_amax, unsigned sr_seed) {
+    cf_check(cf_lion_step_f32_state(d_w, d_m, d_grad, n, lr, beta1, beta2, wd, stream, d_weight_amax, sr_seed), "lion_step");
+}
+void lion_step(__nv_bfloat16* d_w, __nv_bfloat16* d_m, const float* d_grad, std::size_t n, float lr, float beta1,
+               float beta2, float wd, cudaStream_t stream, float* d_weight_amax, unsigned sr_seed) {
+    cf_check(cf_lion_step_bf16_state(d_w, d_m, d_grad, n, lr, beta1, beta2, wd, stream, d_weight_amax, sr_seed), "lion_step");
+}
+
 // kernels/activations.cu:76-87; kernels/moe.cu:338-345, 519-521
 void swiglu_forward(const __nv_bfloat16* d_gate, const __nv_bfloat16* d_up, __nv_bfloat16* d_out, int N, cudaStream_t stream) {
     const int rc = cf_swiglu_forward(d_gate, d_up, d_out, N, stream);

@@ -264,6 +264,15 @@ int cf_fp8_linear_static_scratch(const void* d_x, int M, int K, const float* d_x
                                  const void* d_w8, const float* d_w_descale, int N, const void* d_bias, int bias_mode,
                                  void* d_y, int ldy, int* d_status_or_null, void* stream);
 
+/* kernels/lion.cu:121-144, include/ida_native/kernels.hpp:1089-1108 (both lion_step overloads): Lion update with the
+ * stochastic-rounding bf16 weight write and, when d_weight_amax is non-NULL, max |w_new| of the fp32 value before
+ * rounding accumulated into it (integer atomicMax; the caller zeroes it) — the amax cf_refresh_fp8_weight consumes with
+ * recompute_amax = 0. Momentum state fp32 or bf16 (bf16 state is itself rounded stochastically). */
+int cf_lion_step_f32_state(void* d_w, float* d_m, const float* d_grad, size_t n, float lr, float beta1, float beta2, float wd,
+                           void* stream, float* d_weight_amax, unsigned sr_seed);
+int cf_lion_step_bf16_state(void* d_w, void* d_m, const float* d_grad, size_t n, float lr, float beta1, float beta2, float wd,
+                            void* stream, float* d_weight_amax, unsigned sr_seed);
+
 /* ------------------------------------------------------------------ elementwise neighbours of the GEMMs */
 
 /* kernels/moe.cu:338-345, kernels.hpp:243-247. */

@@ -416,6 +416,45 @@ void orc_swiglu_forward(const uint16_t* gate, const uint16_t* up, uint16_t* out,
     }
 }
 
+// ---- kernels/lion.cu:39-76 (fp32 state) and :78-119 (bf16 state) ------------------------------------------
+// The GPU compiler may contract a*b+c into one fused multiply-add; this host restatement keeps the products and
+// sums separate (volatile temporaries), so comparisons with the GPU allow the last-bit difference that makes.
+static inline uint16_t lion_sr(float x, unsigned rnd) {
+    uint32_t bits = f32_to_bits(x);
+    if ((bits & 0x7f800000u) == 0x7f800000u) return f32_to_bf16(x);
+    bits += (rnd & 0xffffu);
+    return static_cast<uint16_t>(bits >> 16);
+}
+void orc_lion_step(uint16_t* w, void* m, int m_is_bf16, const float* grad, int64_t n, float lr, float beta1, float beta2,
+                   float wd, float* amax_io, unsigned seed) {
+    float amax = 0.0f;
+    for (int64_t i = 0; i < n; ++i) {
+        const float g = grad[i];
+        const float m_prev = m_is_bf16 ? bf16_to_f32(static_cast<uint16_t*>(m)[i]) : static_cast<float*>(m)[i];
+        volatile float t1 = beta1 * m_prev, t2 = (1.0f - beta1) * g;
+        const float blend = t1 + t2;
+        const float update = static_cast<float>((blend > 0.0f) - (blend < 0.0f));
+        volatile float t3 = beta2 * m_prev, t4 = (1.0f - beta2) * g;
+        const float m_new = t3 + t4;
+        unsigned h = static_cast<unsigned>(i) * 2654435761u ^ seed;
+        h ^= h >> 16; h *= 0x85ebca6bu; h ^= h >> 13; h *= 0xc2b2ae35u; h ^= h >> 16;
+        if (m_is_bf16) static_cast<uint16_t*>(m)[i] = lion_sr(m_new, h ^ 0x9e3779b9u);
+        else static_cast<float*>(m)[i] = m_new;
+        const float w_f32 = bf16_to_f32(w[i]);
+        volatile float t5 = wd * w_f32;
+        volatile float t6 = lr * (update + t5);
+        const float w_new = w_f32 - t6;
+        w[i] = lion_sr(w_new, h);
+        amax = std::fmax(amax, std::fabs(w_new));
+    }
+    if (amax_io) {
+        int32_t cur, loc;
+        std::memcpy(&cur, amax_io, 4);
+        std::memcpy(&loc, &amax, 4);
+        if (loc > cur) std::memcpy(amax_io, &loc, 4);
+    }
+}
+
 // ---- row-wise (per-token) scaling: kernels/fp8.cu:34-49 applied per row (no reference code; documented
 // generalisation for configuration 3). swiglu != 0 quantises bf16(silu(gate)*up) (kernels/activations.cu:28-40).
 void orc_quantize_rowwise_e4m3(const uint16_t* a, const uint16_t* b_or_null, int64_t ld_in, uint8_t* out, int64_t ld_out,

@@ -1,7 +1,7 @@
 // C-linkage doorway to the REFERENCE's own CUDA operators (namespace
 // ida_native, include/ida_native/kernels.hpp), linked from the reference's
-// kernels/fp8.cu, kernels/moe.cu, kernels/activations.cu and
-// kernels/cross_entropy.cu compiled where they lie for sm_100a. Output goes to
+// kernels/fp8.cu, kernels/moe.cu, kernels/activations.cu,
+// kernels/lion.cu and kernels/cross_entropy.cu compiled where they lie for sm_100a. Output goes to
 // oracle/_ref/libref_gpu.so and is used by the GPU parity tests as the
 // reference-on-the-same-GPU comparator. Test infrastructure only.
 #include "ida_native/kernels.hpp"
@@ -29,6 +29,9 @@ int ref_fp8_elem_clip_count(const void* x, const float* sc, float mx, size_t n, 
 int ref_fp8_pack_bf16_e4m3_raw(const void* x, uint8_t* o, float* am, float* sc, float* de, int* bad, size_t n, void* s) { try { fp8_pack_bf16_e4m3_raw(BF(x), o, am, sc, de, bad, n, S(s)); } catch (...) { return 1; } return 0; }
 int ref_fp8_pack_bf16_e4m3_raw_and_dequant(const void* x, uint8_t* o, void* dq, float* am, float* sc, float* de, int* bad, size_t n, void* s) { try { fp8_pack_bf16_e4m3_raw_and_dequant(BF(x), o, BFW(dq), am, sc, de, bad, n, S(s)); } catch (...) { return 1; } return 0; }
 int ref_fp8_unpack_e4m3_raw_bf16(const uint8_t* in, const float* de, void* o, size_t n, void* s) { try { fp8_unpack_e4m3_raw_bf16(in, de, BFW(o), n, S(s)); } catch (...) { return 1; } return 0; }
+
+int ref_lion_step_f32(void* w, float* m, const float* g, size_t n, float lr, float b1, float b2, float wd, void* s, float* amax, unsigned seed) { try { lion_step(BFW(w), m, g, n, lr, b1, b2, wd, S(s), amax, seed); } catch (...) { return 1; } return 0; }
+int ref_lion_step_bf16(void* w, void* m, const float* g, size_t n, float lr, float b1, float b2, float wd, void* s, float* amax, unsigned seed) { try { lion_step(BFW(w), BFW(m), g, n, lr, b1, b2, wd, S(s), amax, seed); } catch (...) { return 1; } return 0; }
 
 int ref_swiglu_forward(const void* g, const void* u, void* o, int n, void* s) { try { swiglu_forward(BF(g), BF(u), BFW(o), n, S(s)); } catch (...) { return 1; } return 0; }
 int ref_gelu_forward(const void* x, void* o, size_t n, void* s) { try { gelu_forward(BF(x), BFW(o), n, S(s)); } catch (...) { return 1; } return 0; }

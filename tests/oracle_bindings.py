@@ -174,6 +174,13 @@ class Oracle:
         self.lib.orc_swiglu_forward(_ptr(gate), _ptr(up), _ptr(out), c_i64(gate.size))
         return out
 
+    def lion_step(self, w, m, grad, lr, beta1, beta2, wd, amax=0.0, seed=0):
+        """In place on w (uint16) and m (float32 or uint16). Returns the updated amax."""
+        am = c_f(amax)
+        self.lib.orc_lion_step(_ptr(w), _ptr(m), c_i(int(m.dtype == np.uint16)), _ptr(grad), c_i64(w.size), c_f(lr),
+                               c_f(beta1), c_f(beta2), c_f(wd), C.byref(am), C.c_uint(seed))
+        return np.float32(am.value)
+
     def quantize_rowwise_e4m3(self, a, b=None):
         """a (and optional b for the SwiGLU form): uint16 [rows, cols] contiguous."""
         rows, cols = a.shape

@@ -319,3 +319,45 @@ def test_argument_errors(cfb):
         cfb.fp8_quantize_e4m3(randn_bf16((16,)), None, sc)
     with pytest.raises(cfb.CanopyError):
         cfb.swiglu_forward(randn_bf16((16,)), randn_bf16((16,)), torch.empty(16, dtype=torch.bfloat16, device="cuda"), n=-1)
+
+
+@pytest.mark.parametrize("bf16_state", [False, True])
+@pytest.mark.parametrize("n", [1, 5, 1024, 100003])
+def test_lion_step_with_fused_weight_amax(cfb, oracle, refgpu, n, bf16_state):
+    """lion_step (kernels/lion.cu): bit for bit against the reference kernel on the same GPU; against the host
+    restatement up to the last bit a fused multiply-add may change; the fused amax feeds the weight refresh."""
+    g = torch.Generator(device="cuda").manual_seed(n)
+    w0 = torch.randn(n, generator=g, device="cuda").to(torch.bfloat16)
+    grad = torch.randn(n, generator=g, device="cuda")
+    m0 = torch.randn(n, generator=g, device="cuda") * 0.1
+    if bf16_state:
+        m0 = m0.to(torch.bfloat16)
+    hp = (3e-3, 0.9, 0.99, 0.1)
+    w, m = w0.clone(), m0.clone()
+    am = f32_scalar()
+    cfb.lion_step(w, m, grad, *hp, weight_amax=am, sr_seed=77)
+    if refgpu is not None:
+        wr, mr = w0.clone(), m0.clone()
+        amr = f32_scalar()
+        refgpu.call("ref_lion_step_bf16" if bf16_state else "ref_lion_step_f32", wr, mr, grad, C.c_size_t(n),
+                    C.c_float(hp[0]), C.c_float(hp[1]), C.c_float(hp[2]), C.c_float(hp[3]), stream_ptr(), amr, C.c_uint(77))
+        torch.cuda.synchronize()
+        assert torch.equal(w.view(torch.int16), wr.view(torch.int16))
+        assert torch.equal(m.view(torch.int16) if bf16_state else m, mr.view(torch.int16) if bf16_state else mr)
+        assert am[0].item() == amr[0].item()
+    wo = bf16_to_u16(w0).copy()
+    mo = bf16_to_u16(m0).copy() if bf16_state else m0.cpu().numpy().copy()
+    a_o = oracle.lion_step(wo, mo, grad.cpu().numpy(), *hp, amax=0.0, seed=77)
+    diff = np.abs(bf16_to_u16(w).astype(np.int32) - wo.astype(np.int32))
+    assert (diff > 1).sum() == 0 and (diff > 0).mean() < 0.02
+    np.testing.assert_allclose(am[0].item(), a_o, rtol=1e-6)
+    # without an amax pointer nothing is recorded
+    cfb.lion_step(w0.clone(), m0.clone(), grad, *hp, weight_amax=None, sr_seed=77)
+    # the recorded amax drives the weight refresh without another pass over the weight
+    if n == 1024:
+        wt = w.view(32, 32).contiguous()
+        fw = cfb.Fp8Weight(wt, stored_out_major=True)
+        fw.amax[0] = am[0]
+        cfb.refresh_fp8_weight(fw, recompute_amax=False)
+        s_o, _ = oracle.scale_from_amax(am[0].item(), 448.0)
+        assert np.array_equal(fw.fwd8.cpu().numpy(), oracle.quantize_bf16(bf16_to_u16(wt), s_o))

@@ -243,3 +243,29 @@ def test_grouped_expert_forward_restatement(oracle):
         want += rw[:, e:e + 1].astype(np.float64) * y
     got = oracle.bf16_to_f32(mixed)
     assert np.linalg.norm(got - want) / np.linalg.norm(want) < 8e-3
+
+
+def test_lion_step_restatement(oracle):
+    """kernels/lion.cu: sign update, decoupled weight decay, hash-driven stochastic rounding, pre-rounding amax."""
+    rng = np.random.default_rng(7)
+    n = 1000
+    w0 = oracle.to_bf16(rng.standard_normal(n).astype(np.float32))
+    g = rng.standard_normal(n).astype(np.float32)
+    m0 = (rng.standard_normal(n) * 0.1).astype(np.float32)
+    w, m = w0.copy(), m0.copy()
+    am = oracle.lion_step(w, m, g, 1e-2, 0.9, 0.99, 0.1, amax=0.0, seed=123)
+    wf = oracle.bf16_to_f32(w0).astype(np.float64)
+    blend = 0.9 * m0.astype(np.float64) + 0.1 * g
+    w_new = wf - 1e-2 * (np.sign(blend) + 0.1 * wf)
+    np.testing.assert_allclose(m, 0.99 * m0 + 0.01 * g, rtol=1e-6, atol=1e-7)
+    # stochastic rounding moves a value to one of its two bf16 neighbours
+    got = oracle.bf16_to_f32(w).astype(np.float64)
+    assert np.all(np.abs(got - w_new) <= np.abs(w_new) * 2.0 ** -7 + 1e-30)
+    assert abs(float(am) - np.abs(w_new).max()) <= 1e-6 * np.abs(w_new).max()
+    # same seed, same result; different seed, different rounding somewhere
+    w2, m2 = w0.copy(), m0.copy()
+    oracle.lion_step(w2, m2, g, 1e-2, 0.9, 0.99, 0.1, seed=123)
+    assert np.array_equal(w2, w)
+    w3, m3 = w0.copy(), m0.copy()
+    oracle.lion_step(w3, m3, g, 1e-2, 0.9, 0.99, 0.1, seed=124)
+    assert not np.array_equal(w3, w)

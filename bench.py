@@ -232,8 +232,11 @@ def run_moe(args):
     wgu8, dgu = quant_experts((n_local, 2 * F, H), 0.02, 50 + rank)
     wd8, dd = quant_experts((n_local, H, F), 0.02, 70 + rank)
     mixed = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
+    fused_swiglu = not use_ep and not args.moe_unfused_swiglu
+    if fused_swiglu:
+        wgu8 = cfb.fp8_interleave_gate_up(wgu8)       # one-time weight layout for the fused SwiGLU epilogue
     layer = par.EpMoeSwigluFp8(cfb, ctx, rows, H, F, E, TOPK, device=dev, fused_return=args.moe_fused_return) if use_ep else \
-        cfb.MoeSwigluFp8(ctx, rows, H, F, E, TOPK, device=dev)
+        cfb.MoeSwigluFp8(ctx, rows, H, F, E, TOPK, device=dev, fused_swiglu=fused_swiglu)
 
     def step():
         rw = logits.clone()
@@ -277,6 +280,7 @@ def run_moe(args):
             "config": {"workload": "moe_swiglu_fp8_32768tok_H4096_E8_F14336_top2_zipf1.1 (BASELINE config 4)",
                        "parallelism": (f"ep{world} (all-to-all, experts placed by load{', GEMM-fused return leg' if args.moe_fused_return else ''})" if use_ep else
                                        f"dp{world} (experts replicated, tokens sharded, no collective)") if world > 1 else "single GPU",
+                       "swiglu": "fused into the gate/up GEMM epilogue" if fused_swiglu else "separate pass over the bf16 intermediate",
                        "max_rows_on_one_rank": int(lmax.item()), "mean_rows_per_rank": TOK * TOPK / world,
                        "l2": "inputs larger than L2 (1.4 GB of expert weights per step)"},
             "tflops": flop / (ms * 1e-3) / 1e12, "gpu_launches": int(launches), "clocks": clocks}), flush=True)
@@ -295,6 +299,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--bias-mode", type=int, default=2, help="2 = reference rounding order, 1 = single rounding")
+    ap.add_argument("--moe-unfused-swiglu", action="store_true", help="keep the [T,2F] bf16 intermediate (separate SwiGLU pass)")
     ap.add_argument("--moe-fused-return", action="store_true",
                     help="ep mode: the down GEMM stores its rows straight into the owners' buffers over NVLink (no return all-to-all)")
     ap.add_argument("--moe-mode", default="ep", choices=["ep", "dp"],

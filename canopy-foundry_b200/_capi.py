@@ -73,6 +73,8 @@ SIGNATURES = {
     "cf_act_slot_init": (ci, [vp, C.POINTER(ActSlotStruct), cf, ci, vp]),
     "cf_fp8_quant_act": (ci, [vp, C.POINTER(ActSlotStruct), vp, sz, vp, vp, ci]),
     "cf_fp8_swiglu_quant_act": (ci, [vp, C.POINTER(ActSlotStruct), vp, vp, ci, ci, ci, vp, vp]),
+    "cf_gemm_fp8_swiglu_quant_act": (ci, [vp, C.POINTER(ActSlotStruct), ci, ci, ip, ci, ci, ci, ip, ip, vp, ci, ci, fp, ci, vp, fp, vp, ci, vp]),
+    "cf_fp8_interleave_gate_up": (ci, [vp, vp, vp, ci, ci, ci, vp]),
     "cf_refresh_fp8_weight": (ci, [C.POINTER(Fp8WeightStruct), ci, vp]),
     "cf_fp8_linear_forward": (ci, [vp, C.POINTER(ActSlotStruct), vp, ci, ci, vp, fp, ci, vp, ci, vp, ci, vp]),
     "cf_fp8_linear_static_scratch": (ci, [vp, ci, ci, fp, fp, vp, fp, ci, vp, ci, vp, ci, ip, vp]),

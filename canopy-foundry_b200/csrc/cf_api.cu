@@ -434,6 +434,56 @@ int cf_fp8_swiglu_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_gate, 
     return CF_OK;
 }
 
+int cf_gemm_fp8_swiglu_quant_act(cf_ctx* ctx, cf_act_slot* slot, int num_segments, int num_weights,
+                                 const int* d_segment_weight, int max_total_rows, int F, int K, const int* d_counts,
+                                 const int* d_offsets, const void* d_A, int lda, int a_is_e5m2, const float* d_a_descale,
+                                 int per_segment_a_descale, const void* d_W_interleaved, const float* d_w_descale,
+                                 void* d_h8, int ldh, void* stream) {
+    CF_REQUIRE(ctx && slot && slot->amax, "cf_gemm_fp8_swiglu_quant_act: null context or uninitialised slot");
+    CF_REQUIRE(slot->fp8_max == CF_E4M3_MAX, "cf_gemm_fp8_swiglu_quant_act: E4M3 slots only");
+    CF_REQUIRE(max_total_rows >= 0 && F > 0 && K > 0 && num_segments >= 1 && num_weights >= 1, "cf_gemm_fp8_swiglu_quant_act: bad shape");
+    CF_REQUIRE(F % 32 == 0, "cf_gemm_fp8_swiglu_quant_act: F must be a multiple of 32 (gate/up rows interleave in groups of 32)");
+    CF_REQUIRE((d_counts == nullptr) == (d_offsets == nullptr), "cf_gemm_fp8_swiglu_quant_act: counts and offsets go together");
+    CF_REQUIRE(d_counts != nullptr || num_segments == 1, "cf_gemm_fp8_swiglu_quant_act: the dense form has one segment");
+    CF_REQUIRE(lda >= K && ldh >= F, "cf_gemm_fp8_swiglu_quant_act: leading dimension smaller than the row length");
+    if (max_total_rows == 0) return CF_OK;
+    CF_REQUIRE(d_A && d_a_descale && d_W_interleaved && d_w_descale && d_h8, "cf_gemm_fp8_swiglu_quant_act: null pointer");
+    cudaStream_t st = as_stream(stream);
+    GemmParams p;
+    p.groups = num_segments;
+    p.M = max_total_rows;
+    p.N = 2 * F; p.K = K;
+    p.d_counts = d_counts; p.d_offsets = d_offsets; p.d_group_weight = d_segment_weight;
+    p.d_a_descale = d_a_descale; p.a_descale_per_group = per_segment_a_descale ? 1 : 0;
+    p.d_b_descale = d_w_descale;
+    p.C = d_h8; p.ldc = ldh; p.out_kind = 4;
+    p.a_e5m2 = a_is_e5m2 ? 1 : 0;
+    p.d_quant_scale = slot->scale; p.d_amax_out = slot->amax;
+    p.d_status = reinterpret_cast<Ctx*>(ctx)->d_status;
+    const int n_blocks = (2 * F + gemm_tile_n() - 1) / gemm_tile_n();
+    const int m_blocks = (max_total_rows + gemm_tile_m() - 1) / gemm_tile_m() + (d_counts ? num_segments : 0);
+    const long long b_rows = static_cast<long long>(num_weights) * 2 * F;
+    auto run = [&]() { return launch_gemm_fp8_nt(d_A, lda, max_total_rows, d_W_interleaved, b_rows, p, m_blocks * n_blocks, st); };
+    if (!slot->init) {
+        // first use: one pass with scale 0 only records the exact amax, the second pass quantises with it
+        // (the sequence of fp8_quant_act's first call, src/trainer.cu:4793-4815, around a producer that is a GEMM)
+        CF_CUDA(cudaMemsetAsync(slot->amax, 0, sizeof(float), st));
+        CF_CUDA(cudaMemsetAsync(slot->scale, 0, sizeof(float), st));
+        CF_TRY(run());
+        CF_TRY(cf_fp8_scale_from_amax(slot->amax, slot->fp8_max, slot->scale, slot->descale, stream));
+        CF_CUDA(cudaMemcpyAsync(slot->scale_snapshot, slot->scale, sizeof(float), cudaMemcpyDeviceToDevice, st));
+        CF_CUDA(cudaMemcpyAsync(slot->descale_snapshot, slot->descale, sizeof(float), cudaMemcpyDeviceToDevice, st));
+        CF_CUDA(cudaMemsetAsync(slot->amax, 0, sizeof(float), st));
+        CF_TRY(run());
+        slot->init = 1;
+    } else {
+        CF_TRY(slot_begin(slot->scale, slot->descale, slot->scale_snapshot, slot->descale_snapshot, slot->amax, st));
+        CF_TRY(run());
+    }
+    return cf_fp8_update_delayed_scale(slot->amax, slot->fp8_max, slot->scale, slot->descale, slot->history, kHistoryLen,
+                                       slot->history_cursor, slot->history_count, stream);
+}
+
 int cf_refresh_fp8_weight(const cf_fp8_weight* w, int recompute_amax, void* stream) {
     CF_REQUIRE(w && w->w && w->fwd8 && w->bwd8 && w->amax && w->scale && w->descale, "cf_refresh_fp8_weight: null pointer");
     CF_REQUIRE(w->in_dim > 0 && w->out_dim > 0, "cf_refresh_fp8_weight: bad dims");

@@ -3,10 +3,11 @@
 //
 //   C[m,n] = (dA * dB) * sum_k A8[m,k] * B8[n,k]          (src/trainer.cu:4498-4534)
 //
-// One persistent CTA per SM, 192 threads:
+// One persistent CTA per SM, 320 threads:
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      TMEM allocator + MMA issuer (one elected lane)
-//   warps 2..5  epilogue: tcgen05.ld the accumulator, scale, bias, convert, store
+//   warps 2..9  epilogue: tcgen05.ld the accumulator, scale, bias / SwiGLU, convert, store (two warps per TMEM
+//               lane quarter, each draining 128 of the tile's 256 columns)
 // The same kernel serves the dense call, the beta=1 weight-gradient forms and the ragged
 // per-expert (grouped) schedule: a tile is (expert, 128-row block of that expert, 256-column block).
 //
@@ -28,15 +29,16 @@ constexpr int BM = 128;                 // rows of A / C per CTA (TMEM lanes)
 constexpr int BN = 256;                 // output columns per tile
 constexpr int BK = 128;                 // bytes == FP8 elements per k-block (one 128B swizzle row)
 constexpr int UMMA_K = 32;              // FP8 elements per tcgen05.mma
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;        // warp 0 producer, warp 1 MMA issuer, warps 2..9 epilogue
+constexpr int EPI_WARPS = 8;            // two per TMEM lane quarter: each handles 128 of the tile's 256 columns
 constexpr int TMEM_COLS = 512;          // two 128x256 fp32 accumulators per CTA
 constexpr unsigned long long WAIT_NS = 1500ull * 1000ull * 1000ull;   // per-wait deadline
 constexpr unsigned long long DRAIN_NS = 20ull * 1000ull * 1000ull;
 
-// Output staging for the TMA-store epilogue: per epilogue warp two 32-row x 128-byte (64 bf16) boxes.
+// Output staging for the TMA-store epilogue: per epilogue warp one 32-row x 128-byte (64 bf16) box.
 constexpr int C_BOX_COLS = 64;
 constexpr int C_BOX_BYTES = 32 * C_BOX_COLS * 2;           // 4 KiB
-constexpr int C_STAGING = 4 * 2 * C_BOX_BYTES;             // 32 KiB
+constexpr int C_STAGING = EPI_WARPS * C_BOX_BYTES;         // 32 KiB
 
 // Shape of the shared-memory ring. Single CTA: the CTA loads all 256 rows of the B tile. CTA pair
 // (cta_group::2, one 256x256 tile per pair): each CTA loads its own 128 rows of A and HALF of the B tile,
@@ -110,7 +112,7 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
                  ::"l"(map), "r"(src), "r"(x), "r"(y), "l"(policy) : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
@@ -266,6 +268,12 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, i
     return c;
 }
 
+// kernels/activations.cu:11-17
+__device__ __forceinline__ float swiglu_sigmoid(float x) {
+    if (x >= 0.0f) return __fdiv_rn(1.0f, 1.0f + expf(-x));
+    const float e = expf(x);
+    return __fdiv_rn(e, 1.0f + e);
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
@@ -325,7 +333,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar + 8 * a, 1);                 // one tcgen05.commit
-            mbar_init(tempty_bar + 8 * a, PAIR ? 8 : 4);     // one arrive per epilogue warp (of both CTAs)
+            mbar_init(tempty_bar + 8 * a, PAIR ? 2 * EPI_WARPS : EPI_WARPS);   // one arrive per epilogue warp (of both CTAs)
         }
         mbar_init(drain_bar, 1);
         s_abort[0] = 0;
@@ -439,10 +447,10 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     } else {
         // ------------------------------------------------------------ epilogue warps (both CTAs of a pair)
         const int quarter = warp & 3;                      // TMEM lanes this warp may read
+        const int col_half = (warp - 2) >> 2;              // which 128 columns of the tile this warp drains
         const int trow = quarter * 32 + lane;
         const uint32_t tempty_dst = PAIR ? mapa(tempty_bar, 0) : tempty_bar;
         int local_tile = 0;
-        uint32_t store_seq = 0;                            // alternates this warp's two staging boxes
         const uint64_t store_policy = l2_policy_evict_first();
         bool ok = true;
         for (int tile = unit; ok && tile < total_tiles; tile += n_units, ++local_tile) {
@@ -460,21 +468,59 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             }
             const float db_t = p.d_b_col_descale ? 1.0f : *p.d_b_descale;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+            if (p.out_kind == 4) {
+                // SwiGLU -> E4M3 epilogue. B's rows are interleaved in groups of 64 = 32 gate rows followed by the 32 up
+                // rows of the same features, so chunk 2c holds gate and chunk 2c+1 holds up for features
+                // n0/2 + 32c .. +31. Rounding points are those of the unfused sequence: GEMM output to bf16
+                // (src/trainer.cu:6310-6313), silu(g)*u to bf16 (kernels/activations.cu:39), then the record-quantise
+                // of kernels/fp8.cu:67-84 with the slot's scale; the amax of the bf16 product goes to p.d_amax_out.
+                const float hs = *p.d_quant_scale;
+                const float dab = da * db_t;
+                float local_amax = 0.0f;
+                uint8_t* orow = static_cast<uint8_t*>(tc.out_base) + grow * p.ldc + (tc.n0 >> 1);
+#pragma unroll 1
+                for (int c = col_half * 2; c < col_half * 2 + 2; ++c) {
+                    const int col0 = tc.n0 + c * 64;
+                    if (col0 >= p.N) break;                // warp-uniform
+                    uint32_t vg[32], vu[32];
+                    tmem_ld32(taddr + c * 64, vg);
+                    tmem_ld32(taddr + c * 64 + 32, vu);
+                    tmem_ld_wait();
+                    if (!row_ok) continue;
+                    uint32_t q[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float h[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float gb = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vg[4 * j + e]) * dab));
+                            const float ub = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vu[4 * j + e]) * dab));
+                            h[e] = __bfloat162float(__float2bfloat16_rn(gb * swiglu_sigmoid(gb) * ub));
+                            local_amax = fmaxf(local_amax, fabsf(h[e]));
+                        }
+                        q[j] = cvt_fp8x4<false>(h[0] * hs, h[1] * hs, h[2] * hs, h[3] * hs);
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+                    dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
+                    dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+                }
+                local_amax = warp_max(local_amax);
+                if (lane == 0 && local_amax > 0.0f) atomicMax(reinterpret_cast<int*>(p.d_amax_out), __float_as_int(local_amax));
+            } else {
             // Full boxes of bf16 output go through shared memory and TMA stores (whole 128-byte lines per row);
             // ragged rows of a grouped tile, column tails and the fp32 / accumulate forms use direct stores.
             const int warp_row0 = static_cast<int>(cta_rank) * BM + quarter * 32;
             const bool warp_rows_full = (p.d_counts == nullptr) || (warp_row0 + 32 <= tc.valid_rows);
             if (p.tma_store && warp_rows_full && warp_row0 < tc.valid_rows) {
-                const uint32_t stage0 = smem_c + static_cast<uint32_t>(warp - 2) * 2 * C_BOX_BYTES;
+                const uint32_t buf = smem_c + static_cast<uint32_t>(warp - 2) * C_BOX_BYTES;
                 const uint32_t row_off = static_cast<uint32_t>(lane) * 128u;
                 const uint32_t sw = static_cast<uint32_t>(lane & 7);
-                int ch64 = 0;
+                int ch64 = col_half * 2;
 #pragma unroll 1
-                for (; ch64 < BN / C_BOX_COLS; ++ch64) {
+                for (; ch64 < col_half * 2 + 2; ++ch64) {
                     const int col0 = tc.n0 + ch64 * C_BOX_COLS;
                     if (col0 + C_BOX_COLS > p.N) break;    // warp-uniform; the tail takes the direct path below
-                    const uint32_t buf = stage0 + (store_seq++ & 1u) * C_BOX_BYTES;
-                    if (lane == 0) bulk_wait_read_1();     // the store that last read this buffer has drained it
+                    if (lane == 0) bulk_wait_read_0();     // the store that last read this warp's box has drained it
                     __syncwarp();
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
@@ -534,7 +580,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     }
                 }
                 // column tail (N not a multiple of 64): direct stores
-                for (int ch = ch64 * 2; ch < BN / 32; ++ch) {
+                for (int ch = ch64 * 2; ch < col_half * 4 + 4; ++ch) {
                     const int col0 = tc.n0 + ch * 32;
                     if (col0 >= p.N) break;
                     uint32_t v[32];
@@ -552,7 +598,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 }
             } else {
 #pragma unroll 1
-                for (int ch = 0; ch < BN / 32; ++ch) {
+                for (int ch = col_half * 4; ch < col_half * 4 + 4; ++ch) {
                     const int col0 = tc.n0 + ch * 32;
                     if (col0 >= p.N) break;                    // warp-uniform
     #ifdef CF_GEMM_EXPERIMENT
@@ -605,6 +651,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     }
                 }
     }
+            }   // out_kind != 4
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -764,6 +811,15 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     p.c_vec = (p.out_kind == 0) && (p.d_group_out != nullptr || ca % 16 == 0) && (p.ldc % 8 == 0) &&
               (p.bias == nullptr || reinterpret_cast<uintptr_t>(p.bias) % 4 == 0);
     if (!p.bias) p.bias_mode = 0;
+    if (p.out_kind == 4) {
+        // E4M3 output of width N/2: 16-byte stores need an aligned base and row pitch; whole 64-column groups only
+        if (!tma_ok || ca % 16 != 0 || p.ldc % 16 != 0 || p.N % 64 != 0 || !p.d_quant_scale || !p.d_amax_out ||
+            p.d_a_row_descale || p.d_b_col_descale || p.d_group_out) {
+            set_error("swiglu epilogue: needs TMA-aligned operands, N %% 64 == 0, a 16-byte aligned E4M3 output, per-tensor scales");
+            return CF_ERR_UNSUPPORTED;
+        }
+        p.c_vec = 0;
+    }
 #ifdef CF_GEMM_EXPERIMENT
     { const char* e = std::getenv("CF_GEMM_EXPERIMENT"); p.experiment = e ? std::atoi(e) : 0; }
     { const char* e = std::getenv("CF_GEMM_RASTER"); if (e && std::atoi(e) > 0) p.raster_m = std::atoi(e); }

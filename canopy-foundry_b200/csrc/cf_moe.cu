@@ -145,6 +145,22 @@ __global__ void __launch_bounds__(1024) k_build_row_lists(const float* __restric
     if (threadIdx.x == 0) counts[e] = s_base;
 }
 
+// Interleaves gate and up weight rows in groups of 32: output row (f/32)*64 + f%32 is gate row f, +32 is up row f.
+__global__ void __launch_bounds__(kT) k_interleave_gate_up(const uint8_t* __restrict__ gate, const uint8_t* __restrict__ up,
+                                                           uint8_t* __restrict__ out, long long experts, int F, int K) {
+    const long long chunks_per_row = K / 16;
+    const long long total = experts * 2 * F * chunks_per_row;
+    for (long long i = static_cast<long long>(blockIdx.x) * kT + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * kT) {
+        const long long row = i / chunks_per_row, c = i - row * chunks_per_row;
+        const long long e = row / (2 * F);
+        const int r = static_cast<int>(row - e * 2 * F);
+        const int f = (r >> 6) * 32 + (r & 31);
+        const uint8_t* src = ((r & 32) ? up : gate) + (e * F + f) * static_cast<long long>(K);
+        *reinterpret_cast<uint4*>(out + row * K + c * 16) = *reinterpret_cast<const uint4*>(src + c * 16);
+    }
+}
+
 __global__ void k_offsets(const int* counts, int* offsets, int E) {
     int acc = 0;
     for (int e = 0; e < E; ++e) { offsets[e] = acc; acc += counts[e]; }
@@ -309,6 +325,19 @@ int cf_gelu_forward(const void* d_x, void* d_out, size_t n, void* stream) {
     k_act<1><<<grid_for(n, kT * 16), kT, 0, as_stream(stream)>>>(static_cast<const uint16_t*>(d_x), nullptr,
                                                                  static_cast<uint16_t*>(d_out), n, vec);
     CF_LAUNCH_CHECK("gelu_forward");
+    return CF_OK;
+}
+
+int cf_fp8_interleave_gate_up(const void* d_gate8, const void* d_up8, void* d_out8, int num_experts, int F, int K, void* stream) {
+    CF_REQUIRE(num_experts >= 1 && F > 0 && K > 0, "cf_fp8_interleave_gate_up: bad shape");
+    CF_REQUIRE(F % 32 == 0 && K % 16 == 0, "cf_fp8_interleave_gate_up: F must be a multiple of 32 and K of 16");
+    CF_REQUIRE(d_gate8 && d_up8 && d_out8, "cf_fp8_interleave_gate_up: null pointer");
+    CF_REQUIRE(((reinterpret_cast<uintptr_t>(d_gate8) | reinterpret_cast<uintptr_t>(d_up8) | reinterpret_cast<uintptr_t>(d_out8)) % 16) == 0,
+               "cf_fp8_interleave_gate_up: pointers must be 16-byte aligned");
+    const size_t items = static_cast<size_t>(num_experts) * 2 * F * (K / 16);
+    k_interleave_gate_up<<<grid_for(items, kT * 4), kT, 0, as_stream(stream)>>>(
+        static_cast<const uint8_t*>(d_gate8), static_cast<const uint8_t*>(d_up8), static_cast<uint8_t*>(d_out8), num_experts, F, K);
+    CF_LAUNCH_CHECK("interleave_gate_up");
     return CF_OK;
 }
 

@@ -20,7 +20,7 @@ __all__ = [
     "fp8_quantize_transpose_e4m3", "fp8_quant_and_transpose_e4m3", "transpose_u8", "fp8_clip_probe",
     "fp8_elem_clip_count", "fp8_pack_bf16_e4m3_raw", "fp8_pack_bf16_e4m3_raw_and_dequant",
     "fp8_unpack_e4m3_raw_bf16", "lt_gemm_fp8_nt", "lt_gemm_fp8_tn_accum_f32", "gemm_fp8_nt_grouped", "gemm_fp8_nt_segments", "gemm_fp8_nt_segments_scatter",
-    "fp8_quant_act", "fp8_swiglu_quant_act", "refresh_fp8_weight", "fp8_linear_forward", "bias_add_strided_bf16", "swiglu_forward",
+    "fp8_quant_act", "fp8_swiglu_quant_act", "gemm_fp8_swiglu_quant_act", "fp8_interleave_gate_up", "refresh_fp8_weight", "fp8_linear_forward", "bias_add_strided_bf16", "swiglu_forward",
     "gelu_forward", "lion_step", "fp8_quantize_rowwise_e4m3", "swiglu_quantize_rowwise_e4m3", "swiglu_quantize_e4m3_record",
     "moe_topk_route_f32", "moe_build_expert_row_lists", "moe_expert_offsets_from_counts",
     "moe_gather_rows_u8", "moe_gather_rows_bf16", "moe_scatter_accumulate_rows_bf16",
@@ -231,6 +231,25 @@ def fp8_swiglu_quant_act(ctx, slot, gate, up, ld_in, rows, cols, out8):
     check(_L().cf_fp8_swiglu_quant_act(ctx.handle, C.byref(slot.c), _p(gate), _p(up), ld_in, rows, cols, _p(out8), _s()))
 
 
+def fp8_interleave_gate_up(w_gateup8):
+    """[E, 2F, K] with gate rows first -> the 32-row interleaved layout the fused SwiGLU GEMM reads."""
+    E, F2, K = w_gateup8.shape
+    F = F2 // 2
+    out = torch.empty_like(w_gateup8)
+    gate = w_gateup8[:, :F].contiguous()
+    up = w_gateup8[:, F:].contiguous()
+    check(_L().cf_fp8_interleave_gate_up(_p(gate), _p(up), _p(out), E, F, K, _s()))
+    return out
+
+
+def gemm_fp8_swiglu_quant_act(ctx, slot, num_segments, num_weights, segment_weight, max_total_rows, F, K, counts, offsets, A,
+                              lda, a_is_e5m2, a_descale, per_segment_a_descale, w_interleaved, w_descale, h8, ldh):
+    check(_L().cf_gemm_fp8_swiglu_quant_act(ctx.handle, C.byref(slot.c), num_segments, num_weights, _p(segment_weight),
+                                            max_total_rows, F, K, _p(counts), _p(offsets), _p(A), lda, int(a_is_e5m2),
+                                            _p(a_descale), int(per_segment_a_descale), _p(w_interleaved), _p(w_descale),
+                                            _p(h8), ldh, _s()))
+
+
 # ---------------------------------------------------------------- GEMMs
 def _epi(bias, bias_mode, a_row_descale, b_col_descale, out_fp32=False):
     if bias is None and a_row_descale is None and b_col_descale is None and not out_fp32:
@@ -409,8 +428,11 @@ class MoeSwigluFp8:
     rounding points are those of the reference's SwiGLU expert maths (src/trainer.cu:6510-6529) combined with its
     FP8 quantise / GEMM semantics. Weights: w_gateup8 [E,2F,H] and w_down8 [E,H,F] with one per-tensor descale each."""
 
-    def __init__(self, ctx, rows, H, F, E, top_k, device="cuda"):
+    def __init__(self, ctx, rows, H, F, E, top_k, device="cuda", fused_swiglu=False):
+        """fused_swiglu: gate/up GEMM, SwiGLU and re-quantise run as one launch (cf_gemm_fp8_swiglu_quant_act) and the
+        [T, 2F] bf16 intermediate is never materialised; forward() then expects w_gateup8 in the interleaved layout."""
         self.ctx, self.rows, self.H, self.F, self.E, self.k = ctx, rows, H, F, E, top_k
+        self.fused_swiglu = fused_swiglu
         T = rows * top_k
         self.T = T
         self.counts = torch.zeros(E, dtype=torch.int32, device=device)
@@ -418,7 +440,7 @@ class MoeSwigluFp8:
         self.idx = torch.zeros((E, rows), dtype=torch.int32, device=device)
         self.x8 = torch.empty((rows, H), dtype=torch.uint8, device=device)
         self.xc = torch.empty((T, H), dtype=torch.uint8, device=device)
-        self.gu = torch.empty((T, 2 * F), dtype=torch.bfloat16, device=device)
+        self.gu = None if fused_swiglu else torch.empty((T, 2 * F), dtype=torch.bfloat16, device=device)
         self.h8 = torch.empty((T, F), dtype=torch.uint8, device=device)
         self.yc = torch.empty((T, H), dtype=torch.bfloat16, device=device)
         self.slot_x = ActSlot(ctx, E4M3_MAX)
@@ -432,9 +454,13 @@ class MoeSwigluFp8:
         moe_expert_offsets_from_counts(self.counts, self.offsets, E)
         fp8_quant_act(self.ctx, self.slot_x, x, self.x8)
         moe_gather_all_u8(self.x8, self.xc, self.idx, self.counts, self.offsets, rows, E, H)
-        gemm_fp8_nt_grouped(self.ctx, E, T, 2 * F, H, self.counts, self.offsets, self.xc, H, False,
-                            _DevPtr(self.slot_x.c.descale_snapshot), False, w_gateup8, w_gateup_descale, self.gu, 2 * F)
-        fp8_swiglu_quant_act(self.ctx, self.slot_h, self.gu, self.gu.view(-1)[F:], 2 * F, T, F, self.h8)
+        if self.fused_swiglu:
+            gemm_fp8_swiglu_quant_act(self.ctx, self.slot_h, E, E, None, T, F, H, self.counts, self.offsets, self.xc, H, False,
+                                      _DevPtr(self.slot_x.c.descale_snapshot), False, w_gateup8, w_gateup_descale, self.h8, F)
+        else:
+            gemm_fp8_nt_grouped(self.ctx, E, T, 2 * F, H, self.counts, self.offsets, self.xc, H, False,
+                                _DevPtr(self.slot_x.c.descale_snapshot), False, w_gateup8, w_gateup_descale, self.gu, 2 * F)
+            fp8_swiglu_quant_act(self.ctx, self.slot_h, self.gu, self.gu.view(-1)[F:], 2 * F, T, F, self.h8)
         gemm_fp8_nt_grouped(self.ctx, E, T, H, F, self.counts, self.offsets, self.h8, F, False,
                             _DevPtr(self.slot_h.c.descale_snapshot), False, w_down8, w_down_descale, self.yc, H)
         moe_combine_all_bf16(mixed, self.yc, route_weights, self.idx, self.counts, self.offsets, rows, E, H)

@@ -225,6 +225,22 @@ int cf_fp8_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, size_t n, 
 int cf_fp8_swiglu_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_gate, const void* d_up, int ld_in, int rows,
                             int cols, void* d_out8, void* stream);
 
+/* Gate and up projection, SwiGLU and the re-quantisation that feeds the down projection in ONE GEMM launch: the
+ * epilogue turns each (gate, up) accumulator pair into bf16(silu(bf16 gate) * bf16 up), quantises it with the slot's
+ * delayed scale and records its amax, so the [rows, 2F] bf16 intermediate of src/trainer.cu:6304-6322 and :7138-7140
+ * never exists in HBM. Rounding points are those of the unfused sequence (bit-identical output). The weight is the
+ * stacked [num_weights, 2F, K] E4M3 tensor with gate and up rows interleaved in groups of 32 (cf_fp8_interleave_gate_up);
+ * d_h8 is E4M3 [rows, F] with row pitch ldh bytes (16-byte aligned). Dense form: d_counts = d_offsets = NULL,
+ * num_segments = 1, max_total_rows = M. Segment form: as cf_gemm_fp8_nt_segments. The first call on a fresh slot runs
+ * the GEMM twice (exact amax first). */
+int cf_gemm_fp8_swiglu_quant_act(cf_ctx* ctx, cf_act_slot* slot, int num_segments, int num_weights,
+                                 const int* d_segment_weight, int max_total_rows, int F, int K, const int* d_counts,
+                                 const int* d_offsets, const void* d_A, int lda, int a_is_e5m2, const float* d_a_descale,
+                                 int per_segment_a_descale, const void* d_W_interleaved, const float* d_w_descale,
+                                 void* d_h8, int ldh, void* stream);
+/* out[e, (f/32)*64 + f%32, :] = gate[e, f, :], out[e, (f/32)*64 + 32 + f%32, :] = up[e, f, :]; F % 32 == 0, K % 16 == 0. */
+int cf_fp8_interleave_gate_up(const void* d_gate8, const void* d_up8, void* d_out8, int num_experts, int F, int K, void* stream);
+
 /* One FP8-cached weight (Fp8Slot, src/trainer.cu:3284-3294) and its refresh (:4694-4712): [amax] -> scale ->
  * quantise into the native layout cache -> quantise-transpose into the other one. */
 typedef struct cf_fp8_weight {

@@ -266,3 +266,44 @@ def test_config5_large_shape_forward_and_dgrad(cfb, ctx, oracle):
     cfb.lt_gemm_fp8_nt(ctx, 1024, N, K, a8, K, False, da, fw.fwd8, fw.descale, c_full, N)
     assert torch.equal(c_sh, c_full[:, 3 * (N // 8):4 * (N // 8)])
     ctx.poll_status()
+
+
+@pytest.mark.parametrize("rows,H,F,E", [(700, 256, 512, 4), (64, 128, 96, 2)])
+def test_fused_swiglu_gemm_matches_the_unfused_sequence(cfb, ctx, oracle, rows, H, F, E):
+    """One launch (gate/up GEMM + SwiGLU + delayed-scale re-quantise in the epilogue, interleaved weight rows) against
+    GEMM -> bf16 [T,2F] -> swiglu + quant_act: same E4M3 bytes, same slot scalars, over three steps."""
+    k = 2
+    wgu8, dgu = _tensorquant(cfb, randn_bf16((E, 2 * F, H), std=0.05, seed=4))
+    wd8, dd = _tensorquant(cfb, randn_bf16((E, H, F), std=0.05, seed=5))
+    wgu8_il = cfb.fp8_interleave_gate_up(wgu8)
+    il = wgu8_il.cpu().numpy(); src = wgu8.cpu().numpy()
+    for f in (0, 31, 32, F - 1):
+        assert np.array_equal(il[1, (f // 32) * 64 + f % 32], src[1, f]) and np.array_equal(il[1, (f // 32) * 64 + 32 + f % 32], src[1, F + f])
+    plain = cfb.MoeSwigluFp8(ctx, rows, H, F, E, k)
+    fused = cfb.MoeSwigluFp8(ctx, rows, H, F, E, k, fused_swiglu=True)
+    for step in range(3):
+        x = randn_bf16((rows, H), std=1.0 + step, seed=10 + step)
+        rw_a, rw_b = _zipf_logits(rows, E, 20 + step), _zipf_logits(rows, E, 20 + step)
+        m_a = torch.zeros((rows, H), dtype=torch.bfloat16, device="cuda")
+        m_b = torch.zeros((rows, H), dtype=torch.bfloat16, device="cuda")
+        plain.forward(x, rw_a, wgu8, dgu, wd8, dd, m_a)
+        fused.forward(x, rw_b, wgu8_il, dgu, wd8, dd, m_b)
+        ctx.poll_status()
+        assert torch.equal(fused.h8, plain.h8), step
+        assert torch.equal(m_a.view(torch.int16), m_b.view(torch.int16)), step
+        a, b = plain.slot_h.scalars(), fused.slot_h.scalars()
+        for key in ("amax", "scale", "descale", "scale_snapshot", "descale_snapshot", "cursor", "count"):
+            assert a[key] == b[key], (step, key)
+    # dense form (one segment, no counts) against the same rows through the unfused kernels
+    M = 300
+    x8, dx = _tensorquant(cfb, randn_bf16((M, H), seed=31))
+    slot_a, slot_b = cfb.ActSlot(ctx, cfb.E4M3_MAX), cfb.ActSlot(ctx, cfb.E4M3_MAX)
+    gu = torch.empty((M, 2 * F), dtype=torch.bfloat16, device="cuda")
+    h_a = torch.empty((M, F), dtype=torch.uint8, device="cuda")
+    h_b = torch.empty((M, F), dtype=torch.uint8, device="cuda")
+    for step in range(2):
+        cfb.lt_gemm_fp8_nt(ctx, M, 2 * F, H, x8, H, False, dx, wgu8[0], dgu, gu, 2 * F)
+        cfb.fp8_swiglu_quant_act(ctx, slot_a, gu, gu.view(-1)[F:], 2 * F, M, F, h_a)
+        cfb.gemm_fp8_swiglu_quant_act(ctx, slot_b, 1, 1, None, M, F, H, None, None, x8, H, False, dx, False, wgu8_il[0], dgu, h_b, F)
+        ctx.poll_status()
+        assert torch.equal(h_a, h_b), step

@@ -141,8 +141,12 @@ def cpu_sample(orc, target_seconds, threads):
     t_pilot = run(pilot_rows)
     rows = int(min(M, max(pilot_rows, pilot_rows * target_seconds / max(t_pilot, 1e-6))))
     rows = max(threads, rows - rows % max(threads, 1))
-    t = run(rows)
-    return rows, t, 2.0 * rows * N * K / t / 1e12
+    # when the whole batch takes less than the target, repeat it until about target_seconds of CPU work are timed
+    t, passes = 0.0, 0
+    while passes == 0 or (rows == M and t < target_seconds and passes < 16):
+        t += run(rows)
+        passes += 1
+    return rows * passes, t, 2.0 * rows * passes * N * K / t / 1e12
 
 
 def run_reference(args):
@@ -159,7 +163,7 @@ def run_reference(args):
             vals.append((t, tf))
     ms = 1e3 * sum(t for t, _ in vals) / len(vals)
     tf = sum(v for _, v in vals) / len(vals)
-    sample = f"{rows} of {M} rows of X against the full W[{N}x{K}] per step (record-quantise + GEMM + bias), scaled by flops"
+    sample = f"{rows} rows ({rows / M:.2f} passes over the {M}-row batch) of X against the full W[{N}x{K}] per step (record-quantise + GEMM + bias), scaled by flops"
     line = {
         "impl": "reference", "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -486,7 +490,7 @@ def main():
             threads = orc.lib.orc_hw_threads()
             rows, tsec, tf = cpu_sample(orc, 12.0, threads)
             line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": threads, "kind": "port",
-                                    "sample": f"{rows} of {M} rows against the full W (record-quantise + GEMM + bias), {tsec:.1f} s"}
+                                    "sample": f"{rows} rows ({rows / M:.2f} passes over the {M}-row batch) against the full W: record-quantise + GEMM + bias, {tsec:.1f} s"}
         print(json.dumps(line), flush=True)
     ctx.close()
     if world > 1:

@@ -270,9 +270,10 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, i
 
 // kernels/activations.cu:11-17
 __device__ __forceinline__ float swiglu_sigmoid(float x) {
-    if (x >= 0.0f) return __fdiv_rn(1.0f, 1.0f + expf(-x));
-    const float e = expf(x);
-    return __fdiv_rn(e, 1.0f + e);
+    // Both branches of the reference (1/(1+exp(-x)) for x >= 0, exp(x)/(1+exp(x)) otherwise) share e = exp(-|x|);
+    // one IEEE division with the matching numerator gives the same bits without a divergent branch.
+    const float e = expf(-fabsf(x));
+    return __fdiv_rn(x >= 0.0f ? 1.0f : e, 1.0f + e);
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t r;

@@ -18,9 +18,10 @@ __device__ __forceinline__ uint16_t f2bf(float v) { return __bfloat16_as_ushort(
 
 // kernels/activations.cu:11-21
 __device__ __forceinline__ float stable_sigmoid(float x) {
-    if (x >= 0.0f) return __fdiv_rn(1.0f, 1.0f + expf(-x));
-    const float e = expf(x);
-    return __fdiv_rn(e, 1.0f + e);
+    // Both branches of the reference (1/(1+exp(-x)) for x >= 0, exp(x)/(1+exp(x)) otherwise) share e = exp(-|x|);
+    // one IEEE division with the matching numerator gives the same bits without a divergent branch.
+    const float e = expf(-fabsf(x));
+    return __fdiv_rn(x >= 0.0f ? 1.0f : e, 1.0f + e);
 }
 // kernels/moe.cu:513-514
 __device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + erff(v * 0.7071067811865476f)); }

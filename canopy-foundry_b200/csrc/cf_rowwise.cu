@@ -15,9 +15,10 @@ constexpr int kRT = 256;          // threads per row
 constexpr int kMaxVec = 8;        // 16-byte vectors (8 elements each) a thread keeps in registers: K <= 16384
 
 __device__ __forceinline__ float stable_sigmoid(float x) {
-    if (x >= 0.0f) return __fdiv_rn(1.0f, 1.0f + expf(-x));
-    const float e = expf(x);
-    return __fdiv_rn(e, 1.0f + e);
+    // Both branches of the reference (1/(1+exp(-x)) for x >= 0, exp(x)/(1+exp(x)) otherwise) share e = exp(-|x|);
+    // one IEEE division with the matching numerator gives the same bits without a divergent branch.
+    const float e = expf(-fabsf(x));
+    return __fdiv_rn(x >= 0.0f ? 1.0f : e, 1.0f + e);
 }
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 

@@ -25,7 +25,7 @@ __all__ = [
     "moe_topk_route_f32", "moe_build_expert_row_lists", "moe_expert_offsets_from_counts",
     "moe_gather_rows_u8", "moe_gather_rows_bf16", "moe_scatter_accumulate_rows_bf16",
     "moe_scale_accumulate_bf16", "moe_gather_all_u8", "moe_combine_all_bf16",
-    "moe_grouped_expert_forward_fp8", "launch_count", "swiglu_mlp_fp8_rowwise", "MoeSwigluFp8",
+    "moe_grouped_expert_forward_fp8", "launch_count", "swiglu_mlp_fp8_rowwise", "MoeSwigluFp8", "FfnSwigluFp8",
 ]
 
 
@@ -476,3 +476,27 @@ class _DevPtr:
 
     def data_ptr(self):
         return self._addr
+
+
+class FfnSwigluFp8:
+    """The reference's dense FP8 FFN (src/trainer.cu:6296-6322 and :7138-7146) with per-tensor delayed scaling:
+    fp8_quant_act(x) -> gate and up GEMMs -> swiglu_forward -> fp8_quant_act -> down GEMM, here as three launches
+    after the activation quantise: the gate/up GEMM carries SwiGLU and the re-quantise in its epilogue
+    (cf_gemm_fp8_swiglu_quant_act), so the [M, 2F] bf16 intermediate is never written. `w_gateup8_interleaved` is the
+    [2F, H] E4M3 tensor in the 32-row interleaved layout (fp8_interleave_gate_up), w_down8 is [H, F]."""
+
+    def __init__(self, ctx, M, H, F, device="cuda"):
+        self.ctx, self.M, self.H, self.F = ctx, M, H, F
+        self.x8 = torch.empty((M, H), dtype=torch.uint8, device=device)
+        self.h8 = torch.empty((M, F), dtype=torch.uint8, device=device)
+        self.slot_x = ActSlot(ctx, E4M3_MAX)
+        self.slot_h = ActSlot(ctx, E4M3_MAX)
+
+    def forward(self, x, w_gateup8_interleaved, w_gateup_descale, w_down8, w_down_descale, y, bias=None, bias_mode=2):
+        M, H, F = self.M, self.H, self.F
+        fp8_quant_act(self.ctx, self.slot_x, x, self.x8)
+        gemm_fp8_swiglu_quant_act(self.ctx, self.slot_h, 1, 1, None, M, F, H, None, None, self.x8, H, False,
+                                  _DevPtr(self.slot_x.c.descale_snapshot), False, w_gateup8_interleaved, w_gateup_descale,
+                                  self.h8, F)
+        lt_gemm_fp8_nt(self.ctx, M, y.shape[1], F, self.h8, F, False, _DevPtr(self.slot_h.c.descale_snapshot), w_down8,
+                       w_down_descale, y, y.stride(0), bias=bias, bias_mode=bias_mode)

@@ -307,3 +307,41 @@ def test_fused_swiglu_gemm_matches_the_unfused_sequence(cfb, ctx, oracle, rows, 
         cfb.gemm_fp8_swiglu_quant_act(ctx, slot_b, 1, 1, None, M, F, H, None, None, x8, H, False, dx, False, wgu8_il[0], dgu, h_b, F)
         ctx.poll_status()
         assert torch.equal(h_a, h_b), step
+
+
+def test_dense_ffn_fused_against_reference_sequence_and_oracle(cfb, ctx, oracle):
+    """The reference's dense FP8 FFN with per-tensor delayed scaling: fused three-launch form against the unfused operator
+    sequence (bit-identical) and against the host oracle (<= 1e-2), over two steps, at a reduced size; then the
+    configuration-3 size (16384 x 4096 x 14336) against sampled oracle rows."""
+    for (M, H, F, sample_rows) in [(384, 256, 512, None), (16384, 4096, 14336, [0, 255, 256, 9000, 16383])]:
+        wgu8, dgu = _tensorquant(cfb, randn_bf16((1, 2 * F, H), std=0.02, seed=2))
+        wd8, dd = _tensorquant(cfb, randn_bf16((H, F), std=0.02, seed=3))
+        wgu_il = cfb.fp8_interleave_gate_up(wgu8)[0]
+        ffn = cfb.FfnSwigluFp8(ctx, M, H, F)
+        sx, sh = cfb.ActSlot(ctx, cfb.E4M3_MAX), cfb.ActSlot(ctx, cfb.E4M3_MAX)
+        y = torch.empty((M, H), dtype=torch.bfloat16, device="cuda")
+        for step in range(2):
+            x = randn_bf16((M, H), std=1.0 + step, seed=40 + step)
+            ffn.forward(x, wgu_il, dgu, wd8, dd, y)
+            ctx.poll_status()
+            if sample_rows is None:
+                # the unfused operator sequence the reference runs
+                x8 = torch.empty((M, H), dtype=torch.uint8, device="cuda")
+                cfb.fp8_quant_act(ctx, sx, x, x8)
+                gu = torch.empty((M, 2 * F), dtype=torch.bfloat16, device="cuda")
+                cfb.lt_gemm_fp8_nt(ctx, M, 2 * F, H, x8, H, False, cfb.ops._DevPtr(sx.c.descale_snapshot), wgu8[0], dgu, gu, 2 * F)
+                hb = torch.empty((M, F), dtype=torch.bfloat16, device="cuda")
+                cfb.swiglu_forward(gu[:, :F].contiguous(), gu[:, F:].contiguous(), hb)
+                h8 = torch.empty((M, F), dtype=torch.uint8, device="cuda")
+                cfb.fp8_quant_act(ctx, sh, hb, h8)
+                y2 = torch.empty((M, H), dtype=torch.bfloat16, device="cuda")
+                cfb.lt_gemm_fp8_nt(ctx, M, H, F, h8, F, False, cfb.ops._DevPtr(sh.c.descale_snapshot), wd8, dd, y2, H)
+                assert torch.equal(ffn.h8, h8) and torch.equal(y.view(torch.int16), y2.view(torch.int16)), step
+            rows = list(range(0, M, max(1, M // 24))) if sample_rows is None else sample_rows
+            dx = np.float32(ffn.slot_x.scalars()["descale_snapshot"])
+            s_h = np.float32(ffn.slot_h.scalars()["scale_snapshot"]); d_h = np.float32(ffn.slot_h.scalars()["descale_snapshot"])
+            gu_o = oracle.gemm_fp8_nt(ffn.x8[rows].cpu().numpy(), wgu8[0].cpu().numpy(), dx, dgu[0].item())
+            h_o = oracle.swiglu_forward(np.ascontiguousarray(gu_o[:, :F]), np.ascontiguousarray(gu_o[:, F:]))
+            y_o = oracle.gemm_fp8_nt(oracle.quantize_bf16(h_o, s_h), wd8.cpu().numpy(), d_h, dd[0].item())
+            assert rel_fro(y[rows].float().cpu().numpy(), oracle.bf16_to_f32(y_o)) < TOL, (M, step)
+        del ffn

@@ -226,6 +226,31 @@ int cf_gemm_fp8_tn_accum_bf16(cf_ctx* ctx, int M, int N, int K, const void* d_Xt
     return tn_accum(ctx, M, N, K, d_Xt_e4m3, d_ds_x, d_dYt_e5m2, d_ds_dy, d_dW, ldc, 3, as_stream(stream));
 }
 
+static int dw_accum(cf_ctx* ctx, int M, int N, int K, const void* X8, int ldx, const float* ds_x, const void* dY8, int ldy,
+                    const float* ds_dy, void* dW, int ldc, int out_kind, cudaStream_t st) {
+    const int rc = check_gemm_common("cf_gemm_fp8_dw_accum", ctx, M, N, K, X8, dY8, dW, ds_x, ds_dy);
+    if (rc != CF_OK || M == 0 || N == 0 || K == 0) return rc;
+    CF_REQUIRE(ldx >= M && ldy >= N && ldc >= N, "cf_gemm_fp8_dw_accum: leading dimension smaller than the row length");
+    GemmParams p;
+    p.M = M; p.N = N; p.K = K;
+    p.mn_major = 1; p.ldb = ldy;
+    p.d_a_descale = ds_x; p.d_b_descale = ds_dy;
+    p.C = dW; p.ldc = ldc; p.out_kind = out_kind;
+    p.a_e5m2 = 0; p.b_e5m2 = 1;
+    p.d_status = reinterpret_cast<Ctx*>(ctx)->d_status;
+    const int tiles = ((M + gemm_tile_m() - 1) / gemm_tile_m()) * ((N + gemm_tile_n() - 1) / gemm_tile_n());
+    return launch_gemm_fp8_nt(X8, ldx, K, dY8, K, p, tiles, st);
+}
+
+int cf_gemm_fp8_dw_accum_f32(cf_ctx* ctx, int M, int N, int K, const void* d_X_e4m3, int ldx, const float* d_ds_x,
+                             const void* d_dY_e5m2, int ldy, const float* d_ds_dy, float* d_dW, int ldc, void* stream) {
+    return dw_accum(ctx, M, N, K, d_X_e4m3, ldx, d_ds_x, d_dY_e5m2, ldy, d_ds_dy, d_dW, ldc, 2, as_stream(stream));
+}
+int cf_gemm_fp8_dw_accum_bf16(cf_ctx* ctx, int M, int N, int K, const void* d_X_e4m3, int ldx, const float* d_ds_x,
+                              const void* d_dY_e5m2, int ldy, const float* d_ds_dy, void* d_dW, int ldc, void* stream) {
+    return dw_accum(ctx, M, N, K, d_X_e4m3, ldx, d_ds_x, d_dY_e5m2, ldy, d_ds_dy, d_dW, ldc, 3, as_stream(stream));
+}
+
 int cf_gemm_fp8_nt_grouped(cf_ctx* ctx, int num_experts, int max_total_rows, int N, int K, const int* d_counts,
                            const int* d_offsets, const void* d_A, int lda, int a_is_e5m2, const float* d_a_descale,
                            int per_expert_a_descale, const void* d_B, const float* d_b_descale, void* d_C, int ldc,

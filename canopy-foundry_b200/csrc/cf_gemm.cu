@@ -111,6 +111,12 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
                  ::"l"(map), "r"(src), "r"(x), "r"(y), "l"(policy) : "memory");
 }
+// fp32 accumulate (beta = 1) as a TMA reduction: the staged tile is added to global memory in L2, one addition per
+// element like a read-modify-write epilogue, but with whole 128-byte lines.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read_0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
@@ -200,8 +206,11 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
 
 // kind::f8f6f4 instruction descriptor: D fp32 (bits 4-5 = 1), A format bits 7-9, B format bits 10-12
 // (0 = E4M3, 1 = E5M2), both operands K-major (bits 15,16 = 0), N>>3 in bits 17-22, M>>4 in bits 24-28.
-__device__ __forceinline__ uint32_t make_idesc(int a_e5m2, int b_e5m2, int mma_m) {
+// mn_major: both operands are MN-major in shared memory (rows of the tile run along K, 128 contiguous bytes along
+// M / N): bits 15 and 16.
+__device__ __forceinline__ uint32_t make_idesc(int a_e5m2, int b_e5m2, int mma_m, int mn_major) {
     return (1u << 4) | (static_cast<uint32_t>(a_e5m2) << 7) | (static_cast<uint32_t>(b_e5m2) << 10) |
+           (mn_major ? ((1u << 15) | (1u << 16)) : 0u) |
            (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(mma_m >> 4) << 24);
 }
 
@@ -343,7 +352,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
-        if (p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
+        if (p.tma_store || p.tma_reduce) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
     }
     if (warp == 1) {
         if (PAIR) {
@@ -391,8 +400,12 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
 #endif
                     if (PAIR) {
                         if (leader) mbar_expect_tx(full_bar + 8 * s, 2 * (A_STAGE + B_STAGE));
-                        tma_load_2d_pair(smem_a + s * A_STAGE, &map_a, full_dst + 8 * s, kb * BK, a_row);
-                        tma_load_2d_pair(smem_b + s * B_STAGE, &map_b, full_dst + 8 * s, kb * BK, b_row);
+                        // K-major operands: x runs along K; MN-major operands ([K, M] / [K, N] in memory): x runs
+                        // along M / N and the box rows are K
+                        const int ax = p.mn_major ? a_row : kb * BK, ay = p.mn_major ? kb * BK : a_row;
+                        const int bx = p.mn_major ? b_row : kb * BK, by = p.mn_major ? kb * BK : b_row;
+                        tma_load_2d_pair(smem_a + s * A_STAGE, &map_a, full_dst + 8 * s, ax, ay);
+                        tma_load_2d_pair(smem_b + s * B_STAGE, &map_b, full_dst + 8 * s, bx, by);
                     } else {
                         mbar_expect_tx(full_bar + 8 * s, A_STAGE + B_STAGE);
                         tma_load_2d(smem_a + s * A_STAGE, &map_a, full_bar + 8 * s, kb * BK, a_row);
@@ -411,7 +424,10 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
         if (lane == 0 && leader) {
-            const uint32_t idesc = make_idesc(p.a_e5m2, p.b_e5m2, TM);
+            const uint32_t idesc = make_idesc(p.a_e5m2, p.b_e5m2, TM, p.mn_major);
+            // K-major: 32 elements of K are 32 bytes inside the swizzle row (+2 in 16-byte units); MN-major: 32 rows
+            // of 128 bytes (+256)
+            const uint64_t kstep = p.mn_major ? 256u : 2u;
             int it = 0, local_tile = 0;
             bool ok = true;
             for (int tile = unit; ok && tile < total_tiles; tile += n_units, ++local_tile) {
@@ -428,8 +444,8 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
 #pragma unroll
                     for (int kk = 0; kk < BK / UMMA_K; ++kk) {
                         // advancing 32 bytes inside the 128B swizzle atom = +2 in the (addr >> 4) field
-                        if (PAIR) umma_f8_pair(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
-                        else umma_f8(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        if (PAIR) umma_f8_pair(tmem_d, adesc + kstep * kk, bdesc + kstep * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        else umma_f8(tmem_d, adesc + kstep * kk, bdesc + kstep * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
                     }
                     // frees the stage (in both CTAs of a pair) once these MMAs have read it
                     if (PAIR) tcgen05_commit_pair(empty_bar + 8 * s); else tcgen05_commit(empty_bar + 8 * s);
@@ -512,7 +528,46 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             // ragged rows of a grouped tile, column tails and the fp32 / accumulate forms use direct stores.
             const int warp_row0 = static_cast<int>(cta_rank) * BM + quarter * 32;
             const bool warp_rows_full = (p.d_counts == nullptr) || (warp_row0 + 32 <= tc.valid_rows);
-            if (p.tma_store && warp_rows_full && warp_row0 < tc.valid_rows) {
+            if (p.tma_reduce && warp_rows_full && warp_row0 < tc.valid_rows) {
+                // dW += ...: 32 columns (one 128-byte line of fp32) per box
+                const uint32_t buf = smem_c + static_cast<uint32_t>(warp - 2) * C_BOX_BYTES;
+                const uint32_t row_off = static_cast<uint32_t>(lane) * 128u;
+                const uint32_t sw = static_cast<uint32_t>(lane & 7);
+                const float dab = da * db_t;
+                int ch = col_half * 4;
+#pragma unroll 1
+                for (; ch < col_half * 4 + 4; ++ch) {
+                    const int col0 = tc.n0 + ch * 32;
+                    if (col0 + 32 > p.N) break;            // warp-uniform; the tail takes the direct path below
+                    uint32_t v[32];
+                    tmem_ld32(taddr + ch * 32, v);
+                    tmem_ld_wait();
+                    if (lane == 0) bulk_wait_read_0();
+                    __syncwarp();
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        st_shared_v4(buf + row_off + ((static_cast<uint32_t>(q) ^ sw) << 4),
+                                     __float_as_uint(__uint_as_float(v[4 * q]) * dab), __float_as_uint(__uint_as_float(v[4 * q + 1]) * dab),
+                                     __float_as_uint(__uint_as_float(v[4 * q + 2]) * dab), __float_as_uint(__uint_as_float(v[4 * q + 3]) * dab));
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_reduce_add_2d(&map_c, buf, col0, tc.row0 + warp_row0);
+                        bulk_commit();
+                    }
+                }
+                for (; ch < col_half * 4 + 4; ++ch) {      // column tail: direct read-modify-write
+                    const int col0 = tc.n0 + ch * 32;
+                    if (col0 >= p.N) break;
+                    uint32_t v[32];
+                    tmem_ld32(taddr + ch * 32, v);
+                    tmem_ld_wait();
+                    if (!row_ok) continue;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (col0 + j < p.N) store_one(p, tc.out_base, grow, col0 + j, __uint_as_float(v[j]), da, db_t);
+                }
+            } else if (p.tma_store && warp_rows_full && warp_row0 < tc.valid_rows) {
                 const uint32_t buf = smem_c + static_cast<uint32_t>(warp - 2) * C_BOX_BYTES;
                 const uint32_t row_off = static_cast<uint32_t>(lane) * 128u;
                 const uint32_t sw = static_cast<uint32_t>(lane & 7);
@@ -798,6 +853,21 @@ int make_map_c(CUtensorMap* map, const void* ptr, long long rows, long long N, l
     return CF_OK;
 }
 
+// fp32 accumulator tensor [rows, N] with row pitch ldc elements, box {32 columns, 32 rows}, 128B swizzle.
+int make_map_c_f32(CUtensorMap* map, const void* ptr, long long rows, long long N, long long ldc) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { set_error("cuTensorMapEncodeTiled entry point not available"); return CF_ERR_CUDA; }
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldc) * 4};
+    const cuuint32_t box[2] = {32, 32};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (fp32 output) failed with CUresult %d", static_cast<int>(r)); return CF_ERR_CUDA; }
+    return CF_OK;
+}
+
 }  // namespace
 
 int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const void* d_B, long long b_rows,
@@ -806,7 +876,9 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     const int rc = require_sm100();
     if (rc != CF_OK) return rc;
     const uintptr_t aa = reinterpret_cast<uintptr_t>(d_A), ba = reinterpret_cast<uintptr_t>(d_B);
-    const bool tma_ok = (aa % 16 == 0) && (ba % 16 == 0) && (lda % 16 == 0) && (p.K % 16 == 0);
+    const bool tma_ok = p.mn_major ? ((aa % 16 == 0) && (ba % 16 == 0) && (lda % 16 == 0) && (p.ldb % 16 == 0))
+                                   : ((aa % 16 == 0) && (ba % 16 == 0) && (lda % 16 == 0) && (p.K % 16 == 0));
+    if (p.mn_major && !tma_ok) { set_error("MN-major operands need 16-byte aligned bases and row pitches"); return CF_ERR_UNSUPPORTED; }
     const uintptr_t ca = reinterpret_cast<uintptr_t>(p.C);
     // per-segment output buffers: the caller guarantees 16-byte aligned bases (checked at the API boundary)
     p.c_vec = (p.out_kind == 0) && (p.d_group_out != nullptr || ca % 16 == 0) && (p.ldc % 8 == 0) &&
@@ -835,23 +907,39 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     // keep the 128-row single-CTA tiles. CF_GEMM_TILE=1|2 forces a form (A/B measurements, tests).
     static const int forced = [] { const char* e = std::getenv("CF_GEMM_TILE"); return e ? std::atoi(e) : 0; }();
     const long long rows_per_group = (p.d_counts ? a_rows / (p.groups > 0 ? p.groups : 1) : p.M);
-    bool pair = forced == 2 || (forced != 1 && rows_per_group >= 512);
+    bool pair = forced == 2 || p.mn_major || (forced != 1 && rows_per_group >= 512);
     const int pairs = pair ? max_resident_pairs() : 0;
     if (pairs <= 0) pair = false;
 
     CUtensorMap map_a, map_b, map_c;
-    int r = make_map(&map_a, d_A, a_rows, p.K, lda, BM);
-    if (r != CF_OK) return r;
-    r = make_map(&map_b, d_B, b_rows, p.K, p.K, pair ? Cfg<true>::B_ROWS : Cfg<false>::B_ROWS);
-    if (r != CF_OK) return r;
+    int r;
+    if (p.mn_major) {
+        // A is [K, M] with pitch lda, B is [K, N] with pitch p.ldb: boxes of 128 bytes along M / N by BK rows of K.
+        // Only the pair form is built for this layout (each CTA's share of both operands is one 128-byte swizzle atom).
+        if (!pair) { set_error("MN-major operands need the CTA-pair form (at least 512 rows, clusters available)"); return CF_ERR_UNSUPPORTED; }
+        r = make_map(&map_a, d_A, p.K, p.M, lda, BK);
+        if (r != CF_OK) return r;
+        r = make_map(&map_b, d_B, p.K, p.N, p.ldb, BK);
+        if (r != CF_OK) return r;
+    } else {
+        r = make_map(&map_a, d_A, a_rows, p.K, lda, BM);
+        if (r != CF_OK) return r;
+        r = make_map(&map_b, d_B, b_rows, p.K, p.K, pair ? Cfg<true>::B_ROWS : Cfg<false>::B_ROWS);
+        if (r != CF_OK) return r;
+    }
     p.c_rows = p.d_counts ? a_rows : p.M;
     p.tma_store = (p.c_vec && p.d_group_out == nullptr && p.N >= C_BOX_COLS &&
                    (p.bias == nullptr || reinterpret_cast<uintptr_t>(p.bias) % 16 == 0) &&
                    (p.d_b_col_descale == nullptr || reinterpret_cast<uintptr_t>(p.d_b_col_descale) % 16 == 0)) ? 1 : 0;
     static const bool no_tma_store = [] { const char* e = std::getenv("CF_GEMM_DIRECT_STORE"); return e && e[0] == '1'; }();
     if (no_tma_store) p.tma_store = 0;
+    p.tma_reduce = (p.out_kind == 2 && ca % 16 == 0 && p.ldc % 4 == 0 && p.N >= 32 && p.d_group_out == nullptr &&
+                    p.d_a_row_descale == nullptr && p.d_b_col_descale == nullptr && !no_tma_store) ? 1 : 0;
     if (p.tma_store) {
         r = make_map_c(&map_c, p.C, p.c_rows, p.N, p.ldc);
+        if (r != CF_OK) return r;
+    } else if (p.tma_reduce) {
+        r = make_map_c_f32(&map_c, p.C, p.c_rows, p.N, p.ldc);
         if (r != CF_OK) return r;
     } else {
         map_c = map_a;   // never dereferenced by the kernel when tma_store == 0

@@ -29,7 +29,10 @@ struct GemmParams {
     int bias_mode = 0;
     int c_vec = 0;                  // filled by the launcher
     int tma_store = 0;              // filled by the launcher: bf16 output goes through shared memory + TMA stores
+    int tma_reduce = 0;             // filled by the launcher: fp32 beta=1 output goes through TMA reduce-add
     long long c_rows = 0;           // filled by the launcher: row extent of C for the store tensor map
+    int mn_major = 0;               // operands are [K, M] and [K, N] in memory (un-transposed weight-gradient form)
+    long long ldb = 0;              // mn_major: row pitch of B in bytes
     int a_e5m2 = 0;
     int b_e5m2 = 0;
     int* d_status = nullptr;        // context status word (bounded-wait failures)

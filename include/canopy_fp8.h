@@ -152,6 +152,18 @@ int cf_gemm_fp8_tn_accum_f32(cf_ctx* ctx, int M, int N, int K, const void* d_Xt_
 int cf_gemm_fp8_tn_accum_bf16(cf_ctx* ctx, int M, int N, int K, const void* d_Xt_e4m3, const float* d_ds_x,
                               const void* d_dYt_e5m2, const float* d_ds_dy, void* d_dW, int ldc, void* stream);
 
+/* The weight-gradient GEMM of src/trainer.cu:8269-8317 without its two byte transposes: the reference transposes the
+ * activation snapshot and the gradient (transpose_u8 / the dual quantise kernel) so that cuBLASLt can run the TN form;
+ * here the tensor cores read both operands as they lie in memory,
+ *   dW[M,N] += (*d_ds_x * *d_ds_dy) * sum_k X8[k,m] * dY8[k,n],
+ * X8 E4M3 [K, M] with row pitch ldx, dY8 E5M2 [K, N] with row pitch ldy (K = tokens), dW fp32 or bf16 with pitch ldc.
+ * Needs 16-byte aligned bases and pitches and the CTA-pair form (CF_ERR_UNSUPPORTED otherwise: use the transposes and
+ * cf_gemm_fp8_tn_accum_*). No counterpart in the reference. */
+int cf_gemm_fp8_dw_accum_f32(cf_ctx* ctx, int M, int N, int K, const void* d_X_e4m3, int ldx, const float* d_ds_x,
+                             const void* d_dY_e5m2, int ldy, const float* d_ds_dy, float* d_dW, int ldc, void* stream);
+int cf_gemm_fp8_dw_accum_bf16(cf_ctx* ctx, int M, int N, int K, const void* d_X_e4m3, int ldx, const float* d_ds_x,
+                              const void* d_dY_e5m2, int ldy, const float* d_ds_dy, void* d_dW, int ldc, void* stream);
+
 /* The ragged per-expert GEMMs of src/trainer.cu:6893-6927 as ONE launch with a device-side schedule:
  * for every expert e, rows [d_offsets[e], d_offsets[e]+d_counts[e]) of the compact A8 [total_rows,K]
  * are multiplied with B8[e] ([N,K] slice of a [E,N,K] block) into the same rows of compact C [.,ldc].

@@ -262,3 +262,43 @@ def test_bounded_wait_reports_a_status_and_leaves_the_context_usable(cfb, ctx, o
     ctx.poll_status()
     want = _oracle_gemm(oracle, a8, w8, da, dw)
     assert rel_fro(oracle.bf16_to_f32(bf16_to_u16(c)), oracle.bf16_to_f32(want)) < TIGHT
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 512, 256), (1024, 768, 4096), (640, 1008, 2000), (4096, 4096, 8192)])
+def test_weight_gradient_without_transposes(cfb, ctx, oracle, M, N, K):
+    """dW += X^T . dY read from the un-transposed [tokens, features] operands (MN-major tensor-core operands) equals the
+    reference route: byte-transpose both operands, then the TN GEMM (src/trainer.cu:8269-8277) — bit for bit in fp32."""
+    x8, dx = _quant(cfb, randn_bf16((K, M), seed=81))                    # activations  [tokens, in]
+    dy8, dd = _quant(cfb, randn_bf16((K, N), std=1e-3, seed=82), e5m2=True)   # gradient [tokens, out]
+    init = torch.randn((M, N), device="cuda") * 1e-2
+    dw = init.clone()
+    cfb.gemm_fp8_dw_accum(ctx, M, N, K, x8, M, dx, dy8, N, dd, dw, N)
+    ctx.poll_status()
+    xt = torch.empty((M, K), dtype=torch.uint8, device="cuda"); dyt = torch.empty((N, K), dtype=torch.uint8, device="cuda")
+    cfb.transpose_u8(x8, xt, K, M); cfb.transpose_u8(dy8, dyt, K, N)
+    if M * N <= (1 << 22):
+        want = oracle.gemm_fp8_nt(xt.cpu().numpy(), dyt.cpu().numpy(), dx[0].item(), dd[0].item(), b_is_e5m2=True, out_kind=2,
+                                  C_init=init.cpu().numpy())
+        assert rel_fro(dw.cpu().numpy(), want) < 1e-5
+    if K % 16 == 0:
+        dw2 = init.clone()
+        cfb.lt_gemm_fp8_tn_accum_f32(ctx, M, N, K, xt, dx, dyt, dd, dw2, N)
+        assert rel_fro(dw.cpu().numpy(), dw2.cpu().numpy()) < 1e-6
+    if M * N > (1 << 22):
+        return                       # the bf16 form is checked at the smaller sizes (host oracle time)
+    dwb = init.to(torch.bfloat16)
+    w0 = bf16_to_u16(dwb).copy()
+    cfb.gemm_fp8_dw_accum(ctx, M, N, K, x8, M, dx, dy8, N, dd, dwb, N)
+    wantb = oracle.gemm_fp8_nt(xt.cpu().numpy(), dyt.cpu().numpy(), dx[0].item(), dd[0].item(), b_is_e5m2=True, out_kind=3, C_init=w0)
+    assert rel_fro(oracle.bf16_to_f32(bf16_to_u16(dwb)), oracle.bf16_to_f32(wantb)) < TIGHT
+    ctx.poll_status()
+
+
+def test_weight_gradient_unaligned_pitch_is_refused(cfb, ctx):
+    x8 = torch.zeros((64, 520), dtype=torch.uint8, device="cuda")
+    dy8 = torch.zeros((64, 1000), dtype=torch.uint8, device="cuda")
+    d = f32_scalar(1.0)
+    dw = torch.zeros((520, 1000), dtype=torch.float32, device="cuda")
+    with pytest.raises(cfb.CanopyError) as ei:
+        cfb.gemm_fp8_dw_accum(ctx, 520, 1000, 64, x8, 520, d, dy8, 1000, d, dw, 1000)
+    assert ei.value.code == cfb._capi.CF_ERR_UNSUPPORTED

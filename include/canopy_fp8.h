@@ -285,9 +285,9 @@ int cf_fp8_linear_forward(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, int M
  * outputs; the call itself uses no cudaMalloc, cudaFree or other allocating routine.
  *   y[M,N] bf16 (row stride ldy) = (*d_x_descale * *d_w_descale) * e4m3(x * *d_x_scale) . w8^T  [+ bias]
  * d_status_or_null: optional device int that receives a non-zero code if a bounded device-side wait gave up.
- * The first call on each device looks up the array's device address; make that first call outside any
- * stream capture. All calls share the one array and it keeps the previous call's contents (the call clears
- * the word it needs zeroed): two calls that overlap on the GPU, e.g. on different streams, race on it. */
+ * The first call on each device looks up the array's device address. All calls share the one array and it
+ * keeps the previous call's contents (the call clears the word it needs zeroed): two calls that overlap on
+ * the GPU, e.g. on different streams, race on it. */
 int cf_fp8_linear_static_scratch(const void* d_x, int M, int K, const float* d_x_scale, const float* d_x_descale,
                                  const void* d_w8, const float* d_w_descale, int N, const void* d_bias, int bias_mode,
                                  void* d_y, int ldy, int* d_status_or_null, void* stream);

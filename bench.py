@@ -236,10 +236,11 @@ def run_moe(args):
     wgu8, dgu = quant_experts((n_local, 2 * F, H), 0.02, 50 + rank)
     wd8, dd = quant_experts((n_local, H, F), 0.02, 70 + rank)
     mixed = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
-    fused_swiglu = not use_ep and not args.moe_unfused_swiglu
+    fused_swiglu = not args.moe_unfused_swiglu
     if fused_swiglu:
         wgu8 = cfb.fp8_interleave_gate_up(wgu8)       # one-time weight layout for the fused SwiGLU epilogue
-    layer = par.EpMoeSwigluFp8(cfb, ctx, rows, H, F, E, TOPK, device=dev, fused_return=args.moe_fused_return) if use_ep else \
+    layer = par.EpMoeSwigluFp8(cfb, ctx, rows, H, F, E, TOPK, device=dev, fused_return=args.moe_fused_return,
+                               fused_swiglu=fused_swiglu) if use_ep else \
         cfb.MoeSwigluFp8(ctx, rows, H, F, E, TOPK, device=dev, fused_swiglu=fused_swiglu)
 
     def step():

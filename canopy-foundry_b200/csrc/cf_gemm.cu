@@ -293,7 +293,7 @@ __device__ __forceinline__ uint16_t to_bf16_bits(float v) { return __bfloat16_as
 
 // One output value through the epilogue contract (used by the scalar store paths and by the SIMT kernel).
 __device__ __forceinline__ void store_one(const GemmParams& p, void* cbase, long long grow, int col, float acc, float da, float db) {
-    float v = acc * (da * db);
+    float v = __fmul_rn(acc, da * db);
     if (p.out_kind == 0) {
         uint16_t* c = static_cast<uint16_t*>(cbase) + grow * p.ldc + col;
         if (p.bias && p.bias_mode == 1) v += bf16_bits_to_f32(p.bias[col]);
@@ -304,10 +304,10 @@ __device__ __forceinline__ void store_one(const GemmParams& p, void* cbase, long
         static_cast<float*>(cbase)[grow * p.ldc + col] = v;
     } else if (p.out_kind == 2) {
         float* c = static_cast<float*>(cbase) + grow * p.ldc + col;
-        *c = *c + v;
+        *c = __fadd_rn(*c, v);                   // the product is rounded before the addition (beta = 1 of a library GEMM)
     } else {
         uint16_t* c = static_cast<uint16_t*>(cbase) + grow * p.ldc + col;
-        *c = to_bf16_bits(bf16_bits_to_f32(*c) + v);
+        *c = to_bf16_bits(__fadd_rn(bf16_bits_to_f32(*c), v));
     }
 }
 
@@ -529,7 +529,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             const int warp_row0 = static_cast<int>(cta_rank) * BM + quarter * 32;
             const bool warp_rows_full = (p.d_counts == nullptr) || (warp_row0 + 32 <= tc.valid_rows);
             if (p.tma_reduce && warp_rows_full && warp_row0 < tc.valid_rows) {
-                // dW += ...: 32 columns (one 128-byte line of fp32) per box
+                // fp32 output, added (dW += ...) or stored (partial products): 32 columns = one 128-byte line per box row
                 const uint32_t buf = smem_c + static_cast<uint32_t>(warp - 2) * C_BOX_BYTES;
                 const uint32_t row_off = static_cast<uint32_t>(lane) * 128u;
                 const uint32_t sw = static_cast<uint32_t>(lane & 7);
@@ -552,7 +552,8 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {
-                        tma_reduce_add_2d(&map_c, buf, col0, tc.row0 + warp_row0);
+                        if (p.tma_reduce == 2) tma_store_2d(&map_c, buf, col0, tc.row0 + warp_row0, store_policy);
+                        else tma_reduce_add_2d(&map_c, buf, col0, tc.row0 + warp_row0);
                         bulk_commit();
                     }
                 }
@@ -695,6 +696,25 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                         uint4* dst = reinterpret_cast<uint4*>(crow);
     #pragma unroll
                         for (int q = 0; q < 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+                    } else if (p.out_kind == 3 && p.c_vec && full && !p.d_b_col_descale) {
+                        // bf16 accumulate: 64 bytes of the row in, one fp32 addition and one rounding per element, 64 bytes out
+                        uint4* crow = reinterpret_cast<uint4*>(static_cast<uint16_t*>(tc.out_base) + grow * p.ldc + col0);
+                        const float dab = da * db_t;
+                        uint4 old4[4];
+    #pragma unroll
+                        for (int q = 0; q < 4; ++q) old4[q] = crow[q];
+    #pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint32_t o[4] = {old4[q].x, old4[q].y, old4[q].z, old4[q].w};
+                            uint32_t w4[4];
+    #pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                const int j = 8 * q + 2 * t;
+                                w4[t] = pack_bf16x2(__fadd_rn(__uint_as_float(o[t] << 16), __fmul_rn(__uint_as_float(v[j]), dab)),
+                                                    __fadd_rn(__uint_as_float(o[t] & 0xffff0000u), __fmul_rn(__uint_as_float(v[j + 1]), dab)));
+                            }
+                            crow[q] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                        }
                     } else {
     #pragma unroll
                         for (int j = 0; j < 32; ++j) {
@@ -881,7 +901,7 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     if (p.mn_major && !tma_ok) { set_error("MN-major operands need 16-byte aligned bases and row pitches"); return CF_ERR_UNSUPPORTED; }
     const uintptr_t ca = reinterpret_cast<uintptr_t>(p.C);
     // per-segment output buffers: the caller guarantees 16-byte aligned bases (checked at the API boundary)
-    p.c_vec = (p.out_kind == 0) && (p.d_group_out != nullptr || ca % 16 == 0) && (p.ldc % 8 == 0) &&
+    p.c_vec = (p.out_kind == 0 || p.out_kind == 3) && (p.d_group_out != nullptr || ca % 16 == 0) && (p.ldc % 8 == 0) &&
               (p.bias == nullptr || reinterpret_cast<uintptr_t>(p.bias) % 4 == 0);
     if (!p.bias) p.bias_mode = 0;
     if (p.out_kind == 4) {
@@ -928,13 +948,13 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
         if (r != CF_OK) return r;
     }
     p.c_rows = p.d_counts ? a_rows : p.M;
-    p.tma_store = (p.c_vec && p.d_group_out == nullptr && p.N >= C_BOX_COLS &&
+    p.tma_store = (p.c_vec && p.out_kind == 0 && p.d_group_out == nullptr && p.N >= C_BOX_COLS &&
                    (p.bias == nullptr || reinterpret_cast<uintptr_t>(p.bias) % 16 == 0) &&
                    (p.d_b_col_descale == nullptr || reinterpret_cast<uintptr_t>(p.d_b_col_descale) % 16 == 0)) ? 1 : 0;
     static const bool no_tma_store = [] { const char* e = std::getenv("CF_GEMM_DIRECT_STORE"); return e && e[0] == '1'; }();
     if (no_tma_store) p.tma_store = 0;
-    p.tma_reduce = (p.out_kind == 2 && ca % 16 == 0 && p.ldc % 4 == 0 && p.N >= 32 && p.d_group_out == nullptr &&
-                    p.d_a_row_descale == nullptr && p.d_b_col_descale == nullptr && !no_tma_store) ? 1 : 0;
+    p.tma_reduce = ((p.out_kind == 2 || p.out_kind == 1) && ca % 16 == 0 && p.ldc % 4 == 0 && p.N >= 32 && p.d_group_out == nullptr &&
+                    p.d_a_row_descale == nullptr && p.d_b_col_descale == nullptr && !no_tma_store) ? (p.out_kind == 2 ? 1 : 2) : 0;
     if (p.tma_store) {
         r = make_map_c(&map_c, p.C, p.c_rows, p.N, p.ldc);
         if (r != CF_OK) return r;

@@ -168,8 +168,10 @@ class EpMoeSwigluFp8:
     re-quantise -> ragged down GEMM -> bf16 all-to-all back -> local weighted combine."""
 
     def __init__(self, cfb, ctx, rows, H, F, num_experts, top_k, group=None, device="cuda", recv_capacity=None,
-                 fused_return=False):
-        """fused_return: the down-projection GEMM writes every segment's rows straight into the `back` buffer of the
+                 fused_return=False, fused_swiglu=False):
+        """fused_swiglu: the local gate/up weight is in the interleaved layout (fp8_interleave_gate_up) and the gate/up
+        GEMM's epilogue does SwiGLU and the delayed-scale re-quantise, so the [rows, 2F] bf16 intermediate never
+        exists. fused_return: the down-projection GEMM writes every segment's rows straight into the `back` buffer of the
         rank that owns the tokens (NVLink P2P stores from the GEMM epilogue into symmetric memory), which removes the
         bf16 all-to-all of the return leg; one tiny all-reduce orders the combine behind all ranks' GEMMs."""
         self.cfb, self.ctx, self.group = cfb, ctx, group
@@ -191,6 +193,7 @@ class EpMoeSwigluFp8:
         self.device = dev
         self.plan: Optional[EpPlan] = None
         self.fused_return = bool(fused_return) and self.world > 1
+        self.fused_swiglu = bool(fused_swiglu)
         if self.fused_return:
             import torch.distributed._symmetric_memory as symm_mem
             self.back = symm_mem.empty((self.T, H), dtype=torch.bfloat16, device=dev)
@@ -226,11 +229,15 @@ class EpMoeSwigluFp8:
         e_local = self.e_hi - self.e_lo
         yc = torch.empty((max(R, 1), H), dtype=torch.bfloat16, device=dev)
         if R > 0:
-            gu = torch.empty((R, 2 * F), dtype=torch.bfloat16, device=dev)
             h8 = torch.empty((R, F), dtype=torch.uint8, device=dev)
-            cfb.gemm_fp8_nt_segments(ctx, nseg, e_local, seg_weight, R, 2 * F, H, seg_counts, seg_offsets, recv8, H, False,
-                                     seg_dx, True, w_gateup8_local, w_gateup_descale, gu, 2 * F)
-            cfb.fp8_swiglu_quant_act(ctx, self.slot_h, gu, gu.view(-1)[F:], 2 * F, R, F, h8)
+            if self.fused_swiglu:
+                cfb.gemm_fp8_swiglu_quant_act(ctx, self.slot_h, nseg, e_local, seg_weight, R, F, H, seg_counts, seg_offsets,
+                                              recv8, H, False, seg_dx, True, w_gateup8_local, w_gateup_descale, h8, F)
+            else:
+                gu = torch.empty((R, 2 * F), dtype=torch.bfloat16, device=dev)
+                cfb.gemm_fp8_nt_segments(ctx, nseg, e_local, seg_weight, R, 2 * F, H, seg_counts, seg_offsets, recv8, H,
+                                         False, seg_dx, True, w_gateup8_local, w_gateup_descale, gu, 2 * F)
+                cfb.fp8_swiglu_quant_act(ctx, self.slot_h, gu, gu.view(-1)[F:], 2 * F, R, F, h8)
             if self.fused_return:
                 # segment (src, e) returns to rank src at the row where expert e starts in src's compact order
                 row0 = [int(sum(plan.counts_all[src][:self.e_lo + w])) for src, w in zip(plan.seg_source, plan.seg_weight)]

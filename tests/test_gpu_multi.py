@@ -100,6 +100,16 @@ def _worker(rank, world, port, ret):
             ep2.forward(xs[rank], rw2, wgu8[e_lo:e_hi].contiguous(), dgu, wd8[e_lo:e_hi].contiguous(), dd, mixed_f)
             ctx.poll_status()
         assert torch.equal(mixed_f.view(torch.int16), mixed.view(torch.int16))
+        # SwiGLU and the re-quantise done by the gate/up GEMM's epilogue: same bits again
+        ep3 = par.EpMoeSwigluFp8(cfb, ctx, rows, H, F, E, k, device=dev, fused_swiglu=True)
+        wgu8_il = cfb.fp8_interleave_gate_up(wgu8[e_lo:e_hi].contiguous())
+        mixed_s = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
+        for step in range(2):
+            rw3 = logits[rank].clone()
+            mixed_s.zero_()
+            ep3.forward(xs[rank], rw3, wgu8_il, dgu, wd8[e_lo:e_hi].contiguous(), dd, mixed_s)
+            ctx.poll_status()
+        assert torch.equal(mixed_s.view(torch.int16), mixed.view(torch.int16))
         # Host oracle on sampled tokens with the very scales the distributed layer used: this rank's activation
         # scale for x, and for every expert the SwiGLU slot scale of the rank that owns it.
         import sys

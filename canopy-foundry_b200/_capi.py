@@ -82,6 +82,10 @@ SIGNATURES = {
     "cf_fp8_linear_static_scratch": (ci, [vp, ci, ci, fp, fp, vp, fp, ci, vp, ci, vp, ci, ip, vp]),
     "cf_lion_step_f32_state": (ci, [vp, fp, fp, sz, cf, cf, cf, cf, vp, fp, C.c_uint]),
     "cf_lion_step_bf16_state": (ci, [vp, vp, fp, sz, cf, cf, cf, cf, vp, fp, C.c_uint]),
+    "cf_rmsnorm_forward": (ci, [vp, vp, vp, fp, ci, ci, cf, vp]),
+    "cf_rmsnorm_quantize_e4m3_record": (ci, [vp, vp, vp, fp, vp, fp, fp, ci, ci, cf, vp]),
+    "cf_rmsnorm_quantize_rowwise_e4m3": (ci, [vp, vp, vp, fp, vp, fp, fp, ci, ci, cf, vp]),
+    "cf_fp8_rmsnorm_quant_act": (ci, [vp, C.POINTER(ActSlotStruct), vp, vp, vp, fp, ci, ci, cf, vp, vp]),
     "cf_bias_add_strided_bf16": (ci, [vp, vp, ci, ci, ci, ci, vp]),
     "cf_swiglu_forward": (ci, [vp, vp, vp, ci, vp]),
     "cf_gelu_forward": (ci, [vp, vp, sz, vp]),

@@ -141,27 +141,7 @@ __global__ void __launch_bounds__(kRT) k_swiglu_record(const uint16_t* __restric
         out[r * ld_out + c] = cvt_fp8<false>(x * s);
     }
     block_amax_commit(local, amax);
-    if (tail.ticket != nullptr && threadIdx.x == 0) {
-        // last block to finish runs the delayed-scale ring update (kernels/fp8.cu:105-142)
-        __threadfence();
-        if (atomicAdd(tail.ticket, 1u) == gridDim.x - 1) {
-            __threadfence();
-            const float a = fmaxf(__int_as_float(atomicMax(reinterpret_cast<int*>(amax), 0)), 1e-12f);
-            int cursor = *tail.history_cursor, count = *tail.history_count;
-            if (cursor < 0 || cursor >= tail.history_len) cursor = 0;
-            tail.history[cursor] = a;
-            cursor = (cursor + 1) % tail.history_len;
-            if (count < tail.history_len) ++count;
-            float m = tail.history[0];
-            for (int i = 1; i < count; ++i) m = fmaxf(m, tail.history[i]);
-            m = fmaxf(m, 1e-12f);
-            *tail.history_cursor = cursor;
-            *tail.history_count = count;
-            *tail.scale = __fdiv_rn(tail.fp8_max, m);
-            *tail.descale = __fdiv_rn(m, tail.fp8_max);
-            *tail.ticket = 0;
-        }
-    }
+    if (tail.ticket != nullptr && threadIdx.x == 0) ring_tail_last_block(tail, amax);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }

@@ -22,6 +22,7 @@ __all__ = [
     "fp8_unpack_e4m3_raw_bf16", "lt_gemm_fp8_nt", "lt_gemm_fp8_tn_accum_f32", "gemm_fp8_dw_accum", "gemm_fp8_nt_grouped", "gemm_fp8_nt_segments", "gemm_fp8_nt_segments_scatter",
     "fp8_quant_act", "fp8_swiglu_quant_act", "gemm_fp8_swiglu_quant_act", "fp8_interleave_gate_up", "refresh_fp8_weight", "fp8_linear_forward", "bias_add_strided_bf16", "swiglu_forward",
     "gelu_forward", "lion_step", "fp8_quantize_rowwise_e4m3", "swiglu_quantize_rowwise_e4m3", "swiglu_quantize_e4m3_record",
+    "rmsnorm_forward", "rmsnorm_quantize_e4m3_record", "rmsnorm_quantize_rowwise_e4m3", "fp8_rmsnorm_quant_act",
     "moe_topk_route_f32", "moe_build_expert_row_lists", "moe_expert_offsets_from_counts",
     "moe_gather_rows_u8", "moe_gather_rows_bf16", "moe_scatter_accumulate_rows_bf16",
     "moe_scale_accumulate_bf16", "moe_gather_all_u8", "moe_combine_all_bf16",
@@ -341,6 +342,28 @@ def fp8_quantize_rowwise_e4m3(x, out, row_descale, row_scale=None, rows=None, co
 def swiglu_quantize_rowwise_e4m3(gate, up, out, row_descale, rows, cols, ld_in, ld_out=None, row_scale=None):
     check(_L().cf_swiglu_quantize_rowwise_e4m3(_p(gate), _p(up), ld_in, _p(out), cols if ld_out is None else ld_out,
                                                _p(row_scale), _p(row_descale), rows, cols, _s()))
+
+
+def rmsnorm_forward(x, scale, out, rms, rows, H, eps=1e-6):
+    """out = bf16(x / rms * scale) per row, rms kept for the backward pass (kernels/rmsnorm.cu:101-108)."""
+    check(_L().cf_rmsnorm_forward(_p(x), _p(scale), _p(out), _p(rms), rows, H, eps, _s()))
+
+
+def rmsnorm_quantize_e4m3_record(x, scale, normed, rms, out8, quant_scale, amax, rows, H, eps=1e-6):
+    """rmsnorm_forward + fp8_quantize_e4m3_record in one pass; normed / rms may be None."""
+    check(_L().cf_rmsnorm_quantize_e4m3_record(_p(x), _p(scale), _p(normed), _p(rms), _p(out8), _p(quant_scale), _p(amax),
+                                               rows, H, eps, _s()))
+
+
+def rmsnorm_quantize_rowwise_e4m3(x, scale, normed, rms, out8, row_descale, rows, H, eps=1e-6, row_scale=None):
+    check(_L().cf_rmsnorm_quantize_rowwise_e4m3(_p(x), _p(scale), _p(normed), _p(rms), _p(out8), _p(row_scale),
+                                                _p(row_descale), rows, H, eps, _s()))
+
+
+def fp8_rmsnorm_quant_act(ctx, slot, x, scale, normed, rms, rows, H, out8, eps=1e-6):
+    """rmsnorm_forward followed by fp8_quant_act on its output (src/trainer.cu:6097,6115) as one pass."""
+    check(_L().cf_fp8_rmsnorm_quant_act(ctx.handle, C.byref(slot.c), _p(x), _p(scale), _p(normed), _p(rms), rows, H, eps,
+                                        _p(out8), _s()))
 
 
 def swiglu_quantize_e4m3_record(gate, up, out, scale, amax, rows, cols, ld_in, ld_out=None):

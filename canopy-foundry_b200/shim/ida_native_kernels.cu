@@ -95,6 +95,12 @@ void lion_step(__nv_bfloat16* d_w, __nv_bfloat16* d_m, const float* d_grad, std:
     cf_check(cf_lion_step_bf16_state(d_w, d_m, d_grad, n, lr, beta1, beta2, wd, stream, d_weight_amax, sr_seed), "lion_step");
 }
 
+// kernels/rmsnorm.cu:101-108 (the forward only: rmsnorm_backward stays in the reference's translation unit)
+void rmsnorm_forward(const __nv_bfloat16* d_x, const __nv_bfloat16* d_scale, __nv_bfloat16* d_out, float* d_rms, int rows, int H,
+                     float eps, cudaStream_t stream) {
+    cf_check(cf_rmsnorm_forward(d_x, d_scale, d_out, d_rms, rows, H, eps, stream), "rmsnorm_forward");
+}
+
 // kernels/activations.cu:76-87; kernels/moe.cu:338-345, 519-521
 void swiglu_forward(const __nv_bfloat16* d_gate, const __nv_bfloat16* d_up, __nv_bfloat16* d_out, int N, cudaStream_t stream) {
     const int rc = cf_swiglu_forward(d_gate, d_up, d_out, N, stream);

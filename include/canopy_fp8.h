@@ -301,6 +301,32 @@ int cf_lion_step_f32_state(void* d_w, float* d_m, const float* d_grad, size_t n,
 int cf_lion_step_bf16_state(void* d_w, void* d_m, const float* d_grad, size_t n, float lr, float beta1, float beta2, float wd,
                             void* stream, float* d_weight_amax, unsigned sr_seed);
 
+/* ------------------------------------------------------------------ RMSNorm feeding the quantiser */
+
+/* kernels/rmsnorm.cu:13-54,101-108, include/ida_native/kernels.hpp:117-124 (rmsnorm_forward): out = bf16((x / rms) * scale),
+ * rms = sqrt(mean(x^2) + eps) per row, rms values kept for the backward pass when d_rms_or_null is given. Same
+ * summation order as the reference kernel (bit-identical rows). x, out: bf16 [rows, H] contiguous; d_scale: bf16 [H].
+ * H below 512 must be a multiple of 32 (the reference's reduction is undefined otherwise); H <= 16384. */
+int cf_rmsnorm_forward(const void* d_x, const void* d_scale, void* d_out, float* d_rms_or_null, int rows, int H, float eps,
+                       void* stream);
+/* rmsnorm_forward followed by fp8_quantize_e4m3_record on its output (kernels/fp8.cu:67-84) in one pass over x: the
+ * normalised row is rounded to bf16 exactly as rmsnorm_forward would store it, then quantised with *d_quant_scale and
+ * its amax accumulated into the caller-zeroed *d_amax. d_normed_or_null: also keep the bf16 row (the backward pass of
+ * the reference reads it). */
+int cf_rmsnorm_quantize_e4m3_record(const void* d_x, const void* d_scale, void* d_normed_or_null, float* d_rms_or_null,
+                                    void* d_out8, const float* d_quant_scale, float* d_amax, int rows, int H, float eps,
+                                    void* stream);
+/* No counterpart in the reference (it scales per tensor): the same pass with one scale per token, as
+ * cf_fp8_quantize_rowwise_e4m3 would compute from the normalised row. */
+int cf_rmsnorm_quantize_rowwise_e4m3(const void* d_x, const void* d_scale, void* d_normed_or_null, float* d_rms_or_null,
+                                     void* d_out8, float* d_row_scale_or_null, float* d_row_descale, int rows, int H,
+                                     float eps, void* stream);
+/* src/trainer.cu:6097 + :6115 (rmsnorm_forward, then fp8_quant_act on sb.normed) as one call: the slot's delayed-scale
+ * state machine around cf_rmsnorm_quantize_e4m3_record. E4M3 slots without calibration; the first call on a fresh slot
+ * takes an exact amax first. With slot->ticket set a steady-state call is two launches (snapshot, fused pass). */
+int cf_fp8_rmsnorm_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, const void* d_norm_scale, void* d_normed_or_null,
+                             float* d_rms_or_null, int rows, int H, float eps, void* d_out8, void* stream);
+
 /* ------------------------------------------------------------------ elementwise neighbours of the GEMMs */
 
 /* kernels/moe.cu:338-345, kernels.hpp:243-247. */

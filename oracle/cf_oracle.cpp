@@ -409,6 +409,49 @@ void orc_bias_add_strided_bf16(uint16_t* inout, const uint16_t* bias, int rows, 
 }
 
 // ---- kernels/activations.cu:28-40  k_swiglu_forward -------------------------
+// kernels/rmsnorm.cu:13-54,101-108 (k_rmsnorm_fwd, rmsnorm_forward): one block of T = min(H, 512) threads per row.
+// Thread t sums x[h]^2 for h = t, t+T, ... in that order (the compiler contracts `ms += v * v` into a fused
+// multiply-add), lanes combine with an xor-butterfly (all lanes hold the same value after each step because fp32
+// addition commutes), warp leaders' sums go through shared memory and a second butterfly over the warp count with
+// zeros in the unused lanes. rms = sqrtf(sum / H + eps); out = bf16((x * (1/rms)) * scale). H must fill whole warps
+// (H >= 512 or H % 32 == 0): the reference's full-mask shuffles are undefined otherwise.
+void orc_rmsnorm_forward(const uint16_t* x, const uint16_t* scale, uint16_t* out, float* rms_or_null, int64_t rows, int H,
+                         float eps) {
+    const int T = H < 512 ? H : 512;
+    const int warps = (T + 31) / 32;
+    std::vector<float> part(static_cast<size_t>(warps) * 32);
+    for (int64_t r = 0; r < rows; ++r) {
+        const uint16_t* xr = x + r * H;
+        std::fill(part.begin(), part.end(), 0.0f);
+        for (int t = 0; t < T; ++t) {
+            float ms = 0.0f;
+            for (int h = t; h < H; h += T) { const float v = bf16_to_f32(xr[h]); ms = std::fmaf(v, v, ms); }
+            part[t] = ms;
+        }
+        float wsum[32];
+        for (int i = 0; i < 32; ++i) wsum[i] = 0.0f;
+        for (int w = 0; w < warps; ++w) {
+            float l[32];
+            for (int i = 0; i < 32; ++i) l[i] = part[w * 32 + i];
+            for (int off = 16; off > 0; off >>= 1) {
+                float n[32];
+                for (int i = 0; i < 32; ++i) n[i] = l[i] + l[i ^ off];
+                std::memcpy(l, n, sizeof(l));
+            }
+            wsum[w] = l[0];
+        }
+        for (int off = 16; off > 0; off >>= 1) {
+            float n[32];
+            for (int i = 0; i < 32; ++i) n[i] = wsum[i] + wsum[i ^ off];
+            std::memcpy(wsum, n, sizeof(wsum));
+        }
+        const float rms = std::sqrt(wsum[0] / static_cast<float>(H) + eps);
+        if (rms_or_null) rms_or_null[r] = rms;
+        const float inv = 1.0f / rms;
+        for (int h = 0; h < H; ++h) out[r * H + h] = f32_to_bf16(bf16_to_f32(xr[h]) * inv * bf16_to_f32(scale[h]));
+    }
+}
+
 void orc_swiglu_forward(const uint16_t* gate, const uint16_t* up, uint16_t* out, int64_t n) {
     for (int64_t i = 0; i < n; ++i) {
         const float g = bf16_to_f32(gate[i]);

@@ -33,6 +33,7 @@ int ref_fp8_unpack_e4m3_raw_bf16(const uint8_t* in, const float* de, void* o, si
 int ref_lion_step_f32(void* w, float* m, const float* g, size_t n, float lr, float b1, float b2, float wd, void* s, float* amax, unsigned seed) { try { lion_step(BFW(w), m, g, n, lr, b1, b2, wd, S(s), amax, seed); } catch (...) { return 1; } return 0; }
 int ref_lion_step_bf16(void* w, void* m, const float* g, size_t n, float lr, float b1, float b2, float wd, void* s, float* amax, unsigned seed) { try { lion_step(BFW(w), BFW(m), g, n, lr, b1, b2, wd, S(s), amax, seed); } catch (...) { return 1; } return 0; }
 
+int ref_rmsnorm_forward(const void* x, const void* g, void* o, float* rms, int rows, int H, float eps, void* s) { try { rmsnorm_forward(BF(x), BF(g), BFW(o), rms, rows, H, eps, S(s)); } catch (...) { return 1; } return 0; }
 int ref_swiglu_forward(const void* g, const void* u, void* o, int n, void* s) { try { swiglu_forward(BF(g), BF(u), BFW(o), n, S(s)); } catch (...) { return 1; } return 0; }
 int ref_gelu_forward(const void* x, void* o, size_t n, void* s) { try { gelu_forward(BF(x), BFW(o), n, S(s)); } catch (...) { return 1; } return 0; }
 int ref_bias_add_strided_bf16(void* io, const void* b, int rows, int cols, int stride, int base, void* s) { try { bias_add_strided_bf16(BFW(io), BF(b), rows, cols, stride, base, S(s)); } catch (...) { return 1; } return 0; }

@@ -169,6 +169,14 @@ class Oracle:
     def bias_add_strided_bf16(self, inout, bias, rows, cols, row_stride, base):
         self.lib.orc_bias_add_strided_bf16(_ptr(inout), _ptr(bias), c_i(rows), c_i(cols), c_i(row_stride), c_i(base))
 
+    def rmsnorm_forward(self, x, scale, eps):
+        """x uint16 [rows, H], scale uint16 [H] -> (out uint16 [rows, H], rms float32 [rows])."""
+        rows, H = x.shape
+        out = np.empty((rows, H), dtype=np.uint16)
+        rms = np.empty(rows, dtype=np.float32)
+        self.lib.orc_rmsnorm_forward(_ptr(x), _ptr(scale), _ptr(out), _ptr(rms), c_i64(rows), c_i(H), c_f(eps))
+        return out, rms
+
     def swiglu_forward(self, gate, up):
         out = np.empty(gate.shape, dtype=np.uint16)
         self.lib.orc_swiglu_forward(_ptr(gate), _ptr(up), _ptr(out), c_i64(gate.size))

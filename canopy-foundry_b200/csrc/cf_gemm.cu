@@ -311,7 +311,9 @@ __device__ __forceinline__ void store_one(const GemmParams& p, void* cbase, long
     }
 }
 
-template <bool PAIR>
+// WIDE = true adds the fp32-output and accumulate epilogues (out_kind 1, 2, 3); the bf16-store and SwiGLU forms run the
+// WIDE = false instantiation, whose epilogue stays small.
+template <bool PAIR, bool WIDE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
               const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
@@ -402,8 +404,9 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                         if (leader) mbar_expect_tx(full_bar + 8 * s, 2 * (A_STAGE + B_STAGE));
                         // K-major operands: x runs along K; MN-major operands ([K, M] / [K, N] in memory): x runs
                         // along M / N and the box rows are K
-                        const int ax = p.mn_major ? a_row : kb * BK, ay = p.mn_major ? kb * BK : a_row;
-                        const int bx = p.mn_major ? b_row : kb * BK, by = p.mn_major ? kb * BK : b_row;
+                        const bool mn = WIDE && p.mn_major;
+                        const int ax = mn ? a_row : kb * BK, ay = mn ? kb * BK : a_row;
+                        const int bx = mn ? b_row : kb * BK, by = mn ? kb * BK : b_row;
                         tma_load_2d_pair(smem_a + s * A_STAGE, &map_a, full_dst + 8 * s, ax, ay);
                         tma_load_2d_pair(smem_b + s * B_STAGE, &map_b, full_dst + 8 * s, bx, by);
                     } else {
@@ -424,10 +427,8 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
         if (lane == 0 && leader) {
-            const uint32_t idesc = make_idesc(p.a_e5m2, p.b_e5m2, TM, p.mn_major);
-            // K-major: 32 elements of K are 32 bytes inside the swizzle row (+2 in 16-byte units); MN-major: 32 rows
-            // of 128 bytes (+256)
-            const uint64_t kstep = p.mn_major ? 256u : 2u;
+            const bool mn = WIDE && p.mn_major;
+            const uint32_t idesc = make_idesc(p.a_e5m2, p.b_e5m2, TM, mn);
             int it = 0, local_tile = 0;
             bool ok = true;
             for (int tile = unit; ok && tile < total_tiles; tile += n_units, ++local_tile) {
@@ -441,11 +442,20 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     tcgen05_fence_after();
                     const uint64_t adesc = make_smem_desc(smem_a + s * A_STAGE);
                     const uint64_t bdesc = make_smem_desc(smem_b + s * B_STAGE);
+                    if (WIDE && mn) {
+                        // MN-major: 32 elements of K are 32 rows of 128 bytes = +256 in the (addr >> 4) field
 #pragma unroll
-                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                        // advancing 32 bytes inside the 128B swizzle atom = +2 in the (addr >> 4) field
-                        if (PAIR) umma_f8_pair(tmem_d, adesc + kstep * kk, bdesc + kstep * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
-                        else umma_f8(tmem_d, adesc + kstep * kk, bdesc + kstep * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                            if (PAIR) umma_f8_pair(tmem_d, adesc + 256 * kk, bdesc + 256 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                            else umma_f8(tmem_d, adesc + 256 * kk, bdesc + 256 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        }
+                    } else {
+                        // K-major: advancing 32 bytes inside the 128B swizzle atom = +2 in the (addr >> 4) field
+#pragma unroll
+                        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                            if (PAIR) umma_f8_pair(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                            else umma_f8(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        }
                     }
                     // frees the stage (in both CTAs of a pair) once these MMAs have read it
                     if (PAIR) tcgen05_commit_pair(empty_bar + 8 * s); else tcgen05_commit(empty_bar + 8 * s);
@@ -528,7 +538,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             // ragged rows of a grouped tile, column tails and the fp32 / accumulate forms use direct stores.
             const int warp_row0 = static_cast<int>(cta_rank) * BM + quarter * 32;
             const bool warp_rows_full = (p.d_counts == nullptr) || (warp_row0 + 32 <= tc.valid_rows);
-            if (p.tma_reduce && warp_rows_full && warp_row0 < tc.valid_rows) {
+            if (WIDE && p.tma_reduce && warp_rows_full && warp_row0 < tc.valid_rows) {
                 // fp32 output, added (dW += ...) or stored (partial products): 32 columns = one 128-byte line per box row
                 const uint32_t buf = smem_c + static_cast<uint32_t>(warp - 2) * C_BOX_BYTES;
                 const uint32_t row_off = static_cast<uint32_t>(lane) * 128u;
@@ -696,7 +706,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                         uint4* dst = reinterpret_cast<uint4*>(crow);
     #pragma unroll
                         for (int q = 0; q < 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
-                    } else if (p.out_kind == 3 && p.c_vec && full && !p.d_b_col_descale) {
+                    } else if (WIDE && p.out_kind == 3 && p.c_vec && full && !p.d_b_col_descale) {
                         // bf16 accumulate: 64 bytes of the row in, one fp32 addition and one rounding per element, 64 bytes out
                         uint4* crow = reinterpret_cast<uint4*>(static_cast<uint16_t*>(tc.out_base) + grow * p.ldc + col0);
                         const float dab = da * db_t;
@@ -840,7 +850,8 @@ int max_resident_pairs() {
     if (cudaGetDevice(&dev) != cudaSuccess) return 0;
     std::call_once(once[dev & 63], [&] {
         int n = 0;
-        if (cudaFuncSetAttribute(k_gemm_fp8_nt<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true>::SMEM_BYTES) == cudaSuccess) {
+        if (cudaFuncSetAttribute(k_gemm_fp8_nt<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true>::SMEM_BYTES) == cudaSuccess &&
+            cudaFuncSetAttribute(k_gemm_fp8_nt<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<true>::SMEM_BYTES) == cudaSuccess) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(2 * sm_count());
             cfg.blockDim = dim3(NUM_THREADS);
@@ -850,7 +861,7 @@ int max_resident_pairs() {
             at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
             cfg.attrs = at;
             cfg.numAttrs = 1;
-            if (cudaOccupancyMaxActiveClusters(&n, k_gemm_fp8_nt<true>, &cfg) != cudaSuccess) n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, k_gemm_fp8_nt<true, true>, &cfg) != cudaSuccess) n = 0;
         }
         (void)cudaGetLastError();
         cached[dev & 63] = n;
@@ -966,6 +977,7 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     }
     int dev = 0;
     CF_CUDA(cudaGetDevice(&dev));
+    const bool wide = p.out_kind >= 1 && p.out_kind <= 3;
     if (pair) {
         // tile_upper_bound counts 128-row blocks; a pair tile covers two of them
         const int n_blocks = (p.N + BN - 1) / BN;
@@ -984,19 +996,23 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
         at[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = at;
         cfg.numAttrs = 2;
-        CF_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_fp8_nt<true>, map_a, map_b, map_c, p));
+        if (wide) CF_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_fp8_nt<true, true>, map_a, map_b, map_c, p));
+        else CF_CUDA(cudaLaunchKernelEx(&cfg, k_gemm_fp8_nt<true, false>, map_a, map_b, map_c, p));
         CF_LAUNCH_CHECK("gemm_fp8_nt<pair>");
         return CF_OK;
     }
     static std::once_flag attr_once[64];
     cudaError_t attr_err = cudaSuccess;
     std::call_once(attr_once[dev & 63], [&] {
-        attr_err = cudaFuncSetAttribute(k_gemm_fp8_nt<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<false>::SMEM_BYTES);
+        attr_err = cudaFuncSetAttribute(k_gemm_fp8_nt<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<false>::SMEM_BYTES);
+        if (attr_err == cudaSuccess)
+            attr_err = cudaFuncSetAttribute(k_gemm_fp8_nt<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<false>::SMEM_BYTES);
     });
     if (attr_err != cudaSuccess) return cuda_fail(attr_err, "cudaFuncSetAttribute(k_gemm_fp8_nt)");
     const int sms = sm_count();
     const int grid = tile_upper_bound < sms ? tile_upper_bound : sms;
-    CF_CUDA(launch_pdl(k_gemm_fp8_nt<false>, dim3(grid), dim3(NUM_THREADS), Cfg<false>::SMEM_BYTES, st, map_a, map_b, map_c, p));
+    if (wide) CF_CUDA(launch_pdl(k_gemm_fp8_nt<false, true>, dim3(grid), dim3(NUM_THREADS), Cfg<false>::SMEM_BYTES, st, map_a, map_b, map_c, p));
+    else CF_CUDA(launch_pdl(k_gemm_fp8_nt<false, false>, dim3(grid), dim3(NUM_THREADS), Cfg<false>::SMEM_BYTES, st, map_a, map_b, map_c, p));
     CF_LAUNCH_CHECK("gemm_fp8_nt");
     return CF_OK;
 }

@@ -245,8 +245,7 @@ def run_moe(args):
 
     def step():
         rw = logits.clone()
-        mixed.zero_()
-        layer.forward(x, rw, wgu8, dgu, wd8, dd, mixed)
+        layer.forward(x, rw, wgu8, dgu, wd8, dd, mixed, accumulate=False)
 
     def barrier():
         if world > 1:

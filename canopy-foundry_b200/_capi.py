@@ -101,6 +101,7 @@ SIGNATURES = {
     "cf_moe_scale_accumulate_bf16": (ci, [vp, vp, fp, ci, ci, ci, ci, vp]),
     "cf_moe_gather_all_u8": (ci, [vp, vp, ip, ip, ip, ci, ci, ci, vp]),
     "cf_moe_combine_all_bf16": (ci, [vp, vp, fp, ip, ip, ip, ci, ci, ci, vp]),
+    "cf_moe_combine_sorted_bf16": (ci, [vp, vp, fp, ip, ip, ip, ci, ci, ci, ci, vp]),
     "cf_moe_grouped_expert_forward_fp8": (ci, [vp, vp, fp, ci, fp, ip, ip, ip, vp, fp, vp, fp, vp, ci, ci, ci, ci, ci, vp]),
 }
 

@@ -239,6 +239,98 @@ __global__ void __launch_bounds__(kT) k_scatter_acc(uint16_t* __restrict__ mixed
     }
 }
 
+// ---- single-pass combine over ascending dispatch lists ----------------------------------------------
+// One warp per token row, no block-wide barrier: lane e finds the row's position in expert e's list by binary search
+// (the lists of k_build_row_lists are ascending), a ballot compacts the selected experts into lanes 0..n-1 in
+// ascending expert order, then the 32 lanes stream the row, adding the selected experts' rows with the rounding
+// points of k_scatter_acc (one bf16 rounding per expert added). mixed is read (accumulate != 0) and written once
+// instead of once per expert. Many rows are in flight per SM, which hides the latency of the searches.
+constexpr int kCombineMaxE = 32;
+constexpr int kCombineWarps = 2;           // warps that share a row (each repeats the cheap search, no barrier)
+
+__device__ __forceinline__ uint4 combine_add(uint4 m, uint4 t, float w) {
+    const uint32_t tw[4] = {t.x, t.y, t.z, t.w}, mw[4] = {m.x, m.y, m.z, m.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float r0 = __uint_as_float(mw[q] << 16) + w * __uint_as_float(tw[q] << 16);
+        const float r1 = __uint_as_float(mw[q] & 0xffff0000u) + w * __uint_as_float(tw[q] & 0xffff0000u);
+        o[q] = static_cast<uint32_t>(f2bf(r0)) | (static_cast<uint32_t>(f2bf(r1)) << 16);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+__global__ void __launch_bounds__(kT) k_combine_rows(uint16_t* __restrict__ mixed, const uint16_t* __restrict__ compact,
+                                                     const float* __restrict__ rw, const int* __restrict__ row_indices,
+                                                     const int* __restrict__ counts, const int* __restrict__ offsets,
+                                                     int rows, int E, int H, int accumulate) {
+    const int cpr = H / 8;
+    const int lane = threadIdx.x & 31;
+    const int gwarp = (blockIdx.x * kT + threadIdx.x) >> 5;
+    const int part = gwarp % kCombineWarps;
+    const int row_stride = ((gridDim.x * kT) >> 5) / kCombineWarps;
+    for (int row = gwarp / kCombineWarps; row < rows; row += row_stride) {
+        const float w = lane < E ? rw[static_cast<size_t>(row) * E + lane] : 0.0f;
+        long long pos = -1;
+        if (w > 0.0f) {
+            const int* list = row_indices + static_cast<size_t>(lane) * rows;
+            const int n = counts[lane];
+            int lo = 0, hi = n;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (list[mid] < row) lo = mid + 1; else hi = mid;
+            }
+            if (lo < n && list[lo] == row) pos = static_cast<long long>(offsets[lane]) + lo;
+        }
+        const unsigned sel = __ballot_sync(0xffffffffu, pos >= 0);
+        const int n = __popc(sel);
+        // lane i takes over the i-th selected expert; the first four are then broadcast to every lane
+        const int src = lane < n ? static_cast<int>(__fns(sel, 0, lane + 1)) : 0;
+        const long long my_pos = __shfl_sync(0xffffffffu, pos, src);
+        const float my_w = __shfl_sync(0xffffffffu, w, src);
+        const uint16_t* p4[4];
+        float w4[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            p4[j] = compact + __shfl_sync(0xffffffffu, my_pos, j) * H;     // never dereferenced when j >= n
+            w4[j] = __shfl_sync(0xffffffffu, my_w, j);
+        }
+        uint16_t* mrow = mixed + static_cast<size_t>(row) * H;
+        for (int c0 = part * 64; c0 < cpr; c0 += kCombineWarps * 64) {
+            // two 16-byte columns per lane and pass, all loads of both issued before the arithmetic
+            const int ca = c0 + lane, cb = c0 + 32 + lane;
+            const bool ona = ca < cpr, onb = cb < cpr;
+            uint4 ma = make_uint4(0u, 0u, 0u, 0u), mb = ma, ta[4], tb[4];
+            if (accumulate) {
+                if (ona) ma = *reinterpret_cast<const uint4*>(mrow + ca * 8);
+                if (onb) mb = *reinterpret_cast<const uint4*>(mrow + cb * 8);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (j < n) {
+                    if (ona) ta[j] = __ldcs(reinterpret_cast<const uint4*>(p4[j] + ca * 8));
+                    if (onb) tb[j] = __ldcs(reinterpret_cast<const uint4*>(p4[j] + cb * 8));
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (j < n) {
+                    ma = combine_add(ma, ta[j], w4[j]);
+                    mb = combine_add(mb, tb[j], w4[j]);
+                }
+            }
+            for (int i = 4; i < n; ++i) {                    // more than four experts per token
+                const uint16_t* pi = compact + __shfl_sync(0xffffffffu, my_pos, i) * H;
+                const float wi = __shfl_sync(0xffffffffu, my_w, i);
+                if (ona) ma = combine_add(ma, __ldcs(reinterpret_cast<const uint4*>(pi + ca * 8)), wi);
+                if (onb) mb = combine_add(mb, __ldcs(reinterpret_cast<const uint4*>(pi + cb * 8)), wi);
+            }
+            if (ona) *reinterpret_cast<uint4*>(mrow + ca * 8) = ma;
+            if (onb) *reinterpret_cast<uint4*>(mrow + cb * 8) = mb;
+        }
+    }
+}
+
 // ---- dense combine: mixed[row,:] += rw[row,e] * term[row,:] -----------------------------------------
 __global__ void __launch_bounds__(kT) k_scale_acc(uint16_t* __restrict__ mixed, const uint16_t* __restrict__ term,
                                                   const float* __restrict__ rw, long long rows, int expert, int E, int H) {
@@ -426,6 +518,28 @@ int cf_moe_combine_all_bf16(void* d_mixed, const void* d_compact, const float* d
     for (int e = 0; e < num_experts; ++e)
         CF_TRY(scatter_acc(d_mixed, d_compact, d_route_weights, d_row_indices + static_cast<size_t>(e) * rows, d_counts,
                            d_offsets, rows, e, num_experts, H, as_stream(stream)));
+    return CF_OK;
+}
+
+int cf_moe_combine_sorted_bf16(void* d_mixed, const void* d_compact, const float* d_route_weights, const int* d_row_indices,
+                               const int* d_counts, const int* d_offsets, int rows, int num_experts, int H, int accumulate,
+                               void* stream) {
+    CF_REQUIRE(rows >= 0 && H >= 0 && num_experts >= 1, "cf_moe_combine_sorted_bf16: bad shape");
+    if (rows == 0 || H == 0) return CF_OK;
+    CF_REQUIRE(d_mixed && d_compact && d_route_weights && d_row_indices && d_counts && d_offsets, "cf_moe_combine_sorted_bf16: null pointer");
+    const bool vec = (H % 8 == 0) && ((reinterpret_cast<uintptr_t>(d_mixed) | reinterpret_cast<uintptr_t>(d_compact)) % 16 == 0);
+    if (!vec || num_experts > kCombineMaxE) {
+        // odd widths: zero fill (when not accumulating) and the per-expert passes
+        if (!accumulate) CF_CUDA(cudaMemsetAsync(d_mixed, 0, static_cast<size_t>(rows) * H * 2, as_stream(stream)));
+        return cf_moe_combine_all_bf16(d_mixed, d_compact, d_route_weights, d_row_indices, d_counts, d_offsets, rows,
+                                       num_experts, H, stream);
+    }
+    const int rows_per_block = kT / 32 / kCombineWarps;
+    const int cap = sm_count() * 8, want = (rows + rows_per_block - 1) / rows_per_block;
+    k_combine_rows<<<want < cap ? want : cap, kT, 0, as_stream(stream)>>>(
+        static_cast<uint16_t*>(d_mixed), static_cast<const uint16_t*>(d_compact), d_route_weights, d_row_indices, d_counts,
+        d_offsets, rows, num_experts, H, accumulate);
+    CF_LAUNCH_CHECK("moe_combine_sorted_bf16");
     return CF_OK;
 }
 

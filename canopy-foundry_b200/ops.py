@@ -25,7 +25,7 @@ __all__ = [
     "rmsnorm_forward", "rmsnorm_quantize_e4m3_record", "rmsnorm_quantize_rowwise_e4m3", "fp8_rmsnorm_quant_act",
     "moe_topk_route_f32", "moe_build_expert_row_lists", "moe_expert_offsets_from_counts",
     "moe_gather_rows_u8", "moe_gather_rows_bf16", "moe_scatter_accumulate_rows_bf16",
-    "moe_scale_accumulate_bf16", "moe_gather_all_u8", "moe_combine_all_bf16",
+    "moe_scale_accumulate_bf16", "moe_gather_all_u8", "moe_combine_all_bf16", "moe_combine_sorted_bf16",
     "moe_grouped_expert_forward_fp8", "launch_count", "swiglu_mlp_fp8_rowwise", "MoeSwigluFp8", "FfnSwigluFp8",
 ]
 
@@ -410,6 +410,14 @@ def moe_combine_all_bf16(mixed, compact, route_weights, row_indices, counts, off
                                        _p(offsets), rows, num_experts, H, _s()))
 
 
+def moe_combine_sorted_bf16(mixed, compact, route_weights, row_indices, counts, offsets, rows, num_experts, H,
+                            accumulate=True):
+    """One pass over the token rows (ascending dispatch lists): mixed is read (accumulate) or started from zero, and
+    written once; equals zero-fill + moe_combine_all_bf16 bit for bit."""
+    check(_L().cf_moe_combine_sorted_bf16(_p(mixed), _p(compact), _p(route_weights), _p(row_indices), _p(counts),
+                                          _p(offsets), rows, num_experts, H, int(accumulate), _s()))
+
+
 def moe_grouped_expert_forward_fp8(ctx, hidden, fcin_descale, fcin_is_e5m2, route_weights, counts, offsets, row_indices,
                                    fc_in_w, fc_in_descale, fc_out_w, fc_out_descale, mixed, rows, H, Ie, num_experts,
                                    total_selected_rows):
@@ -475,8 +483,9 @@ class MoeSwigluFp8:
         self.slot_x = ActSlot(ctx, E4M3_MAX)
         self.slot_h = ActSlot(ctx, E4M3_MAX)
 
-    def forward(self, x, route_weights, w_gateup8, w_gateup_descale, w_down8, w_down_descale, mixed):
-        """route_weights: float32 [rows,E] router logits, overwritten in place by the sparse route weights."""
+    def forward(self, x, route_weights, w_gateup8, w_gateup_descale, w_down8, w_down_descale, mixed, accumulate=True):
+        """route_weights: float32 [rows,E] router logits, overwritten in place by the sparse route weights.
+        accumulate=False: mixed is overwritten (as if it had been zero-filled first) instead of added to."""
         rows, H, F, E, T = self.rows, self.H, self.F, self.E, self.T
         moe_topk_route_f32(route_weights, rows, E, self.k)
         moe_build_expert_row_lists(route_weights, self.counts, self.idx, rows, E)
@@ -492,7 +501,7 @@ class MoeSwigluFp8:
             fp8_swiglu_quant_act(self.ctx, self.slot_h, self.gu, self.gu.view(-1)[F:], 2 * F, T, F, self.h8)
         gemm_fp8_nt_grouped(self.ctx, E, T, H, F, self.counts, self.offsets, self.h8, F, False,
                             _DevPtr(self.slot_h.c.descale_snapshot), False, w_down8, w_down_descale, self.yc, H)
-        moe_combine_all_bf16(mixed, self.yc, route_weights, self.idx, self.counts, self.offsets, rows, E, H)
+        moe_combine_sorted_bf16(mixed, self.yc, route_weights, self.idx, self.counts, self.offsets, rows, E, H, accumulate)
 
 
 class _DevPtr:

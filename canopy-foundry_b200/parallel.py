@@ -203,7 +203,8 @@ class EpMoeSwigluFp8:
                 assert t.data_ptr() % 16 == 0
             self._fence = torch.zeros(1, dtype=torch.float32, device=dev)
 
-    def forward(self, x, route_weights, w_gateup8_local, w_gateup_descale, w_down8_local, w_down_descale, mixed):
+    def forward(self, x, route_weights, w_gateup8_local, w_gateup_descale, w_down8_local, w_down_descale, mixed,
+                accumulate=True):
         cfb, ctx = self.cfb, self.ctx
         rows, H, F, E = self.rows, self.H, self.F, self.E
         cfb.moe_topk_route_f32(route_weights, rows, E, self.k)
@@ -257,7 +258,7 @@ class EpMoeSwigluFp8:
             back = self.back
         else:
             back = all_to_all_rows(yc[:R], plan.recv_splits, plan.send_splits, self.group)
-        cfb.moe_combine_all_bf16(mixed, back, route_weights, self.idx, self.counts, self.offsets, rows, E, H)
+        cfb.moe_combine_sorted_bf16(mixed, back, route_weights, self.idx, self.counts, self.offsets, rows, E, H, accumulate)
 
 
 def _copy_device_scalar(cfb, dst_tensor, src_addr):

@@ -383,6 +383,14 @@ int cf_moe_gather_all_u8(const uint8_t* d_src, uint8_t* d_dst, const int* d_row_
 int cf_moe_combine_all_bf16(void* d_mixed, const void* d_compact, const float* d_route_weights,
                             const int* d_row_indices, const int* d_counts, const int* d_offsets, int rows,
                             int num_experts, int H, void* stream);
+/* The same combine in one pass over the token rows, for dispatch lists in ascending row order (what
+ * cf_moe_build_expert_row_lists writes; the reference's own builder orders them arbitrarily, use cf_moe_combine_all_bf16
+ * for those): every row of mixed is read (accumulate != 0) or started from zero (accumulate == 0) and written once, the
+ * selected experts are added in ascending expert order with one bf16 rounding each, so the result equals zero-fill +
+ * cf_moe_combine_all_bf16 bit for bit. */
+int cf_moe_combine_sorted_bf16(void* d_mixed, const void* d_compact, const float* d_route_weights, const int* d_row_indices,
+                               const int* d_counts, const int* d_offsets, int rows, int num_experts, int H, int accumulate,
+                               void* stream);
 
 /* kernels/moe.cu:1062-1127, kernels.hpp:414-423: grouped selected-expert FP8 forward with exact-erf GELU,
  * accumulating rw*y into d_mixed. The tensor-core implementation needs workspace, which the reference

@@ -166,6 +166,15 @@ def test_permute_and_combine(cfb, oracle, width):
                                                 i_n[e, :c_n[e]], e)
     cfb.moe_combine_all_bf16(mixed_b, y, rw, idx, counts, offs, rows, E, width)
     assert np.array_equal(bf16_to_u16(mixed_a), m_o) and torch.equal(mixed_a, mixed_b)
+    # the single-pass form over the ascending lists: accumulating, and starting from zero
+    mixed_s = randn_bf16((rows, width), seed=10)
+    cfb.moe_combine_sorted_bf16(mixed_s, y, rw, idx, counts, offs, rows, E, width, accumulate=True)
+    assert torch.equal(mixed_s.view(torch.int16), mixed_a.view(torch.int16))
+    zero_then_all = torch.zeros((rows, width), dtype=torch.bfloat16, device="cuda")
+    cfb.moe_combine_all_bf16(zero_then_all, y, rw, idx, counts, offs, rows, E, width)
+    fresh = randn_bf16((rows, width), seed=13)          # stale contents must not leak into the result
+    cfb.moe_combine_sorted_bf16(fresh, y, rw, idx, counts, offs, rows, E, width, accumulate=False)
+    assert torch.equal(fresh.view(torch.int16), zero_then_all.view(torch.int16))
     term = randn_bf16((rows, width), seed=11)
     mixed_c = randn_bf16((rows, width), seed=12)
     m2 = bf16_to_u16(mixed_c).copy()

@@ -401,14 +401,19 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     }
 #endif
                     if (PAIR) {
-                        if (leader) mbar_expect_tx(full_bar + 8 * s, 2 * (A_STAGE + B_STAGE));
+                        bool load_a = true, load_b = true;
+#ifdef CF_GEMM_EXPERIMENT
+                        if ((p.experiment & 8) && it >= STAGES) load_b = false;    // stale B after the first ring fill
+                        if ((p.experiment & 16) && it >= STAGES) load_a = false;   // stale A after the first ring fill
+#endif
+                        if (leader) mbar_expect_tx(full_bar + 8 * s, 2 * ((load_a ? A_STAGE : 0) + (load_b ? B_STAGE : 0)));
                         // K-major operands: x runs along K; MN-major operands ([K, M] / [K, N] in memory): x runs
                         // along M / N and the box rows are K
                         const bool mn = WIDE && p.mn_major;
                         const int ax = mn ? a_row : kb * BK, ay = mn ? kb * BK : a_row;
                         const int bx = mn ? b_row : kb * BK, by = mn ? kb * BK : b_row;
-                        tma_load_2d_pair(smem_a + s * A_STAGE, &map_a, full_dst + 8 * s, ax, ay);
-                        tma_load_2d_pair(smem_b + s * B_STAGE, &map_b, full_dst + 8 * s, bx, by);
+                        if (load_a) tma_load_2d_pair(smem_a + s * A_STAGE, &map_a, full_dst + 8 * s, ax, ay);
+                        if (load_b) tma_load_2d_pair(smem_b + s * B_STAGE, &map_b, full_dst + 8 * s, bx, by);
                     } else {
                         mbar_expect_tx(full_bar + 8 * s, A_STAGE + B_STAGE);
                         tma_load_2d(smem_a + s * A_STAGE, &map_a, full_bar + 8 * s, kb * BK, a_row);

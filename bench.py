@@ -293,6 +293,90 @@ def run_moe(args):
         dist.destroy_process_group()
 
 
+def run_rowparallel(args):
+    """Configuration-3 down projection (M 16384, N 4096, K 14336) with K sharded over the ranks: the strong-scaling
+    form whose exchange is a reduce-scatter of the fp32 partial products. Two arms in one run: GEMM to fp32 + NCCL
+    all-reduce + rounding, and the GEMM whose epilogue adds its tiles straight into the owners' slices (NVLink
+    reduce-adds), followed by the bf16 read-out of this rank's rows."""
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    cfb = importlib.import_module("canopy-foundry_b200")
+    par = cfb.parallel
+    M, N, K = 16384, 4096, 14336
+    k0, k1 = par.shard_range(K, world, rank, 128)
+    Kl = k1 - k0
+    ctx = cfb.Fp8Ctx(act8_bytes=0)
+    g = torch.Generator(device=dev).manual_seed(5 + rank)
+    a8 = [torch.randint(0, 0x60, (M, Kl), generator=g, dtype=torch.uint8, device=dev) for _ in range(2)]
+    w8 = torch.randint(0, 0x60, (N, Kl), generator=g, dtype=torch.uint8, device=dev)
+    d = torch.full((4,), 2.0 ** -8, dtype=torch.float32, device=dev)
+    y_full = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    partial = torch.empty((M, N), dtype=torch.float32, device=dev)
+    y_slice = torch.empty((M // world, N), dtype=torch.bfloat16, device=dev)
+    rs = par.RowParallelReduceScatterGemm(cfb, ctx, M, N, device=dev)
+    it = [0]
+
+    def step_nccl():
+        it[0] += 1
+        par.row_parallel_gemm_fp8(cfb, ctx, M, N, Kl, a8[it[0] & 1], d, w8, d, y_full, partial=partial)
+
+    def step_fused():
+        it[0] += 1
+        rs.forward(a8[it[0] & 1], d, w8, d, y_slice)
+
+    def timed(fn):
+        for _ in range(args.warmup):
+            fn()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item() / args.steps
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    l0 = cfb.launch_count()
+    ms_nccl = timed(step_nccl)
+    ms_fused = timed(step_fused)
+    launches = cfb.launch_count() - l0
+    clocks = sampler.stop()
+    ctx.poll_status()
+    if rank == 0:
+        flop = 2.0 * M * N * K
+        print(json.dumps({
+            "metric": "fp8_row_parallel_gemm_tflops", "value": flop / (ms_fused * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_fused, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": "fp8_down_projection_M16384_N4096_K14336 (BASELINE config 3), K sharded over the ranks",
+                       "exchange": "reduce-scatter fused into the GEMM epilogue (bulk reduce-adds into the owners' slices)",
+                       "l2": "two rotating activation shards, operands and output larger than L2"},
+            "gemm_plus_nccl_allreduce": {"ms_per_step": ms_nccl, "tflops": flop / (ms_nccl * 1e-3) / 1e12,
+                                         "note": "fp32 partial product + NCCL all-reduce + rounding; every rank ends with all rows"},
+            "gpu_launches": int(launches), "clocks": clocks}), flush=True)
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -308,13 +392,15 @@ def main():
                     help="ep mode: the down GEMM stores its rows straight into the owners' buffers over NVLink (no return all-to-all)")
     ap.add_argument("--moe-mode", default="ep", choices=["ep", "dp"],
                     help="N > 1: ep = expert parallel with all-to-all (experts placed by load), dp = experts replicated, tokens sharded")
-    ap.add_argument("--workload", default="linear", choices=["linear", "moe"],
+    ap.add_argument("--workload", default="linear", choices=["linear", "moe", "rowparallel"],
                     help="linear = BASELINE configuration 2 (the headline line); moe = configuration 4 tokens/s")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
         return
+    if args.workload == "rowparallel":
+        return run_rowparallel(args)
     if args.workload == "moe":
         run_moe(args)
         return

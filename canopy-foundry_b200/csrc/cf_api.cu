@@ -65,6 +65,7 @@ struct Ctx {
     int scalar_used = 0;
     void* workspace = nullptr;
     size_t workspace_bytes = 0;
+    void* d_peer_maps = nullptr;      // 16 tensor maps for the reduce-scatter GEMM
     std::mutex mu;
 };
 
@@ -99,6 +100,7 @@ int cf_ctx_create(cf_ctx** out, size_t act8_bytes) {
     cudaError_t e = cudaGetDevice(&c->device);
     if (e == cudaSuccess) e = cudaMalloc(&c->d_status, 64);
     if (e == cudaSuccess) e = cudaMemset(c->d_status, 0, 64);
+    if (e == cudaSuccess) e = cudaMalloc(&c->d_peer_maps, 16 * 128);
     if (e == cudaSuccess && act8_bytes) { e = cudaMalloc(&c->act8, act8_bytes); c->act8_bytes = act8_bytes; }
     if (e == cudaSuccess) {
         c->scalar_blocks = kMaxSlots;
@@ -106,6 +108,7 @@ int cf_ctx_create(cf_ctx** out, size_t act8_bytes) {
     }
     if (e != cudaSuccess) {
         if (c->d_status) cudaFree(c->d_status);
+        if (c->d_peer_maps) cudaFree(c->d_peer_maps);
         if (c->act8) cudaFree(c->act8);
         if (c->scalar_pool) cudaFree(c->scalar_pool);
         delete c;
@@ -119,6 +122,7 @@ int cf_ctx_destroy(cf_ctx* ctx) {
     if (!ctx) return CF_OK;
     Ctx* c = reinterpret_cast<Ctx*>(ctx);
     if (c->d_status) cudaFree(c->d_status);
+    if (c->d_peer_maps) cudaFree(c->d_peer_maps);
     if (c->act8) cudaFree(c->act8);
     if (c->scalar_pool) cudaFree(c->scalar_pool);
     if (c->workspace) cudaFree(c->workspace);
@@ -198,6 +202,26 @@ int cf_gemm_fp8_nt(cf_ctx* ctx, int M, int N, int K, const void* d_A, int lda, i
         set_error("cf_gemm_fp8_nt: K == 0 is not supported");
         return CF_ERR_UNSUPPORTED;
     }
+    const int tiles = ((M + gemm_tile_m() - 1) / gemm_tile_m()) * ((N + gemm_tile_n() - 1) / gemm_tile_n());
+    return launch_gemm_fp8_nt(d_A, lda, M, d_B, N, p, tiles, as_stream(stream));
+}
+
+int cf_gemm_fp8_nt_reduce_scatter_f32(cf_ctx* ctx, int M, int N, int K, const void* d_A, int lda, int a_is_e5m2,
+                                      const float* d_a_descale, const void* d_B, const float* d_b_descale,
+                                      void* const* slices, int num_slices, void* stream) {
+    CF_REQUIRE(ctx != nullptr, "cf_gemm_fp8_nt_reduce_scatter_f32: null context");
+    CF_REQUIRE(M > 0 && N > 0 && K > 0 && lda >= K, "cf_gemm_fp8_nt_reduce_scatter_f32: bad shape");
+    CF_REQUIRE(d_A && d_B && d_a_descale && d_b_descale && slices, "cf_gemm_fp8_nt_reduce_scatter_f32: null pointer");
+    CF_REQUIRE(num_slices >= 1 && num_slices <= 16 && M % num_slices == 0, "cf_gemm_fp8_nt_reduce_scatter_f32: M must split evenly over 1..16 slices");
+    GemmParams p;
+    p.M = M; p.N = N; p.K = K;
+    p.d_a_descale = d_a_descale; p.d_b_descale = d_b_descale;
+    p.C = nullptr; p.ldc = N; p.out_kind = 2;
+    p.a_e5m2 = a_is_e5m2 ? 1 : 0;
+    p.peer_out_host = slices; p.peer_count = num_slices; p.rows_per_peer = M / num_slices;
+    Ctx* c = reinterpret_cast<Ctx*>(ctx);
+    p.d_peer_maps = c->d_peer_maps;
+    p.d_status = c->d_status;
     const int tiles = ((M + gemm_tile_m() - 1) / gemm_tile_m()) * ((N + gemm_tile_n() - 1) / gemm_tile_n());
     return launch_gemm_fp8_nt(d_A, lda, M, d_B, N, p, tiles, as_stream(stream));
 }

@@ -354,7 +354,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
-        if (p.tma_store || p.tma_reduce) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
+        if (p.tma_store || (p.tma_reduce && p.d_peer_maps == nullptr)) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
     }
     if (warp == 1) {
         if (PAIR) {
@@ -567,8 +567,17 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {
-                        if (p.tma_reduce == 2) tma_store_2d(&map_c, buf, col0, tc.row0 + warp_row0, store_policy);
-                        else tma_reduce_add_2d(&map_c, buf, col0, tc.row0 + warp_row0);
+                        if (p.tma_reduce == 2) {
+                            tma_store_2d(&map_c, buf, col0, tc.row0 + warp_row0, store_policy);
+                        } else if (p.d_peer_maps != nullptr) {
+                            // reduce-scatter: the slice that owns these rows, wherever it lives (NVLink for a peer's)
+                            const int grow0 = tc.row0 + warp_row0;
+                            const int owner = grow0 / p.rows_per_peer;
+                            tma_reduce_add_2d(static_cast<const CUtensorMap*>(p.d_peer_maps) + owner, buf, col0,
+                                              grow0 - owner * p.rows_per_peer);
+                        } else {
+                            tma_reduce_add_2d(&map_c, buf, col0, tc.row0 + warp_row0);
+                        }
                         bulk_commit();
                     }
                 }
@@ -933,6 +942,10 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     { const char* e = std::getenv("CF_GEMM_EXPERIMENT"); p.experiment = e ? std::atoi(e) : 0; }
     { const char* e = std::getenv("CF_GEMM_RASTER"); if (e && std::atoi(e) > 0) p.raster_m = std::atoi(e); }
 #endif
+    if (p.peer_out_host != nullptr && !tma_ok) {
+        set_error("reduce-scatter GEMM: operands must be 16-byte aligned with K %% 16 == 0");
+        return CF_ERR_UNSUPPORTED;
+    }
     if (!tma_ok) {
         const int grid = sm_count() * 4;
         k_gemm_fp8_nt_simt<<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(d_A), lda, static_cast<const uint8_t*>(d_B), p);
@@ -969,9 +982,35 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
                    (p.d_b_col_descale == nullptr || reinterpret_cast<uintptr_t>(p.d_b_col_descale) % 16 == 0)) ? 1 : 0;
     static const bool no_tma_store = [] { const char* e = std::getenv("CF_GEMM_DIRECT_STORE"); return e && e[0] == '1'; }();
     if (no_tma_store) p.tma_store = 0;
-    p.tma_reduce = ((p.out_kind == 2 || p.out_kind == 1) && ca % 16 == 0 && p.ldc % 4 == 0 && p.N >= 32 && p.d_group_out == nullptr &&
-                    p.d_a_row_descale == nullptr && p.d_b_col_descale == nullptr && !no_tma_store) ? (p.out_kind == 2 ? 1 : 2) : 0;
-    if (p.tma_store) {
+    if (p.peer_out_host != nullptr) {
+        // every tile must lie inside one slice and take the TMA path as a whole (no ragged rows, no column tail)
+        if (p.out_kind != 2 || p.d_counts != nullptr || p.peer_count < 1 || p.peer_count > 16 || p.d_peer_maps == nullptr ||
+            p.rows_per_peer <= 0 || p.rows_per_peer % 256 != 0 || p.M != p.rows_per_peer * p.peer_count || p.N % 32 != 0 ||
+            !tma_ok || p.d_a_row_descale || p.d_b_col_descale) {
+            set_error("reduce-scatter GEMM: needs TMA-aligned operands, N %% 32 == 0, M = peers x rows_per_peer with rows_per_peer %% 256 == 0, per-tensor scales");
+            return CF_ERR_UNSUPPORTED;
+        }
+        CUtensorMap hmaps[16];
+        for (int i = 0; i < p.peer_count; ++i) {
+            if (p.peer_out_host[i] == nullptr || reinterpret_cast<uintptr_t>(p.peer_out_host[i]) % 16 != 0) {
+                set_error("reduce-scatter GEMM: slice %d is null or not 16-byte aligned", i);
+                return CF_ERR_INVALID_ARG;
+            }
+            r = make_map_c_f32(&hmaps[i], p.peer_out_host[i], p.rows_per_peer, p.N, p.N);
+            if (r != CF_OK) return r;
+        }
+        // pageable source: the runtime stages the bytes before the call returns, so the stack array may go
+        CF_CUDA(cudaMemcpyAsync(p.d_peer_maps, hmaps, sizeof(CUtensorMap) * p.peer_count, cudaMemcpyHostToDevice, st));
+        p.peer_out_host = nullptr;          // host pointer: of no use to the kernel
+    } else {
+        p.d_peer_maps = nullptr;
+    }
+    const bool f32_tma = (p.out_kind == 2 || p.out_kind == 1) && ca % 16 == 0 && p.ldc % 4 == 0 && p.N >= 32 &&
+                         p.d_group_out == nullptr && p.d_a_row_descale == nullptr && p.d_b_col_descale == nullptr && !no_tma_store;
+    p.tma_reduce = p.d_peer_maps ? 1 : (f32_tma ? (p.out_kind == 2 ? 1 : 2) : 0);
+    if (p.d_peer_maps) {
+        map_c = map_a;   // the kernel takes its output maps from d_peer_maps
+    } else if (p.tma_store) {
         r = make_map_c(&map_c, p.C, p.c_rows, p.N, p.ldc);
         if (r != CF_OK) return r;
     } else if (p.tma_reduce) {

@@ -31,6 +31,13 @@ struct GemmParams {
     int tma_store = 0;              // filled by the launcher: bf16 output goes through shared memory + TMA stores
     int tma_reduce = 0;             // filled by the launcher: fp32 beta=1 output goes through TMA reduce-add
     long long c_rows = 0;           // filled by the launcher: row extent of C for the store tensor map
+    // Reduce-scatter form (out_kind 2 only): rows [r * rows_per_peer, (r + 1) * rows_per_peer) of the product are added
+    // into peer_out_host[r], rank r's fp32 [rows_per_peer, N] slice as mapped in this process (may be a peer GPU's
+    // memory). The launcher encodes one tensor map per slice into d_peer_maps (device, peer_count * 128 bytes).
+    void* const* peer_out_host = nullptr;
+    int peer_count = 0;
+    int rows_per_peer = 0;
+    void* d_peer_maps = nullptr;
     int mn_major = 0;               // operands are [K, M] and [K, N] in memory (un-transposed weight-gradient form)
     long long ldb = 0;              // mn_major: row pitch of B in bytes
     int a_e5m2 = 0;

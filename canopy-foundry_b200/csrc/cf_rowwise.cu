@@ -146,6 +146,28 @@ __global__ void __launch_bounds__(kRT) k_swiglu_record(const uint16_t* __restric
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// out = bf16(acc), acc = 0: the reader side of a reduce-scatter into an fp32 accumulation slice.
+__global__ void __launch_bounds__(kRT) k_finish_f32(float* __restrict__ acc, uint16_t* __restrict__ out, size_t n, int vec) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * kRT;
+    const size_t nv = vec ? n / 8 : 0;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * kRT + threadIdx.x; i < nv; i += stride) {
+        float4* a = reinterpret_cast<float4*>(acc) + 2 * i;
+        const float4 lo = a[0], hi = a[1];
+        uint4 o;
+        o.x = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(lo.x))) | (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(lo.y))) << 16);
+        o.y = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(lo.z))) | (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(lo.w))) << 16);
+        o.z = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(hi.x))) | (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(hi.y))) << 16);
+        o.w = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(hi.z))) | (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(hi.w))) << 16);
+        reinterpret_cast<uint4*>(out)[i] = o;
+        a[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+        a[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (size_t i = nv * 8 + static_cast<size_t>(blockIdx.x) * kRT + threadIdx.x; i < n; i += stride) {
+        out[i] = __bfloat16_as_ushort(__float2bfloat16_rn(acc[i]));
+        acc[i] = 0.0f;
+    }
+}
+
 }  // namespace
 
 int swiglu_record_launch(const void* d_gate, const void* d_up, int ld_in, void* d_out, int ld_out, const float* d_scale,
@@ -196,6 +218,19 @@ int cf_swiglu_quantize_rowwise_e4m3(const void* d_gate, const void* d_up, int ld
                                                          ld_in, static_cast<uint8_t*>(d_out), ld_out, d_row_scale,
                                                          d_row_descale, cols, vec);
     CF_LAUNCH_CHECK("swiglu_quantize_rowwise_e4m3");
+    return CF_OK;
+}
+
+int cf_f32_to_bf16_and_zero(float* d_acc, void* d_out, size_t n, void* stream) {
+    if (n == 0) return CF_OK;
+    CF_REQUIRE(d_acc && d_out, "cf_f32_to_bf16_and_zero: null pointer");
+    const int vec = aligned16(d_acc) && aligned16(d_out);
+    size_t blocks = (n / 8 + kRT * 2 - 1) / (kRT * 2);
+    const size_t cap = static_cast<size_t>(sm_count()) * 8;
+    if (blocks < 1) blocks = 1;
+    if (blocks > cap) blocks = cap;
+    k_finish_f32<<<static_cast<unsigned>(blocks), kRT, 0, as_stream(stream)>>>(d_acc, static_cast<uint16_t*>(d_out), n, vec);
+    CF_LAUNCH_CHECK("f32_to_bf16_and_zero");
     return CF_OK;
 }
 

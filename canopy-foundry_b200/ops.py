@@ -19,7 +19,7 @@ __all__ = [
     "fp8_quantize_e4m3_record", "fp8_quantize_e5m2_record", "fp8_update_delayed_scale",
     "fp8_quantize_transpose_e4m3", "fp8_quant_and_transpose_e4m3", "transpose_u8", "fp8_clip_probe",
     "fp8_elem_clip_count", "fp8_pack_bf16_e4m3_raw", "fp8_pack_bf16_e4m3_raw_and_dequant",
-    "fp8_unpack_e4m3_raw_bf16", "lt_gemm_fp8_nt", "lt_gemm_fp8_tn_accum_f32", "gemm_fp8_dw_accum", "gemm_fp8_nt_grouped", "gemm_fp8_nt_segments", "gemm_fp8_nt_segments_scatter",
+    "fp8_unpack_e4m3_raw_bf16", "lt_gemm_fp8_nt", "lt_gemm_fp8_tn_accum_f32", "gemm_fp8_dw_accum", "gemm_fp8_nt_reduce_scatter", "f32_to_bf16_and_zero", "gemm_fp8_nt_grouped", "gemm_fp8_nt_segments", "gemm_fp8_nt_segments_scatter",
     "fp8_quant_act", "fp8_swiglu_quant_act", "gemm_fp8_swiglu_quant_act", "fp8_interleave_gate_up", "refresh_fp8_weight", "fp8_linear_forward", "bias_add_strided_bf16", "swiglu_forward",
     "gelu_forward", "lion_step", "fp8_quantize_rowwise_e4m3", "swiglu_quantize_rowwise_e4m3", "swiglu_quantize_e4m3_record",
     "rmsnorm_forward", "rmsnorm_quantize_e4m3_record", "rmsnorm_quantize_rowwise_e4m3", "fp8_rmsnorm_quant_act",
@@ -279,6 +279,18 @@ def gemm_fp8_dw_accum(ctx, M, N, K, X8, ldx, ds_x, dY8, ldy, ds_dy, dW, ldc):
     """dW[M,N] += X8[K,M]^T . dY8[K,N] straight from the un-transposed operands (fp32 or bf16 dW)."""
     fn = _L().cf_gemm_fp8_dw_accum_f32 if dW.dtype == torch.float32 else _L().cf_gemm_fp8_dw_accum_bf16
     check(fn(ctx.handle, M, N, K, _p(X8), ldx, _p(ds_x), _p(dY8), ldy, _p(ds_dy), _p(dW), ldc, _s()))
+
+
+def gemm_fp8_nt_reduce_scatter(ctx, M, N, K_local, A, lda, a_is_e5m2, a_descale, B, b_descale, slice_ptrs):
+    """Row-parallel GEMM whose epilogue adds every row slice of the fp32 product into its owner's accumulation slice
+    (slice_ptrs: device addresses, one per rank, as mapped in this process)."""
+    arr = (C.c_void_p * len(slice_ptrs))(*[C.c_void_p(int(x)) for x in slice_ptrs])
+    check(_L().cf_gemm_fp8_nt_reduce_scatter_f32(ctx.handle, M, N, K_local, _p(A), lda, int(a_is_e5m2), _p(a_descale), _p(B),
+                                                 _p(b_descale), arr, len(slice_ptrs), _s()))
+
+
+def f32_to_bf16_and_zero(acc, out):
+    check(_L().cf_f32_to_bf16_and_zero(_p(acc), _p(out), acc.numel(), _s()))
 
 
 def gemm_fp8_nt_grouped(ctx, num_experts, max_total_rows, N, K, counts, offsets, A, lda, a_is_e5m2, a_descale,

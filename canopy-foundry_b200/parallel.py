@@ -161,6 +161,58 @@ def row_parallel_gemm_fp8(cfb, ctx, M, N, K_local, a8_local, a_descale, w8_local
     return out_bf16
 
 
+class RowParallelReduceScatterGemm:
+    """K-sharded (row-parallel) NT GEMM whose epilogue IS the reduce-scatter: every rank adds the row slices of its fp32
+    partial product straight into the owning rank's accumulation slice (bulk reduce-add copies into symmetric memory,
+    over NVLink for the other ranks' slices), so the exchange overlaps the main loop tile by tile and no fp32 partial
+    ever goes through a collective. Rank r ends up with rows [r * M/world, (r + 1) * M/world) of the product in bf16.
+    Two accumulation slices alternate: the one used by call i is zeroed again while it is read out, and the barrier of
+    call i + 1 orders that behind every rank's next use of it."""
+
+    def __init__(self, cfb, ctx, M, N, group=None, device="cuda"):
+        self.cfb, self.ctx, self.group, self.M, self.N = cfb, ctx, group, M, N
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        assert M % self.world == 0 and (M // self.world) % 256 == 0, "row slices must be multiples of 256 rows"
+        assert N % 32 == 0
+        self.rows = M // self.world
+        self._peers = []          # keeps the peer views alive
+        self.acc, self.ptrs = [], []
+        for _ in range(2):
+            if self.world > 1:
+                import torch.distributed._symmetric_memory as symm_mem
+                a = symm_mem.empty((self.rows, N), dtype=torch.float32, device=device)
+                hdl = symm_mem.rendezvous(a, group if group is not None else dist.group.WORLD)
+                views = [hdl.get_buffer(r, (self.rows, N), torch.float32) for r in range(self.world)]
+                self._peers.append((hdl, views))
+                ptrs = [v.data_ptr() for v in views]
+            else:
+                a = torch.empty((self.rows, N), dtype=torch.float32, device=device)
+                ptrs = [a.data_ptr()]
+            a.zero_()
+            self.acc.append(a)
+            self.ptrs.append(ptrs)
+        self._fence = torch.zeros(1, dtype=torch.float32, device=device)
+        self._flip = 0
+        self._barrier()           # every slice is zero before anyone adds to it
+
+    def _barrier(self):
+        if self.world > 1:
+            dist.all_reduce(self._fence, group=self.group)
+
+    def forward(self, a8_local, a_descale, w8_local, w_descale, out_slice_bf16):
+        """a8_local [M, K_local] E4M3 (this rank's K slice of every row), w8_local [N, K_local]; out_slice_bf16
+        [M/world, N] receives this rank's rows of the full product."""
+        b = self._flip
+        self._flip ^= 1
+        K_local = a8_local.shape[1]
+        self.cfb.gemm_fp8_nt_reduce_scatter(self.ctx, self.M, self.N, K_local, a8_local, a8_local.stride(0), False, a_descale,
+                                            w8_local, w_descale, self.ptrs[b])
+        self._barrier()           # every rank's GEMM, and the adds it sent here, have completed
+        self.cfb.f32_to_bf16_and_zero(self.acc[b], out_slice_bf16)
+        return out_slice_bf16
+
+
 class EpMoeSwigluFp8:
     """Expert-parallel form of ops.MoeSwigluFp8: tokens are data-parallel (this rank holds `rows` of them), experts
     are sharded over the ranks. Per layer: route locally -> counts all-gather -> E4M3 rows all-to-all -> ragged

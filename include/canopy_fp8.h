@@ -144,6 +144,21 @@ int cf_gemm_fp8_nt(cf_ctx* ctx, int M, int N, int K, const void* d_A, int lda, i
                    const float* d_a_descale, const void* d_B, const float* d_b_descale, void* d_C, int ldc,
                    const cf_gemm_epilogue* epi, void* stream);
 
+/* No counterpart in the reference (it runs on one GPU). Row-parallel (K-sharded) form of lt_gemm_fp8_nt with the
+ * reduce-scatter fused into the epilogue: this rank multiplies its K slice, A8[M, K_local] . B8[N, K_local]^T, and ADDS
+ * rows [r * M/num_slices, (r + 1) * M/num_slices) of the scaled fp32 product into slices[r], rank r's fp32
+ * [M/num_slices, N] accumulation slice as mapped in this process (symmetric / peer-mapped memory for r != own rank).
+ * The tiles leave the SM as bulk reduce-add copies (whole 128-byte lines, one fp32 addition per element at the
+ * destination), so the transfer over NVLink overlaps the main loop tile by tile. `slices` is a HOST array of
+ * num_slices (1..16) device pointers, 16-byte aligned. The caller zeroes its own slice beforehand and orders the
+ * readers behind every rank's launch (a barrier after the call). Needs M/num_slices % 256 == 0, N % 32 == 0,
+ * 16-byte aligned operands, K % 16 == 0, per-tensor scales. */
+int cf_gemm_fp8_nt_reduce_scatter_f32(cf_ctx* ctx, int M, int N, int K, const void* d_A, int lda, int a_is_e5m2,
+                                      const float* d_a_descale, const void* d_B, const float* d_b_descale,
+                                      void* const* slices, int num_slices, void* stream);
+/* Finishes a reduce-scatter: out[i] = bf16(acc[i]) and acc[i] = 0 (ready for the next accumulation). */
+int cf_f32_to_bf16_and_zero(float* d_acc, void* d_out, size_t n, void* stream);
+
 /* src/trainer.cu:4596-4625 and :4670-4691 (lt_gemm_fp8_tn_accum_f32, fp32 and bf16 accumulators).
  * dW[M,N] += (*d_ds_x * *d_ds_dy) * sum_k Xt[m,k] * dYt[n,k]; Xt E4M3 [M,K], dYt E5M2 [N,K], both
  * contiguous with leading dimension K. */

@@ -302,3 +302,32 @@ def test_weight_gradient_unaligned_pitch_is_refused(cfb, ctx):
     with pytest.raises(cfb.CanopyError) as ei:
         cfb.gemm_fp8_dw_accum(ctx, 520, 1000, 64, x8, 520, d, dy8, 1000, d, dw, 1000)
     assert ei.value.code == cfb._capi.CF_ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("slices", [1, 2, 4])
+def test_reduce_scatter_epilogue_on_one_gpu(cfb, slices):
+    """The reduce-scatter GEMM with every slice on this GPU: slice r receives rows [r*M/slices, (r+1)*M/slices) of the
+    product, added to what it held: two calls over the two K halves leave the sum of the two fp32 partial products."""
+    M, N, K = 1024, 320, 1024
+    a8 = torch.randint(0, 0x58, (M, K), dtype=torch.uint8, device="cuda")
+    w8 = torch.randint(0, 0x58, (N, K), dtype=torch.uint8, device="cuda")
+    da, dw = f32_scalar(2.0 ** -6), f32_scalar(2.0 ** -5)
+    ctx = cfb.Fp8Ctx(0)
+    h = K // 2
+    p1 = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    p2 = torch.empty_like(p1)
+    cfb.lt_gemm_fp8_nt(ctx, M, N, h, a8[:, :h], K, False, da, w8[:, :h].contiguous(), dw, p1, N)
+    cfb.lt_gemm_fp8_nt(ctx, M, N, h, a8[:, h:], K, False, da, w8[:, h:].contiguous(), dw, p2, N)
+    want = p1 + p2                      # one fp32 addition per element, as the reduce-adds perform it
+    acc = [torch.zeros((M // slices, N), dtype=torch.float32, device="cuda") for _ in range(slices)]
+    ptrs = [a.data_ptr() for a in acc]
+    cfb.gemm_fp8_nt_reduce_scatter(ctx, M, N, h, a8[:, :h], K, False, da, w8[:, :h].contiguous(), dw, ptrs)
+    cfb.gemm_fp8_nt_reduce_scatter(ctx, M, N, h, a8[:, h:], K, False, da, w8[:, h:].contiguous(), dw, ptrs)
+    got = torch.cat(acc)
+    assert torch.equal(got, want)
+    out = torch.empty((M // slices, N), dtype=torch.bfloat16, device="cuda")
+    cfb.f32_to_bf16_and_zero(acc[0], out)
+    assert torch.equal(out, want[:M // slices].to(torch.bfloat16)) and int(acc[0].abs().max().item()) == 0
+    with pytest.raises(cfb.CanopyError):      # 300-row slices are not multiples of 256
+        cfb.gemm_fp8_nt_reduce_scatter(ctx, 600, N, h, a8[:600, :h], K, False, da, w8[:, :h].contiguous(), dw, ptrs[:2])
+    ctx.poll_status()

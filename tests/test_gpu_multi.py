@@ -72,6 +72,23 @@ def _worker(rank, world, port, ret):
         y_rp = torch.empty_like(y_ref)
         par.row_parallel_gemm_fp8(cfb, ctx, Mr, Nr, khi - klo, a8f[:, klo:khi], daf, w8f[:, klo:khi].contiguous(), dwf, y_rp)
         assert rel_fro(y_rp.float().cpu().numpy(), y_ref.float().cpu().numpy()) < 3e-3
+        # ---- the same GEMM with the reduce-scatter fused into its epilogue (bulk reduce-adds into the owners' slices
+        # over NVLink): with two ranks the fp32 sum has one order, so the rows equal the all-reduce form bit for bit
+        Mf, Nf, Kf = 1024, 384, 2048
+        a_f = randn_bf16((Mf, Kf), seed=15, device=dev)
+        w_f = randn_bf16((Nf, Kf), std=0.02, seed=16, device=dev)
+        a8g, dag = _tensorquant(cfb, a_f)
+        w8g, dwg = _tensorquant(cfb, w_f)
+        k0, k1 = par.shard_range(Kf, world, rank, 128)
+        want = torch.empty((Mf, Nf), dtype=torch.bfloat16, device=dev)
+        par.row_parallel_gemm_fp8(cfb, ctx, Mf, Nf, k1 - k0, a8g[:, k0:k1], dag, w8g[:, k0:k1].contiguous(), dwg, want)
+        rs = par.RowParallelReduceScatterGemm(cfb, ctx, Mf, Nf, device=dev)
+        got = torch.empty((Mf // world, Nf), dtype=torch.bfloat16, device=dev)
+        for _ in range(3):          # both accumulation slices, and the re-zeroing between uses
+            got.zero_()
+            rs.forward(a8g[:, k0:k1], dag, w8g[:, k0:k1].contiguous(), dwg, got)
+            assert torch.equal(got.view(torch.int16), want[rank * (Mf // world):(rank + 1) * (Mf // world)].view(torch.int16))
+        ctx.poll_status()
         # ---- expert-parallel MoE vs the single-GPU layer on all tokens
         rows, H, F, E, k = 256, 128, 256, 4, 2
         gw = torch.Generator(device=dev).manual_seed(11)

@@ -216,15 +216,28 @@ def run_moe(args):
     p = torch.tensor([pz[e] for e in perm], device=dev, dtype=torch.float32)
     logits = (torch.randn((rows, E), generator=g, device=dev) + torch.log(p / p.sum())).contiguous()
 
+    # Expert parallelism under the skewed load: popular experts are replicated so that every rank expects the same
+    # number of rows (ReplicaPlacement). The expected load is the observed one of a calibration routing of this batch
+    # (summed over the ranks), as a trainer would take it from the previous steps.
+    placement = None
+    if use_ep and not args.moe_no_replicas:
+        rw0 = logits.clone()
+        cfb.moe_topk_route_f32(rw0, rows, E, TOPK)
+        load = (rw0 > 0).sum(dim=0).to(torch.float32)
+        dist.all_reduce(load)
+        placement = par.ReplicaPlacement.build(load.cpu().tolist(), world)
+        local_ids = placement.local_experts(rank)
+    else:
+        local_ids = list(range(e_lo, e_hi))
+
     def quant_experts(shape, std, seed):
-        gw = torch.Generator(device=dev).manual_seed(seed)
         amax = torch.zeros(4, dtype=torch.float32, device=dev)
         sc, de = torch.zeros_like(amax), torch.zeros_like(amax)
         w8 = torch.empty(shape, dtype=torch.uint8, device=dev)
         ws = []
-        for e in range(shape[0]):                       # one expert at a time keeps the bf16 staging small
-            w = (torch.randn(shape[1:], generator=gw, device=dev, dtype=torch.float32) * std).to(torch.bfloat16)
-            ws.append(w)
+        for e in local_ids:                             # replicas of one expert hold the same weights on every rank
+            gw = torch.Generator(device=dev).manual_seed(seed + perm[e])
+            ws.append((torch.randn(shape[1:], generator=gw, device=dev, dtype=torch.float32) * std).to(torch.bfloat16))
         wall = torch.stack(ws)
         cfb.fp8_amax_bf16(wall, amax)
         par.allreduce_max_(amax)                        # one per-tensor scale over all experts of all ranks
@@ -232,16 +245,20 @@ def run_moe(args):
         cfb.fp8_quantize_e4m3(wall, w8, sc)
         return w8, de
 
-    n_local = e_hi - e_lo
-    wgu8, dgu = quant_experts((n_local, 2 * F, H), 0.02, 50 + rank)
-    wd8, dd = quant_experts((n_local, H, F), 0.02, 70 + rank)
+    n_local = len(local_ids)
+    wgu8, dgu = quant_experts((n_local, 2 * F, H), 0.02, 50)
+    wd8, dd = quant_experts((n_local, H, F), 0.02, 70)
     mixed = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
     fused_swiglu = not args.moe_unfused_swiglu
     if fused_swiglu:
         wgu8 = cfb.fp8_interleave_gate_up(wgu8)       # one-time weight layout for the fused SwiGLU epilogue
-    layer = par.EpMoeSwigluFp8(cfb, ctx, rows, H, F, E, TOPK, device=dev, fused_return=args.moe_fused_return,
-                               fused_swiglu=fused_swiglu) if use_ep else \
-        cfb.MoeSwigluFp8(ctx, rows, H, F, E, TOPK, device=dev, fused_swiglu=fused_swiglu)
+    if use_ep and args.moe_direct:
+        layer = par.EpMoeSwigluFp8Direct(cfb, ctx, rows, H, F, E, TOPK, placement=placement, device=dev)
+    elif use_ep:
+        layer = par.EpMoeSwigluFp8(cfb, ctx, rows, H, F, E, TOPK, device=dev, fused_return=args.moe_fused_return,
+                                   fused_swiglu=fused_swiglu, placement=placement)
+    else:
+        layer = cfb.MoeSwigluFp8(ctx, rows, H, F, E, TOPK, device=dev, fused_swiglu=fused_swiglu)
 
     def step():
         rw = logits.clone()
@@ -269,7 +286,7 @@ def run_moe(args):
     launches = cfb.launch_count() - l0
     ctx.poll_status()
     t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    loads = torch.tensor([float(layer.plan.total_recv) if use_ep else float(rows * TOPK)], dtype=torch.float64, device=dev)
+    loads = torch.tensor([float(layer.grp_counts.sum().item()) if (use_ep and args.moe_direct) else float(layer.plan.total_recv) if use_ep else float(rows * TOPK)], dtype=torch.float64, device=dev)
     lmax = loads.clone()
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -282,7 +299,7 @@ def run_moe(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
             "config": {"workload": "moe_swiglu_fp8_32768tok_H4096_E8_F14336_top2_zipf1.1 (BASELINE config 4)",
-                       "parallelism": (f"ep{world} (all-to-all, experts placed by load{', GEMM-fused return leg' if args.moe_fused_return else ''})" if use_ep else
+                       "parallelism": (f"ep{world} ({'device-planned dispatch, rows stored into the serving ranks over NVLink' if args.moe_direct else 'all-to-all'}, {'popular experts replicated: ' + str(placement.num_replicas) + ' replicas of ' + str(E) + ' experts' if placement else 'experts placed by load'}{', GEMM-fused return leg' if args.moe_fused_return else ''})" if use_ep else
                                        f"dp{world} (experts replicated, tokens sharded, no collective)") if world > 1 else "single GPU",
                        "swiglu": "fused into the gate/up GEMM epilogue" if fused_swiglu else "separate pass over the bf16 intermediate",
                        "max_rows_on_one_rank": int(lmax.item()), "mean_rows_per_rank": TOK * TOPK / world,
@@ -390,6 +407,10 @@ def main():
     ap.add_argument("--moe-unfused-swiglu", action="store_true", help="keep the [T,2F] bf16 intermediate (separate SwiGLU pass)")
     ap.add_argument("--moe-fused-return", action="store_true",
                     help="ep mode: the down GEMM stores its rows straight into the owners' buffers over NVLink (no return all-to-all)")
+    ap.add_argument("--moe-direct", action="store_true",
+                    help="expert parallel with plan, dispatch and return on the device (no host copy of the counts)")
+    ap.add_argument("--moe-no-replicas", action="store_true",
+                    help="expert parallel without replicas of the popular experts (one owner per expert, placed by load)")
     ap.add_argument("--moe-mode", default="ep", choices=["ep", "dp"],
                     help="N > 1: ep = expert parallel with all-to-all (experts placed by load), dp = experts replicated, tokens sharded")
     ap.add_argument("--workload", default="linear", choices=["linear", "moe", "rowparallel"],

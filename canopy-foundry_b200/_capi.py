@@ -104,6 +104,9 @@ SIGNATURES = {
     "cf_moe_gather_all_u8": (ci, [vp, vp, ip, ip, ip, ci, ci, ci, vp]),
     "cf_moe_combine_all_bf16": (ci, [vp, vp, fp, ip, ip, ip, ci, ci, ci, vp]),
     "cf_moe_combine_sorted_bf16": (ci, [vp, vp, fp, ip, ip, ip, ci, ci, ci, ci, vp]),
+    "cf_moe_expand_route_replicas": (ci, [fp, fp, ci, ci, ci, ip, fp, C.c_uint, vp]),
+    "cf_moe_ep_plan": (ci, [ip, ci, ci, ci, ip, ip, vp, ip, ip, vp, vp]),
+    "cf_moe_send_row_runs": (ci, [vp, ip, C.c_longlong, vp, ci, ci, vp, C.c_longlong, fp, vp, vp]),
     "cf_moe_grouped_expert_forward_fp8": (ci, [vp, vp, fp, ci, fp, ip, ip, ip, vp, fp, vp, fp, vp, ci, ci, ci, ci, ci, vp]),
 }
 

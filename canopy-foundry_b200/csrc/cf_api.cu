@@ -543,7 +543,8 @@ int cf_gemm_fp8_swiglu_quant_act(cf_ctx* ctx, cf_act_slot* slot, int num_segment
     p.M = max_total_rows;
     p.N = 2 * F; p.K = K;
     p.d_counts = d_counts; p.d_offsets = d_offsets; p.d_group_weight = d_segment_weight;
-    p.d_a_descale = d_a_descale; p.a_descale_per_group = per_segment_a_descale ? 1 : 0;
+    p.d_a_descale = d_a_descale; p.a_descale_per_group = per_segment_a_descale == 1 ? 1 : 0;
+    if (per_segment_a_descale == 2) p.d_a_row_descale = d_a_descale;      // one descale per row of A
     p.d_b_descale = d_w_descale;
     p.C = d_h8; p.ldc = ldh; p.out_kind = 4;
     p.a_e5m2 = a_is_e5m2 ? 1 : 0;

@@ -932,8 +932,8 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     if (p.out_kind == 4) {
         // E4M3 output of width N/2: 16-byte stores need an aligned base and row pitch; whole 64-column groups only
         if (!tma_ok || ca % 16 != 0 || p.ldc % 16 != 0 || p.N % 64 != 0 || !p.d_quant_scale || !p.d_amax_out ||
-            p.d_a_row_descale || p.d_b_col_descale || p.d_group_out) {
-            set_error("swiglu epilogue: needs TMA-aligned operands, N %% 64 == 0, a 16-byte aligned E4M3 output, per-tensor scales");
+            p.d_b_col_descale || p.d_group_out) {
+            set_error("swiglu epilogue: needs TMA-aligned operands, N %% 64 == 0, a 16-byte aligned E4M3 output, no per-column scales");
             return CF_ERR_UNSUPPORTED;
         }
         p.c_vec = 0;

@@ -331,6 +331,93 @@ __global__ void __launch_bounds__(kT) k_combine_rows(uint16_t* __restrict__ mixe
     }
 }
 
+// ---- expert replicas: spread every expert's tokens over its replicas ------------------------------
+// route weights [rows, E] -> [rows, V] over "virtual experts" (expert e owns the virtual ids [vstart[e], vstart[e+1]),
+// each one a replica of e's weights on some rank). A selected (row, e) goes to exactly one replica, picked by a hash of
+// the global row index against the replicas' cumulative shares, so every replica receives its share of the expert's rows.
+__device__ __forceinline__ float replica_u01(unsigned row, unsigned e) {
+    unsigned h = (row * 0x9E3779B1u) ^ ((e + 1u) * 0x85EBCA77u);
+    h ^= h >> 15; h *= 0x2C1B3C6Du; h ^= h >> 12; h *= 0x297A2D39u; h ^= h >> 15;
+    return static_cast<float>(h >> 8) * (1.0f / 16777216.0f);
+}
+__global__ void __launch_bounds__(kT) k_expand_route(const float* __restrict__ rw, float* __restrict__ rwv, int rows, int E, int V,
+                                                     const int* __restrict__ vstart, const float* __restrict__ vcum,
+                                                     unsigned row0) {
+    const int row = blockIdx.x * kT + threadIdx.x;
+    if (row >= rows) return;
+    float* out = rwv + static_cast<size_t>(row) * V;
+    for (int v = 0; v < V; ++v) out[v] = 0.0f;
+    for (int e = 0; e < E; ++e) {
+        const float w = rw[static_cast<size_t>(row) * E + e];
+        if (!(w > 0.0f)) continue;
+        const float u = replica_u01(row0 + static_cast<unsigned>(row), static_cast<unsigned>(e));
+        int v = vstart[e];
+        const int last = vstart[e + 1] - 1;
+        while (v < last && u >= vcum[v]) ++v;
+        out[v] = w;
+    }
+}
+
+// ---- expert parallelism without a host round trip ---------------------------------------------------
+// All ranks hold the same table counts_all[world, V] (rows every source routes to every replica). Replica v lives on the
+// rank whose range [lo, hi) contains it; in that rank's receive buffer the replicas follow each other in id order and,
+// inside a replica, the sources in rank order ("expert-major"), so each replica is ONE ragged GEMM group whatever the
+// number of sources. One thread per replica derives where this rank's rows go, what this rank serves, and where the
+// results return to (the source's compact order: replica after replica).
+__global__ void k_ep_plan(const int* __restrict__ counts_all, int world, int me, int V, const int* __restrict__ lo,
+                          const int* __restrict__ hi, cf_row_run* __restrict__ send_runs, int* __restrict__ grp_counts,
+                          int* __restrict__ grp_offsets, cf_row_run* __restrict__ ret_runs) {
+    const int v = blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= V) return;
+    int owner = 0;
+    for (int g = 0; g < world; ++g) if (lo[g] <= v && v < hi[g]) owner = g;
+    long long base = 0;
+    for (int u = lo[owner]; u < v; ++u)
+        for (int s = 0; s < world; ++s) base += max(counts_all[s * V + u], 0);
+    long long pre_me = 0;
+    for (int s = 0; s < me; ++s) pre_me += max(counts_all[s * V + v], 0);
+    cf_row_run r;
+    r.src_row = 0; r.dst_row = base + pre_me; r.rows = max(counts_all[me * V + v], 0); r.dst = owner;
+    send_runs[v] = r;
+    if (owner != me) return;
+    const int vl = v - lo[me];
+    long long pre = 0;
+    for (int s = 0; s < world; ++s) {
+        const int c = max(counts_all[s * V + v], 0);
+        long long off_s = 0;
+        for (int u = 0; u < v; ++u) off_s += max(counts_all[s * V + u], 0);
+        cf_row_run q;
+        q.src_row = base + pre; q.dst_row = off_s; q.rows = c; q.dst = s;
+        ret_runs[vl * world + s] = q;
+        pre += c;
+    }
+    grp_counts[vl] = static_cast<int>(pre);
+    grp_offsets[vl] = static_cast<int>(base);
+}
+
+// Copies runs of rows to per-run destinations that may live on peer GPUs (plain 16-byte stores, whole rows contiguous).
+// blockIdx.y = run. Source rows: row_indices[run * idx_stride + i] when an index table is given, else src_row + i.
+// With a tag, the first thread of every row also stores *tag_value at tag_bases[dst][dst_row + i] (the row's descale).
+__global__ void __launch_bounds__(kT) k_send_rows(const uint8_t* __restrict__ src, const int* __restrict__ row_indices,
+                                                  long long idx_stride, const cf_row_run* __restrict__ runs,
+                                                  void* const* __restrict__ dst_bases, long long width_bytes,
+                                                  const float* __restrict__ tag_value, float* const* __restrict__ tag_bases) {
+    const cf_row_run run = runs[blockIdx.y];
+    if (run.rows <= 0) return;
+    uint8_t* dst = static_cast<uint8_t*>(dst_bases[run.dst]) + run.dst_row * width_bytes;
+    const int* idx = row_indices ? row_indices + blockIdx.y * idx_stride : nullptr;
+    const long long cpr = width_bytes / 16;
+    const long long total = static_cast<long long>(run.rows) * cpr;
+    const float tag = tag_value ? *tag_value : 0.0f;
+    float* tdst = tag_value ? tag_bases[run.dst] + run.dst_row : nullptr;
+    for (long long i = static_cast<long long>(blockIdx.x) * kT + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * kT) {
+        const long long r = i / cpr, c = i - r * cpr;
+        const long long srow = idx ? idx[r] : run.src_row + r;
+        *reinterpret_cast<uint4*>(dst + r * width_bytes + c * 16) = *reinterpret_cast<const uint4*>(src + srow * width_bytes + c * 16);
+        if (tdst && c == 0) tdst[r] = tag;
+    }
+}
+
 // ---- dense combine: mixed[row,:] += rw[row,e] * term[row,:] -----------------------------------------
 __global__ void __launch_bounds__(kT) k_scale_acc(uint16_t* __restrict__ mixed, const uint16_t* __restrict__ term,
                                                   const float* __restrict__ rw, long long rows, int expert, int E, int H) {
@@ -540,6 +627,50 @@ int cf_moe_combine_sorted_bf16(void* d_mixed, const void* d_compact, const float
         static_cast<uint16_t*>(d_mixed), static_cast<const uint16_t*>(d_compact), d_route_weights, d_row_indices, d_counts,
         d_offsets, rows, num_experts, H, accumulate);
     CF_LAUNCH_CHECK("moe_combine_sorted_bf16");
+    return CF_OK;
+}
+
+int cf_moe_expand_route_replicas(const float* d_route_weights, float* d_replica_weights, int rows, int num_experts,
+                                 int num_replicas, const int* d_replica_start, const float* d_replica_cum_share,
+                                 unsigned first_row, void* stream) {
+    CF_REQUIRE(rows >= 0 && num_experts >= 1 && num_replicas >= num_experts, "cf_moe_expand_route_replicas: bad shape");
+    if (rows == 0) return CF_OK;
+    CF_REQUIRE(d_route_weights && d_replica_weights && d_replica_start && d_replica_cum_share, "cf_moe_expand_route_replicas: null pointer");
+    k_expand_route<<<(rows + kT - 1) / kT, kT, 0, as_stream(stream)>>>(d_route_weights, d_replica_weights, rows, num_experts,
+                                                                       num_replicas, d_replica_start, d_replica_cum_share, first_row);
+    CF_LAUNCH_CHECK("moe_expand_route_replicas");
+    return CF_OK;
+}
+
+int cf_moe_ep_plan(const int* d_counts_all, int world, int rank, int num_replicas, const int* d_range_lo, const int* d_range_hi,
+                   cf_row_run* d_send_runs, int* d_group_counts, int* d_group_offsets, cf_row_run* d_return_runs, void* stream) {
+    CF_REQUIRE(world >= 1 && rank >= 0 && rank < world && num_replicas >= 1, "cf_moe_ep_plan: bad shape");
+    CF_REQUIRE(d_counts_all && d_range_lo && d_range_hi && d_send_runs && d_group_counts && d_group_offsets && d_return_runs,
+               "cf_moe_ep_plan: null pointer");
+    k_ep_plan<<<(num_replicas + 63) / 64, 64, 0, as_stream(stream)>>>(d_counts_all, world, rank, num_replicas, d_range_lo,
+                                                                      d_range_hi, d_send_runs, d_group_counts, d_group_offsets,
+                                                                      d_return_runs);
+    CF_LAUNCH_CHECK("moe_ep_plan");
+    return CF_OK;
+}
+
+int cf_moe_send_row_runs(const void* d_src, const int* d_row_indices_or_null, long long index_stride, const cf_row_run* d_runs,
+                         int num_runs, int max_rows_per_run, void* const* d_dst_bases, long long row_bytes,
+                         const float* d_tag_value_or_null, float* const* d_tag_bases_or_null, void* stream) {
+    CF_REQUIRE(num_runs >= 0 && max_rows_per_run >= 0 && row_bytes > 0 && row_bytes % 16 == 0,
+               "cf_moe_send_row_runs: rows must be whole 16-byte units");
+    if (num_runs == 0 || max_rows_per_run == 0) return CF_OK;
+    CF_REQUIRE(d_src && d_runs && d_dst_bases, "cf_moe_send_row_runs: null pointer");
+    CF_REQUIRE((d_tag_value_or_null == nullptr) == (d_tag_bases_or_null == nullptr), "cf_moe_send_row_runs: tag value and tag bases go together");
+    CF_REQUIRE(reinterpret_cast<uintptr_t>(d_src) % 16 == 0, "cf_moe_send_row_runs: source not 16-byte aligned");
+    const size_t items = static_cast<size_t>(max_rows_per_run) * static_cast<size_t>(row_bytes / 16);
+    unsigned gx = grid_for(items, kT * 4);
+    const unsigned cap = static_cast<unsigned>(sm_count()) * 8u / static_cast<unsigned>(num_runs) + 1u;
+    if (gx > cap) gx = cap;
+    dim3 grid(gx, num_runs);
+    k_send_rows<<<grid, kT, 0, as_stream(stream)>>>(static_cast<const uint8_t*>(d_src), d_row_indices_or_null, index_stride, d_runs,
+                                                    d_dst_bases, row_bytes, d_tag_value_or_null, d_tag_bases_or_null);
+    CF_LAUNCH_CHECK("moe_send_row_runs");
     return CF_OK;
 }
 

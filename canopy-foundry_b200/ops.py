@@ -25,7 +25,7 @@ __all__ = [
     "rmsnorm_forward", "rmsnorm_quantize_e4m3_record", "rmsnorm_quantize_rowwise_e4m3", "fp8_rmsnorm_quant_act",
     "moe_topk_route_f32", "moe_build_expert_row_lists", "moe_expert_offsets_from_counts",
     "moe_gather_rows_u8", "moe_gather_rows_bf16", "moe_scatter_accumulate_rows_bf16",
-    "moe_scale_accumulate_bf16", "moe_gather_all_u8", "moe_combine_all_bf16", "moe_combine_sorted_bf16",
+    "moe_scale_accumulate_bf16", "moe_gather_all_u8", "moe_combine_all_bf16", "moe_combine_sorted_bf16", "moe_expand_route_replicas", "moe_ep_plan", "moe_send_row_runs", "ROW_RUN_BYTES",
     "moe_grouped_expert_forward_fp8", "launch_count", "swiglu_mlp_fp8_rowwise", "MoeSwigluFp8", "FfnSwigluFp8",
 ]
 
@@ -428,6 +428,31 @@ def moe_combine_sorted_bf16(mixed, compact, route_weights, row_indices, counts, 
     written once; equals zero-fill + moe_combine_all_bf16 bit for bit."""
     check(_L().cf_moe_combine_sorted_bf16(_p(mixed), _p(compact), _p(route_weights), _p(row_indices), _p(counts),
                                           _p(offsets), rows, num_experts, H, int(accumulate), _s()))
+
+
+def moe_expand_route_replicas(route_weights, replica_weights, rows, num_experts, num_replicas, replica_start,
+                              replica_cum_share, first_row=0):
+    """[rows, E] sparse route weights -> [rows, V] over expert replicas (one replica per selected expert and row)."""
+    check(_L().cf_moe_expand_route_replicas(_p(route_weights), _p(replica_weights), rows, num_experts, num_replicas,
+                                            _p(replica_start), _p(replica_cum_share), int(first_row) & 0xffffffff, _s()))
+
+
+ROW_RUN_BYTES = 24      # sizeof(cf_row_run): two int64 and two int32
+
+
+def moe_ep_plan(counts_all, world, rank, num_replicas, range_lo, range_hi, send_runs, group_counts, group_offsets,
+                return_runs):
+    """Device-side plan of one expert-parallel layer from the gathered count table (no host copy)."""
+    check(_L().cf_moe_ep_plan(_p(counts_all), world, rank, num_replicas, _p(range_lo), _p(range_hi), _p(send_runs),
+                              _p(group_counts), _p(group_offsets), _p(return_runs), _s()))
+
+
+def moe_send_row_runs(src, row_indices, index_stride, runs, num_runs, max_rows_per_run, dst_bases, row_bytes,
+                      tag_value=None, tag_bases=None):
+    """Copies planned runs of rows into (peer) destination buffers; optional gather through an index table and a
+    per-row float tag. dst_bases / tag_bases: int64 device tensors of base addresses."""
+    check(_L().cf_moe_send_row_runs(_p(src), _p(row_indices), index_stride, _p(runs), num_runs, max_rows_per_run,
+                                    _p(dst_bases), row_bytes, _p(tag_value), _p(tag_bases), _s()))
 
 
 def moe_grouped_expert_forward_fp8(ctx, hidden, fcin_descale, fcin_is_e5m2, route_weights, counts, offsets, row_indices,

@@ -75,6 +75,86 @@ def all_to_all_rows(send, send_splits, recv_splits, group=None):
 
 
 @dataclass
+class ReplicaPlacement:
+    """Expert placement for a skewed load: the experts are laid end to end on a line, each as long as its expected share
+    of the rows, and the line is cut into `world` equal pieces, one per rank. Every (expert, rank) overlap is a replica
+    ("virtual expert") of that expert on that rank and receives the overlapping fraction of the expert's rows. Replica
+    ids ascend along the line, so every rank owns a contiguous id range (the layout EpPlan needs), ids ascend with the
+    expert id (the combine adds experts in the single-GPU order), and every rank expects the same number of rows.
+    A uniform load with world | E degenerates to plain expert sharding (one replica per expert)."""
+    world: int
+    num_experts: int
+    replica_expert: List[int]            # expert of each replica
+    replica_rank: List[int]              # rank that holds it
+    replica_share: List[float]           # fraction of its expert's rows it takes
+    replica_start: List[int]             # [E + 1] first replica id of each expert
+    replica_cum_share: List[float]       # cumulative share inside the expert (last replica of an expert: 1.0)
+    rank_ranges: List[tuple]             # [world] (lo, hi) replica ids per rank
+
+    @property
+    def num_replicas(self):
+        return len(self.replica_expert)
+
+    @classmethod
+    def build(cls, popularity, world, min_share=0.02):
+        """popularity: expected share of the rows per expert (any positive scale). Overlaps below `min_share` of a
+        rank's piece are not worth a weight copy: they are merged into the expert's neighbouring replica."""
+        E = len(popularity)
+        tot = float(sum(popularity))
+        assert tot > 0 and all(p >= 0 for p in popularity)
+        p = [float(x) / tot for x in popularity]
+        piece = 1.0 / world
+        rep_e, rep_r, rep_len = [], [], []
+        pos = 0.0
+        for e in range(E):
+            lo, hi = pos, pos + p[e]
+            pos = hi
+            g0 = min(int(lo / piece + 1e-12), world - 1)
+            g1 = min(int((hi - 1e-12) / piece), world - 1) if hi > lo else g0
+            parts = []
+            for g in range(g0, max(g1, g0) + 1):
+                ov = min(hi, (g + 1) * piece) - max(lo, g * piece)
+                parts.append([g, max(ov, 0.0)])
+            # drop slivers (keep at least one part)
+            keep = [q for q in parts if q[1] >= min_share * piece]
+            if not keep:
+                keep = [max(parts, key=lambda q: q[1])]
+            lost = sum(q[1] for q in parts) - sum(q[1] for q in keep)
+            keep[max(range(len(keep)), key=lambda i: keep[i][1])][1] += lost
+            for g, ov in keep:
+                rep_e.append(e); rep_r.append(g); rep_len.append(ov)
+        start, cum, share = [0] * (E + 1), [], []
+        v = 0
+        for e in range(E):
+            start[e] = v
+            ids = [i for i in range(len(rep_e)) if rep_e[i] == e]
+            tot_e = sum(rep_len[i] for i in ids) or 1.0
+            run = 0.0
+            for n, i in enumerate(ids):
+                sh = rep_len[i] / tot_e if p[e] > 0 else 1.0 / len(ids)
+                run += sh
+                share.append(sh)
+                cum.append(1.0 if n == len(ids) - 1 else run)
+                v += 1
+        start[E] = v
+        ranges = []
+        for g in range(world):
+            ids = [i for i in range(v) if rep_r[i] == g]
+            ranges.append((ids[0], ids[-1] + 1) if ids else (0, 0))
+        # ranks along the line are non-decreasing, so each rank's ids are contiguous; an empty rank gets an empty range
+        # placed where it belongs in the order
+        for g in range(world):
+            if ranges[g] == (0, 0):
+                prev_hi = max([ranges[q][1] for q in range(g) if ranges[q] != (0, 0)], default=0)
+                ranges[g] = (prev_hi, prev_hi)
+        return cls(world, E, rep_e, rep_r, share, start, cum, ranges)
+
+    def local_experts(self, rank):
+        lo, hi = self.rank_ranges[rank]
+        return [self.replica_expert[v] for v in range(lo, hi)]
+
+
+@dataclass
 class EpPlan:
     """Who sends how many rows to whom for one expert-parallel MoE layer.
 
@@ -98,10 +178,12 @@ class EpPlan:
         return shard_range(num_experts, world, rank)
 
     @classmethod
-    def build(cls, counts_all, rank):
+    def build(cls, counts_all, rank, ranges=None):
+        """ranges: per rank the contiguous (lo, hi) expert ids it serves; default: balanced contiguous sharding."""
         world = len(counts_all)
         num_experts = len(counts_all[0])
-        ranges = [cls.expert_range(num_experts, world, r) for r in range(world)]
+        if ranges is None:
+            ranges = [cls.expert_range(num_experts, world, r) for r in range(world)]
         send_splits = [int(sum(counts_all[rank][lo:hi])) for lo, hi in ranges]
         lo, hi = ranges[rank]
         recv_splits = [int(sum(counts_all[src][lo:hi])) for src in range(world)]
@@ -220,24 +302,37 @@ class EpMoeSwigluFp8:
     re-quantise -> ragged down GEMM -> bf16 all-to-all back -> local weighted combine."""
 
     def __init__(self, cfb, ctx, rows, H, F, num_experts, top_k, group=None, device="cuda", recv_capacity=None,
-                 fused_return=False, fused_swiglu=False):
+                 fused_return=False, fused_swiglu=False, placement=None):
         """fused_swiglu: the local gate/up weight is in the interleaved layout (fp8_interleave_gate_up) and the gate/up
         GEMM's epilogue does SwiGLU and the delayed-scale re-quantise, so the [rows, 2F] bf16 intermediate never
         exists. fused_return: the down-projection GEMM writes every segment's rows straight into the `back` buffer of the
         rank that owns the tokens (NVLink P2P stores from the GEMM epilogue into symmetric memory), which removes the
-        bf16 all-to-all of the return leg; one tiny all-reduce orders the combine behind all ranks' GEMMs."""
+        bf16 all-to-all of the return leg; one tiny all-reduce orders the combine behind all ranks' GEMMs.
+        placement: a ReplicaPlacement; the layer then dispatches over its replicas ("virtual experts") instead of the
+        experts, and the local weight stacks passed to forward() hold placement.local_experts(rank) in that order."""
         self.cfb, self.ctx, self.group = cfb, ctx, group
         self.rows, self.H, self.F, self.E, self.k = rows, H, F, num_experts, top_k
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        self.e_lo, self.e_hi = EpPlan.expert_range(num_experts, self.world, self.rank)
+        self.placement = placement
+        if placement is not None:
+            assert placement.world == self.world and placement.num_experts == num_experts
+            self.V = placement.num_replicas
+            self.ranges = [tuple(r) for r in placement.rank_ranges]
+            self.rep_start = torch.tensor(placement.replica_start, dtype=torch.int32, device=device)
+            self.rep_cum = torch.tensor(placement.replica_cum_share, dtype=torch.float32, device=device)
+            self.rwv = torch.zeros((rows, self.V), dtype=torch.float32, device=device)
+        else:
+            self.V = num_experts
+            self.ranges = [EpPlan.expert_range(num_experts, self.world, r) for r in range(self.world)]
+        self.e_lo, self.e_hi = self.ranges[self.rank]
         self.T = rows * top_k
         # worst case every token of every rank picks this rank's experts
         self.cap = recv_capacity or self.T * self.world
         dev = device
-        self.counts = torch.zeros(num_experts, dtype=torch.int32, device=dev)
-        self.offsets = torch.zeros(num_experts, dtype=torch.int32, device=dev)
-        self.idx = torch.zeros((num_experts, rows), dtype=torch.int32, device=dev)
+        self.counts = torch.zeros(self.V, dtype=torch.int32, device=dev)
+        self.offsets = torch.zeros(self.V, dtype=torch.int32, device=dev)
+        self.idx = torch.zeros((self.V, rows), dtype=torch.int32, device=dev)
         self.x8 = torch.empty((rows, H), dtype=torch.uint8, device=dev)
         self.xc = torch.empty((self.T, H), dtype=torch.uint8, device=dev)
         self.slot_x = cfb.ActSlot(ctx, cfb.E4M3_MAX)
@@ -258,14 +353,20 @@ class EpMoeSwigluFp8:
     def forward(self, x, route_weights, w_gateup8_local, w_gateup_descale, w_down8_local, w_down_descale, mixed,
                 accumulate=True):
         cfb, ctx = self.cfb, self.ctx
-        rows, H, F, E = self.rows, self.H, self.F, self.E
-        cfb.moe_topk_route_f32(route_weights, rows, E, self.k)
+        rows, H, F = self.rows, self.H, self.F
+        cfb.moe_topk_route_f32(route_weights, rows, self.E, self.k)
+        if self.placement is not None:
+            # every selected (row, expert) moves to one replica of that expert; from here on "experts" are replicas
+            cfb.moe_expand_route_replicas(route_weights, self.rwv, rows, self.E, self.V, self.rep_start, self.rep_cum,
+                                          first_row=self.rank * rows)
+            route_weights = self.rwv
+        E = self.V
         cfb.moe_build_expert_row_lists(route_weights, self.counts, self.idx, rows, E)
         cfb.moe_expert_offsets_from_counts(self.counts, self.offsets, E)
         cfb.fp8_quant_act(ctx, self.slot_x, x, self.x8)
         cfb.moe_gather_all_u8(self.x8, self.xc, self.idx, self.counts, self.offsets, rows, E, H)
         # exchange: counts (host-visible), every rank's activation descale, then the rows
-        plan = EpPlan.build(gather_counts(self.counts, self.group), self.rank)
+        plan = EpPlan.build(gather_counts(self.counts, self.group), self.rank, self.ranges)
         self.plan = plan
         dx_local = torch.empty(1, dtype=torch.float32, device=self.device)
         _copy_device_scalar(cfb, dx_local, self.slot_x.c.descale_snapshot)
@@ -311,6 +412,113 @@ class EpMoeSwigluFp8:
         else:
             back = all_to_all_rows(yc[:R], plan.recv_splits, plan.send_splits, self.group)
         cfb.moe_combine_sorted_bf16(mixed, back, route_weights, self.idx, self.counts, self.offsets, rows, E, H, accumulate)
+
+
+class EpMoeSwigluFp8Direct:
+    """Expert-parallel SwiGLU MoE layer that never visits the host between its launches: the count table is gathered on
+    the device, every rank derives the same plan from it with one small kernel (cf_moe_ep_plan), rows are permuted and
+    sent in one pass straight into the serving ranks' buffers (plain stores over NVLink into symmetric memory, the
+    sender's activation descale travelling with each row), each replica a rank serves is ONE ragged GEMM group whatever
+    the number of sources (gate/up GEMM with the SwiGLU + re-quantise epilogue and a per-row descale, then the down
+    GEMM), and the results are stored back into the owners' compact buffers the same way. Two one-float all-reduces
+    order the readers behind the writers. Buffers are sized for the worst case (every token of every rank on one rank),
+    so no count ever has to be known on the host.
+    Weights: gate/up interleaved (fp8_interleave_gate_up), stacked in placement.local_experts(rank) order."""
+
+    def __init__(self, cfb, ctx, rows, H, F, num_experts, top_k, placement=None, group=None, device="cuda"):
+        self.cfb, self.ctx, self.group = cfb, ctx, group
+        self.rows, self.H, self.F, self.E, self.k = rows, H, F, num_experts, top_k
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if placement is None:
+            placement = ReplicaPlacement.build([1.0] * num_experts, self.world)
+        assert placement.world == self.world and placement.num_experts == num_experts
+        assert H % 16 == 0 and F % 32 == 0
+        self.placement = placement
+        self.V = V = placement.num_replicas
+        self.lo, self.hi = placement.rank_ranges[self.rank]
+        self.n_local = self.hi - self.lo
+        assert self.n_local >= 1, "a rank without replicas has nothing to serve"
+        self.T = T = rows * top_k
+        self.cap = cap = T * self.world
+        dev = self.device = device
+        i32, f32 = torch.int32, torch.float32
+        self.rep_start = torch.tensor(placement.replica_start, dtype=i32, device=dev)
+        self.rep_cum = torch.tensor(placement.replica_cum_share, dtype=f32, device=dev)
+        self.range_lo = torch.tensor([r[0] for r in placement.rank_ranges], dtype=i32, device=dev)
+        self.range_hi = torch.tensor([r[1] for r in placement.rank_ranges], dtype=i32, device=dev)
+        self.rwv = torch.zeros((rows, V), dtype=f32, device=dev)
+        self.counts = torch.zeros(V, dtype=i32, device=dev)
+        self.offsets = torch.zeros(V, dtype=i32, device=dev)
+        self.idx = torch.zeros((V, rows), dtype=i32, device=dev)
+        self.counts_all = torch.zeros((self.world, V), dtype=i32, device=dev)
+        self.x8 = torch.empty((rows, H), dtype=torch.uint8, device=dev)
+        self.h8 = torch.empty((cap, F), dtype=torch.uint8, device=dev)
+        self.yc = torch.empty((cap, H), dtype=torch.bfloat16, device=dev)
+        self.send_runs = torch.zeros(V * cfb.ROW_RUN_BYTES, dtype=torch.uint8, device=dev)
+        self.ret_runs = torch.zeros(self.n_local * self.world * cfb.ROW_RUN_BYTES, dtype=torch.uint8, device=dev)
+        self.grp_counts = torch.zeros(self.n_local, dtype=i32, device=dev)
+        self.grp_offsets = torch.zeros(self.n_local, dtype=i32, device=dev)
+        self.slot_x = cfb.ActSlot(ctx, cfb.E4M3_MAX)
+        self.slot_h = cfb.ActSlot(ctx, cfb.E4M3_MAX)
+        self._keep = []
+        self.recv8, p8 = self._shared((cap, H), torch.uint8)
+        self.recv_dx, pdx = self._shared((cap,), f32)
+        self.back, pback = self._shared((T, H), torch.bfloat16)
+        self.recv_dx.fill_(1.0)
+        self.peer_recv8 = torch.tensor(p8, dtype=torch.int64, device=dev)
+        self.peer_recv_dx = torch.tensor(pdx, dtype=torch.int64, device=dev)
+        self.peer_back = torch.tensor(pback, dtype=torch.int64, device=dev)
+        self._fence = torch.zeros(1, dtype=f32, device=dev)
+        self._barrier()
+
+    def _shared(self, shape, dtype):
+        """A buffer every rank can store into: symmetric memory when there are peers, a plain tensor otherwise."""
+        if self.world == 1:
+            t = torch.zeros(shape, dtype=dtype, device=self.device)
+            return t, [t.data_ptr()]
+        import torch.distributed._symmetric_memory as symm_mem
+        t = symm_mem.empty(shape, dtype=dtype, device=self.device)
+        hdl = symm_mem.rendezvous(t, self.group if self.group is not None else dist.group.WORLD)
+        views = [hdl.get_buffer(r, shape, dtype) for r in range(self.world)]
+        self._keep.append((hdl, views))
+        for v in views:
+            assert v.data_ptr() % 16 == 0
+        return t, [v.data_ptr() for v in views]
+
+    def _barrier(self):
+        if self.world > 1:
+            dist.all_reduce(self._fence, group=self.group)
+
+    def forward(self, x, route_weights, w_gateup8_local, w_gateup_descale, w_down8_local, w_down_descale, mixed,
+                accumulate=True):
+        cfb, ctx = self.cfb, self.ctx
+        rows, H, F, V, W = self.rows, self.H, self.F, self.V, self.world
+        cfb.moe_topk_route_f32(route_weights, rows, self.E, self.k)
+        cfb.moe_expand_route_replicas(route_weights, self.rwv, rows, self.E, V, self.rep_start, self.rep_cum,
+                                      first_row=self.rank * rows)
+        cfb.moe_build_expert_row_lists(self.rwv, self.counts, self.idx, rows, V)
+        cfb.moe_expert_offsets_from_counts(self.counts, self.offsets, V)
+        if W > 1:
+            dist.all_gather_into_tensor(self.counts_all, self.counts, group=self.group)
+        else:
+            self.counts_all.copy_(self.counts.view(1, V))
+        cfb.fp8_quant_act(ctx, self.slot_x, x, self.x8)
+        cfb.moe_ep_plan(self.counts_all, W, self.rank, V, self.range_lo, self.range_hi, self.send_runs, self.grp_counts,
+                        self.grp_offsets, self.ret_runs)
+        # permute + dispatch in one pass; every row carries the descale of the rank that quantised it
+        cfb.moe_send_row_runs(self.x8, self.idx, rows, self.send_runs, V, rows, self.peer_recv8, H,
+                              tag_value=cfb.ops._DevPtr(self.slot_x.c.descale_snapshot), tag_bases=self.peer_recv_dx)
+        self._barrier()          # every rank's rows have arrived
+        cfb.gemm_fp8_swiglu_quant_act(ctx, self.slot_h, self.n_local, self.n_local, None, self.cap, F, H, self.grp_counts,
+                                      self.grp_offsets, self.recv8, H, False, self.recv_dx, 2, w_gateup8_local,
+                                      w_gateup_descale, self.h8, F)
+        cfb.gemm_fp8_nt_grouped(ctx, self.n_local, self.cap, H, F, self.grp_counts, self.grp_offsets, self.h8, F, False,
+                                cfb.ops._DevPtr(self.slot_h.c.descale_snapshot), False, w_down8_local, w_down_descale,
+                                self.yc, H)
+        cfb.moe_send_row_runs(self.yc, None, 0, self.ret_runs, self.n_local * W, rows, self.peer_back, 2 * H)
+        self._barrier()          # every rank's results are back
+        cfb.moe_combine_sorted_bf16(mixed, self.back, self.rwv, self.idx, self.counts, self.offsets, rows, V, H, accumulate)
 
 
 def _copy_device_scalar(cfb, dst_tensor, src_addr):

@@ -258,8 +258,9 @@ int cf_fp8_swiglu_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_gate, 
  * never exists in HBM. Rounding points are those of the unfused sequence (bit-identical output). The weight is the
  * stacked [num_weights, 2F, K] E4M3 tensor with gate and up rows interleaved in groups of 32 (cf_fp8_interleave_gate_up);
  * d_h8 is E4M3 [rows, F] with row pitch ldh bytes (16-byte aligned). Dense form: d_counts = d_offsets = NULL,
- * num_segments = 1, max_total_rows = M. Segment form: as cf_gemm_fp8_nt_segments. The first call on a fresh slot runs
- * the GEMM twice (exact amax first). */
+ * num_segments = 1, max_total_rows = M. Segment form: as cf_gemm_fp8_nt_segments. per_segment_a_descale: 0 = one
+ * descale, 1 = d_a_descale[segment], 2 = d_a_descale[row] (one float per row of A). The first call on a fresh slot
+ * runs the GEMM twice (exact amax first). */
 int cf_gemm_fp8_swiglu_quant_act(cf_ctx* ctx, cf_act_slot* slot, int num_segments, int num_weights,
                                  const int* d_segment_weight, int max_total_rows, int F, int K, const int* d_counts,
                                  const int* d_offsets, const void* d_A, int lda, int a_is_e5m2, const float* d_a_descale,
@@ -406,6 +407,45 @@ int cf_moe_combine_all_bf16(void* d_mixed, const void* d_compact, const float* d
 int cf_moe_combine_sorted_bf16(void* d_mixed, const void* d_compact, const float* d_route_weights, const int* d_row_indices,
                                const int* d_counts, const int* d_offsets, int rows, int num_experts, int H, int accumulate,
                                void* stream);
+/* No counterpart in the reference (single GPU). Expert parallelism under a skewed load: a popular expert is held by
+ * several ranks, each replica being a "virtual expert". Rewrites sparse route weights [rows, num_experts] as
+ * [rows, num_replicas]: expert e owns the replica ids [d_replica_start[e], d_replica_start[e + 1]); every selected
+ * (row, e) keeps its weight on exactly one of them, chosen by a hash of (first_row + row, e) against the replicas'
+ * cumulative shares d_replica_cum_share (ascending inside each expert, the last one 1). Replica ids ascend with the
+ * expert id, so combining over replicas in ascending id order adds the experts in the single-GPU order. */
+int cf_moe_expand_route_replicas(const float* d_route_weights, float* d_replica_weights, int rows, int num_experts,
+                                 int num_replicas, const int* d_replica_start, const float* d_replica_cum_share,
+                                 unsigned first_row, void* stream);
+
+/* A run of rows on its way to another buffer: `rows` rows starting at src_row (ignored when the call gathers through an
+ * index table) go to row dst_row of destination buffer number dst. */
+typedef struct cf_row_run {
+    long long src_row;
+    long long dst_row;
+    int rows;
+    int dst;
+} cf_row_run;
+
+/* No counterpart in the reference (single GPU). Device-side plan of one expert-parallel layer, computed by every rank
+ * from the same table d_counts_all[world, num_replicas] (rows each source rank routes to each replica; gathered with
+ * one collective, never copied to the host). Replica v is served by the rank whose id range
+ * [d_range_lo[g], d_range_hi[g]) holds it; a serving rank receives its replicas one after the other and, inside a
+ * replica, the sources in rank order, so every replica is one ragged GEMM group.
+ *   d_send_runs[num_replicas]          where this rank's rows for each replica land (dst = serving rank)
+ *   d_group_counts/offsets[n_local]    the ragged groups this rank serves (n_local = its range length)
+ *   d_return_runs[n_local * world]     where each (replica, source) block of results returns to (dst = source rank,
+ *                                      dst_row = that replica's offset in the source's own compact order) */
+int cf_moe_ep_plan(const int* d_counts_all, int world, int rank, int num_replicas, const int* d_range_lo, const int* d_range_hi,
+                   cf_row_run* d_send_runs, int* d_group_counts, int* d_group_offsets, cf_row_run* d_return_runs, void* stream);
+/* Copies the runs of a device plan: whole rows of row_bytes (a multiple of 16) from d_src to
+ * d_dst_bases[run.dst] + run.dst_row * row_bytes; the destinations may be peer GPUs' buffers mapped into this process
+ * (plain stores over NVLink). With an index table the i-th row of run r is row d_row_indices[r * index_stride + i] of
+ * d_src (permute and send in one pass). With a tag, *d_tag_value is also stored at d_tag_bases[run.dst][run.dst_row + i]
+ * for every row (the sender's activation descale travelling with its rows). d_dst_bases / d_tag_bases are DEVICE arrays
+ * of base pointers; max_rows_per_run only sizes the grid. */
+int cf_moe_send_row_runs(const void* d_src, const int* d_row_indices_or_null, long long index_stride, const cf_row_run* d_runs,
+                         int num_runs, int max_rows_per_run, void* const* d_dst_bases, long long row_bytes,
+                         const float* d_tag_value_or_null, float* const* d_tag_bases_or_null, void* stream);
 
 /* kernels/moe.cu:1062-1127, kernels.hpp:414-423: grouped selected-expert FP8 forward with exact-erf GELU,
  * accumulating rw*y into d_mixed. The tensor-core implementation needs workspace, which the reference

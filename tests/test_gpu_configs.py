@@ -309,6 +309,34 @@ def test_fused_swiglu_gemm_matches_the_unfused_sequence(cfb, ctx, oracle, rows, 
         assert torch.equal(h_a, h_b), step
 
 
+@pytest.mark.parametrize("rows,H,F,E", [(700, 256, 512, 4), (1100, 128, 96, 8)])
+def test_device_planned_expert_parallel_layer_on_one_rank(cfb, ctx, rows, H, F, E):
+    """The expert-parallel layer whose plan, dispatch and return run on the device, with a single rank (every destination
+    is the local GPU): same bits as the single-GPU layer over three steps, including the delayed scales."""
+    k = 2
+    wgu8, dgu = _tensorquant(cfb, randn_bf16((E, 2 * F, H), std=0.05, seed=4))
+    wd8, dd = _tensorquant(cfb, randn_bf16((E, H, F), std=0.05, seed=5))
+    wgu8_il = cfb.fp8_interleave_gate_up(wgu8)
+    single = cfb.MoeSwigluFp8(ctx, rows, H, F, E, k, fused_swiglu=True)
+    direct = cfb.parallel.EpMoeSwigluFp8Direct(cfb, ctx, rows, H, F, E, k)
+    assert direct.V == E and direct.n_local == E
+    for step in range(3):
+        x = randn_bf16((rows, H), std=1.0 + step, seed=40 + step)
+        rw_a, rw_b = _zipf_logits(rows, E, 50 + step), _zipf_logits(rows, E, 50 + step)
+        m_a = torch.zeros((rows, H), dtype=torch.bfloat16, device="cuda")
+        m_b = randn_bf16((rows, H), seed=60 + step)          # overwritten: accumulate=False
+        single.forward(x, rw_a, wgu8_il, dgu, wd8, dd, m_a)
+        direct.forward(x, rw_b, wgu8_il, dgu, wd8, dd, m_b, accumulate=False)
+        ctx.poll_status()
+        assert torch.equal(rw_a, rw_b)
+        assert torch.equal(direct.counts_all.view(-1), single.counts) and torch.equal(direct.grp_counts, single.counts)
+        assert torch.equal(direct.grp_offsets, single.offsets)
+        total = int(single.counts.sum().item())
+        assert torch.equal(direct.recv8[:total], single.xc[:total])
+        assert torch.equal(direct.h8[:total], single.h8[:total]), step
+        assert torch.equal(m_a.view(torch.int16), m_b.view(torch.int16)), step
+
+
 def test_dense_ffn_fused_against_reference_sequence_and_oracle(cfb, ctx, oracle):
     """The reference's dense FP8 FFN with per-tensor delayed scaling: fused three-launch form against the unfused operator
     sequence (bit-identical) and against the host oracle (<= 1e-2), over two steps, at a reduced size; then the

@@ -128,33 +128,67 @@ def _worker(rank, world, port, ret):
             ctx.poll_status()
         assert torch.equal(mixed_s.view(torch.int16), mixed.view(torch.int16))
         # Host oracle on sampled tokens with the very scales the distributed layer used: this rank's activation
-        # scale for x, and for every expert the SwiGLU slot scale of the rank that owns it.
+        # scale for x, and for every expert the SwiGLU slot scale of the rank that served it.
         import sys
         sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
         from oracle_bindings import Oracle
         orc = Oracle()
-        hs = ep.slot_h.scalars()
-        mine = torch.tensor([hs["scale_snapshot"], hs["descale_snapshot"]], dtype=torch.float32, device=dev)
-        allh = [torch.empty_like(mine) for _ in range(world)]
-        dist.all_gather(allh, mine)
-        dx = np.float32(ep.slot_x.scalars()["descale_snapshot"])
-        x8 = ep.x8.cpu().numpy()
-        rw_n = rw.cpu().numpy()
-        sample = list(range(0, rows, 16))
-        want = np.zeros((len(sample), H), dtype=np.uint16)
-        for i, r in enumerate(sample):
-            for e in range(E):
-                wgt = rw_n[r, e]
-                if wgt <= 0:
-                    continue
-                owner = [q for q in range(world) if par.EpPlan.expert_range(E, world, q)[0] <= e < par.EpPlan.expert_range(E, world, q)[1]][0]
-                sh_, dh_ = (np.float32(v) for v in allh[owner].cpu().tolist())
-                gu = orc.gemm_fp8_nt(x8[r:r + 1], wgu8[e].cpu().numpy(), dx, dgu[0].item())
-                h = orc.swiglu_forward(np.ascontiguousarray(gu[:, :F]), np.ascontiguousarray(gu[:, F:]))
-                ye = orc.gemm_fp8_nt(orc.quantize_bf16(h, sh_), wd8[e].cpu().numpy(), dh_, dd[0].item())
-                want[i] = orc.to_bf16(orc.bf16_to_f32(want[i:i + 1]) + wgt * orc.bf16_to_f32(ye))[0]
-        err = rel_fro(mixed[sample].float().cpu().numpy(), orc.bf16_to_f32(want))
-        assert err < 1e-2, err
+
+        def check_against_oracle(layer, out, weights_n, expert_of, rank_of):
+            """weights_n [rows, V] sparse weights the layer combined with; column v is expert expert_of[v] served by rank_of[v]."""
+            hs = layer.slot_h.scalars()
+            mine = torch.tensor([hs["scale_snapshot"], hs["descale_snapshot"]], dtype=torch.float32, device=dev)
+            allh = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(allh, mine)
+            dxs = np.float32(layer.slot_x.scalars()["descale_snapshot"])
+            x8n = layer.x8.cpu().numpy()
+            sample = list(range(0, rows, 16))
+            want = np.zeros((len(sample), H), dtype=np.uint16)
+            for i, r in enumerate(sample):
+                for v in range(weights_n.shape[1]):
+                    wgt = weights_n[r, v]
+                    if wgt <= 0:
+                        continue
+                    e = expert_of[v]
+                    sh_, dh_ = (np.float32(q) for q in allh[rank_of[v]].cpu().tolist())
+                    gu = orc.gemm_fp8_nt(x8n[r:r + 1], wgu8[e].cpu().numpy(), dxs, dgu[0].item())
+                    h = orc.swiglu_forward(np.ascontiguousarray(gu[:, :F]), np.ascontiguousarray(gu[:, F:]))
+                    ye = orc.gemm_fp8_nt(orc.quantize_bf16(h, sh_), wd8[e].cpu().numpy(), dh_, dd[0].item())
+                    want[i] = orc.to_bf16(orc.bf16_to_f32(want[i:i + 1]) + wgt * orc.bf16_to_f32(ye))[0]
+            err = rel_fro(out[sample].float().cpu().numpy(), orc.bf16_to_f32(want))
+            assert err < 1e-2, err
+
+        owners = [[q for q in range(world) if par.EpPlan.expert_range(E, world, q)[0] <= e < par.EpPlan.expert_range(E, world, q)[1]][0]
+                  for e in range(E)]
+        check_against_oracle(ep, mixed, rw.cpu().numpy(), list(range(E)), owners)
+        # ---- popular experts replicated: expert 0 is expected to take most rows, so both ranks serve it; every
+        # selected (row, expert) goes to exactly one replica and the rows of an expert split by the replicas' shares
+        pl = par.ReplicaPlacement.build([5.0, 1.0, 1.0, 1.0], world)
+        assert pl.num_replicas > E and pl.replica_expert == sorted(pl.replica_expert)
+        loc = pl.local_experts(rank)
+        ep4 = par.EpMoeSwigluFp8(cfb, ctx, rows, H, F, E, k, device=dev, placement=pl)
+        mixed_r = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
+        for step in range(2):
+            rw4 = logits[rank].clone()
+            ep4.forward(xs[rank], rw4, wgu8[loc].contiguous(), dgu, wd8[loc].contiguous(), dd, mixed_r, accumulate=False)
+            ctx.poll_status()
+        rwv_n, rw4_n = ep4.rwv.cpu().numpy(), rw4.cpu().numpy()
+        for e in range(E):
+            cols = rwv_n[:, pl.replica_start[e]:pl.replica_start[e + 1]]
+            assert np.array_equal(cols.sum(axis=1), rw4_n[:, e]) and ((cols > 0).sum(axis=1) <= 1).all()
+        assert np.array_equal(rw4_n, rw.cpu().numpy())
+        check_against_oracle(ep4, mixed_r, rwv_n, pl.replica_expert, pl.replica_rank)
+        # ---- the same layer with plan, dispatch and return on the device (no host copy of the counts, rows stored
+        # straight into the serving ranks' buffers, one ragged group per replica): same bits as the all-to-all form
+        ep5 = par.EpMoeSwigluFp8Direct(cfb, ctx, rows, H, F, E, k, placement=pl, device=dev)
+        wgu_il_loc = cfb.fp8_interleave_gate_up(wgu8[loc].contiguous())
+        mixed_d = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
+        for step in range(2):
+            rw5 = logits[rank].clone()
+            ep5.forward(xs[rank], rw5, wgu_il_loc, dgu, wd8[loc].contiguous(), dd, mixed_d, accumulate=False)
+            ctx.poll_status()
+        assert torch.equal(ep5.counts, ep4.counts) and int(ep5.grp_counts.sum().item()) == ep4.plan.total_recv
+        assert torch.equal(mixed_d.view(torch.int16), mixed_r.view(torch.int16))
         # and against the single-GPU layer on all tokens: a different scale granularity (one activation scale per rank
         # instead of one over all tokens), so the two differ by FP8 quantisation noise, not by more
         single = cfb.MoeSwigluFp8(ctx, rows * world, H, F, E, k, device=dev)

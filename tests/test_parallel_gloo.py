@@ -134,3 +134,49 @@ def test_plan_is_consistent_across_ranks():
         for b in range(4):
             assert plans[a].send_splits[b] == plans[b].recv_splits[a]
     assert sum(p.total_recv for p in plans) == int(np.sum(table))
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("skew", [0.0, 1.1, 2.5])
+def test_replica_placement_balances_a_skewed_load(world, skew):
+    """Every rank expects the same share of the rows, owns a contiguous replica range, replica ids ascend with the expert
+    id, the shares of an expert's replicas sum to one, and the plan built over the replica ranges is consistent."""
+    par = package().parallel
+    E = 8
+    pop = [(e + 1) ** -skew for e in range(E)]
+    pl = par.ReplicaPlacement.build(pop, world, min_share=0.0)
+    V = pl.num_replicas
+    assert pl.replica_expert == sorted(pl.replica_expert) and set(pl.replica_expert) == set(range(E))
+    assert pl.replica_rank == sorted(pl.replica_rank)
+    assert pl.replica_start[0] == 0 and pl.replica_start[E] == V
+    load = [0.0] * world
+    for e in range(E):
+        ids = list(range(pl.replica_start[e], pl.replica_start[e + 1]))
+        assert ids and all(pl.replica_expert[v] == e for v in ids)
+        assert abs(sum(pl.replica_share[v] for v in ids) - 1.0) < 1e-9 and pl.replica_cum_share[ids[-1]] == 1.0
+        assert all(pl.replica_cum_share[a] < pl.replica_cum_share[b] for a, b in zip(ids, ids[1:]))
+        for v in ids:
+            load[pl.replica_rank[v]] += pop[e] / sum(pop) * pl.replica_share[v]
+    assert max(load) - min(load) < 1e-9
+    covered = []
+    for g, (lo, hi) in enumerate(pl.rank_ranges):
+        assert all(pl.replica_rank[v] == g for v in range(lo, hi))
+        covered += list(range(lo, hi))
+    assert covered == list(range(V))
+    rng = np.random.default_rng(1)
+    table = rng.integers(0, 50, size=(world, V)).tolist()
+    plans = [par.EpPlan.build(table, r, pl.rank_ranges) for r in range(world)]
+    for a in range(world):
+        for b in range(world):
+            assert plans[a].send_splits[b] == plans[b].recv_splits[a]
+    assert sum(p.total_recv for p in plans) == int(np.sum(table))
+
+
+def test_replica_placement_drops_slivers_and_degenerates_to_sharding():
+    par = package().parallel
+    pl = par.ReplicaPlacement.build([1.0] * 8, 4)
+    assert pl.replica_expert == list(range(8)) and pl.replica_rank == [0, 0, 1, 1, 2, 2, 3, 3]
+    assert pl.rank_ranges == [(0, 2), (2, 4), (4, 6), (6, 8)]
+    # a 1 % overlap with the next rank's piece is not worth a copy of the weights
+    pl = par.ReplicaPlacement.build([0.505, 0.495], 2, min_share=0.05)
+    assert pl.replica_expert == [0, 1] and pl.replica_rank == [0, 1]

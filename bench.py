@@ -249,10 +249,10 @@ def run_moe(args):
     wgu8, dgu = quant_experts((n_local, 2 * F, H), 0.02, 50)
     wd8, dd = quant_experts((n_local, H, F), 0.02, 70)
     mixed = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
-    fused_swiglu = not args.moe_unfused_swiglu
+    fused_swiglu = (not args.moe_unfused_swiglu) or (use_ep and not args.moe_a2a)    # the device-planned form is fused only
     if fused_swiglu:
         wgu8 = cfb.fp8_interleave_gate_up(wgu8)       # one-time weight layout for the fused SwiGLU epilogue
-    if use_ep and args.moe_direct:
+    if use_ep and (not args.moe_a2a):
         layer = par.EpMoeSwigluFp8Direct(cfb, ctx, rows, H, F, E, TOPK, placement=placement, device=dev)
     elif use_ep:
         layer = par.EpMoeSwigluFp8(cfb, ctx, rows, H, F, E, TOPK, device=dev, fused_return=args.moe_fused_return,
@@ -286,7 +286,7 @@ def run_moe(args):
     launches = cfb.launch_count() - l0
     ctx.poll_status()
     t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    loads = torch.tensor([float(layer.grp_counts.sum().item()) if (use_ep and args.moe_direct) else float(layer.plan.total_recv) if use_ep else float(rows * TOPK)], dtype=torch.float64, device=dev)
+    loads = torch.tensor([float(layer.grp_counts.sum().item()) if (use_ep and (not args.moe_a2a)) else float(layer.plan.total_recv) if use_ep else float(rows * TOPK)], dtype=torch.float64, device=dev)
     lmax = loads.clone()
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -299,7 +299,7 @@ def run_moe(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
             "config": {"workload": "moe_swiglu_fp8_32768tok_H4096_E8_F14336_top2_zipf1.1 (BASELINE config 4)",
-                       "parallelism": (f"ep{world} ({'device-planned dispatch, rows stored into the serving ranks over NVLink' if args.moe_direct else 'all-to-all'}, {'popular experts replicated: ' + str(placement.num_replicas) + ' replicas of ' + str(E) + ' experts' if placement else 'experts placed by load'}{', GEMM-fused return leg' if args.moe_fused_return else ''})" if use_ep else
+                       "parallelism": (f"ep{world} ({'device-planned dispatch, rows stored into the serving ranks over NVLink' if (not args.moe_a2a) else 'all-to-all'}, {'popular experts replicated: ' + str(placement.num_replicas) + ' replicas of ' + str(E) + ' experts' if placement else 'experts placed by load'}{', GEMM-fused return leg' if args.moe_fused_return else ''})" if use_ep else
                                        f"dp{world} (experts replicated, tokens sharded, no collective)") if world > 1 else "single GPU",
                        "swiglu": "fused into the gate/up GEMM epilogue" if fused_swiglu else "separate pass over the bf16 intermediate",
                        "max_rows_on_one_rank": int(lmax.item()), "mean_rows_per_rank": TOK * TOPK / world,
@@ -407,8 +407,9 @@ def main():
     ap.add_argument("--moe-unfused-swiglu", action="store_true", help="keep the [T,2F] bf16 intermediate (separate SwiGLU pass)")
     ap.add_argument("--moe-fused-return", action="store_true",
                     help="ep mode: the down GEMM stores its rows straight into the owners' buffers over NVLink (no return all-to-all)")
-    ap.add_argument("--moe-direct", action="store_true",
-                    help="expert parallel with plan, dispatch and return on the device (no host copy of the counts)")
+    ap.add_argument("--moe-a2a", action="store_true",
+                    help="expert parallel through NCCL all-to-all with a host-side plan (default: plan, dispatch and return on "
+                         "the device, rows stored straight into the serving ranks' buffers)")
     ap.add_argument("--moe-no-replicas", action="store_true",
                     help="expert parallel without replicas of the popular experts (one owner per expert, placed by load)")
     ap.add_argument("--moe-mode", default="ep", choices=["ep", "dp"],

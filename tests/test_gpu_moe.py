@@ -293,3 +293,58 @@ def test_ragged_expert_sequence(cfb, ctx, oracle):
         ye = oracle.gemm_fp8_nt(oracle.quantize_bf16(he, s_e), wout8[e].cpu().numpy(), d_e, dwout[0].item())
         oracle.moe_scatter_accumulate_rows_bf16(m_o, ye, rw_n, sel, e)
     assert rel_fro(oracle.bf16_to_f32(bf16_to_u16(mixed)), oracle.bf16_to_f32(m_o)) < TOL
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_expert_parallel_device_plan_for_every_rank(cfb, world):
+    """cf_moe_ep_plan evaluated for every rank of a world on one GPU, against a host restatement: send runs tile the
+    serving ranks' buffers without gaps or overlaps, groups are the replicas in id order, return runs mirror the sends."""
+    par = cfb.parallel
+    E = 8
+    pl = par.ReplicaPlacement.build([(e + 1) ** -1.1 for e in range(E)], world)
+    V = pl.num_replicas
+    rng = np.random.default_rng(world)
+    table = rng.integers(0, 40, size=(world, V)).astype(np.int32)
+    table[rng.random((world, V)) < 0.15] = 0
+    counts_all = torch.from_numpy(table).cuda()
+    lo = torch.tensor([r[0] for r in pl.rank_ranges], dtype=torch.int32, device="cuda")
+    hi = torch.tensor([r[1] for r in pl.rank_ranges], dtype=torch.int32, device="cuda")
+    run_dt = np.dtype([("src_row", "<i8"), ("dst_row", "<i8"), ("rows", "<i4"), ("dst", "<i4")])
+    assert run_dt.itemsize == cfb.ROW_RUN_BYTES
+    owner = [next(g for g, (a, b) in enumerate(pl.rank_ranges) if a <= v < b) for v in range(V)]
+    tot = table.sum(axis=0)
+    covered = {g: [] for g in range(world)}
+    sends, rets, groups = {}, {}, {}
+    for me in range(world):
+        n_local = pl.rank_ranges[me][1] - pl.rank_ranges[me][0]
+        send = torch.zeros(V * cfb.ROW_RUN_BYTES, dtype=torch.uint8, device="cuda")
+        ret = torch.zeros(max(n_local, 1) * world * cfb.ROW_RUN_BYTES, dtype=torch.uint8, device="cuda")
+        gc = torch.zeros(max(n_local, 1), dtype=torch.int32, device="cuda")
+        go = torch.zeros(max(n_local, 1), dtype=torch.int32, device="cuda")
+        cfb.moe_ep_plan(counts_all, world, me, V, lo, hi, send, gc, go, ret)
+        sends[me] = send.cpu().numpy().view(run_dt)
+        rets[me] = ret.cpu().numpy().view(run_dt)[:n_local * world]
+        groups[me] = (gc.cpu().numpy()[:n_local], go.cpu().numpy()[:n_local])
+    for me in range(world):
+        a, b = pl.rank_ranges[me]
+        gc, go = groups[me]
+        assert np.array_equal(gc, tot[a:b]) and np.array_equal(go, np.concatenate([[0], np.cumsum(tot[a:b])[:-1]]) if b > a else gc)
+        for v in range(V):
+            s = sends[me][v]
+            assert s["rows"] == table[me, v] and s["dst"] == owner[v]
+            base = tot[pl.rank_ranges[owner[v]][0]:v].sum()
+            assert s["dst_row"] == base + table[:me, v].sum()
+            covered[owner[v]].append((int(s["dst_row"]), int(s["rows"])))
+        for vl, v in enumerate(range(a, b)):
+            for src in range(world):
+                r = rets[me][vl * world + src]
+                assert r["rows"] == table[src, v] and r["dst"] == src
+                assert r["src_row"] == sends[src][v]["dst_row"]              # what a source sent is what returns to it
+                assert r["dst_row"] == table[src, :v].sum()                  # the source's own compact order
+    for g in range(world):                                                   # receive buffers: contiguous, no overlap
+        pos = 0
+        for start, n in sorted(x for x in covered[g] if x[1] > 0):
+            assert start == pos
+            pos += n
+        a, b = pl.rank_ranges[g]
+        assert pos == tot[a:b].sum()

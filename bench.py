@@ -394,6 +394,76 @@ def run_rowparallel(args):
         dist.destroy_process_group()
 
 
+def run_quantize(args):
+    """HBM-bound side of the path on one GPU: the quantise family and the RMSNorm -> E4M3 fusion on 32768 x 4096 bf16
+    activations (268 MB, three rotating inputs, all larger than L2). One step = one launch of each kernel; the line's
+    value is the bandwidth of the steady-state activation kernel (record-quantise, 3 B/element)."""
+    import torch
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    cfb = importlib.import_module("canopy-foundry_b200")
+    peaks = load_peaks()
+    rows, H = 32768, 4096
+    n = rows * H
+    g = torch.Generator(device=dev).manual_seed(3)
+    xs = [torch.randn((rows, H), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16) for _ in range(3)]
+    gamma = torch.ones(H, dtype=torch.bfloat16, device=dev)
+    out8 = torch.empty((rows, H), dtype=torch.uint8, device=dev)
+    out8t = torch.empty((H, rows), dtype=torch.uint8, device=dev)
+    normed = torch.empty((rows, H), dtype=torch.bfloat16, device=dev)
+    rms = torch.empty(rows, dtype=torch.float32, device=dev)
+    rowd = torch.empty(rows, dtype=torch.float32, device=dev)
+    scale = torch.full((4,), 20.0, dtype=torch.float32, device=dev)
+    amax = torch.zeros(4, dtype=torch.float32, device=dev)
+    it = [0]
+
+    def nx():
+        it[0] += 1
+        return xs[it[0] % 3]
+
+    kernels = [
+        ("record_quantise_e4m3", 3, lambda: cfb.fp8_quantize_e4m3_record(nx(), out8, scale, amax)),
+        ("amax_only", 2, lambda: cfb.fp8_amax_bf16(nx(), amax)),
+        ("quantise_both_layouts", 4, lambda: cfb.fp8_quant_and_transpose_e4m3(nx(), out8, out8t, scale, rows, H)),
+        ("rowwise_quantise_e4m3", 3, lambda: cfb.fp8_quantize_rowwise_e4m3(nx(), out8, rowd)),
+        ("rmsnorm", 4, lambda: cfb.rmsnorm_forward(nx(), gamma, normed, rms, rows, H)),
+        ("rmsnorm_record_quantise_keep_bf16", 5, lambda: cfb.rmsnorm_quantize_e4m3_record(nx(), gamma, normed, rms, out8, scale, amax, rows, H)),
+        ("rmsnorm_record_quantise_e4m3_only", 3, lambda: cfb.rmsnorm_quantize_e4m3_record(nx(), gamma, None, rms, out8, scale, amax, rows, H)),
+    ]
+    sampler = ClockSampler(0)
+    sampler.start()
+    l0 = cfb.launch_count()
+    res = {}
+    for name, bpe, fn in kernels:
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        res[name] = {"ms": ms, "bytes_per_element": bpe, "GBps": bpe * n / (ms * 1e-3) / 1e9,
+                     "frac_of_measured_hbm": bpe * n / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+    launches = cfb.launch_count() - l0
+    clocks = sampler.stop()
+    head = res["record_quantise_e4m3"]
+    print(json.dumps({
+        "metric": "fp8_quantize_GBps", "value": head["GBps"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": head["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 -> fp8_e4m3", "data": "synthetic",
+        "config": {"workload": "quantize_family_32768x4096_bf16 (BASELINE configuration 3/4 activation size)",
+                   "l2": "three rotating 268 MB inputs, larger than L2"},
+        "roofline": {"bound": "hbm", "kernel": "k_stream<e4m3, quantise, record>", "achieved": head["GBps"],
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": head["frac_of_measured_hbm"], "traffic": None,
+                     "peak_source": f"STREAM-style copy figure of MEASURED_PEAKS.json ({peaks['source']})",
+                     "frac_of_nominal_8000": head["GBps"] / 8000.0},
+        "kernels": res, "gpu_launches": int(launches), "clocks": clocks}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -414,7 +484,7 @@ def main():
                     help="expert parallel without replicas of the popular experts (one owner per expert, placed by load)")
     ap.add_argument("--moe-mode", default="ep", choices=["ep", "dp"],
                     help="N > 1: ep = expert parallel with all-to-all (experts placed by load), dp = experts replicated, tokens sharded")
-    ap.add_argument("--workload", default="linear", choices=["linear", "moe", "rowparallel"],
+    ap.add_argument("--workload", default="linear", choices=["linear", "moe", "rowparallel", "quantize"],
                     help="linear = BASELINE configuration 2 (the headline line); moe = configuration 4 tokens/s")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -423,6 +493,8 @@ def main():
         return
     if args.workload == "rowparallel":
         return run_rowparallel(args)
+    if args.workload == "quantize":
+        return run_quantize(args)
     if args.workload == "moe":
         run_moe(args)
         return

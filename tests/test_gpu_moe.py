@@ -348,3 +348,33 @@ def test_expert_parallel_device_plan_for_every_rank(cfb, world):
             pos += n
         a, b = pl.rank_ranges[g]
         assert pos == tot[a:b].sum()
+
+
+def test_route_expansion_over_replicas_keeps_weights_and_follows_the_shares(cfb):
+    """Every selected (row, expert) keeps its weight on exactly one replica of that expert, unselected experts stay
+    zero, and the rows of an expert split over its replicas in proportion to their shares."""
+    par = cfb.parallel
+    rows, E, k, world = 20000, 8, 2, 8
+    pl = par.ReplicaPlacement.build([(e + 1) ** -1.1 for e in range(E)], world)
+    V = pl.num_replicas
+    rw = _zipf_logits(rows, E, 5)
+    cfb.moe_topk_route_f32(rw, rows, E, k)
+    start = torch.tensor(pl.replica_start, dtype=torch.int32, device="cuda")
+    cum = torch.tensor(pl.replica_cum_share, dtype=torch.float32, device="cuda")
+    rwv = torch.full((rows, V), -1.0, dtype=torch.float32, device="cuda")
+    cfb.moe_expand_route_replicas(rw, rwv, rows, E, V, start, cum, first_row=12345)
+    a, b = rw.cpu().numpy(), rwv.cpu().numpy()
+    assert (b >= 0).all()
+    for e in range(E):
+        cols = b[:, pl.replica_start[e]:pl.replica_start[e + 1]]
+        assert np.array_equal(cols.sum(axis=1), a[:, e])
+        assert ((cols > 0).sum(axis=1) == (a[:, e] > 0)).all()
+        n = (a[:, e] > 0).sum()
+        if n > 500:
+            frac = (cols > 0).sum(axis=0) / n
+            want = np.array(pl.replica_share[pl.replica_start[e]:pl.replica_start[e + 1]])
+            assert np.abs(frac - want).max() < 0.05, (e, frac, want)
+    # another first_row picks other replicas for the same rows: the choice follows the global row index
+    rwv2 = torch.zeros_like(rwv)
+    cfb.moe_expand_route_replicas(rw, rwv2, rows, E, V, start, cum, first_row=99999)
+    assert not torch.equal(rwv, rwv2)

@@ -7,9 +7,12 @@ and the partitioning below is new work:
   * dense GEMMs: weights sharded by output columns (gate/up, forward GEMMs) or by the contraction dimension
     (down projection, dgrad). A per-tensor weight scale needs the amax of the WHOLE tensor: one max-all-reduce of
     one float keeps the scale bit-identical to the single-GPU one. Row-parallel partial products are summed in
-    fp32 by an all-reduce.
-  * MoE: experts are sharded (expert parallelism), tokens stay data-parallel. Rows travel as E4M3 bytes
-    (1 byte per element on the wire) with one all-to-all out and one bf16 all-to-all back.
+    fp32, either by an NCCL all-reduce (row_parallel_gemm_fp8) or inside the GEMM's epilogue, which adds every
+    tile straight into the owning rank's slice over NVLink (RowParallelReduceScatterGemm).
+  * MoE: experts are sharded (expert parallelism), tokens stay data-parallel; popular experts can be replicated so
+    that a skewed load spreads evenly (ReplicaPlacement). Rows travel as E4M3 bytes (1 byte per element on the
+    wire). EpMoeSwigluFp8 plans on the host and exchanges with NCCL all-to-all; EpMoeSwigluFp8Direct plans on the
+    device and stores the rows straight into the serving ranks' buffers.
 
 The planning code is pure host logic and runs on CPU tensors with the gloo backend too (tests use that).
 """

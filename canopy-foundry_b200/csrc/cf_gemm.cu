@@ -990,17 +990,20 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
             set_error("reduce-scatter GEMM: needs TMA-aligned operands, N %% 32 == 0, M = peers x rows_per_peer with rows_per_peer %% 256 == 0, per-tensor scales");
             return CF_ERR_UNSUPPORTED;
         }
-        CUtensorMap hmaps[16];
-        for (int i = 0; i < p.peer_count; ++i) {
-            if (p.peer_out_host[i] == nullptr || reinterpret_cast<uintptr_t>(p.peer_out_host[i]) % 16 != 0) {
-                set_error("reduce-scatter GEMM: slice %d is null or not 16-byte aligned", i);
-                return CF_ERR_INVALID_ARG;
+        if (!p.peer_maps_ready) {
+            CUtensorMap hmaps[16];
+            for (int i = 0; i < p.peer_count; ++i) {
+                if (p.peer_out_host[i] == nullptr || reinterpret_cast<uintptr_t>(p.peer_out_host[i]) % 16 != 0) {
+                    set_error("reduce-scatter GEMM: slice %d is null or not 16-byte aligned", i);
+                    return CF_ERR_INVALID_ARG;
+                }
+                r = make_map_c_f32(&hmaps[i], p.peer_out_host[i], p.rows_per_peer, p.N, p.N);
+                if (r != CF_OK) return r;
             }
-            r = make_map_c_f32(&hmaps[i], p.peer_out_host[i], p.rows_per_peer, p.N, p.N);
-            if (r != CF_OK) return r;
+            // pageable source: the runtime stages the bytes before the call returns, so the stack array may go (the
+            // copy waits for the stream's earlier work first, which is why the caller caches the maps)
+            CF_CUDA(cudaMemcpyAsync(p.d_peer_maps, hmaps, sizeof(CUtensorMap) * p.peer_count, cudaMemcpyHostToDevice, st));
         }
-        // pageable source: the runtime stages the bytes before the call returns, so the stack array may go
-        CF_CUDA(cudaMemcpyAsync(p.d_peer_maps, hmaps, sizeof(CUtensorMap) * p.peer_count, cudaMemcpyHostToDevice, st));
         p.peer_out_host = nullptr;          // host pointer: of no use to the kernel
     } else {
         p.d_peer_maps = nullptr;

@@ -38,6 +38,7 @@ struct GemmParams {
     int peer_count = 0;
     int rows_per_peer = 0;
     void* d_peer_maps = nullptr;
+    int peer_maps_ready = 0;        // the maps at d_peer_maps already describe peer_out_host (cached by the caller)
     int mn_major = 0;               // operands are [K, M] and [K, N] in memory (un-transposed weight-gradient form)
     long long ldb = 0;              // mn_major: row pitch of B in bytes
     int a_e5m2 = 0;

@@ -152,7 +152,8 @@ int cf_gemm_fp8_nt(cf_ctx* ctx, int M, int N, int K, const void* d_A, int lda, i
  * destination), so the transfer over NVLink overlaps the main loop tile by tile. `slices` is a HOST array of
  * num_slices (1..16) device pointers, 16-byte aligned. The caller zeroes its own slice beforehand and orders the
  * readers behind every rank's launch (a barrier after the call). Needs M/num_slices % 256 == 0, N % 32 == 0,
- * 16-byte aligned operands, K % 16 == 0, per-tensor scales. */
+ * 16-byte aligned operands, K % 16 == 0, per-tensor scales. The context keeps the tensor maps of the last four
+ * slice sets on the device; calls that share a context must be on one stream. */
 int cf_gemm_fp8_nt_reduce_scatter_f32(cf_ctx* ctx, int M, int N, int K, const void* d_A, int lda, int a_is_e5m2,
                                       const float* d_a_descale, const void* d_B, const float* d_b_descale,
                                       void* const* slices, int num_slices, void* stream);

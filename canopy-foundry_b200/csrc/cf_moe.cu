@@ -245,8 +245,8 @@ __global__ void __launch_bounds__(kT) k_scatter_acc(uint16_t* __restrict__ mixed
 // ascending expert order, then the 32 lanes stream the row, adding the selected experts' rows with the rounding
 // points of k_scatter_acc (one bf16 rounding per expert added). mixed is read (accumulate != 0) and written once
 // instead of once per expert. Many rows are in flight per SM, which hides the latency of the searches.
-constexpr int kCombineMaxE = 32;
-constexpr int kCombineWarps = 2;           // warps that share a row (each repeats the cheap search, no barrier)
+constexpr int kCombineMaxE = 64;
+constexpr int kCombineThreads = 64;        // small blocks: many rows in flight per SM hide the latency of the searches
 
 __device__ __forceinline__ uint4 combine_add(uint4 m, uint4 t, float w) {
     const uint32_t tw[4] = {t.x, t.y, t.z, t.w}, mw[4] = {m.x, m.y, m.z, m.w};
@@ -260,74 +260,83 @@ __device__ __forceinline__ uint4 combine_add(uint4 m, uint4 t, float w) {
     return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-__global__ void __launch_bounds__(kT) k_combine_rows(uint16_t* __restrict__ mixed, const uint16_t* __restrict__ compact,
-                                                     const float* __restrict__ rw, const int* __restrict__ row_indices,
-                                                     const int* __restrict__ counts, const int* __restrict__ offsets,
-                                                     int rows, int E, int H, int accumulate) {
+// One 64-thread block per token row at a time: thread e finds the row's position in expert e's list by binary search
+// (the lists of k_build_row_lists are ascending), the first warp compacts the selected experts in ascending order, then
+// the block streams the row, adding the selected experts' rows with the rounding points of k_scatter_acc (one bf16
+// rounding per expert added). mixed is read (accumulate != 0) and written once instead of once per expert.
+__global__ void __launch_bounds__(kCombineThreads) k_combine_rows(uint16_t* __restrict__ mixed, const uint16_t* __restrict__ compact,
+                                                                  const float* __restrict__ rw, const int* __restrict__ row_indices,
+                                                                  const int* __restrict__ counts, const int* __restrict__ offsets,
+                                                                  int rows, int E, int H, int accumulate) {
+    __shared__ long long s_pos[2][kCombineMaxE];   // selected experts only, ascending; two copies alternate between rows
+    __shared__ float s_w[2][kCombineMaxE];
+    __shared__ int s_n[2];
     const int cpr = H / 8;
-    const int lane = threadIdx.x & 31;
-    const int gwarp = (blockIdx.x * kT + threadIdx.x) >> 5;
-    const int part = gwarp % kCombineWarps;
-    const int row_stride = ((gridDim.x * kT) >> 5) / kCombineWarps;
-    for (int row = gwarp / kCombineWarps; row < rows; row += row_stride) {
-        const float w = lane < E ? rw[static_cast<size_t>(row) * E + lane] : 0.0f;
+    const int t = threadIdx.x, lane = t & 31;
+    int par = 0;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x, par ^= 1) {
+        // E <= 64: thread e searches expert e; the two warps compact their halves, the second one after the first
+        const float w = t < E ? rw[static_cast<size_t>(row) * E + t] : 0.0f;
         long long pos = -1;
         if (w > 0.0f) {
-            const int* list = row_indices + static_cast<size_t>(lane) * rows;
-            const int n = counts[lane];
+            const int* list = row_indices + static_cast<size_t>(t) * rows;
+            const int n = counts[t];
             int lo = 0, hi = n;
             while (lo < hi) {
                 const int mid = (lo + hi) >> 1;
                 if (list[mid] < row) lo = mid + 1; else hi = mid;
             }
-            if (lo < n && list[lo] == row) pos = static_cast<long long>(offsets[lane]) + lo;
+            if (lo < n && list[lo] == row) pos = static_cast<long long>(offsets[t]) + lo;
         }
         const unsigned sel = __ballot_sync(0xffffffffu, pos >= 0);
-        const int n = __popc(sel);
-        // lane i takes over the i-th selected expert; the first four are then broadcast to every lane
-        const int src = lane < n ? static_cast<int>(__fns(sel, 0, lane + 1)) : 0;
-        const long long my_pos = __shfl_sync(0xffffffffu, pos, src);
-        const float my_w = __shfl_sync(0xffffffffu, w, src);
-        const uint16_t* p4[4];
-        float w4[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            p4[j] = compact + __shfl_sync(0xffffffffu, my_pos, j) * H;     // never dereferenced when j >= n
-            w4[j] = __shfl_sync(0xffffffffu, my_w, j);
+        const int before = __popc(sel & ((1u << lane) - 1u));
+        if (t < 32) {
+            if (pos >= 0) { s_pos[par][before] = pos; s_w[par][before] = w; }
+            if (lane == 0) s_n[par] = __popc(sel);
         }
+        __syncthreads();
+        if (t >= 32) {
+            const int base = s_n[par];
+            if (pos >= 0) { s_pos[par][base + before] = pos; s_w[par][base + before] = w; }
+        }
+        __syncthreads();
+        if (t == 32) s_n[par] += __popc(sel);
+        __syncthreads();
+        const int n = s_n[par];
         uint16_t* mrow = mixed + static_cast<size_t>(row) * H;
-        for (int c0 = part * 64; c0 < cpr; c0 += kCombineWarps * 64) {
-            // two 16-byte columns per lane and pass, all loads of both issued before the arithmetic
-            const int ca = c0 + lane, cb = c0 + 32 + lane;
+        for (int c0 = 0; c0 < cpr; c0 += 2 * kCombineThreads) {
+            // two 16-byte columns per thread and pass; the loads of up to four experts are issued before the arithmetic
+            const int ca = c0 + t, cb = c0 + kCombineThreads + t;
             const bool ona = ca < cpr, onb = cb < cpr;
-            uint4 ma = make_uint4(0u, 0u, 0u, 0u), mb = ma, ta[4], tb[4];
+            uint4 ma = make_uint4(0u, 0u, 0u, 0u), mb = ma;
             if (accumulate) {
                 if (ona) ma = *reinterpret_cast<const uint4*>(mrow + ca * 8);
                 if (onb) mb = *reinterpret_cast<const uint4*>(mrow + cb * 8);
             }
+            for (int i0 = 0; i0 < n; i0 += 4) {
+                uint4 ta[4], tb[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (j < n) {
-                    if (ona) ta[j] = __ldcs(reinterpret_cast<const uint4*>(p4[j] + ca * 8));
-                    if (onb) tb[j] = __ldcs(reinterpret_cast<const uint4*>(p4[j] + cb * 8));
+                for (int j = 0; j < 4; ++j) {
+                    if (i0 + j < n) {
+                        const uint16_t* src = compact + s_pos[par][i0 + j] * H;
+                        if (ona) ta[j] = __ldcs(reinterpret_cast<const uint4*>(src + ca * 8));
+                        if (onb) tb[j] = __ldcs(reinterpret_cast<const uint4*>(src + cb * 8));
+                    }
                 }
-            }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (j < n) {
-                    ma = combine_add(ma, ta[j], w4[j]);
-                    mb = combine_add(mb, tb[j], w4[j]);
+                for (int j = 0; j < 4; ++j) {
+                    if (i0 + j < n) {
+                        const float wj = s_w[par][i0 + j];
+                        ma = combine_add(ma, ta[j], wj);
+                        mb = combine_add(mb, tb[j], wj);
+                    }
                 }
-            }
-            for (int i = 4; i < n; ++i) {                    // more than four experts per token
-                const uint16_t* pi = compact + __shfl_sync(0xffffffffu, my_pos, i) * H;
-                const float wi = __shfl_sync(0xffffffffu, my_w, i);
-                if (ona) ma = combine_add(ma, __ldcs(reinterpret_cast<const uint4*>(pi + ca * 8)), wi);
-                if (onb) mb = combine_add(mb, __ldcs(reinterpret_cast<const uint4*>(pi + cb * 8)), wi);
             }
             if (ona) *reinterpret_cast<uint4*>(mrow + ca * 8) = ma;
             if (onb) *reinterpret_cast<uint4*>(mrow + cb * 8) = mb;
         }
+        // the next row writes the other copy of s_pos / s_w / s_n; the copy after that is written only behind this
+        // row's barriers of the next iteration, which every thread passes after it has left the loop above
     }
 }
 
@@ -621,9 +630,11 @@ int cf_moe_combine_sorted_bf16(void* d_mixed, const void* d_compact, const float
         return cf_moe_combine_all_bf16(d_mixed, d_compact, d_route_weights, d_row_indices, d_counts, d_offsets, rows,
                                        num_experts, H, stream);
     }
-    const int rows_per_block = kT / 32 / kCombineWarps;
-    const int cap = sm_count() * 8, want = (rows + rows_per_block - 1) / rows_per_block;
-    k_combine_rows<<<want < cap ? want : cap, kT, 0, as_stream(stream)>>>(
+    int per_sm = 0;
+    CF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_combine_rows, kCombineThreads, 0));
+    if (per_sm < 1) per_sm = 1;
+    const long long cap = static_cast<long long>(sm_count()) * per_sm;
+    k_combine_rows<<<static_cast<unsigned>(rows < cap ? rows : cap), kCombineThreads, 0, as_stream(stream)>>>(
         static_cast<uint16_t*>(d_mixed), static_cast<const uint16_t*>(d_compact), d_route_weights, d_row_indices, d_counts,
         d_offsets, rows, num_experts, H, accumulate);
     CF_LAUNCH_CHECK("moe_combine_sorted_bf16");

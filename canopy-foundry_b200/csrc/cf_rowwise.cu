@@ -8,6 +8,8 @@
 #include "cf_common.cuh"
 #include "cf_internal.cuh"
 
+#define CF_TRY_RET(expr) do { const int rc__ = (expr); if (rc__ != CF_OK) return rc__; } while (0)
+
 namespace cf {
 namespace {
 
@@ -99,6 +101,106 @@ __global__ void __launch_bounds__(kRT) k_rowwise(const uint16_t* __restrict__ a,
         if (SWIGLU) x = bf16_round(x * stable_sigmoid(x) * bf16_bits_to_f32(br[c]));
         orow[c] = cvt_fp8<false>(x * s);
     }
+}
+
+// Fast form for 16-byte aligned rows with cols % 8 == 0: 64 threads per row, thread j keeps the vectors j, j+64, ...
+// of the row in registers (packed bf16) between the amax and the quantise pass, blocks stride over rows. Small blocks
+// keep many rows in flight per SM, which is what a one-row-at-a-time kernel needs to reach HBM bandwidth.
+constexpr int kFastT = 64;
+
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+    return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(lo))) |
+           (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(hi))) << 16);
+}
+
+template <bool SWIGLU, int NV>
+__global__ void __launch_bounds__(kFastT) k_rowwise_fast(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b,
+                                                         long long ld_in, uint8_t* __restrict__ out, long long ld_out,
+                                                         float* __restrict__ row_scale, float* __restrict__ row_descale,
+                                                         int rows, int cols) {
+    __shared__ float s_m[2][2];
+    const int j = threadIdx.x;
+    const int nvec = cols / 8;
+    int par = 0;
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x, par ^= 1) {
+        const uint4* ar = reinterpret_cast<const uint4*>(a + row * ld_in);
+        const uint4* br = SWIGLU ? reinterpret_cast<const uint4*>(b + row * ld_in) : nullptr;
+        uint4 v[NV];
+        float local = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            if (j + kFastT * i < nvec) v[i] = __ldcs(ar + j + kFastT * i);
+        if (SWIGLU) {
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                if (j + kFastT * i < nvec) {
+                    float g[8], u[8];
+                    unpack8(v[i], g);
+                    unpack8(__ldcs(br + j + kFastT * i), u);
+                    // the product is rounded to bf16 as swiglu_forward would store it
+                    v[i].x = pack2_bf16(g[0] * stable_sigmoid(g[0]) * u[0], g[1] * stable_sigmoid(g[1]) * u[1]);
+                    v[i].y = pack2_bf16(g[2] * stable_sigmoid(g[2]) * u[2], g[3] * stable_sigmoid(g[3]) * u[3]);
+                    v[i].z = pack2_bf16(g[4] * stable_sigmoid(g[4]) * u[4], g[5] * stable_sigmoid(g[5]) * u[5]);
+                    v[i].w = pack2_bf16(g[6] * stable_sigmoid(g[6]) * u[6], g[7] * stable_sigmoid(g[7]) * u[7]);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (j + kFastT * i < nvec) {
+                float f[8];
+                unpack8(v[i], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) local = fmaxf(local, fabsf(f[e]));
+            }
+        }
+        local = warp_max(local);
+        if ((j & 31) == 0) s_m[par][j >> 5] = local;
+        __syncthreads();
+        const float amax = fmaxf(fmaxf(s_m[par][0], s_m[par][1]), 1e-12f);
+        const float s = __fdiv_rn(448.0f, amax);
+        if (j == 0) {
+            if (row_scale) row_scale[row] = s;
+            row_descale[row] = __fdiv_rn(amax, 448.0f);
+        }
+        uint2* orow = reinterpret_cast<uint2*>(out + row * ld_out);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (j + kFastT * i < nvec) {
+                float f[8];
+                unpack8(v[i], f);
+                uint2 q;
+                q.x = cvt_fp8x4<false>(f[0] * s, f[1] * s, f[2] * s, f[3] * s);
+                q.y = cvt_fp8x4<false>(f[4] * s, f[5] * s, f[6] * s, f[7] * s);
+                orow[j + kFastT * i] = q;
+            }
+        }
+        // s_m alternates between two copies: the one written next is read by no thread that is still in this row
+    }
+}
+
+template <bool SWIGLU, int NV>
+int launch_rowwise_fast(const uint16_t* a, const uint16_t* b, long long ld_in, uint8_t* out, long long ld_out, float* row_scale,
+                        float* row_descale, int rows, int cols, cudaStream_t st) {
+    int per_sm = 0;
+    CF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_rowwise_fast<SWIGLU, NV>, kFastT, 0));
+    if (per_sm < 1) per_sm = 1;
+    long long grid = static_cast<long long>(sm_count()) * per_sm;
+    if (grid > rows) grid = rows;
+    k_rowwise_fast<SWIGLU, NV><<<static_cast<unsigned>(grid), kFastT, 0, st>>>(a, b, ld_in, out, ld_out, row_scale, row_descale,
+                                                                              rows, cols);
+    return CF_OK;
+}
+
+template <bool SWIGLU>
+int launch_rowwise_fast_nv(const uint16_t* a, const uint16_t* b, long long ld_in, uint8_t* out, long long ld_out,
+                           float* row_scale, float* row_descale, int rows, int cols, cudaStream_t st) {
+    const int nv = (cols / 8 + kFastT - 1) / kFastT;
+    if (nv <= 2) return launch_rowwise_fast<SWIGLU, 2>(a, b, ld_in, out, ld_out, row_scale, row_descale, rows, cols, st);
+    if (nv <= 4) return launch_rowwise_fast<SWIGLU, 4>(a, b, ld_in, out, ld_out, row_scale, row_descale, rows, cols, st);
+    if (nv <= 8) return launch_rowwise_fast<SWIGLU, 8>(a, b, ld_in, out, ld_out, row_scale, row_descale, rows, cols, st);
+    if (nv <= 16) return launch_rowwise_fast<SWIGLU, 16>(a, b, ld_in, out, ld_out, row_scale, row_descale, rows, cols, st);
+    return launch_rowwise_fast<SWIGLU, 32>(a, b, ld_in, out, ld_out, row_scale, row_descale, rows, cols, st);
 }
 
 // Per-tensor delayed-scaling form: out = e4m3(bf16(silu(g)*u) * *scale), amax of the bf16 product recorded.
@@ -199,6 +301,12 @@ int cf_fp8_quantize_rowwise_e4m3(const void* d_x, int ld_x, void* d_out, int ld_
     CF_REQUIRE(d_x && d_out && d_row_descale, "cf_fp8_quantize_rowwise_e4m3: null pointer");
     if (cols > kRT * kMaxVec * 8) { set_error("cf_fp8_quantize_rowwise_e4m3: at most %d columns", kRT * kMaxVec * 8); return CF_ERR_LIMIT; }
     const int vec = aligned16(d_x) && (ld_x % 8 == 0) && ((reinterpret_cast<uintptr_t>(d_out) & 7) == 0) && (ld_out % 8 == 0);
+    if (vec && cols % 8 == 0) {
+        CF_TRY_RET(launch_rowwise_fast_nv<false>(static_cast<const uint16_t*>(d_x), nullptr, ld_x, static_cast<uint8_t*>(d_out), ld_out,
+                                                 d_row_scale, d_row_descale, rows, cols, as_stream(stream)));
+        CF_LAUNCH_CHECK("quantize_rowwise_e4m3");
+        return CF_OK;
+    }
     k_rowwise<false><<<rows, kRT, 0, as_stream(stream)>>>(static_cast<const uint16_t*>(d_x), nullptr, ld_x,
                                                           static_cast<uint8_t*>(d_out), ld_out, d_row_scale, d_row_descale,
                                                           cols, vec);
@@ -214,6 +322,13 @@ int cf_swiglu_quantize_rowwise_e4m3(const void* d_gate, const void* d_up, int ld
     if (cols > kRT * kMaxVec * 8) { set_error("cf_swiglu_quantize_rowwise_e4m3: at most %d columns", kRT * kMaxVec * 8); return CF_ERR_LIMIT; }
     const int vec = aligned16(d_gate) && aligned16(d_up) && (ld_in % 8 == 0) &&
                     ((reinterpret_cast<uintptr_t>(d_out) & 7) == 0) && (ld_out % 8 == 0);
+    if (vec && cols % 8 == 0) {
+        CF_TRY_RET(launch_rowwise_fast_nv<true>(static_cast<const uint16_t*>(d_gate), static_cast<const uint16_t*>(d_up), ld_in,
+                                                static_cast<uint8_t*>(d_out), ld_out, d_row_scale, d_row_descale, rows, cols,
+                                                as_stream(stream)));
+        CF_LAUNCH_CHECK("swiglu_quantize_rowwise_e4m3");
+        return CF_OK;
+    }
     k_rowwise<true><<<rows, kRT, 0, as_stream(stream)>>>(static_cast<const uint16_t*>(d_gate), static_cast<const uint16_t*>(d_up),
                                                          ld_in, static_cast<uint8_t*>(d_out), ld_out, d_row_scale,
                                                          d_row_descale, cols, vec);

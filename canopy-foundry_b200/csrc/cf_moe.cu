@@ -34,7 +34,26 @@ unsigned grid_for(size_t work_items, int per_block) {
 
 // ---- bias ------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kT) k_bias_add(uint16_t* __restrict__ io, const uint16_t* __restrict__ bias, int rows,
-                                                 int cols, long long stride, int base) {
+                                                 int cols, long long stride, int base, int vec) {
+    if (vec) {          // 8 columns (16 bytes) per thread: rows, the slice base and the bias are 16-byte aligned
+        const int cpr = cols / 8;
+        const long long total = static_cast<long long>(rows) * cpr;
+        for (long long i = static_cast<long long>(blockIdx.x) * kT + threadIdx.x; i < total;
+             i += static_cast<long long>(gridDim.x) * kT) {
+            const long long r = i / cpr;
+            const int c = static_cast<int>(i - r * cpr);
+            uint4* p = reinterpret_cast<uint4*>(io + r * stride + base) + c;
+            const uint4 v = *p, b = __ldg(reinterpret_cast<const uint4*>(bias) + c);
+            const uint32_t vw[4] = {v.x, v.y, v.z, v.w}, bw[4] = {b.x, b.y, b.z, b.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                o[j] = static_cast<uint32_t>(f2bf(__uint_as_float(vw[j] << 16) + __uint_as_float(bw[j] << 16))) |
+                       (static_cast<uint32_t>(f2bf(__uint_as_float(vw[j] & 0xffff0000u) + __uint_as_float(bw[j] & 0xffff0000u))) << 16);
+            *p = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        return;
+    }
     const long long total = static_cast<long long>(rows) * cols;
     for (long long i = static_cast<long long>(blockIdx.x) * kT + threadIdx.x; i < total;
          i += static_cast<long long>(gridDim.x) * kT) {
@@ -487,8 +506,10 @@ int cf_bias_add_strided_bf16(void* d_inout, const void* d_bias, int rows, int co
     CF_REQUIRE(rows >= 0 && cols >= 0 && base >= 0 && row_stride >= 0, "cf_bias_add_strided_bf16: negative argument");
     if (rows == 0 || cols == 0) return CF_OK;
     CF_REQUIRE(d_inout && d_bias, "cf_bias_add_strided_bf16: null pointer");
-    k_bias_add<<<grid_for(static_cast<size_t>(rows) * cols, kT * 4), kT, 0, as_stream(stream)>>>(
-        static_cast<uint16_t*>(d_inout), static_cast<const uint16_t*>(d_bias), rows, cols, row_stride, base);
+    const int vec = cols % 8 == 0 && row_stride % 8 == 0 && base % 8 == 0 &&
+                    ((reinterpret_cast<uintptr_t>(d_inout) | reinterpret_cast<uintptr_t>(d_bias)) % 16) == 0;
+    k_bias_add<<<grid_for(static_cast<size_t>(rows) * cols, kT * 16), kT, 0, as_stream(stream)>>>(
+        static_cast<uint16_t*>(d_inout), static_cast<const uint16_t*>(d_bias), rows, cols, row_stride, base, vec);
     CF_LAUNCH_CHECK("bias_add_strided_bf16");
     return CF_OK;
 }

@@ -264,11 +264,21 @@ __global__ void k_clip_probe(const float* amax, const float* scale, float fp8_ma
 }
 
 __global__ void __launch_bounds__(kThreads) k_elem_clip_count(const uint16_t* __restrict__ x, const float* scale,
-                                                              float fp8_max, size_t n, float* out) {
+                                                              float fp8_max, size_t n, float* out, int vec) {
     const float s = *scale;
     unsigned long long clipped = 0;
-    for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n;
-         i += static_cast<size_t>(gridDim.x) * kThreads)
+    const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+    const size_t nvec = vec ? n / 8 : 0;                          // 16-byte loads when the base is aligned
+    for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < nvec; i += stride) {
+        const uint4 v = __ldcs(reinterpret_cast<const uint4*>(x) + i);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (fabsf(__uint_as_float(w[j] << 16)) * s > fp8_max) ++clipped;
+            if (fabsf(__uint_as_float(w[j] & 0xffff0000u)) * s > fp8_max) ++clipped;
+        }
+    }
+    for (size_t i = nvec * 8 + static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride)
         if (fabsf(bf16_bits_to_f32(x[i])) * s > fp8_max) ++clipped;
     // one float atomic per warp instead of per thread: integer partial sums stay exact below 2^24
 #pragma unroll
@@ -278,11 +288,26 @@ __global__ void __launch_bounds__(kThreads) k_elem_clip_count(const uint16_t* __
 }
 
 // ---- raw-byte E4M3 storage path (include/ida_native/fp8_e4m3.hpp semantics) -----------------
-__global__ void __launch_bounds__(kThreads) k_pack_raw_stats(const uint16_t* __restrict__ x, size_t n, float* amax, int* bad) {
+__global__ void __launch_bounds__(kThreads) k_pack_raw_stats(const uint16_t* __restrict__ x, size_t n, float* amax, int* bad,
+                                                             int vec) {
     float local = 0.0f;
     int local_bad = 0;
-    for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n;
-         i += static_cast<size_t>(gridDim.x) * kThreads) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+    const size_t nvec = vec ? n / 8 : 0;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < nvec; i += stride) {
+        const uint4 v = __ldcs(reinterpret_cast<const uint4*>(x) + i);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t b = h ? (w[j] >> 16) : (w[j] & 0xffffu);
+                if ((b & 0x7f80u) == 0x7f80u) local_bad = 1;        // Inf or NaN
+                else local = fmaxf(local, bf16_bits_to_f32(b & 0x7fffu));
+            }
+        }
+    }
+    for (size_t i = nvec * 8 + static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) {
         const uint32_t b = x[i];
         if ((b & 0x7f80u) == 0x7f80u) local_bad = 1;            // Inf or NaN
         else local = fmaxf(local, bf16_bits_to_f32(b & 0x7fffu));
@@ -309,12 +334,31 @@ __device__ __forceinline__ float unpack_e4m3(uint8_t c) { return fp8_to_f32<fals
 template <bool DEQUANT>
 __global__ void __launch_bounds__(kThreads) k_pack_raw(const uint16_t* __restrict__ x, uint8_t* __restrict__ out,
                                                        uint16_t* __restrict__ dequant, const float* scale,
-                                                       const float* descale, int* bad, size_t n) {
+                                                       const float* descale, int* bad, size_t n, int vec) {
     const float s = *scale;
     const float d = DEQUANT ? *descale : 0.0f;
     int nbad = 0;
-    for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n;
-         i += static_cast<size_t>(gridDim.x) * kThreads) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+    const size_t nvec = vec ? n / 8 : 0;          // 8 elements per thread: 16 bytes in, 8 bytes (+16 bytes) out
+    for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < nvec; i += stride) {
+        const uint4 v = __ldcs(reinterpret_cast<const uint4*>(x) + i);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t codes[2] = {0u, 0u}, dq[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int nf0 = 0, nf1 = 0;
+            const uint32_t c0 = pack_e4m3(__uint_as_float(w[j] << 16) * s, nf0);
+            const uint32_t c1 = pack_e4m3(__uint_as_float(w[j] & 0xffff0000u) * s, nf1);
+            nbad += nf0 + nf1;
+            codes[j >> 1] |= (c0 | (c1 << 8)) << (16 * (j & 1));
+            if (DEQUANT)
+                dq[j] = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16(unpack_e4m3(static_cast<uint8_t>(c0)) * d))) |
+                        (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16(unpack_e4m3(static_cast<uint8_t>(c1)) * d))) << 16);
+        }
+        reinterpret_cast<uint2*>(out)[i] = make_uint2(codes[0], codes[1]);
+        if (DEQUANT) reinterpret_cast<uint4*>(dequant)[i] = make_uint4(dq[0], dq[1], dq[2], dq[3]);
+    }
+    for (size_t i = nvec * 8 + static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) {
         int nf = 0;
         const uint8_t c = pack_e4m3(bf16_bits_to_f32(x[i]) * s, nf);
         nbad += nf;
@@ -327,10 +371,23 @@ __global__ void __launch_bounds__(kThreads) k_pack_raw(const uint16_t* __restric
 }
 
 __global__ void __launch_bounds__(kThreads) k_unpack_raw(const uint8_t* __restrict__ in, const float* descale,
-                                                         uint16_t* __restrict__ out, size_t n) {
+                                                         uint16_t* __restrict__ out, size_t n, int vec) {
     const float d = *descale;
-    for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n;
-         i += static_cast<size_t>(gridDim.x) * kThreads)
+    const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+    const size_t nvec = vec ? n / 8 : 0;          // 8 codes in, 16 bytes of bf16 out
+    for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < nvec; i += stride) {
+        const uint2 c = __ldcs(reinterpret_cast<const uint2*>(in) + i);
+        const uint32_t w[2] = {c.x, c.y};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t pair = (w[j >> 1] >> (16 * (j & 1))) & 0xffffu;
+            o[j] = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16(unpack_e4m3(static_cast<uint8_t>(pair & 0xffu)) * d))) |
+                   (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16(unpack_e4m3(static_cast<uint8_t>(pair >> 8)) * d))) << 16);
+        }
+        reinterpret_cast<uint4*>(out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    for (size_t i = nvec * 8 + static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride)
         out[i] = __bfloat16_as_ushort(__float2bfloat16(unpack_e4m3(in[i]) * d));
 }
 
@@ -613,8 +670,8 @@ int cf_fp8_clip_probe(const float* d_amax, const float* d_scale, float fp8_max, 
 
 int cf_fp8_elem_clip_count(const void* d_x, const float* d_scale, float fp8_max, size_t n, float* d_out, void* stream) {
     CF_REQUIRE(d_scale && d_out && (n == 0 || d_x), "cf_fp8_elem_clip_count: null pointer");
-    k_elem_clip_count<<<flat_grid(n, kThreads * 8), kThreads, 0, as_stream(stream)>>>(
-        static_cast<const uint16_t*>(d_x), d_scale, fp8_max, n, d_out);
+    k_elem_clip_count<<<flat_grid(n, kThreads * 16), kThreads, 0, as_stream(stream)>>>(
+        static_cast<const uint16_t*>(d_x), d_scale, fp8_max, n, d_out, reinterpret_cast<uintptr_t>(d_x) % 16 == 0);
     CF_LAUNCH_CHECK("elem_clip_count");
     return CF_OK;
 }
@@ -624,17 +681,19 @@ static int pack_raw_common(const void* d_x, uint8_t* d_out, void* d_dequant, flo
     CF_REQUIRE(d_amax && d_scale && d_descale && d_bad && (n == 0 || (d_x && d_out)), "cf_fp8_pack_bf16_e4m3_raw: null pointer");
     CF_CUDA(cudaMemsetAsync(d_amax, 0, sizeof(float), st));
     CF_CUDA(cudaMemsetAsync(d_bad, 0, sizeof(int), st));
-    const unsigned grid = flat_grid(n, kThreads * 8);
-    k_pack_raw_stats<<<grid, kThreads, 0, st>>>(static_cast<const uint16_t*>(d_x), n, d_amax, d_bad);
+    const unsigned grid = flat_grid(n, kThreads * 16);
+    const int vec_in = reinterpret_cast<uintptr_t>(d_x) % 16 == 0;
+    const int vec = vec_in && reinterpret_cast<uintptr_t>(d_out) % 8 == 0 && reinterpret_cast<uintptr_t>(d_dequant) % 16 == 0;
+    k_pack_raw_stats<<<grid, kThreads, 0, st>>>(static_cast<const uint16_t*>(d_x), n, d_amax, d_bad, vec_in);
     CF_LAUNCH_CHECK("pack_raw_stats");
     k_scale_from_amax<<<1, 1, 0, st>>>(d_amax, 448.0f, d_scale, d_descale);
     CF_LAUNCH_CHECK("scale_from_amax");
     if (d_dequant)
         k_pack_raw<true><<<grid, kThreads, 0, st>>>(static_cast<const uint16_t*>(d_x), d_out,
-                                                    static_cast<uint16_t*>(d_dequant), d_scale, d_descale, d_bad, n);
+                                                    static_cast<uint16_t*>(d_dequant), d_scale, d_descale, d_bad, n, vec);
     else
         k_pack_raw<false><<<grid, kThreads, 0, st>>>(static_cast<const uint16_t*>(d_x), d_out, nullptr, d_scale,
-                                                     d_descale, d_bad, n);
+                                                     d_descale, d_bad, n, vec);
     CF_LAUNCH_CHECK("pack_raw");
     return CF_OK;
 }
@@ -650,8 +709,9 @@ int cf_fp8_pack_bf16_e4m3_raw_and_dequant(const void* d_x, uint8_t* d_out, void*
 }
 int cf_fp8_unpack_e4m3_raw_bf16(const uint8_t* d_in, const float* d_descale, void* d_out, size_t n, void* stream) {
     CF_REQUIRE(d_descale && (n == 0 || (d_in && d_out)), "cf_fp8_unpack_e4m3_raw_bf16: null pointer");
-    k_unpack_raw<<<flat_grid(n, kThreads * 8), kThreads, 0, as_stream(stream)>>>(d_in, d_descale,
-                                                                                static_cast<uint16_t*>(d_out), n);
+    const int vec = reinterpret_cast<uintptr_t>(d_in) % 8 == 0 && reinterpret_cast<uintptr_t>(d_out) % 16 == 0;
+    k_unpack_raw<<<flat_grid(n, kThreads * 16), kThreads, 0, as_stream(stream)>>>(d_in, d_descale,
+                                                                                 static_cast<uint16_t*>(d_out), n, vec);
     CF_LAUNCH_CHECK("unpack_raw");
     return CF_OK;
 }

@@ -89,6 +89,14 @@ def test_elementwise(cfb, oracle, refgpu):
     cfb.bias_add_strided_bf16(x, b, rows, H, 3 * H, H)
     oracle.bias_add_strided_bf16(xs, bf16_to_u16(b), rows, H, 3 * H, H)
     assert np.array_equal(bf16_to_u16(x), xs)
+    # shapes the 16-byte path cannot take: odd width, odd slice base, odd row pitch
+    for (r2, c2, stride, base) in [(19, 45, 3 * 48, 48), (19, 48, 3 * 48, 3), (19, 48, 147, 48)]:
+        x2 = randn_bf16((r2, stride), seed=5)
+        b2 = randn_bf16((c2,), std=0.1, seed=6)
+        xs2 = bf16_to_u16(x2).copy()
+        cfb.bias_add_strided_bf16(x2, b2, r2, c2, stride, base)
+        oracle.bias_add_strided_bf16(xs2, bf16_to_u16(b2), r2, c2, stride, base)
+        assert np.array_equal(bf16_to_u16(x2), xs2), (r2, c2, stride, base)
 
 
 @pytest.mark.parametrize("rows,E,k", [(1, 3, 2), (257, 8, 2), (4096, 8, 2), (1000, 11, 3), (64, 4, 4)])

@@ -234,13 +234,15 @@ def test_raw_pack_path(cfb, oracle, refgpu):
     big = randn_bf16((n + 8,), seed=10)
     out_u = torch.zeros(n + 8, dtype=torch.uint8, device="cuda")
     dq_u = torch.zeros(n + 8, dtype=torch.bfloat16, device="cuda")
+    am_u, sc_u, de_u = f32_scalar(), f32_scalar(), f32_scalar()
+    bad_u = torch.zeros(1, dtype=torch.int32, device="cuda")
     for off in (1, 3):
         xo = big[off:off + 4099]
-        cfb.fp8_pack_bf16_e4m3_raw_and_dequant(xo, out_u[off:off + 4099], dq_u[off:off + 4099], am, sc, de, bad)
+        cfb.fp8_pack_bf16_e4m3_raw_and_dequant(xo, out_u[off:off + 4099], dq_u[off:off + 4099], am_u, sc_u, de_u, bad_u)
         w2, wdq2, a2, s2, d2, _, _ = oracle.pack_raw_e4m3(bf16_to_u16(xo), want_dequant=True)
         assert np.array_equal(out_u[off:off + 4099].cpu().numpy(), w2) and np.array_equal(bf16_to_u16(dq_u[off:off + 4099]), wdq2)
         back_u = torch.zeros(n + 8, dtype=torch.bfloat16, device="cuda")
-        cfb.fp8_unpack_e4m3_raw_bf16(out_u[off:off + 4099], de, back_u[off:off + 4099])
+        cfb.fp8_unpack_e4m3_raw_bf16(out_u[off:off + 4099], de_u, back_u[off:off + 4099])
         assert np.array_equal(bf16_to_u16(back_u[off:off + 4099]), oracle.unpack_raw_e4m3_bf16(w2, d2))
     if refgpu is not None:
         r = torch.empty(n, dtype=torch.uint8, device="cuda")

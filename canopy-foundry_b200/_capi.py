@@ -107,6 +107,7 @@ SIGNATURES = {
     "cf_moe_expand_route_replicas": (ci, [fp, fp, ci, ci, ci, ip, fp, C.c_uint, vp]),
     "cf_moe_ep_plan": (ci, [ip, ci, ci, ci, ip, ip, vp, ip, ip, vp, vp]),
     "cf_moe_send_row_runs": (ci, [vp, ip, C.c_longlong, vp, ci, ci, vp, C.c_longlong, fp, vp, vp]),
+    "cf_gemm_fp8_nt_grouped_return": (ci, [vp, ci, ci, ci, ci, ip, ip, vp, ci, ci, fp, vp, fp, vp, ci, C.POINTER(vp), ci, ci, ci, vp]),
     "cf_moe_grouped_expert_forward_fp8": (ci, [vp, vp, fp, ci, fp, ip, ip, ip, vp, fp, vp, fp, vp, ci, ci, ci, ci, ci, vp]),
 }
 

@@ -68,11 +68,12 @@ struct Ctx {
     // reduce-scatter GEMM: kPeerMapSets sets of 16 tensor maps on the device, each remembered with the slices it
     // describes, so that repeated calls on the same slices re-encode and copy nothing
     void* d_peer_maps = nullptr;
-    struct PeerMapKey { int count = 0, rows = 0, n = 0; void* ptr[16] = {}; } peer_key[4];
+    struct PeerMapKey { int kind = 0, count = 0, rows = 0, n = 0; long long ld = 0; void* ptr[16] = {}; } peer_key[4];
     int peer_next = 0;
     std::mutex mu;
 };
 
+constexpr int kPeerSetBytes = 16 * 128 + 16 * 8;   // 16 tensor maps followed by 16 base pointers
 constexpr int kSlotFloats = 24;        // 8 scalars padded to 4 floats each is overkill; layout below
 constexpr int kMaxSlots = 4096;
 constexpr int kHistoryLen = 8;         // kActHistoryLen, src/trainer.cu:3213
@@ -82,6 +83,30 @@ void* ctx_workspace(cf_ctx* c, size_t* bytes) {
     Ctx* x = reinterpret_cast<Ctx*>(c);
     *bytes = x->workspace_bytes;
     return x->workspace;
+}
+
+// Slot of the context's device-side tensor-map sets that describes these buffers, and whether its contents are current.
+int peer_set_lookup(Ctx* c, int kind, void* const* ptrs, int count, int rows, int n, long long ld, int* ready) {
+    std::lock_guard<std::mutex> lk(c->mu);
+    for (int i = 0; i < 4; ++i) {
+        const Ctx::PeerMapKey& k = c->peer_key[i];
+        if (k.count == count && k.kind == kind && k.rows == rows && k.n == n && k.ld == ld &&
+            std::memcmp(k.ptr, ptrs, sizeof(void*) * count) == 0) {
+            *ready = 1;
+            return i;
+        }
+    }
+    const int set = c->peer_next;
+    c->peer_next = (c->peer_next + 1) % 4;
+    c->peer_key[set].count = 0;            // invalid until the launch that fills it has been issued
+    *ready = 0;
+    return set;
+}
+void peer_set_commit(Ctx* c, int set, int kind, void* const* ptrs, int count, int rows, int n, long long ld) {
+    std::lock_guard<std::mutex> lk(c->mu);
+    Ctx::PeerMapKey& k = c->peer_key[set];
+    k.kind = kind; k.count = count; k.rows = rows; k.n = n; k.ld = ld;
+    std::memcpy(k.ptr, ptrs, sizeof(void*) * count);
 }
 
 }  // namespace cf
@@ -104,7 +129,7 @@ int cf_ctx_create(cf_ctx** out, size_t act8_bytes) {
     cudaError_t e = cudaGetDevice(&c->device);
     if (e == cudaSuccess) e = cudaMalloc(&c->d_status, 64);
     if (e == cudaSuccess) e = cudaMemset(c->d_status, 0, 64);
-    if (e == cudaSuccess) e = cudaMalloc(&c->d_peer_maps, 4 * 16 * 128);
+    if (e == cudaSuccess) e = cudaMalloc(&c->d_peer_maps, 4 * kPeerSetBytes);
     if (e == cudaSuccess && act8_bytes) { e = cudaMalloc(&c->act8, act8_bytes); c->act8_bytes = act8_bytes; }
     if (e == cudaSuccess) {
         c->scalar_blocks = kMaxSlots;
@@ -224,32 +249,46 @@ int cf_gemm_fp8_nt_reduce_scatter_f32(cf_ctx* ctx, int M, int N, int K, const vo
     p.a_e5m2 = a_is_e5m2 ? 1 : 0;
     p.peer_out_host = slices; p.peer_count = num_slices; p.rows_per_peer = M / num_slices;
     Ctx* c = reinterpret_cast<Ctx*>(ctx);
-    int set = -1;
-    {
-        std::lock_guard<std::mutex> lk(c->mu);
-        for (int i = 0; i < 4 && set < 0; ++i) {
-            const Ctx::PeerMapKey& k = c->peer_key[i];
-            if (k.count == num_slices && k.rows == p.rows_per_peer && k.n == N &&
-                std::memcmp(k.ptr, slices, sizeof(void*) * num_slices) == 0) set = i;
-        }
-        if (set >= 0) {
-            p.peer_maps_ready = 1;
-        } else {
-            set = c->peer_next;
-            c->peer_next = (c->peer_next + 1) % 4;
-            c->peer_key[set].count = 0;           // filled in below once the launch has taken the maps
-        }
-    }
-    p.d_peer_maps = static_cast<char*>(c->d_peer_maps) + static_cast<size_t>(set) * 16 * 128;
+    const int set = peer_set_lookup(c, 0, slices, num_slices, p.rows_per_peer, N, N, &p.peer_maps_ready);
+    p.d_peer_maps = static_cast<char*>(c->d_peer_maps) + static_cast<size_t>(set) * kPeerSetBytes;
     p.d_status = c->d_status;
     const int tiles = ((M + gemm_tile_m() - 1) / gemm_tile_m()) * ((N + gemm_tile_n() - 1) / gemm_tile_n());
     const int rc = launch_gemm_fp8_nt(d_A, lda, M, d_B, N, p, tiles, as_stream(stream));
-    if (rc == CF_OK && !p.peer_maps_ready) {
-        std::lock_guard<std::mutex> lk(c->mu);
-        Ctx::PeerMapKey& k = c->peer_key[set];
-        k.count = num_slices; k.rows = p.rows_per_peer; k.n = N;
-        std::memcpy(k.ptr, slices, sizeof(void*) * num_slices);
-    }
+    if (rc == CF_OK && !p.peer_maps_ready) peer_set_commit(c, set, 0, slices, num_slices, p.rows_per_peer, N, N);
+    return rc;
+}
+
+int cf_gemm_fp8_nt_grouped_return(cf_ctx* ctx, int num_groups, int max_total_rows, int N, int K, const int* d_counts,
+                                  const int* d_offsets, const void* d_A, int lda, int a_is_e5m2, const float* d_a_descale,
+                                  const void* d_B, const float* d_b_descale, const cf_row_run* d_return_runs,
+                                  int runs_per_group, void* const* dst_buffers, int num_dst, int dst_rows, int ldc,
+                                  void* stream) {
+    CF_REQUIRE(ctx != nullptr, "cf_gemm_fp8_nt_grouped_return: null context");
+    CF_REQUIRE(num_groups >= 1 && max_total_rows >= 0 && N > 0 && K > 0 && lda >= K && ldc >= N,
+               "cf_gemm_fp8_nt_grouped_return: bad shape");
+    if (max_total_rows == 0) return CF_OK;
+    CF_REQUIRE(d_counts && d_offsets && d_A && d_B && d_a_descale && d_b_descale && d_return_runs && dst_buffers,
+               "cf_gemm_fp8_nt_grouped_return: null pointer");
+    CF_REQUIRE(runs_per_group >= 1 && num_dst >= 1 && num_dst <= 16 && dst_rows > 0,
+               "cf_gemm_fp8_nt_grouped_return: 1..16 destination buffers");
+    GemmParams p;
+    p.groups = num_groups;
+    p.M = max_total_rows; p.N = N; p.K = K;
+    p.d_counts = d_counts; p.d_offsets = d_offsets;
+    p.d_a_descale = d_a_descale; p.d_b_descale = d_b_descale;
+    p.C = nullptr; p.ldc = ldc; p.out_kind = 0;
+    p.a_e5m2 = a_is_e5m2 ? 1 : 0;
+    p.d_out_runs = d_return_runs; p.runs_per_group = runs_per_group;
+    p.peer_out_host = dst_buffers; p.peer_count = num_dst; p.rows_per_peer = dst_rows;
+    Ctx* c = reinterpret_cast<Ctx*>(ctx);
+    const int set = peer_set_lookup(c, 1, dst_buffers, num_dst, dst_rows, N, ldc, &p.peer_maps_ready);
+    p.d_peer_maps = static_cast<char*>(c->d_peer_maps) + static_cast<size_t>(set) * kPeerSetBytes;
+    p.d_status = c->d_status;
+    const int n_blocks = (N + gemm_tile_n() - 1) / gemm_tile_n();
+    const int m_blocks = (max_total_rows + gemm_tile_m() - 1) / gemm_tile_m() + num_groups;
+    const long long b_rows = static_cast<long long>(num_groups) * N;
+    const int rc = launch_gemm_fp8_nt(d_A, lda, max_total_rows, d_B, b_rows, p, m_blocks * n_blocks, as_stream(stream));
+    if (rc == CF_OK && !p.peer_maps_ready) peer_set_commit(c, set, 1, dst_buffers, num_dst, dst_rows, N, ldc);
     return rc;
 }
 

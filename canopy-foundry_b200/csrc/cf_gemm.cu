@@ -543,6 +543,26 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             // ragged rows of a grouped tile, column tails and the fp32 / accumulate forms use direct stores.
             const int warp_row0 = static_cast<int>(cta_rank) * BM + quarter * 32;
             const bool warp_rows_full = (p.d_counts == nullptr) || (warp_row0 + 32 <= tc.valid_rows);
+            // Where this lane's row and this warp's 32-row box go. Normally the tile's own output; in the return form
+            // every run of rows inside the group has its own destination buffer (possibly on a peer GPU).
+            const CUtensorMap* cmap = &map_c;
+            int ystore = tc.row0 + warp_row0;
+            void* out_base_l = tc.out_base;
+            long long grow_l = grow;
+            bool box_tma = p.tma_store && warp_rows_full && warp_row0 < tc.valid_rows;
+            if (WIDE && p.d_out_runs != nullptr) {
+                const cf_row_run* runs = p.d_out_runs + static_cast<long long>(tc.group) * p.runs_per_group;
+                const long long r_l = static_cast<long long>(tc.row0) + row_in_tile;
+                int s_l = 0;
+                for (int s = 1; s < p.runs_per_group; ++s)
+                    if (r_l >= runs[s].src_row) s_l = s;          // runs ascend; empty ones share their successor's start
+                out_base_l = p.d_peer_bases[runs[s_l].dst];
+                grow_l = runs[s_l].dst_row + (r_l - runs[s_l].src_row);
+                const int s_first = __shfl_sync(0xffffffffu, s_l, 0), s_last = __shfl_sync(0xffffffffu, s_l, 31);
+                box_tma = box_tma && s_first == s_last;           // the whole box belongs to one run
+                cmap = static_cast<const CUtensorMap*>(p.d_peer_maps) + runs[s_first].dst;
+                ystore = static_cast<int>(runs[s_first].dst_row + (tc.row0 + warp_row0 - runs[s_first].src_row));
+            }
             if (WIDE && p.tma_reduce && warp_rows_full && warp_row0 < tc.valid_rows) {
                 // fp32 output, added (dW += ...) or stored (partial products): 32 columns = one 128-byte line per box row
                 const uint32_t buf = smem_c + static_cast<uint32_t>(warp - 2) * C_BOX_BYTES;
@@ -592,7 +612,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     for (int j = 0; j < 32; ++j)
                         if (col0 + j < p.N) store_one(p, tc.out_base, grow, col0 + j, __uint_as_float(v[j]), da, db_t);
                 }
-            } else if (p.tma_store && warp_rows_full && warp_row0 < tc.valid_rows) {
+            } else if (box_tma) {
                 const uint32_t buf = smem_c + static_cast<uint32_t>(warp - 2) * C_BOX_BYTES;
                 const uint32_t row_off = static_cast<uint32_t>(lane) * 128u;
                 const uint32_t sw = static_cast<uint32_t>(lane & 7);
@@ -656,7 +676,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {
-                        tma_store_2d(&map_c, buf, col0, tc.row0 + warp_row0, store_policy);
+                        tma_store_2d(cmap, buf, col0, ystore, store_policy);
                         bulk_commit();
                     }
                 }
@@ -673,7 +693,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                         const int col = col0 + j;
                         if (col < p.N) {
                             const float db = p.d_b_col_descale ? p.d_b_col_descale[col] : db_t;
-                            store_one(p, tc.out_base, grow, col, __uint_as_float(v[j]), da, db);
+                            store_one(p, out_base_l, grow_l, col, __uint_as_float(v[j]), da, db);
                         }
                     }
                 }
@@ -694,7 +714,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     #endif
                     const bool full = col0 + 32 <= p.N;
                     if (p.out_kind == 0 && p.c_vec && full) {
-                        uint16_t* crow = static_cast<uint16_t*>(tc.out_base) + grow * p.ldc + col0;
+                        uint16_t* crow = static_cast<uint16_t*>(out_base_l) + grow_l * p.ldc + col0;
                         uint32_t w[16];
     #pragma unroll
                         for (int j = 0; j < 16; ++j) {
@@ -745,7 +765,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                             const int col = col0 + j;
                             if (col < p.N) {
                                 const float db = p.d_b_col_descale ? p.d_b_col_descale[col] : db_t;
-                                store_one(p, tc.out_base, grow, col, __uint_as_float(v[j]), da, db);
+                                store_one(p, out_base_l, grow_l, col, __uint_as_float(v[j]), da, db);
                             }
                         }
                     }
@@ -982,7 +1002,32 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
                    (p.d_b_col_descale == nullptr || reinterpret_cast<uintptr_t>(p.d_b_col_descale) % 16 == 0)) ? 1 : 0;
     static const bool no_tma_store = [] { const char* e = std::getenv("CF_GEMM_DIRECT_STORE"); return e && e[0] == '1'; }();
     if (no_tma_store) p.tma_store = 0;
-    if (p.peer_out_host != nullptr) {
+    const bool return_form = p.d_out_runs != nullptr;
+    if (return_form) {
+        // grouped bf16 output whose runs of rows go to per-run destination buffers
+        if (p.out_kind != 0 || p.d_counts == nullptr || p.peer_out_host == nullptr || p.peer_count < 1 || p.peer_count > 16 ||
+            p.d_peer_maps == nullptr || p.rows_per_peer <= 0 || p.runs_per_group < 1 || p.N % 64 != 0 || p.ldc % 8 != 0 ||
+            p.bias || p.d_group_out || !tma_ok) {
+            set_error("return-form GEMM: needs a grouped bf16 product, TMA-aligned operands, N %% 64 == 0, 1..16 destination buffers");
+            return CF_ERR_UNSUPPORTED;
+        }
+        if (!p.peer_maps_ready) {
+            struct { CUtensorMap maps[16]; void* bases[16]; } host;
+            for (int i = 0; i < 16; ++i) host.bases[i] = nullptr;
+            for (int i = 0; i < p.peer_count; ++i) {
+                if (p.peer_out_host[i] == nullptr || reinterpret_cast<uintptr_t>(p.peer_out_host[i]) % 16 != 0) {
+                    set_error("return-form GEMM: destination %d is null or not 16-byte aligned", i);
+                    return CF_ERR_INVALID_ARG;
+                }
+                r = make_map_c(&host.maps[i], p.peer_out_host[i], p.rows_per_peer, p.N, p.ldc);
+                if (r != CF_OK) return r;
+                host.bases[i] = p.peer_out_host[i];
+            }
+            CF_CUDA(cudaMemcpyAsync(p.d_peer_maps, &host, sizeof(host), cudaMemcpyHostToDevice, st));
+        }
+        p.d_peer_bases = reinterpret_cast<void* const*>(static_cast<char*>(p.d_peer_maps) + 16 * sizeof(CUtensorMap));
+        p.peer_out_host = nullptr;
+    } else if (p.peer_out_host != nullptr) {
         // every tile must lie inside one slice and take the TMA path as a whole (no ragged rows, no column tail)
         if (p.out_kind != 2 || p.d_counts != nullptr || p.peer_count < 1 || p.peer_count > 16 || p.d_peer_maps == nullptr ||
             p.rows_per_peer <= 0 || p.rows_per_peer % 256 != 0 || p.M != p.rows_per_peer * p.peer_count || p.N % 32 != 0 ||
@@ -1010,7 +1055,8 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     }
     const bool f32_tma = (p.out_kind == 2 || p.out_kind == 1) && ca % 16 == 0 && p.ldc % 4 == 0 && p.N >= 32 &&
                          p.d_group_out == nullptr && p.d_a_row_descale == nullptr && p.d_b_col_descale == nullptr && !no_tma_store;
-    p.tma_reduce = p.d_peer_maps ? 1 : (f32_tma ? (p.out_kind == 2 ? 1 : 2) : 0);
+    p.tma_reduce = return_form ? 0 : p.d_peer_maps ? 1 : (f32_tma ? (p.out_kind == 2 ? 1 : 2) : 0);
+    if (return_form) p.tma_store = no_tma_store ? 0 : 1;
     if (p.d_peer_maps) {
         map_c = map_a;   // the kernel takes its output maps from d_peer_maps
     } else if (p.tma_store) {
@@ -1024,7 +1070,7 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     }
     int dev = 0;
     CF_CUDA(cudaGetDevice(&dev));
-    const bool wide = p.out_kind >= 1 && p.out_kind <= 3;
+    const bool wide = (p.out_kind >= 1 && p.out_kind <= 3) || p.d_out_runs != nullptr;
     if (pair) {
         // tile_upper_bound counts 128-row blocks; a pair tile covers two of them
         const int n_blocks = (p.N + BN - 1) / BN;

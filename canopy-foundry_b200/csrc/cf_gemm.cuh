@@ -3,6 +3,8 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 
+#include "canopy_fp8.h"
+
 namespace cf {
 
 struct GemmParams {
@@ -38,6 +40,12 @@ struct GemmParams {
     int peer_count = 0;
     int rows_per_peer = 0;
     void* d_peer_maps = nullptr;
+    // Return form (out_kind 0, grouped): the rows of group g are runs d_out_runs[g * runs_per_group + s] (ascending
+    // src_row in the compact row space of A); run s goes to rows dst_row.. of destination buffer `dst` (bf16
+    // [rows_per_peer, N], pitch ldc), whose tensor maps sit at d_peer_maps and whose base pointers at d_peer_bases.
+    const cf_row_run* d_out_runs = nullptr;
+    int runs_per_group = 0;
+    void* const* d_peer_bases = nullptr;
     int peer_maps_ready = 0;        // the maps at d_peer_maps already describe peer_out_host (cached by the caller)
     int mn_major = 0;               // operands are [K, M] and [K, N] in memory (un-transposed weight-gradient form)
     long long ldb = 0;              // mn_major: row pitch of B in bytes

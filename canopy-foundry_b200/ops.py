@@ -25,7 +25,7 @@ __all__ = [
     "rmsnorm_forward", "rmsnorm_quantize_e4m3_record", "rmsnorm_quantize_rowwise_e4m3", "fp8_rmsnorm_quant_act",
     "moe_topk_route_f32", "moe_build_expert_row_lists", "moe_expert_offsets_from_counts",
     "moe_gather_rows_u8", "moe_gather_rows_bf16", "moe_scatter_accumulate_rows_bf16",
-    "moe_scale_accumulate_bf16", "moe_gather_all_u8", "moe_combine_all_bf16", "moe_combine_sorted_bf16", "moe_expand_route_replicas", "moe_ep_plan", "moe_send_row_runs", "ROW_RUN_BYTES",
+    "moe_scale_accumulate_bf16", "moe_gather_all_u8", "moe_combine_all_bf16", "moe_combine_sorted_bf16", "moe_expand_route_replicas", "moe_ep_plan", "gemm_fp8_nt_grouped_return", "moe_send_row_runs", "ROW_RUN_BYTES",
     "moe_grouped_expert_forward_fp8", "launch_count", "swiglu_mlp_fp8_rowwise", "MoeSwigluFp8", "FfnSwigluFp8",
 ]
 
@@ -453,6 +453,16 @@ def moe_send_row_runs(src, row_indices, index_stride, runs, num_runs, max_rows_p
     per-row float tag. dst_bases / tag_bases: int64 device tensors of base addresses."""
     check(_L().cf_moe_send_row_runs(_p(src), _p(row_indices), index_stride, _p(runs), num_runs, max_rows_per_run,
                                     _p(dst_bases), row_bytes, _p(tag_value), _p(tag_bases), _s()))
+
+
+def gemm_fp8_nt_grouped_return(ctx, num_groups, max_total_rows, N, K, counts, offsets, A, lda, a_is_e5m2, a_descale, B,
+                               b_descale, return_runs, runs_per_group, dst_ptrs, dst_rows, ldc):
+    """Ragged grouped GEMM whose epilogue stores every run of rows into its destination buffer (dst_ptrs: device
+    addresses as mapped in this process, one per rank)."""
+    arr = (C.c_void_p * len(dst_ptrs))(*[C.c_void_p(int(x)) for x in dst_ptrs])
+    check(_L().cf_gemm_fp8_nt_grouped_return(ctx.handle, num_groups, max_total_rows, N, K, _p(counts), _p(offsets), _p(A),
+                                             lda, int(a_is_e5m2), _p(a_descale), _p(B), _p(b_descale), _p(return_runs),
+                                             runs_per_group, arr, len(dst_ptrs), dst_rows, ldc, _s()))
 
 
 def moe_grouped_expert_forward_fp8(ctx, hidden, fcin_descale, fcin_is_e5m2, route_weights, counts, offsets, row_indices,

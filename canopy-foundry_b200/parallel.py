@@ -428,8 +428,12 @@ class EpMoeSwigluFp8Direct:
     so no count ever has to be known on the host.
     Weights: gate/up interleaved (fp8_interleave_gate_up), stacked in placement.local_experts(rank) order."""
 
-    def __init__(self, cfb, ctx, rows, H, F, num_experts, top_k, placement=None, group=None, device="cuda"):
+    def __init__(self, cfb, ctx, rows, H, F, num_experts, top_k, placement=None, group=None, device="cuda",
+                 fused_return=True):
+        """fused_return: the down GEMM's epilogue stores every run of result rows straight into the owner's buffer
+        (cf_gemm_fp8_nt_grouped_return) instead of writing them locally and copying them out afterwards."""
         self.cfb, self.ctx, self.group = cfb, ctx, group
+        self.fused_return = bool(fused_return) and H % 64 == 0
         self.rows, self.H, self.F, self.E, self.k = rows, H, F, num_experts, top_k
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -472,6 +476,7 @@ class EpMoeSwigluFp8Direct:
         self.peer_recv8 = torch.tensor(p8, dtype=torch.int64, device=dev)
         self.peer_recv_dx = torch.tensor(pdx, dtype=torch.int64, device=dev)
         self.peer_back = torch.tensor(pback, dtype=torch.int64, device=dev)
+        self.back_ptrs = list(pback)
         self._fence = torch.zeros(1, dtype=f32, device=dev)
         self._barrier()
 
@@ -516,10 +521,15 @@ class EpMoeSwigluFp8Direct:
         cfb.gemm_fp8_swiglu_quant_act(ctx, self.slot_h, self.n_local, self.n_local, None, self.cap, F, H, self.grp_counts,
                                       self.grp_offsets, self.recv8, H, False, self.recv_dx, 2, w_gateup8_local,
                                       w_gateup_descale, self.h8, F)
-        cfb.gemm_fp8_nt_grouped(ctx, self.n_local, self.cap, H, F, self.grp_counts, self.grp_offsets, self.h8, F, False,
-                                cfb.ops._DevPtr(self.slot_h.c.descale_snapshot), False, w_down8_local, w_down_descale,
-                                self.yc, H)
-        cfb.moe_send_row_runs(self.yc, None, 0, self.ret_runs, self.n_local * W, rows, self.peer_back, 2 * H)
+        if self.fused_return:
+            cfb.gemm_fp8_nt_grouped_return(ctx, self.n_local, self.cap, H, F, self.grp_counts, self.grp_offsets, self.h8, F,
+                                           False, cfb.ops._DevPtr(self.slot_h.c.descale_snapshot), w_down8_local,
+                                           w_down_descale, self.ret_runs, W, self.back_ptrs, self.T, H)
+        else:
+            cfb.gemm_fp8_nt_grouped(ctx, self.n_local, self.cap, H, F, self.grp_counts, self.grp_offsets, self.h8, F, False,
+                                    cfb.ops._DevPtr(self.slot_h.c.descale_snapshot), False, w_down8_local, w_down_descale,
+                                    self.yc, H)
+            cfb.moe_send_row_runs(self.yc, None, 0, self.ret_runs, self.n_local * W, rows, self.peer_back, 2 * H)
         self._barrier()          # every rank's results are back
         cfb.moe_combine_sorted_bf16(mixed, self.back, self.rwv, self.idx, self.counts, self.offsets, rows, V, H, accumulate)
 

@@ -447,6 +447,18 @@ int cf_moe_ep_plan(const int* d_counts_all, int world, int rank, int num_replica
 int cf_moe_send_row_runs(const void* d_src, const int* d_row_indices_or_null, long long index_stride, const cf_row_run* d_runs,
                          int num_runs, int max_rows_per_run, void* const* d_dst_bases, long long row_bytes,
                          const float* d_tag_value_or_null, float* const* d_tag_bases_or_null, void* stream);
+/* The down projection of a device-planned expert-parallel layer with the return leg in its epilogue: a ragged grouped
+ * NT GEMM (as cf_gemm_fp8_nt_grouped) whose output rows leave straight for the buffers of the ranks that own the tokens.
+ * Inside group g the rows are the runs d_return_runs[g * runs_per_group + s] in ascending src_row (compact rows of A);
+ * run s is written to rows dst_row.. of dst_buffers[run.dst], bf16 [dst_rows, N] with pitch ldc (peer-mapped memory
+ * for other ranks). 32-row boxes that lie inside one run leave as TMA stores, boxes that straddle two runs row by row.
+ * dst_buffers is a HOST array of num_dst (1..16) device pointers; the context caches their tensor maps on the device.
+ * Needs N % 64 == 0, ldc % 8 == 0, 16-byte aligned operands, K % 16 == 0. */
+int cf_gemm_fp8_nt_grouped_return(cf_ctx* ctx, int num_groups, int max_total_rows, int N, int K, const int* d_counts,
+                                  const int* d_offsets, const void* d_A, int lda, int a_is_e5m2, const float* d_a_descale,
+                                  const void* d_B, const float* d_b_descale, const cf_row_run* d_return_runs,
+                                  int runs_per_group, void* const* dst_buffers, int num_dst, int dst_rows, int ldc,
+                                  void* stream);
 
 /* kernels/moe.cu:1062-1127, kernels.hpp:414-423: grouped selected-expert FP8 forward with exact-erf GELU,
  * accumulating rw*y into d_mixed. The tensor-core implementation needs workspace, which the reference

@@ -309,8 +309,9 @@ def test_fused_swiglu_gemm_matches_the_unfused_sequence(cfb, ctx, oracle, rows, 
         assert torch.equal(h_a, h_b), step
 
 
+@pytest.mark.parametrize("fused_return", [True, False])
 @pytest.mark.parametrize("rows,H,F,E", [(700, 256, 512, 4), (1100, 128, 96, 8)])
-def test_device_planned_expert_parallel_layer_on_one_rank(cfb, ctx, rows, H, F, E):
+def test_device_planned_expert_parallel_layer_on_one_rank(cfb, ctx, rows, H, F, E, fused_return):
     """The expert-parallel layer whose plan, dispatch and return run on the device, with a single rank (every destination
     is the local GPU): same bits as the single-GPU layer over three steps, including the delayed scales."""
     k = 2
@@ -318,7 +319,7 @@ def test_device_planned_expert_parallel_layer_on_one_rank(cfb, ctx, rows, H, F, 
     wd8, dd = _tensorquant(cfb, randn_bf16((E, H, F), std=0.05, seed=5))
     wgu8_il = cfb.fp8_interleave_gate_up(wgu8)
     single = cfb.MoeSwigluFp8(ctx, rows, H, F, E, k, fused_swiglu=True)
-    direct = cfb.parallel.EpMoeSwigluFp8Direct(cfb, ctx, rows, H, F, E, k)
+    direct = cfb.parallel.EpMoeSwigluFp8Direct(cfb, ctx, rows, H, F, E, k, fused_return=fused_return)
     assert direct.V == E and direct.n_local == E
     for step in range(3):
         x = randn_bf16((rows, H), std=1.0 + step, seed=40 + step)

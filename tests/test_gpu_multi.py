@@ -189,6 +189,14 @@ def _worker(rank, world, port, ret):
             ctx.poll_status()
         assert torch.equal(ep5.counts, ep4.counts) and int(ep5.grp_counts.sum().item()) == ep4.plan.total_recv
         assert torch.equal(mixed_d.view(torch.int16), mixed_r.view(torch.int16))
+        # ... and with the results written locally and copied out afterwards instead of leaving from the GEMM epilogue
+        ep6 = par.EpMoeSwigluFp8Direct(cfb, ctx, rows, H, F, E, k, placement=pl, device=dev, fused_return=False)
+        mixed_e = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
+        for step in range(2):
+            rw6 = logits[rank].clone()
+            ep6.forward(xs[rank], rw6, wgu_il_loc, dgu, wd8[loc].contiguous(), dd, mixed_e, accumulate=False)
+            ctx.poll_status()
+        assert ep5.fused_return and torch.equal(mixed_e.view(torch.int16), mixed_r.view(torch.int16))
         # and against the single-GPU layer on all tokens: a different scale granularity (one activation scale per rank
         # instead of one over all tokens), so the two differ by FP8 quantisation noise, not by more
         single = cfb.MoeSwigluFp8(ctx, rows * world, H, F, E, k, device=dev)

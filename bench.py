@@ -253,7 +253,8 @@ def run_moe(args):
     if fused_swiglu:
         wgu8 = cfb.fp8_interleave_gate_up(wgu8)       # one-time weight layout for the fused SwiGLU epilogue
     if use_ep and (not args.moe_a2a):
-        layer = par.EpMoeSwigluFp8Direct(cfb, ctx, rows, H, F, E, TOPK, placement=placement, device=dev)
+        layer = par.EpMoeSwigluFp8Direct(cfb, ctx, rows, H, F, E, TOPK, placement=placement, device=dev,
+                                         fused_return=not args.moe_copy_return)
     elif use_ep:
         layer = par.EpMoeSwigluFp8(cfb, ctx, rows, H, F, E, TOPK, device=dev, fused_return=args.moe_fused_return,
                                    fused_swiglu=fused_swiglu, placement=placement)
@@ -477,6 +478,9 @@ def main():
     ap.add_argument("--moe-unfused-swiglu", action="store_true", help="keep the [T,2F] bf16 intermediate (separate SwiGLU pass)")
     ap.add_argument("--moe-fused-return", action="store_true",
                     help="ep mode: the down GEMM stores its rows straight into the owners' buffers over NVLink (no return all-to-all)")
+    ap.add_argument("--moe-copy-return", action="store_true",
+                    help="device-planned form: write the results locally and copy them to their owners after the down GEMM "
+                         "(default: the GEMM epilogue stores them straight into the owners' buffers)")
     ap.add_argument("--moe-a2a", action="store_true",
                     help="expert parallel through NCCL all-to-all with a host-side plan (default: plan, dispatch and return on "
                          "the device, rows stored straight into the serving ranks' buffers)")

@@ -507,11 +507,15 @@ class EpMoeSwigluFp8Direct:
                                       first_row=self.rank * rows)
         cfb.moe_build_expert_row_lists(self.rwv, self.counts, self.idx, rows, V)
         cfb.moe_expert_offsets_from_counts(self.counts, self.offsets, V)
+        gathered = None
         if W > 1:
-            dist.all_gather_into_tensor(self.counts_all, self.counts, group=self.group)
+            # the count table travels while the activation is being quantised
+            gathered = dist.all_gather_into_tensor(self.counts_all, self.counts, group=self.group, async_op=True)
         else:
             self.counts_all.copy_(self.counts.view(1, V))
         cfb.fp8_quant_act(ctx, self.slot_x, x, self.x8)
+        if gathered is not None:
+            gathered.wait()
         cfb.moe_ep_plan(self.counts_all, W, self.rank, V, self.range_lo, self.range_hi, self.send_runs, self.grp_counts,
                         self.grp_offsets, self.ret_runs)
         # permute + dispatch in one pass; every row carries the descale of the rank that quantised it

@@ -3,6 +3,7 @@ import json
 import os
 
 import numpy as np
+import pytest
 
 
 def _all_bf16():
@@ -269,3 +270,23 @@ def test_lion_step_restatement(oracle):
     w3, m3 = w0.copy(), m0.copy()
     oracle.lion_step(w3, m3, g, 1e-2, 0.9, 0.99, 0.1, seed=124)
     assert not np.array_equal(w3, w)
+
+
+@pytest.mark.parametrize("rows,H", [(5, 512), (3, 4096), (4, 96), (2, 1000)])
+def test_rmsnorm_restatement(oracle, rows, H):
+    """kernels/rmsnorm.cu:13-54: the restated summation order stays within fp32 rounding of a float64 mean square, the
+    output is x / rms * scale rounded to bf16 once, and a row of constants normalises to +-scale."""
+    rng = np.random.default_rng(H)
+    x = oracle.to_bf16((rng.standard_normal((rows, H)) * 3).astype(np.float32))
+    g = oracle.to_bf16((1 + 0.1 * rng.standard_normal(H)).astype(np.float32))
+    out, rms = oracle.rmsnorm_forward(x, g, 1e-6)
+    xf, gf = oracle.bf16_to_f32(x).astype(np.float64), oracle.bf16_to_f32(g).astype(np.float64)
+    want_rms = np.sqrt((xf * xf).mean(axis=1) + 1e-6)
+    assert np.allclose(rms, want_rms, rtol=2e-6)
+    want = xf / rms.astype(np.float64)[:, None] * gf
+    got = oracle.bf16_to_f32(out).astype(np.float64)
+    assert np.all(np.abs(got - want) <= np.abs(want) * 2.0 ** -8 + 1e-30)         # one bf16 rounding (+ fp32 products)
+    c = oracle.to_bf16(np.full((1, H), -2.5, dtype=np.float32))
+    o2, r2 = oracle.rmsnorm_forward(c, g, 0.0)
+    assert abs(r2[0] - 2.5) < 1e-6
+    assert np.all(np.abs(oracle.bf16_to_f32(o2)[0] + oracle.bf16_to_f32(g)) <= np.abs(oracle.bf16_to_f32(g)) * 2.0 ** -7)

@@ -461,7 +461,8 @@ class EpMoeSwigluFp8Direct:
         self.counts_all = torch.zeros((self.world, V), dtype=i32, device=dev)
         self.x8 = torch.empty((rows, H), dtype=torch.uint8, device=dev)
         self.h8 = torch.empty((cap, F), dtype=torch.uint8, device=dev)
-        self.yc = torch.empty((cap, H), dtype=torch.bfloat16, device=dev)
+        # compact results of the down GEMM: only the copied-return form keeps them locally
+        self.yc = None if self.fused_return else torch.empty((cap, H), dtype=torch.bfloat16, device=dev)
         self.send_runs = torch.zeros(V * cfb.ROW_RUN_BYTES, dtype=torch.uint8, device=dev)
         self.ret_runs = torch.zeros(self.n_local * self.world * cfb.ROW_RUN_BYTES, dtype=torch.uint8, device=dev)
         self.grp_counts = torch.zeros(self.n_local, dtype=i32, device=dev)

@@ -88,6 +88,9 @@ SIGNATURES = {
     "cf_rmsnorm_quantize_e4m3_record": (ci, [vp, vp, vp, fp, vp, fp, fp, ci, ci, cf, vp]),
     "cf_rmsnorm_quantize_rowwise_e4m3": (ci, [vp, vp, vp, fp, vp, fp, fp, ci, ci, cf, vp]),
     "cf_fp8_rmsnorm_quant_act": (ci, [vp, C.POINTER(ActSlotStruct), vp, vp, vp, fp, ci, ci, cf, vp, vp]),
+    "cf_rmsnorm_clip_forward": (ci, [vp, vp, vp, fp, ci, ci, cf, cf, vp]),
+    "cf_rmsnorm_clip_quantize_e4m3_record": (ci, [vp, vp, vp, fp, vp, fp, fp, ci, ci, cf, cf, vp]),
+    "cf_fp8_rmsnorm_clip_quant_act": (ci, [vp, C.POINTER(ActSlotStruct), vp, vp, vp, fp, ci, ci, cf, cf, vp, vp]),
     "cf_bias_add_strided_bf16": (ci, [vp, vp, ci, ci, ci, ci, vp]),
     "cf_swiglu_forward": (ci, [vp, vp, vp, ci, vp]),
     "cf_gelu_forward": (ci, [vp, vp, sz, vp]),

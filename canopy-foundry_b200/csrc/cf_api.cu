@@ -549,10 +549,11 @@ int cf_fp8_swiglu_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_gate, 
     return CF_OK;
 }
 
-int cf_fp8_rmsnorm_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, const void* d_norm_scale, void* d_normed_or_null,
-                             float* d_rms_or_null, int rows, int H, float eps, void* d_out8, void* stream) {
-    CF_REQUIRE(ctx && slot && slot->amax, "cf_fp8_rmsnorm_quant_act: null or uninitialised slot");
-    CF_REQUIRE(slot->fp8_max == CF_E4M3_MAX, "cf_fp8_rmsnorm_quant_act: E4M3 slots only");
+int cf_fp8_rmsnorm_clip_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, const void* d_norm_scale,
+                                  void* d_normed_or_null, float* d_rms_or_null, int rows, int H, float eps,
+                                  float clip_ceiling, void* d_out8, void* stream) {
+    CF_REQUIRE(ctx && slot && slot->amax, "cf_fp8_rmsnorm_clip_quant_act: null or uninitialised slot");
+    CF_REQUIRE(slot->fp8_max == CF_E4M3_MAX, "cf_fp8_rmsnorm_clip_quant_act: E4M3 slots only");
     cudaStream_t st = as_stream(stream);
     if (!slot->init) {
         // first use: exact amax of the normalised rows (a record pass whose codes are overwritten below), then the
@@ -560,12 +561,12 @@ int cf_fp8_rmsnorm_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, co
         CF_CUDA(cudaMemsetAsync(slot->amax, 0, sizeof(float), st));
         CF_CUDA(cudaMemsetAsync(slot->scale, 0, sizeof(float), st));
         CF_TRY(rmsnorm_launch(1, d_x, d_norm_scale, d_normed_or_null, d_rms_or_null, d_out8, slot->scale, slot->amax, nullptr,
-                              nullptr, rows, H, eps, RingTail(), st));
+                              nullptr, rows, H, eps, RingTail(), st, clip_ceiling));
         CF_TRY(cf_fp8_scale_from_amax(slot->amax, slot->fp8_max, slot->scale, slot->descale, stream));
         CF_CUDA(cudaMemcpyAsync(slot->scale_snapshot, slot->scale, sizeof(float), cudaMemcpyDeviceToDevice, st));
         CF_CUDA(cudaMemcpyAsync(slot->descale_snapshot, slot->descale, sizeof(float), cudaMemcpyDeviceToDevice, st));
         CF_TRY(rmsnorm_launch(1, d_x, d_norm_scale, d_normed_or_null, d_rms_or_null, d_out8, slot->scale, slot->amax, nullptr,
-                              nullptr, rows, H, eps, RingTail(), st));
+                              nullptr, rows, H, eps, RingTail(), st, clip_ceiling));
         CF_TRY(cf_fp8_update_delayed_scale(slot->amax, slot->fp8_max, slot->scale, slot->descale, slot->history,
                                            kHistoryLen, slot->history_cursor, slot->history_count, stream));
         slot->init = 1;
@@ -582,11 +583,17 @@ int cf_fp8_rmsnorm_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, co
     // the kernel reads the scale it quantises with from the snapshot: the tail may rewrite slot->scale while
     // other blocks are still running
     CF_TRY(rmsnorm_launch(1, d_x, d_norm_scale, d_normed_or_null, d_rms_or_null, d_out8, slot->scale_snapshot, slot->amax,
-                          nullptr, nullptr, rows, H, eps, tail, st));
+                          nullptr, nullptr, rows, H, eps, tail, st, clip_ceiling));
     if (!slot->ticket)
         CF_TRY(cf_fp8_update_delayed_scale(slot->amax, slot->fp8_max, slot->scale, slot->descale, slot->history,
                                            kHistoryLen, slot->history_cursor, slot->history_count, stream));
     return CF_OK;
+}
+
+int cf_fp8_rmsnorm_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, const void* d_norm_scale, void* d_normed_or_null,
+                             float* d_rms_or_null, int rows, int H, float eps, void* d_out8, void* stream) {
+    return cf_fp8_rmsnorm_clip_quant_act(ctx, slot, d_x, d_norm_scale, d_normed_or_null, d_rms_or_null, rows, H, eps, 0.0f,
+                                         d_out8, stream);
 }
 
 int cf_gemm_fp8_swiglu_quant_act(cf_ctx* ctx, cf_act_slot* slot, int num_segments, int num_weights,

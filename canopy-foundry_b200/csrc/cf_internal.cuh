@@ -39,9 +39,10 @@ int quant_dual_from_amax(const void* d_in, void* d_direct, void* d_transposed, c
 
 // mode 0: normalise only; 1: + per-tensor E4M3 codes with *d_scale, amax of the normalised bf16 row recorded;
 // 2: + per-row scale derived from the row's own amax (row_scale / row_descale written).
+// clip_ceiling > 0: rows of the normalised bf16 tensor whose L2 norm exceeds it are rescaled first (act_row_clip).
 int rmsnorm_launch(int mode, const void* d_x, const void* d_gamma, void* d_normed_or_null, float* d_rms_or_null, void* d_out8,
                    const float* d_scale, float* d_amax, float* d_row_scale, float* d_row_descale, int rows, int H, float eps,
-                   const RingTail& tail, cudaStream_t st);
+                   const RingTail& tail, cudaStream_t st, float clip_ceiling = 0.0f);
 
 int swiglu_record_launch(const void* d_gate, const void* d_up, int ld_in, void* d_out, int ld_out, const float* d_scale,
                          float* d_amax, int rows, int cols, const RingTail& tail, cudaStream_t st);

@@ -12,6 +12,8 @@
 // out = bf16((x * (1 / rms)) * scale[h]). What differs is the data movement: 16-byte loads fill a shared-memory copy
 // of the row, each thread picks its strided elements from there, and results return to HBM as 16-byte stores.
 #include "cf_common.cuh"
+#include <cstdlib>
+
 #include "cf_internal.cuh"
 
 namespace cf {
@@ -281,13 +283,203 @@ int launch_fast_nv(int nv, const uint16_t* x, const uint16_t* g, uint16_t* o, fl
     return launch_fast<MODE, 32>(x, g, o, rms, q, scale, amax, row_scale, row_descale, rows, H, eps, tail, st);
 }
 
+// Warp-per-row form (H % 512 == 0, H <= 8192), optionally with the row clip the reference runs between the norm and
+// the quantiser (act_row_clip, src/trainer.cu:3822-3845 and 3940-3991: squared row norm of the normalised bf16 row by
+// a 256-thread block, rows whose norm exceeds an absolute ceiling are rescaled and rounded to bf16 again). Lane j holds
+// the vectors j, j+32, j+64, ...: element h = 8(j + 32 i) + e. That one lane owns, complete and in order, both
+//   * the reference norm kernel's threads t = 8j + e + 256 (i & 1)   (512 threads, elements t, t+512, ...), and
+//   * the clip kernel's threads          t' = 8j + e                 (256 threads, elements t', t'+256, ...),
+// so every fused-multiply-add chain of the two reference reductions runs inside one lane, the xor-butterflies of both
+// (offsets 16, 8 between lanes j^2, j^1; 4, 2, 1 inside the lane) stay inside the warp, and no block barrier is needed.
+constexpr int kWarpRowThreads = 128;
+
+template <int MODE, int NV, bool CLIP>
+__global__ void __launch_bounds__(kWarpRowThreads) k_rmsnorm_warp(const uint16_t* __restrict__ x, const uint16_t* __restrict__ gamma,
+                                                                  uint16_t* __restrict__ out, float* __restrict__ rms_out,
+                                                                  uint8_t* __restrict__ out8, const float* __restrict__ scale,
+                                                                  float* __restrict__ amax, float* __restrict__ row_scale,
+                                                                  float* __restrict__ row_descale, int rows, int H, float eps,
+                                                                  float clip_ceiling, const RingTail tail) {
+    const int j = threadIdx.x & 31;
+    const int nv = H / 256;                               // vectors per lane
+    const float s1 = MODE == 1 ? *scale : 0.0f;
+    const uint4* g4 = reinterpret_cast<const uint4*>(gamma);
+    const long long warps = (static_cast<long long>(gridDim.x) * kWarpRowThreads) >> 5;
+    float local = 0.0f;
+    for (long long row = (static_cast<long long>(blockIdx.x) * kWarpRowThreads + threadIdx.x) >> 5; row < rows; row += warps) {
+        const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
+        uint4 v[NV];
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            if (i < nv) v[i] = __ldcs(xr + j + 32 * i);
+        // mean square in the norm kernel's order: acc[p][e] is its thread 8j + e + 256p
+        float acc[2][8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { acc[0][e] = 0.0f; acc[1][e] = 0.0f; }
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (i < nv) {
+                float f[8];
+                unpack8(v[i], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[i & 1][e] = fmaf(f[e], f[e], acc[i & 1][e]);
+            }
+        }
+        float wsum[2];
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[p][e] = __fadd_rn(acc[p][e], __shfl_xor_sync(0xffffffffu, acc[p][e], 2));
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[p][e] = __fadd_rn(acc[p][e], __shfl_xor_sync(0xffffffffu, acc[p][e], 1));
+            const float a0 = __fadd_rn(acc[p][0], acc[p][4]), a1 = __fadd_rn(acc[p][1], acc[p][5]);
+            const float a2 = __fadd_rn(acc[p][2], acc[p][6]), a3 = __fadd_rn(acc[p][3], acc[p][7]);
+            wsum[p] = __fadd_rn(__fadd_rn(a0, a2), __fadd_rn(a1, a3));      // the norm kernel's warp j/4 + 8p
+        }
+        float b[16];
+#pragma unroll
+        for (int w = 0; w < 16; ++w) b[w] = __fadd_rn(__shfl_sync(0xffffffffu, wsum[w >> 3], 4 * (w & 7)), 0.0f);
+#pragma unroll
+        for (int w = 0; w < 8; ++w) b[w] = __fadd_rn(b[w], b[w + 8]);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) b[w] = __fadd_rn(b[w], b[w + 4]);
+        const float total = __fadd_rn(__fadd_rn(b[0], b[2]), __fadd_rn(b[1], b[3]));
+        const float rms_val = sqrtf(__fadd_rn(__fdiv_rn(total, static_cast<float>(H)), eps));
+        if (j == 0 && rms_out) rms_out[row] = rms_val;
+        const float inv_rms = __fdiv_rn(1.0f, rms_val);
+
+        // normalise, round to bf16 (kept packed in v[])
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (i < nv) {
+                float f[8], gg[8];
+                unpack8(v[i], f);
+                unpack8(__ldg(g4 + j + 32 * i), gg);
+                v[i].x = pack2(__fmul_rn(__fmul_rn(f[0], inv_rms), gg[0]), __fmul_rn(__fmul_rn(f[1], inv_rms), gg[1]));
+                v[i].y = pack2(__fmul_rn(__fmul_rn(f[2], inv_rms), gg[2]), __fmul_rn(__fmul_rn(f[3], inv_rms), gg[3]));
+                v[i].z = pack2(__fmul_rn(__fmul_rn(f[4], inv_rms), gg[4]), __fmul_rn(__fmul_rn(f[5], inv_rms), gg[5]));
+                v[i].w = pack2(__fmul_rn(__fmul_rn(f[6], inv_rms), gg[6]), __fmul_rn(__fmul_rn(f[7], inv_rms), gg[7]));
+            }
+        }
+        if (CLIP) {
+            // squared norm of the bf16 row in the clip kernel's order: c[e] is its thread 8j + e
+            float c[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) c[e] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                if (i < nv) {
+                    float f[8];
+                    unpack8(v[i], f);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) c[e] = fmaf(f[e], f[e], c[e]);
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) c[e] = __fadd_rn(c[e], __shfl_xor_sync(0xffffffffu, c[e], 2));
+#pragma unroll
+            for (int e = 0; e < 8; ++e) c[e] = __fadd_rn(c[e], __shfl_xor_sync(0xffffffffu, c[e], 1));
+            const float c0 = __fadd_rn(c[0], c[4]), c1 = __fadd_rn(c[1], c[5]), c2 = __fadd_rn(c[2], c[6]), c3 = __fadd_rn(c[3], c[7]);
+            const float cw = __fadd_rn(__fadd_rn(c0, c2), __fadd_rn(c1, c3));            // the clip kernel's warp j/4
+            float t = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) t = __fadd_rn(t, __shfl_sync(0xffffffffu, cw, 4 * w));   // thread 0 adds the warps in order
+            const float norm = sqrtf(t);
+            if (norm > clip_ceiling) {                     // warp-uniform
+                const float scalef = __fdiv_rn(clip_ceiling, norm);
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    if (i < nv) {
+                        float f[8];
+                        unpack8(v[i], f);
+                        v[i].x = pack2(__fmul_rn(f[0], scalef), __fmul_rn(f[1], scalef));
+                        v[i].y = pack2(__fmul_rn(f[2], scalef), __fmul_rn(f[3], scalef));
+                        v[i].z = pack2(__fmul_rn(f[4], scalef), __fmul_rn(f[5], scalef));
+                        v[i].w = pack2(__fmul_rn(f[6], scalef), __fmul_rn(f[7], scalef));
+                    }
+                }
+            }
+        }
+        float rmax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (i < nv) {
+                const int vi = j + 32 * i;
+                if (out) reinterpret_cast<uint4*>(out + row * H)[vi] = v[i];
+                if (MODE != 0) {
+                    float f[8];
+                    unpack8(v[i], f);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) rmax = fmaxf(rmax, fabsf(f[e]));
+                    if (MODE == 1) {
+                        uint2 q;
+                        q.x = cvt_fp8x4<false>(f[0] * s1, f[1] * s1, f[2] * s1, f[3] * s1);
+                        q.y = cvt_fp8x4<false>(f[4] * s1, f[5] * s1, f[6] * s1, f[7] * s1);
+                        reinterpret_cast<uint2*>(out8 + row * H)[vi] = q;
+                    }
+                }
+            }
+        }
+        if (MODE == 1) local = fmaxf(local, rmax);
+        if (MODE == 2) {
+            const float a = fmaxf(warp_max(rmax), 1e-12f);
+            const float s2 = __fdiv_rn(448.0f, a);
+            if (j == 0) {
+                if (row_scale) row_scale[row] = s2;
+                row_descale[row] = __fdiv_rn(a, 448.0f);
+            }
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                if (i < nv) {
+                    float f[8];
+                    unpack8(v[i], f);
+                    uint2 q;
+                    q.x = cvt_fp8x4<false>(f[0] * s2, f[1] * s2, f[2] * s2, f[3] * s2);
+                    q.y = cvt_fp8x4<false>(f[4] * s2, f[5] * s2, f[6] * s2, f[7] * s2);
+                    reinterpret_cast<uint2*>(out8 + row * H)[j + 32 * i] = q;
+                }
+            }
+        }
+    }
+    if (MODE == 1) {
+        block_amax_commit(local, amax);
+        if (tail.ticket != nullptr && threadIdx.x == 0) ring_tail_last_block(tail, amax);
+    }
+}
+
+template <int MODE, int NV, bool CLIP>
+int launch_warp(const uint16_t* x, const uint16_t* g, uint16_t* o, float* rms, uint8_t* q, const float* scale, float* amax,
+                float* row_scale, float* row_descale, int rows, int H, float eps, float ceiling, const RingTail& tail,
+                cudaStream_t st) {
+    int per_sm = 0;
+    CF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_rmsnorm_warp<MODE, NV, CLIP>, kWarpRowThreads, 0));
+    if (per_sm < 1) per_sm = 1;
+    long long grid = static_cast<long long>(sm_count()) * per_sm;
+    const long long want = (static_cast<long long>(rows) + kWarpRowThreads / 32 - 1) / (kWarpRowThreads / 32);
+    if (grid > want) grid = want;
+    k_rmsnorm_warp<MODE, NV, CLIP><<<static_cast<unsigned>(grid), kWarpRowThreads, 0, st>>>(
+        x, g, o, rms, q, scale, amax, row_scale, row_descale, rows, H, eps, ceiling, tail);
+    CF_LAUNCH_CHECK("rmsnorm");
+    return CF_OK;
+}
+
+template <int MODE, bool CLIP>
+int launch_warp_nv(int nv, const uint16_t* x, const uint16_t* g, uint16_t* o, float* rms, uint8_t* q, const float* scale,
+                   float* amax, float* row_scale, float* row_descale, int rows, int H, float eps, float ceiling,
+                   const RingTail& tail, cudaStream_t st) {
+    if (nv <= 4) return launch_warp<MODE, 4, CLIP>(x, g, o, rms, q, scale, amax, row_scale, row_descale, rows, H, eps, ceiling, tail, st);
+    if (nv <= 8) return launch_warp<MODE, 8, CLIP>(x, g, o, rms, q, scale, amax, row_scale, row_descale, rows, H, eps, ceiling, tail, st);
+    if (nv <= 16) return launch_warp<MODE, 16, CLIP>(x, g, o, rms, q, scale, amax, row_scale, row_descale, rows, H, eps, ceiling, tail, st);
+    return launch_warp<MODE, 32, CLIP>(x, g, o, rms, q, scale, amax, row_scale, row_descale, rows, H, eps, ceiling, tail, st);
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace
 
 int rmsnorm_launch(int mode, const void* d_x, const void* d_gamma, void* d_normed_or_null, float* d_rms_or_null, void* d_out8,
                    const float* d_scale, float* d_amax, float* d_row_scale, float* d_row_descale, int rows, int H, float eps,
-                   const RingTail& tail, cudaStream_t st) {
+                   const RingTail& tail, cudaStream_t st, float clip_ceiling) {
     CF_REQUIRE(rows >= 0 && H > 0, "rmsnorm: bad shape");
     if (rows == 0) return CF_OK;
     CF_REQUIRE(d_x && d_gamma, "rmsnorm: null input pointer");
@@ -314,6 +506,22 @@ int rmsnorm_launch(int mode, const void* d_x, const void* d_gamma, void* d_norme
     const bool fast = H % 512 == 0 && aligned16(d_x) && aligned16(d_gamma) &&
                       (d_normed_or_null == nullptr || aligned16(d_normed_or_null)) &&
                       (mode == 0 || (reinterpret_cast<uintptr_t>(d_out8) & 7) == 0);
+    if (clip_ceiling > 0.0f && !(fast && H <= 8192)) {
+        set_error("rmsnorm with row clip: needs 16-byte aligned rows of a multiple of 512 and at most 8192 columns (got %d)", H);
+        return CF_ERR_UNSUPPORTED;
+    }
+    static const int warp_form = [] { const char* e = std::getenv("CF_NORM_WARP"); return e ? std::atoi(e) : 0; }();
+    if (fast && H <= 8192 && (clip_ceiling > 0.0f || warp_form)) {
+        const int nv = H / 256;
+        if (clip_ceiling > 0.0f) {
+            if (mode == 0) return launch_warp_nv<0, true>(nv, x, g, o, d_rms_or_null, q, d_scale, d_amax, d_row_scale, d_row_descale, rows, H, eps, clip_ceiling, tail, st);
+            if (mode == 1) return launch_warp_nv<1, true>(nv, x, g, o, d_rms_or_null, q, d_scale, d_amax, d_row_scale, d_row_descale, rows, H, eps, clip_ceiling, tail, st);
+            return launch_warp_nv<2, true>(nv, x, g, o, d_rms_or_null, q, d_scale, d_amax, d_row_scale, d_row_descale, rows, H, eps, clip_ceiling, tail, st);
+        }
+        if (mode == 0) return launch_warp_nv<0, false>(nv, x, g, o, d_rms_or_null, q, d_scale, d_amax, d_row_scale, d_row_descale, rows, H, eps, 0.0f, tail, st);
+        if (mode == 1) return launch_warp_nv<1, false>(nv, x, g, o, d_rms_or_null, q, d_scale, d_amax, d_row_scale, d_row_descale, rows, H, eps, 0.0f, tail, st);
+        return launch_warp_nv<2, false>(nv, x, g, o, d_rms_or_null, q, d_scale, d_amax, d_row_scale, d_row_descale, rows, H, eps, 0.0f, tail, st);
+    }
     if (fast) {
         const int nv = H / 512;
         if (mode == 0) return launch_fast_nv<0>(nv, x, g, o, d_rms_or_null, q, d_scale, d_amax, d_row_scale, d_row_descale, rows, H, eps, tail, st);
@@ -360,6 +568,19 @@ int cf_rmsnorm_quantize_rowwise_e4m3(const void* d_x, const void* d_scale, void*
                                      float eps, void* stream) {
     return rmsnorm_launch(2, d_x, d_scale, d_normed_or_null, d_rms_or_null, d_out8, nullptr, nullptr, d_row_scale_or_null,
                           d_row_descale, rows, H, eps, RingTail(), as_stream(stream));
+}
+
+int cf_rmsnorm_clip_quantize_e4m3_record(const void* d_x, const void* d_scale, void* d_normed_or_null, float* d_rms_or_null,
+                                         void* d_out8, const float* d_quant_scale, float* d_amax, int rows, int H, float eps,
+                                         float clip_ceiling, void* stream) {
+    return rmsnorm_launch(1, d_x, d_scale, d_normed_or_null, d_rms_or_null, d_out8, d_quant_scale, d_amax, nullptr, nullptr,
+                          rows, H, eps, RingTail(), as_stream(stream), clip_ceiling);
+}
+
+int cf_rmsnorm_clip_forward(const void* d_x, const void* d_scale, void* d_out, float* d_rms_or_null, int rows, int H, float eps,
+                            float clip_ceiling, void* stream) {
+    return rmsnorm_launch(0, d_x, d_scale, d_out, d_rms_or_null, nullptr, nullptr, nullptr, nullptr, nullptr, rows, H, eps,
+                          RingTail(), as_stream(stream), clip_ceiling);
 }
 
 }  // extern "C"

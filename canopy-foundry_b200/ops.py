@@ -22,7 +22,7 @@ __all__ = [
     "fp8_unpack_e4m3_raw_bf16", "lt_gemm_fp8_nt", "lt_gemm_fp8_tn_accum_f32", "gemm_fp8_dw_accum", "gemm_fp8_nt_reduce_scatter", "f32_to_bf16_and_zero", "gemm_fp8_nt_grouped", "gemm_fp8_nt_segments", "gemm_fp8_nt_segments_scatter",
     "fp8_quant_act", "fp8_swiglu_quant_act", "gemm_fp8_swiglu_quant_act", "fp8_interleave_gate_up", "refresh_fp8_weight", "fp8_linear_forward", "bias_add_strided_bf16", "swiglu_forward",
     "gelu_forward", "lion_step", "fp8_quantize_rowwise_e4m3", "swiglu_quantize_rowwise_e4m3", "swiglu_quantize_e4m3_record",
-    "rmsnorm_forward", "rmsnorm_quantize_e4m3_record", "rmsnorm_quantize_rowwise_e4m3", "fp8_rmsnorm_quant_act",
+    "rmsnorm_forward", "rmsnorm_quantize_e4m3_record", "rmsnorm_quantize_rowwise_e4m3", "fp8_rmsnorm_quant_act", "rmsnorm_clip_forward", "rmsnorm_clip_quantize_e4m3_record", "fp8_rmsnorm_clip_quant_act",
     "moe_topk_route_f32", "moe_build_expert_row_lists", "moe_expert_offsets_from_counts",
     "moe_gather_rows_u8", "moe_gather_rows_bf16", "moe_scatter_accumulate_rows_bf16",
     "moe_scale_accumulate_bf16", "moe_gather_all_u8", "moe_combine_all_bf16", "moe_combine_sorted_bf16", "moe_expand_route_replicas", "moe_ep_plan", "gemm_fp8_nt_grouped_return", "moe_send_row_runs", "ROW_RUN_BYTES",
@@ -376,6 +376,22 @@ def fp8_rmsnorm_quant_act(ctx, slot, x, scale, normed, rms, rows, H, out8, eps=1
     """rmsnorm_forward followed by fp8_quant_act on its output (src/trainer.cu:6097,6115) as one pass."""
     check(_L().cf_fp8_rmsnorm_quant_act(ctx.handle, C.byref(slot.c), _p(x), _p(scale), _p(normed), _p(rms), rows, H, eps,
                                         _p(out8), _s()))
+
+
+def rmsnorm_clip_forward(x, scale, out, rms, rows, H, clip_ceiling, eps=1e-6):
+    """rmsnorm_forward followed by act_row_clip (fixed ceiling) in one pass."""
+    check(_L().cf_rmsnorm_clip_forward(_p(x), _p(scale), _p(out), _p(rms), rows, H, eps, clip_ceiling, _s()))
+
+
+def rmsnorm_clip_quantize_e4m3_record(x, scale, normed, rms, out8, quant_scale, amax, rows, H, clip_ceiling, eps=1e-6):
+    check(_L().cf_rmsnorm_clip_quantize_e4m3_record(_p(x), _p(scale), _p(normed), _p(rms), _p(out8), _p(quant_scale),
+                                                    _p(amax), rows, H, eps, clip_ceiling, _s()))
+
+
+def fp8_rmsnorm_clip_quant_act(ctx, slot, x, scale, normed, rms, rows, H, out8, clip_ceiling, eps=1e-6):
+    """rmsnorm_forward, act_row_clip and fp8_quant_act (src/trainer.cu:6097-6115) as one pass."""
+    check(_L().cf_fp8_rmsnorm_clip_quant_act(ctx.handle, C.byref(slot.c), _p(x), _p(scale), _p(normed), _p(rms), rows, H, eps,
+                                             clip_ceiling, _p(out8), _s()))
 
 
 def swiglu_quantize_e4m3_record(gate, up, out, scale, amax, rows, cols, ld_in, ld_out=None):

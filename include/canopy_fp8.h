@@ -343,6 +343,21 @@ int cf_rmsnorm_quantize_rowwise_e4m3(const void* d_x, const void* d_scale, void*
  * takes an exact amax first. With slot->ticket set a steady-state call is two launches (snapshot, fused pass). */
 int cf_fp8_rmsnorm_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, const void* d_norm_scale, void* d_normed_or_null,
                              float* d_rms_or_null, int rows, int H, float eps, void* d_out8, void* stream);
+/* The same passes with the row clip the reference runs between the norm and the quantiser (act_row_clip in its default
+ * fixed-ceiling mode, src/trainer.cu:3822-3845, 3940-3991: rows of the normalised bf16 tensor whose L2 norm exceeds
+ * clip_ceiling are multiplied by clip_ceiling / norm and rounded to bf16 again; the norm uses the reference kernel's
+ * summation order). One read of x replaces rmsnorm_forward + the clip's norm pass + its conditional rewrite (+ the
+ * quantiser's read). clip_ceiling <= 0: no clip. Needs H % 512 == 0, H <= 8192, 16-byte aligned rows. The statistics
+ * counters of the reference's clip (g_rowclip_stats) are not kept. */
+int cf_rmsnorm_clip_forward(const void* d_x, const void* d_scale, void* d_out, float* d_rms_or_null, int rows, int H, float eps,
+                            float clip_ceiling, void* stream);
+int cf_rmsnorm_clip_quantize_e4m3_record(const void* d_x, const void* d_scale, void* d_normed_or_null, float* d_rms_or_null,
+                                         void* d_out8, const float* d_quant_scale, float* d_amax, int rows, int H, float eps,
+                                         float clip_ceiling, void* stream);
+/* cf_fp8_rmsnorm_quant_act with that clip in between: the sequence of src/trainer.cu:6097-6115 as one pass. */
+int cf_fp8_rmsnorm_clip_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, const void* d_norm_scale,
+                                  void* d_normed_or_null, float* d_rms_or_null, int rows, int H, float eps,
+                                  float clip_ceiling, void* d_out8, void* stream);
 
 /* ------------------------------------------------------------------ elementwise neighbours of the GEMMs */
 

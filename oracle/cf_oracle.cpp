@@ -452,6 +452,39 @@ void orc_rmsnorm_forward(const uint16_t* x, const uint16_t* scale, uint16_t* out
     }
 }
 
+// src/trainer.cu:3822-3845 (k_act_row_normsq), :3940-3962 (k_act_row_clip_apply_abs), :3968-3991 (act_row_clip in its
+// default fixed-ceiling mode): a 256-thread block per row sums v*v for c = t, t+256, ... (fused multiply-add chain),
+// xor-butterfly inside each warp, thread 0 adds the eight warp sums in order; rows whose norm sqrtf(sum) exceeds the
+// ceiling are multiplied by ceiling / norm and rounded to bf16 again. ceiling <= 0 leaves the tensor alone.
+void orc_act_row_clip(uint16_t* x, int64_t rows, int cols, float ceiling, float* normsq_or_null) {
+    if (!(ceiling > 0.0f)) return;
+    for (int64_t r = 0; r < rows; ++r) {
+        uint16_t* xr = x + r * cols;
+        float part[256];
+        for (int t = 0; t < 256; ++t) {
+            float s = 0.0f;
+            for (int c = t; c < cols; c += 256) { const float v = bf16_to_f32(xr[c]); s = std::fmaf(v, v, s); }
+            part[t] = s;
+        }
+        float total = 0.0f;
+        for (int w = 0; w < 8; ++w) {
+            float l[32];
+            for (int i = 0; i < 32; ++i) l[i] = part[w * 32 + i];
+            for (int off = 16; off > 0; off >>= 1) {
+                float n[32];
+                for (int i = 0; i < 32; ++i) n[i] = l[i] + l[i ^ off];
+                std::memcpy(l, n, sizeof(l));
+            }
+            total += l[0];
+        }
+        if (normsq_or_null) normsq_or_null[r] = total;
+        const float norm = std::sqrt(total);
+        if (norm <= ceiling) continue;
+        const float scalef = ceiling / norm;
+        for (int c = 0; c < cols; ++c) xr[c] = f32_to_bf16(bf16_to_f32(xr[c]) * scalef);
+    }
+}
+
 void orc_swiglu_forward(const uint16_t* gate, const uint16_t* up, uint16_t* out, int64_t n) {
     for (int64_t i = 0; i < n; ++i) {
         const float g = bf16_to_f32(gate[i]);

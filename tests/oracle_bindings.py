@@ -177,6 +177,13 @@ class Oracle:
         self.lib.orc_rmsnorm_forward(_ptr(x), _ptr(scale), _ptr(out), _ptr(rms), c_i64(rows), c_i(H), c_f(eps))
         return out, rms
 
+    def act_row_clip(self, x, ceiling):
+        """In place on x (uint16 [rows, cols]); returns the squared row norms the reference's reduction computes."""
+        rows, cols = x.shape
+        nsq = np.zeros(rows, dtype=np.float32)
+        self.lib.orc_act_row_clip(_ptr(x), c_i64(rows), c_i(cols), c_f(ceiling), _ptr(nsq))
+        return nsq
+
     def swiglu_forward(self, gate, up):
         out = np.empty(gate.shape, dtype=np.uint16)
         self.lib.orc_swiglu_forward(_ptr(gate), _ptr(up), _ptr(out), c_i64(gate.size))

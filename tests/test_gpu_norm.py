@@ -116,3 +116,72 @@ def test_rmsnorm_refuses_what_the_reference_cannot_reduce(cfb):
         cfb.rmsnorm_forward(x, g, out, None, 4, 40, 1e-6)       # 40 threads: a partial warp
     with pytest.raises(cfb.CanopyError):
         cfb.rmsnorm_forward(x, g, out, None, 1, 16400, 1e-6)    # beyond the column limit
+
+
+CLIP_SHAPES = [(64, 4096), (300, 512), (40, 1024), (33, 2048), (9, 8192)]
+
+
+@pytest.mark.parametrize("rows,H", CLIP_SHAPES)
+def test_rmsnorm_with_row_clip_matches_the_three_pass_sequence(cfb, oracle, rows, H):
+    """Norm + act_row_clip + record-quantise in one pass against rmsnorm_forward, the host restatement of the clip, and the
+    record-quantise kernel: bf16 rows, rms, E4M3 bytes and amax bit for bit. The ceiling sits inside the range of row
+    norms, so some rows are rescaled and some are left alone; a few rows are made large on purpose."""
+    x, g = _inputs(rows, H, 17)
+    g = (g * 4).contiguous()
+    x[::7] *= 30
+    normed = torch.empty_like(x)
+    rms = torch.empty(rows, dtype=torch.float32, device="cuda")
+    cfb.rmsnorm_forward(x, g, normed, rms, rows, H, 1e-6)
+    n_host = u16(normed).copy()
+    norms = np.sqrt((oracle.bf16_to_f32(n_host).astype(np.float64) ** 2).sum(axis=1))
+    ceiling = float(np.float32(np.median(norms) * 1.0005))
+    oracle.act_row_clip(n_host, ceiling)
+    clipped = np.any(n_host != u16(normed), axis=1)
+    assert clipped.any() and not clipped.all()
+    got = torch.zeros_like(x)
+    got_rms = torch.zeros_like(rms)
+    cfb.rmsnorm_clip_forward(x, g, got, got_rms, rows, H, ceiling)
+    assert torch.equal(got_rms, rms)
+    assert np.array_equal(u16(got), n_host)
+    # ... followed by the quantiser
+    from gpu_util import u16_to_bf16
+    want_n = u16_to_bf16(n_host)
+    scale = f32_scalar(11.0)
+    want8 = torch.empty((rows, H), dtype=torch.uint8, device="cuda")
+    want_amax = f32_scalar(0.0)
+    cfb.fp8_quantize_e4m3_record(want_n, want8, scale, want_amax)
+    got8 = torch.zeros_like(want8)
+    got_amax = f32_scalar(0.0)
+    cfb.rmsnorm_clip_quantize_e4m3_record(x, g, None, None, got8, scale, got_amax, rows, H, ceiling)
+    assert torch.equal(got8, want8) and torch.equal(got_amax, want_amax)
+    # a ceiling nothing reaches (the reference's default of 1000 on normalised rows) changes nothing
+    same = torch.zeros_like(x)
+    cfb.rmsnorm_clip_forward(x, g, same, None, rows, H, 1.0e9)
+    assert torch.equal(same.view(torch.int16), normed.view(torch.int16))
+
+
+def test_rmsnorm_clip_quant_act_and_the_warp_form_without_clip(cfb):
+    """The slot state machine around the clipped pass equals norm -> clip -> fp8_quant_act; with a ceiling of zero the
+    entry point is the plain fused pass."""
+    rows, H = 96, 2048
+    ctx = cfb.Fp8Ctx(0)
+    slot_a, slot_b, slot_c = cfb.ActSlot(ctx, cfb.E4M3_MAX), cfb.ActSlot(ctx, cfb.E4M3_MAX), cfb.ActSlot(ctx, cfb.E4M3_MAX)
+    for step in range(4):
+        x, g = _inputs(rows, H, 70 + step)
+        g = (g * (2 + step)).contiguous()
+        ceiling = 60.0 * (2 + step)
+        clipped = torch.empty_like(x)
+        cfb.rmsnorm_clip_forward(x, g, clipped, None, rows, H, ceiling)
+        want8 = torch.empty((rows, H), dtype=torch.uint8, device="cuda")
+        cfb.fp8_quant_act(ctx, slot_a, clipped, want8)
+        got8 = torch.zeros_like(want8)
+        cfb.fp8_rmsnorm_clip_quant_act(ctx, slot_b, x, g, None, None, rows, H, got8, ceiling)
+        assert torch.equal(got8, want8), step
+        sa, sb = slot_a.scalars(), slot_b.scalars()
+        for k in ("scale", "descale", "scale_snapshot", "descale_snapshot", "cursor", "count"):
+            assert sa[k] == sb[k], (step, k)
+        plain8 = torch.zeros_like(want8)
+        cfb.fp8_rmsnorm_clip_quant_act(ctx, slot_c, x, g, None, None, rows, H, plain8, 0.0)
+    ctx.poll_status()
+    with pytest.raises(cfb.CanopyError):
+        cfb.rmsnorm_clip_forward(x, g, clipped, None, rows, 96, 10.0)       # the clipped pass needs H % 512 == 0

@@ -290,3 +290,24 @@ def test_rmsnorm_restatement(oracle, rows, H):
     o2, r2 = oracle.rmsnorm_forward(c, g, 0.0)
     assert abs(r2[0] - 2.5) < 1e-6
     assert np.all(np.abs(oracle.bf16_to_f32(o2)[0] + oracle.bf16_to_f32(g)) <= np.abs(oracle.bf16_to_f32(g)) * 2.0 ** -7)
+
+
+def test_act_row_clip_restatement(oracle):
+    """src/trainer.cu:3940-3991 (fixed ceiling): rows above the ceiling come out with norm ~ ceiling, rows below are
+    untouched, a non-positive ceiling disables the clip, and the restated reduction agrees with float64 to fp32 rounding."""
+    rng = np.random.default_rng(3)
+    x = oracle.to_bf16((rng.standard_normal((6, 1024)) * np.array([[0.5], [1], [2], [4], [8], [16]])).astype(np.float32))
+    before = x.copy()
+    nsq = oracle.act_row_clip(x, 70.0)
+    ref = (oracle.bf16_to_f32(before).astype(np.float64) ** 2).sum(axis=1)
+    assert np.allclose(nsq, ref, rtol=1e-5)
+    norms = np.sqrt(ref)
+    for r in range(6):
+        if norms[r] <= 70.0:
+            assert np.array_equal(x[r], before[r])
+        else:
+            after = np.sqrt((oracle.bf16_to_f32(x[r]).astype(np.float64) ** 2).sum())
+            assert abs(after - 70.0) < 0.5 and not np.array_equal(x[r], before[r])
+    y = before.copy()
+    oracle.act_row_clip(y, 0.0)
+    assert np.array_equal(y, before)

@@ -261,7 +261,9 @@ int cf_fp8_swiglu_quant_act(cf_ctx* ctx, cf_act_slot* slot, const void* d_gate, 
  * d_h8 is E4M3 [rows, F] with row pitch ldh bytes (16-byte aligned). Dense form: d_counts = d_offsets = NULL,
  * num_segments = 1, max_total_rows = M. Segment form: as cf_gemm_fp8_nt_segments. per_segment_a_descale: 0 = one
  * descale, 1 = d_a_descale[segment], 2 = d_a_descale[row] (one float per row of A). The first call on a fresh slot
- * runs the GEMM twice (exact amax first). */
+ * runs the GEMM twice (exact amax first). The reference's row clip of the SwiGLU output (act_row_clip,
+ * src/trainer.cu:7138, L2 norm of a whole row against a fixed ceiling, 1000 by default) is NOT applied: a row norm
+ * spans every column tile; results equal the reference's whenever no row exceeds that ceiling. */
 int cf_gemm_fp8_swiglu_quant_act(cf_ctx* ctx, cf_act_slot* slot, int num_segments, int num_weights,
                                  const int* d_segment_weight, int max_total_rows, int F, int K, const int* d_counts,
                                  const int* d_offsets, const void* d_A, int lda, int a_is_e5m2, const float* d_a_descale,

@@ -9,7 +9,8 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "libcanopy_fp8.so")
 
-CF_OK, CF_ERR_INVALID_ARG, CF_ERR_UNSUPPORTED, CF_ERR_CUDA, CF_ERR_DEVICE_WAIT, CF_ERR_LIMIT = range(6)
+CF_OK, CF_ERR_INVALID_ARG, CF_ERR_UNSUPPORTED, CF_ERR_CUDA, CF_ERR_DEVICE_WAIT, CF_ERR_LIMIT, CF_ERR_DEVICE_RANGE = range(7)
+ABI_VERSION = 3        # cf_abi_version() of the library this table was written for
 E4M3_MAX = 448.0
 E5M2_MAX = 57344.0
 
@@ -108,8 +109,8 @@ SIGNATURES = {
     "cf_moe_combine_all_bf16": (ci, [vp, vp, fp, ip, ip, ip, ci, ci, ci, vp]),
     "cf_moe_combine_sorted_bf16": (ci, [vp, vp, fp, ip, ip, ip, ci, ci, ci, ci, vp]),
     "cf_moe_expand_route_replicas": (ci, [fp, fp, ci, ci, ci, ip, fp, C.c_uint, vp]),
-    "cf_moe_ep_plan": (ci, [ip, ci, ci, ci, ip, ip, vp, ip, ip, vp, vp]),
-    "cf_moe_send_row_runs": (ci, [vp, ip, C.c_longlong, vp, ci, ci, vp, C.c_longlong, fp, vp, vp]),
+    "cf_moe_ep_plan": (ci, [ip, ci, ci, ci, ip, ip, vp, ip, ip, vp, C.c_longlong, vp, vp]),
+    "cf_moe_send_row_runs": (ci, [vp, ip, C.c_longlong, vp, ci, ci, vp, C.c_longlong, fp, vp, ci, C.c_longlong, vp, vp]),
     "cf_gemm_fp8_nt_grouped_return": (ci, [vp, ci, ci, ci, ci, ip, ip, vp, ci, ci, fp, vp, fp, vp, ci, C.POINTER(vp), ci, ci, ci, vp]),
     "cf_moe_grouped_expert_forward_fp8": (ci, [vp, vp, fp, ci, fp, ip, ip, ip, vp, fp, vp, fp, vp, ci, ci, ci, ci, ci, vp]),
 }
@@ -130,6 +131,9 @@ def load():
             f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
             "or `make -C canopy-foundry_b200/csrc`. There is no fallback path.")
     lib = C.CDLL(LIB_PATH)
+    lib.cf_abi_version.restype = ci
+    if lib.cf_abi_version() != ABI_VERSION:
+        raise ImportError(f"{LIB_PATH} has ABI version {lib.cf_abi_version()}, this binding expects {ABI_VERSION}: rebuild it")
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)      # AttributeError here means the header and the library disagree
         fn.restype = res

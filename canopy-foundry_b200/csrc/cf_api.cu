@@ -116,7 +116,7 @@ using namespace cf;
 extern "C" {
 
 const char* cf_last_error(void) { return t_error; }
-int cf_abi_version(void) { return 2; }
+int cf_abi_version(void) { return 3; }
 uint64_t cf_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int cf_ctx_create(cf_ctx** out, size_t act8_bytes) {
@@ -180,6 +180,11 @@ int cf_ctx_poll_status(cf_ctx* ctx, void* stream) {
     CF_CUDA(cudaStreamSynchronize(as_stream(stream)));
     if (h != 0) {
         CF_CUDA(cudaMemsetAsync(c->d_status, 0, sizeof(int), as_stream(stream)));
+        if (((h >> 8) & 0xf) == 5) {
+            set_error("a planned run of rows left its destination buffer and was not stored (status 0x%x: %s)", h,
+                      (h & 0xff) == 2 ? "receive capacity exceeded in the plan" : "run refused by the sender");
+            return CF_ERR_DEVICE_RANGE;
+        }
         set_error("a tensor-core kernel abandoned a bounded wait (status 0x%x): role %d", h, (h >> 8) & 0xf);
         return CF_ERR_DEVICE_WAIT;
     }

@@ -16,7 +16,6 @@
 // frees TMEM and returns, so a faulty launch cannot hang the GPU.
 #include <cuda.h>
 
-#include <cstdlib>
 #include <mutex>
 
 #include "cf_common.cuh"
@@ -394,26 +393,15 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(empty_bar + 8 * s, ph ^ 1, s_abort)) { ok = false; break; }
-#ifdef CF_GEMM_EXPERIMENT
-                    if ((p.experiment & 1) && it >= STAGES) {      // no operand traffic after the first ring fill
-                        if (leader) mbar_arrive(full_bar + 8 * s);
-                        continue;
-                    }
-#endif
                     if (PAIR) {
-                        bool load_a = true, load_b = true;
-#ifdef CF_GEMM_EXPERIMENT
-                        if ((p.experiment & 8) && it >= STAGES) load_b = false;    // stale B after the first ring fill
-                        if ((p.experiment & 16) && it >= STAGES) load_a = false;   // stale A after the first ring fill
-#endif
-                        if (leader) mbar_expect_tx(full_bar + 8 * s, 2 * ((load_a ? A_STAGE : 0) + (load_b ? B_STAGE : 0)));
+                        if (leader) mbar_expect_tx(full_bar + 8 * s, 2 * (A_STAGE + B_STAGE));
                         // K-major operands: x runs along K; MN-major operands ([K, M] / [K, N] in memory): x runs
                         // along M / N and the box rows are K
                         const bool mn = WIDE && p.mn_major;
                         const int ax = mn ? a_row : kb * BK, ay = mn ? kb * BK : a_row;
                         const int bx = mn ? b_row : kb * BK, by = mn ? kb * BK : b_row;
-                        if (load_a) tma_load_2d_pair(smem_a + s * A_STAGE, &map_a, full_dst + 8 * s, ax, ay);
-                        if (load_b) tma_load_2d_pair(smem_b + s * B_STAGE, &map_b, full_dst + 8 * s, bx, by);
+                        tma_load_2d_pair(smem_a + s * A_STAGE, &map_a, full_dst + 8 * s, ax, ay);
+                        tma_load_2d_pair(smem_b + s * B_STAGE, &map_b, full_dst + 8 * s, bx, by);
                     } else {
                         mbar_expect_tx(full_bar + 8 * s, A_STAGE + B_STAGE);
                         tma_load_2d(smem_a + s * A_STAGE, &map_a, full_bar + 8 * s, kb * BK, a_row);
@@ -702,16 +690,10 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 for (int ch = col_half * 4; ch < col_half * 4 + 4; ++ch) {
                     const int col0 = tc.n0 + ch * 32;
                     if (col0 >= p.N) break;                    // warp-uniform
-    #ifdef CF_GEMM_EXPERIMENT
-                    if (p.experiment & 2) break;               // no accumulator read-out, no stores
-    #endif
                     uint32_t v[32];
                     tmem_ld32(taddr + ch * 32, v);
                     tmem_ld_wait();
                     if (!row_ok) continue;
-    #ifdef CF_GEMM_EXPERIMENT
-                    if (p.experiment & 4) continue;            // accumulator read-out but no stores
-    #endif
                     const bool full = col0 + 32 <= p.N;
                     if (p.out_kind == 0 && p.c_vec && full) {
                         uint16_t* crow = static_cast<uint16_t*>(out_base_l) + grow_l * p.ldc + col0;
@@ -963,10 +945,6 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     // 4096: little output traffic, B re-streamed once per band) measured 2-6 % faster with twice the band height; the
     // bf16-output GEMM of the same shape measured 7 % slower with it and keeps eight.
     if (p.out_kind == 4 && static_cast<long long>(p.N) * p.K > (64ll << 20) && p.K <= 4096) p.raster_m = 16;
-#ifdef CF_GEMM_EXPERIMENT
-    { const char* e = std::getenv("CF_GEMM_EXPERIMENT"); p.experiment = e ? std::atoi(e) : 0; }
-    { const char* e = std::getenv("CF_GEMM_RASTER"); if (e && std::atoi(e) > 0) p.raster_m = std::atoi(e); }
-#endif
     if (p.peer_out_host != nullptr && !tma_ok) {
         set_error("reduce-scatter GEMM: operands must be 16-byte aligned with K %% 16 == 0");
         return CF_ERR_UNSUPPORTED;
@@ -978,10 +956,9 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
         return CF_OK;
     }
     // Paired CTAs (256-row tiles) pay off when the row blocks are mostly full; small or very ragged problems
-    // keep the 128-row single-CTA tiles. CF_GEMM_TILE=1|2 forces a form (A/B measurements, tests).
-    static const int forced = [] { const char* e = std::getenv("CF_GEMM_TILE"); return e ? std::atoi(e) : 0; }();
+    // keep the 128-row single-CTA tiles.
     const long long rows_per_group = (p.d_counts ? a_rows / (p.groups > 0 ? p.groups : 1) : p.M);
-    bool pair = forced == 2 || p.mn_major || (forced != 1 && rows_per_group >= 512);
+    bool pair = p.mn_major || rows_per_group >= 512;
     const int pairs = pair ? max_resident_pairs() : 0;
     if (pairs <= 0) pair = false;
 
@@ -1005,8 +982,6 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     p.tma_store = (p.c_vec && p.out_kind == 0 && p.d_group_out == nullptr && p.N >= C_BOX_COLS &&
                    (p.bias == nullptr || reinterpret_cast<uintptr_t>(p.bias) % 16 == 0) &&
                    (p.d_b_col_descale == nullptr || reinterpret_cast<uintptr_t>(p.d_b_col_descale) % 16 == 0)) ? 1 : 0;
-    static const bool no_tma_store = [] { const char* e = std::getenv("CF_GEMM_DIRECT_STORE"); return e && e[0] == '1'; }();
-    if (no_tma_store) p.tma_store = 0;
     const bool return_form = p.d_out_runs != nullptr;
     if (return_form) {
         // grouped bf16 output whose runs of rows go to per-run destination buffers
@@ -1059,9 +1034,9 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
         p.d_peer_maps = nullptr;
     }
     const bool f32_tma = (p.out_kind == 2 || p.out_kind == 1) && ca % 16 == 0 && p.ldc % 4 == 0 && p.N >= 32 &&
-                         p.d_group_out == nullptr && p.d_a_row_descale == nullptr && p.d_b_col_descale == nullptr && !no_tma_store;
+                         p.d_group_out == nullptr && p.d_a_row_descale == nullptr && p.d_b_col_descale == nullptr;
     p.tma_reduce = return_form ? 0 : p.d_peer_maps ? 1 : (f32_tma ? (p.out_kind == 2 ? 1 : 2) : 0);
-    if (return_form) p.tma_store = no_tma_store ? 0 : 1;
+    if (return_form) p.tma_store = 1;
     if (p.d_peer_maps) {
         map_c = map_a;   // the kernel takes its output maps from d_peer_maps
     } else if (p.tma_store) {

@@ -53,7 +53,6 @@ struct GemmParams {
     int b_e5m2 = 0;
     int* d_status = nullptr;        // context status word (bounded-wait failures)
     int raster_m = 8;               // row blocks per rasterisation band
-    int experiment = 0;             // measurement builds only (-DCF_GEMM_EXPERIMENT): 1 no operand loads, 2 no epilogue, 4 no stores
 };
 
 // a_rows / b_rows: row extents of the two byte matrices as the tensor maps should see them.

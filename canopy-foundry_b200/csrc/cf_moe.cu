@@ -394,7 +394,8 @@ __global__ void __launch_bounds__(kT) k_expand_route(const float* __restrict__ r
 // results return to (the source's compact order: replica after replica).
 __global__ void k_ep_plan(const int* __restrict__ counts_all, int world, int me, int V, const int* __restrict__ lo,
                           const int* __restrict__ hi, cf_row_run* __restrict__ send_runs, int* __restrict__ grp_counts,
-                          int* __restrict__ grp_offsets, cf_row_run* __restrict__ ret_runs) {
+                          int* __restrict__ grp_offsets, cf_row_run* __restrict__ ret_runs, long long capacity,
+                          int* __restrict__ status) {
     const int v = blockIdx.x * blockDim.x + threadIdx.x;
     if (v >= V) return;
     int owner = 0;
@@ -419,8 +420,14 @@ __global__ void k_ep_plan(const int* __restrict__ counts_all, int world, int me,
         ret_runs[vl * world + s] = q;
         pre += c;
     }
+    // A group that would run past the receive buffer (a count table no sender could have produced honestly) is cut
+    // to what fits and reported; the senders skip the same rows (k_send_rows checks every run against the capacity).
+    if (capacity > 0 && base + pre > capacity) {
+        pre = base < capacity ? capacity - base : 0;
+        if (status) atomicExch(status, 0x500 | 2);
+    }
     grp_counts[vl] = static_cast<int>(pre);
-    grp_offsets[vl] = static_cast<int>(base);
+    grp_offsets[vl] = static_cast<int>(base < capacity || capacity <= 0 ? base : 0);
 }
 
 // Copies runs of rows to per-run destinations that may live on peer GPUs (plain 16-byte stores, whole rows contiguous).
@@ -429,9 +436,16 @@ __global__ void k_ep_plan(const int* __restrict__ counts_all, int world, int me,
 __global__ void __launch_bounds__(kT) k_send_rows(const uint8_t* __restrict__ src, const int* __restrict__ row_indices,
                                                   long long idx_stride, const cf_row_run* __restrict__ runs,
                                                   void* const* __restrict__ dst_bases, long long width_bytes,
-                                                  const float* __restrict__ tag_value, float* const* __restrict__ tag_bases) {
+                                                  const float* __restrict__ tag_value, float* const* __restrict__ tag_bases,
+                                                  int num_dst, long long dst_rows, int* __restrict__ status) {
     const cf_row_run run = runs[blockIdx.y];
     if (run.rows <= 0) return;
+    // The destinations may be other GPUs' memory: a run that names no destination or leaves the destination's rows is
+    // not stored at all (nothing faults) and leaves a code in the status word.
+    if (run.dst < 0 || run.dst >= num_dst || run.dst_row < 0 || run.dst_row + run.rows > dst_rows) {
+        if (status && blockIdx.x == 0 && threadIdx.x == 0) atomicExch(status, 0x500 | 1);
+        return;
+    }
     uint8_t* dst = static_cast<uint8_t*>(dst_bases[run.dst]) + run.dst_row * width_bytes;
     const int* idx = row_indices ? row_indices + blockIdx.y * idx_stride : nullptr;
     const long long cpr = width_bytes / 16;
@@ -675,20 +689,25 @@ int cf_moe_expand_route_replicas(const float* d_route_weights, float* d_replica_
 }
 
 int cf_moe_ep_plan(const int* d_counts_all, int world, int rank, int num_replicas, const int* d_range_lo, const int* d_range_hi,
-                   cf_row_run* d_send_runs, int* d_group_counts, int* d_group_offsets, cf_row_run* d_return_runs, void* stream) {
+                   cf_row_run* d_send_runs, int* d_group_counts, int* d_group_offsets, cf_row_run* d_return_runs,
+                   long long recv_capacity_rows, cf_ctx* ctx_or_null, void* stream) {
+    CF_REQUIRE(recv_capacity_rows >= 0, "cf_moe_ep_plan: negative capacity");
     CF_REQUIRE(world >= 1 && rank >= 0 && rank < world && num_replicas >= 1, "cf_moe_ep_plan: bad shape");
     CF_REQUIRE(d_counts_all && d_range_lo && d_range_hi && d_send_runs && d_group_counts && d_group_offsets && d_return_runs,
                "cf_moe_ep_plan: null pointer");
     k_ep_plan<<<(num_replicas + 63) / 64, 64, 0, as_stream(stream)>>>(d_counts_all, world, rank, num_replicas, d_range_lo,
                                                                       d_range_hi, d_send_runs, d_group_counts, d_group_offsets,
-                                                                      d_return_runs);
+                                                                      d_return_runs, recv_capacity_rows,
+                                                                      ctx_or_null ? ctx_status(ctx_or_null) : nullptr);
     CF_LAUNCH_CHECK("moe_ep_plan");
     return CF_OK;
 }
 
 int cf_moe_send_row_runs(const void* d_src, const int* d_row_indices_or_null, long long index_stride, const cf_row_run* d_runs,
                          int num_runs, int max_rows_per_run, void* const* d_dst_bases, long long row_bytes,
-                         const float* d_tag_value_or_null, float* const* d_tag_bases_or_null, void* stream) {
+                         const float* d_tag_value_or_null, float* const* d_tag_bases_or_null, int num_dst, long long dst_rows,
+                         cf_ctx* ctx_or_null, void* stream) {
+    CF_REQUIRE(num_dst >= 1 && dst_rows >= 0, "cf_moe_send_row_runs: needs the number of destination buffers and their row capacity");
     CF_REQUIRE(num_runs >= 0 && max_rows_per_run >= 0 && row_bytes > 0 && row_bytes % 16 == 0,
                "cf_moe_send_row_runs: rows must be whole 16-byte units");
     if (num_runs == 0 || max_rows_per_run == 0) return CF_OK;
@@ -701,7 +720,8 @@ int cf_moe_send_row_runs(const void* d_src, const int* d_row_indices_or_null, lo
     if (gx > cap) gx = cap;
     dim3 grid(gx, num_runs);
     k_send_rows<<<grid, kT, 0, as_stream(stream)>>>(static_cast<const uint8_t*>(d_src), d_row_indices_or_null, index_stride, d_runs,
-                                                    d_dst_bases, row_bytes, d_tag_value_or_null, d_tag_bases_or_null);
+                                                    d_dst_bases, row_bytes, d_tag_value_or_null, d_tag_bases_or_null, num_dst,
+                                                    dst_rows, ctx_or_null ? ctx_status(ctx_or_null) : nullptr);
     CF_LAUNCH_CHECK("moe_send_row_runs");
     return CF_OK;
 }

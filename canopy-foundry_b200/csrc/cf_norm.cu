@@ -12,7 +12,6 @@
 // out = bf16((x * (1 / rms)) * scale[h]). What differs is the data movement: 16-byte loads fill a shared-memory copy
 // of the row, each thread picks its strided elements from there, and results return to HBM as 16-byte stores.
 #include "cf_common.cuh"
-#include <cstdlib>
 
 #include "cf_internal.cuh"
 
@@ -385,7 +384,9 @@ __global__ void __launch_bounds__(kWarpRowThreads) k_rmsnorm_warp(const uint16_t
 #pragma unroll
             for (int w = 0; w < 8; ++w) t = __fadd_rn(t, __shfl_sync(0xffffffffu, cw, 4 * w));   // thread 0 adds the warps in order
             const float norm = sqrtf(t);
-            if (norm > clip_ceiling) {                     // warp-uniform
+            // the reference's test is `if (norm <= ceiling) return;` (src/trainer.cu:3952): a NaN norm falls through
+            // to the rescale and turns the whole row into NaN
+            if (!(norm <= clip_ceiling)) {                 // warp-uniform
                 const float scalef = __fdiv_rn(clip_ceiling, norm);
 #pragma unroll
                 for (int i = 0; i < NV; ++i) {
@@ -473,6 +474,37 @@ int launch_warp_nv(int nv, const uint16_t* x, const uint16_t* g, uint16_t* o, fl
     return launch_warp<MODE, 32, CLIP>(x, g, o, rms, q, scale, amax, row_scale, row_descale, rows, H, eps, ceiling, tail, st);
 }
 
+// act_row_clip for the shapes the warp kernel above does not take (src/trainer.cu:3940-3991, fixed-ceiling mode): one
+// block of 256 threads per row of the normalised bf16 tensor, thread t adds x[c]^2 for c = t, t+256, ... with fused
+// multiply-adds, xor butterfly inside each warp, thread 0 adds the eight warp sums in order, then the conditional
+// rescale. The reference splits this over two kernels with the squared norm in a scratch array; here the row norm
+// stays in shared memory.
+__global__ void __launch_bounds__(256) k_row_clip(uint16_t* __restrict__ x, int cols, float ceiling) {
+    __shared__ float s_w[8];
+    __shared__ float s_norm;
+    uint16_t* xr = x + static_cast<long long>(blockIdx.x) * cols;
+    float s = 0.0f;
+    for (int c = threadIdx.x; c < cols; c += 256) {
+        const float v = bf16_bits_to_f32(xr[c]);
+        s = fmaf(v, v, s);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, off));
+    if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.0f;
+        for (int w = 0; w < 8; ++w) t = __fadd_rn(t, s_w[w]);
+        s_norm = sqrtf(t);
+    }
+    __syncthreads();
+    const float norm = s_norm;
+    if (norm <= ceiling) return;
+    const float scalef = __fdiv_rn(ceiling, norm);
+    for (int c = threadIdx.x; c < cols; c += 256)
+        xr[c] = __bfloat16_as_ushort(__float2bfloat16_rn(__fmul_rn(bf16_bits_to_f32(xr[c]), scalef)));
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace
@@ -507,20 +539,36 @@ int rmsnorm_launch(int mode, const void* d_x, const void* d_gamma, void* d_norme
                       (d_normed_or_null == nullptr || aligned16(d_normed_or_null)) &&
                       (mode == 0 || (reinterpret_cast<uintptr_t>(d_out8) & 7) == 0);
     if (clip_ceiling > 0.0f && !(fast && H <= 8192)) {
-        set_error("rmsnorm with row clip: needs 16-byte aligned rows of a multiple of 512 and at most 8192 columns (got %d)", H);
-        return CF_ERR_UNSUPPORTED;
+        // Shapes the one-pass warp kernel does not take run the reference's own sequence: norm into the bf16 row buffer,
+        // the row clip in place, then the quantiser over the clipped rows.
+        if (d_normed_or_null == nullptr) {
+            set_error("rmsnorm with row clip: for H = %d (not a multiple of 512, above 8192, or unaligned rows) the bf16 row buffer is needed", H);
+            return CF_ERR_UNSUPPORTED;
+        }
+        int r = rmsnorm_launch(0, d_x, d_gamma, d_normed_or_null, d_rms_or_null, nullptr, nullptr, nullptr, nullptr, nullptr,
+                               rows, H, eps, RingTail(), st, 0.0f);
+        if (r != CF_OK) return r;
+        k_row_clip<<<rows, 256, 0, st>>>(o, H, clip_ceiling);
+        CF_LAUNCH_CHECK("row_clip");
+        if (mode == 1) {
+            r = cf_fp8_quantize_e4m3_record(d_normed_or_null, d_out8, d_scale, d_amax, static_cast<size_t>(rows) * H, st);
+            if (r != CF_OK) return r;
+            if (tail.ticket != nullptr)
+                r = cf_fp8_update_delayed_scale(d_amax, tail.fp8_max, tail.scale, tail.descale, tail.history, tail.history_len,
+                                                tail.history_cursor, tail.history_count, st);
+            return r;
+        }
+        if (mode == 2)
+            return cf_fp8_quantize_rowwise_e4m3(d_normed_or_null, H, d_out8, H, d_row_scale, d_row_descale, rows, H, st);
+        return CF_OK;
     }
-    static const int warp_form = [] { const char* e = std::getenv("CF_NORM_WARP"); return e ? std::atoi(e) : 0; }();
-    if (fast && H <= 8192 && (clip_ceiling > 0.0f || warp_form)) {
+    if (fast && H <= 8192 && clip_ceiling > 0.0f) {
         const int nv = H / 256;
         if (clip_ceiling > 0.0f) {
             if (mode == 0) return launch_warp_nv<0, true>(nv, x, g, o, d_rms_or_null, q, d_scale, d_amax, d_row_scale, d_row_descale, rows, H, eps, clip_ceiling, tail, st);
             if (mode == 1) return launch_warp_nv<1, true>(nv, x, g, o, d_rms_or_null, q, d_scale, d_amax, d_row_scale, d_row_descale, rows, H, eps, clip_ceiling, tail, st);
             return launch_warp_nv<2, true>(nv, x, g, o, d_rms_or_null, q, d_scale, d_amax, d_row_scale, d_row_descale, rows, H, eps, clip_ceiling, tail, st);
         }
-        if (mode == 0) return launch_warp_nv<0, false>(nv, x, g, o, d_rms_or_null, q, d_scale, d_amax, d_row_scale, d_row_descale, rows, H, eps, 0.0f, tail, st);
-        if (mode == 1) return launch_warp_nv<1, false>(nv, x, g, o, d_rms_or_null, q, d_scale, d_amax, d_row_scale, d_row_descale, rows, H, eps, 0.0f, tail, st);
-        return launch_warp_nv<2, false>(nv, x, g, o, d_rms_or_null, q, d_scale, d_amax, d_row_scale, d_row_descale, rows, H, eps, 0.0f, tail, st);
     }
     if (fast) {
         const int nv = H / 512;

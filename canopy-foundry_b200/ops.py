@@ -457,18 +457,21 @@ ROW_RUN_BYTES = 24      # sizeof(cf_row_run): two int64 and two int32
 
 
 def moe_ep_plan(counts_all, world, rank, num_replicas, range_lo, range_hi, send_runs, group_counts, group_offsets,
-                return_runs):
+                return_runs, recv_capacity_rows=0, ctx=None):
     """Device-side plan of one expert-parallel layer from the gathered count table (no host copy)."""
     check(_L().cf_moe_ep_plan(_p(counts_all), world, rank, num_replicas, _p(range_lo), _p(range_hi), _p(send_runs),
-                              _p(group_counts), _p(group_offsets), _p(return_runs), _s()))
+                              _p(group_counts), _p(group_offsets), _p(return_runs), int(recv_capacity_rows),
+                              ctx.handle if ctx is not None else None, _s()))
 
 
 def moe_send_row_runs(src, row_indices, index_stride, runs, num_runs, max_rows_per_run, dst_bases, row_bytes,
-                      tag_value=None, tag_bases=None):
+                      num_dst, dst_rows, tag_value=None, tag_bases=None, ctx=None):
     """Copies planned runs of rows into (peer) destination buffers; optional gather through an index table and a
-    per-row float tag. dst_bases / tag_bases: int64 device tensors of base addresses."""
+    per-row float tag. dst_bases / tag_bases: int64 device tensors of num_dst base addresses of dst_rows rows each; a
+    run that leaves its destination is skipped and reported through ctx.poll_status()."""
     check(_L().cf_moe_send_row_runs(_p(src), _p(row_indices), index_stride, _p(runs), num_runs, max_rows_per_run,
-                                    _p(dst_bases), row_bytes, _p(tag_value), _p(tag_bases), _s()))
+                                    _p(dst_bases), row_bytes, _p(tag_value), _p(tag_bases), int(num_dst), int(dst_rows),
+                                    ctx.handle if ctx is not None else None, _s()))
 
 
 def gemm_fp8_nt_grouped_return(ctx, num_groups, max_total_rows, N, K, counts, offsets, A, lda, a_is_e5m2, a_descale, B,
@@ -490,10 +493,10 @@ def moe_grouped_expert_forward_fp8(ctx, hidden, fcin_descale, fcin_is_e5m2, rout
                                                  _p(mixed), rows, H, Ie, num_experts, total_selected_rows, _s()))
 
 
-# ---------------------------------------------------------------- composites for BASELINE configurations 3 and 4
+# ---------------------------------------------------------------- composites: SwiGLU MLP (per-token scales) and MoE SwiGLU experts
 def swiglu_mlp_fp8_rowwise(ctx, x, w_gateup8, w_gateup_descale, w_down8, w_down_descale, y, work=None):
     """Llama-style SwiGLU MLP in FP8 with per-token activation scales and per-output-channel weight scales
-    (configuration 3; the reference has per-tensor scales only, so this follows the documented generalisation
+    (the reference has per-tensor scales only, so this follows the documented generalisation
     C[m,n] = dA[m] * dW[n] * acc):
         x8, dx   = rowwise_quant(x)                      [M,H]
         gu       = x8 . w_gateup8^T  (scales dx, dWgu)   [M,2F]  gate = gu[:, :F], up = gu[:, F:]
@@ -522,7 +525,7 @@ def swiglu_mlp_fp8_rowwise(ctx, x, w_gateup8, w_gateup_descale, w_down8, w_down_
 
 
 class MoeSwigluFp8:
-    """Top-k routed SwiGLU experts in FP8 (configuration 4): route -> dispatch lists -> per-tensor delayed-scale
+    """Top-k routed SwiGLU experts in FP8: route -> dispatch lists -> per-tensor delayed-scale
     quantise of x -> permute -> ragged gate/up GEMM -> SwiGLU + delayed-scale re-quantise -> ragged down GEMM ->
     unpermute + weighted combine. Everything is scheduled on the device (no host copy of the counts); the
     rounding points are those of the reference's SwiGLU expert maths (src/trainer.cu:6510-6529) combined with its

@@ -518,10 +518,10 @@ class EpMoeSwigluFp8Direct:
         if gathered is not None:
             gathered.wait()
         cfb.moe_ep_plan(self.counts_all, W, self.rank, V, self.range_lo, self.range_hi, self.send_runs, self.grp_counts,
-                        self.grp_offsets, self.ret_runs)
+                        self.grp_offsets, self.ret_runs, recv_capacity_rows=self.cap, ctx=ctx)
         # permute + dispatch in one pass; every row carries the descale of the rank that quantised it
-        cfb.moe_send_row_runs(self.x8, self.idx, rows, self.send_runs, V, rows, self.peer_recv8, H,
-                              tag_value=cfb.ops._DevPtr(self.slot_x.c.descale_snapshot), tag_bases=self.peer_recv_dx)
+        cfb.moe_send_row_runs(self.x8, self.idx, rows, self.send_runs, V, rows, self.peer_recv8, H, W, self.cap,
+                              tag_value=cfb.ops._DevPtr(self.slot_x.c.descale_snapshot), tag_bases=self.peer_recv_dx, ctx=ctx)
         self._barrier()          # every rank's rows have arrived
         cfb.gemm_fp8_swiglu_quant_act(ctx, self.slot_h, self.n_local, self.n_local, None, self.cap, F, H, self.grp_counts,
                                       self.grp_offsets, self.recv8, H, False, self.recv_dx, 2, w_gateup8_local,
@@ -534,7 +534,8 @@ class EpMoeSwigluFp8Direct:
             cfb.gemm_fp8_nt_grouped(ctx, self.n_local, self.cap, H, F, self.grp_counts, self.grp_offsets, self.h8, F, False,
                                     cfb.ops._DevPtr(self.slot_h.c.descale_snapshot), False, w_down8_local, w_down_descale,
                                     self.yc, H)
-            cfb.moe_send_row_runs(self.yc, None, 0, self.ret_runs, self.n_local * W, rows, self.peer_back, 2 * H)
+            cfb.moe_send_row_runs(self.yc, None, 0, self.ret_runs, self.n_local * W, rows, self.peer_back, 2 * H, W, self.T,
+                                  ctx=ctx)
         self._barrier()          # every rank's results are back
         cfb.moe_combine_sorted_bf16(mixed, self.back, self.rwv, self.idx, self.counts, self.offsets, rows, V, H, accumulate)
 

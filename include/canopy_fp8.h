@@ -34,7 +34,9 @@ enum {
     CF_ERR_UNSUPPORTED = 2,   /* shape or device this build cannot serve */
     CF_ERR_CUDA = 3,          /* a CUDA runtime / driver call failed; see cf_last_error() */
     CF_ERR_DEVICE_WAIT = 4,   /* a bounded device-side wait gave up (reported by cf_ctx_poll_status) */
-    CF_ERR_LIMIT = 5          /* size beyond a documented fixed limit */
+    CF_ERR_LIMIT = 5,         /* size beyond a documented fixed limit */
+    CF_ERR_DEVICE_RANGE = 6   /* a device-side plan pointed outside a destination buffer; the store was skipped
+                                 (reported by cf_ctx_poll_status) */
 };
 
 #define CF_E4M3_MAX 448.0f     /* src/trainer.cu:3179 */
@@ -110,8 +112,9 @@ int cf_ctx_create(cf_ctx** out, size_t act8_bytes);
 int cf_ctx_destroy(cf_ctx* ctx);
 /* Device pointer of the shared quantised-activation scratch (Fp8Ctx::act8, src/trainer.cu:3339-3340). */
 void* cf_ctx_act8(cf_ctx* ctx);
-/* Synchronises `stream`, then returns CF_OK or CF_ERR_DEVICE_WAIT if any kernel launched through this
- * context since the last poll abandoned a bounded wait (its output is then invalid). Clears the word. */
+/* Synchronises `stream`, then returns CF_OK, CF_ERR_DEVICE_WAIT if any kernel launched through this context since
+ * the last poll abandoned a bounded wait, or CF_ERR_DEVICE_RANGE if a planned run of rows was refused because it
+ * left its destination buffer (the output is invalid in both cases). Clears the word. */
 int cf_ctx_poll_status(cf_ctx* ctx, void* stream);
 /* Failure-detection self-test (no counterpart in the reference): launches one small kernel whose only wait is on a
  * barrier nothing ever signals; the wait gives up after limit_ms (1..1000), the kernel records a status code and
@@ -370,7 +373,7 @@ int cf_swiglu_forward(const void* d_gate, const void* d_up, void* d_out, int n, 
 /* kernels/moe.cu:519-521, kernels.hpp:334.  exact-erf GELU. */
 int cf_gelu_forward(const void* d_x, void* d_out, size_t n, void* stream);
 
-/* Per-token (row-wise) scaling — BASELINE configuration 3's granularity; the reference scales per tensor only, so
+/* Per-token (row-wise) scaling (the granularity of the per-token / per-channel SwiGLU MLP); the reference scales per tensor only, so
  * these generalise kernels/fp8.cu:34-49 per row: a_r = max(amax_r, 1e-12), scale_r = 448/a_r, descale_r = a_r/448,
  * out[r,c] = e4m3(x[r,c] * scale_r). d_row_scale may be NULL. At most 16384 columns. The GEMM consumes d_row_descale
  * through cf_gemm_epilogue.d_a_row_descale. */
@@ -452,18 +455,24 @@ typedef struct cf_row_run {
  *   d_send_runs[num_replicas]          where this rank's rows for each replica land (dst = serving rank)
  *   d_group_counts/offsets[n_local]    the ragged groups this rank serves (n_local = its range length)
  *   d_return_runs[n_local * world]     where each (replica, source) block of results returns to (dst = source rank,
- *                                      dst_row = that replica's offset in the source's own compact order) */
+ *                                      dst_row = that replica's offset in the source's own compact order)
+ * recv_capacity_rows (> 0): rows of this rank's receive buffer; a group that would run past it is cut to what fits and a
+ * code is left in ctx_or_null's status word (CF_ERR_DEVICE_RANGE at the next poll). 0 = unchecked. */
 int cf_moe_ep_plan(const int* d_counts_all, int world, int rank, int num_replicas, const int* d_range_lo, const int* d_range_hi,
-                   cf_row_run* d_send_runs, int* d_group_counts, int* d_group_offsets, cf_row_run* d_return_runs, void* stream);
+                   cf_row_run* d_send_runs, int* d_group_counts, int* d_group_offsets, cf_row_run* d_return_runs,
+                   long long recv_capacity_rows, cf_ctx* ctx_or_null, void* stream);
 /* Copies the runs of a device plan: whole rows of row_bytes (a multiple of 16) from d_src to
  * d_dst_bases[run.dst] + run.dst_row * row_bytes; the destinations may be peer GPUs' buffers mapped into this process
  * (plain stores over NVLink). With an index table the i-th row of run r is row d_row_indices[r * index_stride + i] of
  * d_src (permute and send in one pass). With a tag, *d_tag_value is also stored at d_tag_bases[run.dst][run.dst_row + i]
  * for every row (the sender's activation descale travelling with its rows). d_dst_bases / d_tag_bases are DEVICE arrays
- * of base pointers; max_rows_per_run only sizes the grid. */
+ * of num_dst base pointers, each buffer dst_rows rows long; max_rows_per_run only sizes the grid. A run with dst outside
+ * [0, num_dst) or rows outside [0, dst_rows) is not stored at all (the destinations may be other GPUs' memory) and
+ * leaves a code in ctx_or_null's status word: CF_ERR_DEVICE_RANGE at the next cf_ctx_poll_status. */
 int cf_moe_send_row_runs(const void* d_src, const int* d_row_indices_or_null, long long index_stride, const cf_row_run* d_runs,
                          int num_runs, int max_rows_per_run, void* const* d_dst_bases, long long row_bytes,
-                         const float* d_tag_value_or_null, float* const* d_tag_bases_or_null, void* stream);
+                         const float* d_tag_value_or_null, float* const* d_tag_bases_or_null, int num_dst, long long dst_rows,
+                         cf_ctx* ctx_or_null, void* stream);
 /* The down projection of a device-planned expert-parallel layer with the return leg in its epilogue: a ragged grouped
  * NT GEMM (as cf_gemm_fp8_nt_grouped) whose output rows leave straight for the buffers of the ranks that own the tokens.
  * Inside group g the rows are the runs d_return_runs[g * runs_per_group + s] in ascending src_row (compact rows of A);

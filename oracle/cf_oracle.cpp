@@ -532,7 +532,7 @@ void orc_lion_step(uint16_t* w, void* m, int m_is_bf16, const float* grad, int64
 }
 
 // ---- row-wise (per-token) scaling: kernels/fp8.cu:34-49 applied per row (no reference code; documented
-// generalisation for configuration 3). swiglu != 0 quantises bf16(silu(gate)*up) (kernels/activations.cu:28-40).
+// generalisation for per-token scales). swiglu != 0 quantises bf16(silu(gate)*up) (kernels/activations.cu:28-40).
 void orc_quantize_rowwise_e4m3(const uint16_t* a, const uint16_t* b_or_null, int64_t ld_in, uint8_t* out, int64_t ld_out,
                                float* row_scale, float* row_descale, int rows, int cols) {
     std::vector<float> v(cols);
@@ -687,7 +687,7 @@ void orc_moe_grouped_expert_forward_fp8(const uint8_t* hidden, float dx, int x_i
     }
 }
 
-// ---- BASELINE configuration 1, end to end on the host -----------------------
+// ---- the CPU reference case (256x512 . 512x512, per-tensor scales), end to end on the host -----------------------
 // fp32 A[M,K], W[N,K], bias[N] -> per-tensor amax-scaled E4M3 quantise of both
 // (scale = 448/amax), fp32-accumulate GEMM, dequant by dA*dW, + fp32 bias, fp32
 // out. Returns nothing; used as correctness case and as a timed CPU sample.

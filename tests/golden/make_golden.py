@@ -26,7 +26,9 @@ from oracle_bindings import RefHost  # noqa: E402
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("CANOPY_REFERENCE", "/root/reference")
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("CANOPY_REFERENCE")
+    if not ref_root or not os.path.isdir(ref_root):
+        raise SystemExit("usage: make_golden.py /path/to/reference   (or set CANOPY_REFERENCE)")
     r = RefHost()
     allbf = (np.arange(65536, dtype=np.uint32) << 16).view(np.float32)
     unpack = np.array([r.lib.ref_e4m3_unpack(b) for b in range(256)], dtype=np.float32)

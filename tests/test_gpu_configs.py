@@ -1,5 +1,5 @@
-"""BASELINE configurations 3 (SwiGLU MLP, per-token / per-channel scales), 4 (MoE SwiGLU experts) and 5
-(large-shape E4M3 forward / E5M2 dgrad) as parity cases: reduced sizes against the oracle, full sizes through
+"""The three larger workloads: SwiGLU MLP with per-token / per-channel scales, MoE SwiGLU experts and the large-shape sweep
+(32768 x 8192 x 28672 E4M3 forward / E5M2 dgrad) as parity cases: reduced sizes against the oracle, full sizes through
 sampled rows and size-independent properties."""
 import numpy as np
 import pytest

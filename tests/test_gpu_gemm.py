@@ -1,5 +1,5 @@
 """GPU parity of the tcgen05 FP8 GEMM: relative Frobenius error <= 1e-2 against the CPU oracle (the
-tolerance BASELINE states for GEMM outputs), plus a cross-check against cuBLASLt (torch._scaled_mm), the
+tolerance this path states for GEMM outputs), plus a cross-check against cuBLASLt (torch._scaled_mm), the
 library the reference itself calls (src/trainer.cu:4516-4533)."""
 import numpy as np
 import pytest
@@ -162,7 +162,7 @@ def test_against_cublaslt(cfb, ctx):
 
 
 def test_full_size_properties(cfb, ctx, oracle):
-    """BASELINE configuration 2 at full size (8192 x 4096 x 4096): linearity in the scale, row-slab
+    """The single-GPU FP8 linear at full size (8192 x 4096 x 4096): linearity in the scale, row-slab
     consistency (a row block computed alone equals the same rows of the full product, bit for bit) and a
     sampled comparison with the oracle."""
     M, N, K = 8192, 4096, 4096

@@ -358,6 +358,57 @@ def test_expert_parallel_device_plan_for_every_rank(cfb, world):
         assert pos == tot[a:b].sum()
 
 
+def test_a_run_that_leaves_its_destination_is_skipped_and_reported(cfb):
+    """The sender checks every planned run against the number of destination buffers and their row capacity before it
+    stores anything (the destinations may be other GPUs' memory): an oversize run, a run with a negative row and a run
+    that names no buffer are not stored at all, the guard region behind the buffer stays untouched, the good run
+    arrives, and the context reports CF_ERR_DEVICE_RANGE once and stays usable. Nothing faults."""
+    ctx = cfb.Fp8Ctx(0)
+    width, cap, guard = 64, 16, 8
+    run_dt = np.dtype([("src_row", "<i8"), ("dst_row", "<i8"), ("rows", "<i4"), ("dst", "<i4")])
+    runs = np.zeros(4, dtype=run_dt)
+    runs[0] = (0, 2, 6, 0)          # fine: rows 2..7
+    runs[1] = (6, 12, 8, 0)         # 12 + 8 > 16: refused as a whole
+    runs[2] = (14, -1, 2, 0)        # negative row
+    runs[3] = (16, 0, 2, 3)         # no such buffer
+    src = torch.arange(32 * width, dtype=torch.int32, device="cuda").to(torch.uint8).view(32, width).contiguous()
+    dst = torch.full((cap + guard, width), 0xAB, dtype=torch.uint8, device="cuda")
+    tags = torch.full((cap + guard,), -7.0, dtype=torch.float32, device="cuda")
+    bases = torch.tensor([dst.data_ptr()], dtype=torch.int64, device="cuda")
+    tbases = torch.tensor([tags.data_ptr()], dtype=torch.int64, device="cuda")
+    tag = torch.tensor([0.5, 0, 0, 0], dtype=torch.float32, device="cuda")
+    d_runs = torch.from_numpy(runs.view(np.uint8).copy()).cuda()
+    cfb.moe_send_row_runs(src, None, 0, d_runs, 4, 8, bases, width, 1, cap, tag_value=tag, tag_bases=tbases, ctx=ctx)
+    with pytest.raises(cfb.CanopyError) as ei:
+        ctx.poll_status()
+    assert ei.value.code == cfb._capi.CF_ERR_DEVICE_RANGE
+    ctx.poll_status()                                      # the word was cleared; the context is usable
+    want = torch.full_like(dst, 0xAB)
+    want[2:8] = src[0:6]
+    assert torch.equal(dst, want)
+    want_t = torch.full_like(tags, -7.0)
+    want_t[2:8] = 0.5
+    assert torch.equal(tags, want_t)
+    # the plan cuts a group that would run past the receive capacity and reports it
+    world, V = 1, 2
+    counts_all = torch.tensor([[10, 10]], dtype=torch.int32, device="cuda")
+    lo = torch.tensor([0], dtype=torch.int32, device="cuda")
+    hi = torch.tensor([2], dtype=torch.int32, device="cuda")
+    send = torch.zeros(V * cfb.ROW_RUN_BYTES, dtype=torch.uint8, device="cuda")
+    ret = torch.zeros(V * cfb.ROW_RUN_BYTES, dtype=torch.uint8, device="cuda")
+    gc = torch.zeros(V, dtype=torch.int32, device="cuda")
+    go = torch.zeros(V, dtype=torch.int32, device="cuda")
+    cfb.moe_ep_plan(counts_all, world, 0, V, lo, hi, send, gc, go, ret, recv_capacity_rows=15, ctx=ctx)
+    with pytest.raises(cfb.CanopyError) as ei:
+        ctx.poll_status()
+    assert ei.value.code == cfb._capi.CF_ERR_DEVICE_RANGE
+    assert gc.cpu().tolist() == [10, 5] and go.cpu().tolist() == [0, 10]
+    cfb.moe_ep_plan(counts_all, world, 0, V, lo, hi, send, gc, go, ret, recv_capacity_rows=20, ctx=ctx)
+    ctx.poll_status()
+    assert gc.cpu().tolist() == [10, 10]
+    ctx.close()
+
+
 def test_route_expansion_over_replicas_keeps_weights_and_follows_the_shares(cfb):
     """Every selected (row, expert) keeps its weight on exactly one replica of that expert, unselected experts stay
     zero, and the rows of an expert split over its replicas in proportion to their shares."""

@@ -184,4 +184,72 @@ def test_rmsnorm_clip_quant_act_and_the_warp_form_without_clip(cfb):
         cfb.fp8_rmsnorm_clip_quant_act(ctx, slot_c, x, g, None, None, rows, H, plain8, 0.0)
     ctx.poll_status()
     with pytest.raises(cfb.CanopyError):
-        cfb.rmsnorm_clip_forward(x, g, clipped, None, rows, 96, 10.0)       # the clipped pass needs H % 512 == 0
+        # a shape the one-pass kernel does not take needs the bf16 row buffer for the three-pass sequence
+        cfb.rmsnorm_clip_quantize_e4m3_record(x, g, None, None, plain8, f32_scalar(1.0), f32_scalar(0.0), rows, 96, 10.0)
+
+
+@pytest.mark.parametrize("rows,H", [(16, 4096), (12, 1024), (10, 768), (7, 96)])
+def test_row_clip_on_rows_with_nan_and_inf_follows_the_reference_predicate(cfb, oracle, rows, H):
+    """The reference leaves a row alone only when `norm <= ceiling` holds (src/trainer.cu:3952): a row whose squared norm
+    is NaN fails that test and is rescaled by ceiling / NaN, i.e. becomes NaN everywhere; a row with an infinite norm is
+    multiplied by ceiling / inf = 0 (inf * 0 = NaN for the infinite elements themselves). Host-made inputs, both the
+    one-pass kernel (H % 512 == 0) and the three-pass form (other H) against the host restatement of the clip."""
+    x, g2 = _inputs(rows, H, 23)
+    ceiling = 50.0
+    # the fused entry point sees x and gamma only, so the specials are planted in x: a NaN element makes rms NaN and the
+    # whole normalised row NaN; an infinite element makes rms infinite, the finite elements 0 and itself inf * 0 = NaN
+    x[1, 3] = float("nan")
+    x[2, 5] = float("inf")
+    normed = torch.empty_like(x)
+    cfb.rmsnorm_forward(x, g2, normed, None, rows, H, 1e-6)
+    want = u16(normed).copy()
+    oracle.act_row_clip(want, ceiling)
+    got = torch.zeros_like(x)
+    cfb.rmsnorm_clip_forward(x, g2, got, None, rows, H, ceiling)
+    assert np.array_equal(u16(got), want)
+    # rows 1 and 2 are NaN after the norm (NaN and inf / inf); the clip must not have "skipped" them differently
+    f = oracle.bf16_to_f32(u16(got))
+    assert np.isnan(f[1]).all() and np.isnan(f[2]).any()
+    # the quantiser behind it sees the same rows
+    from gpu_util import u16_to_bf16
+    scale = f32_scalar(3.0)
+    want8 = torch.empty((rows, H), dtype=torch.uint8, device="cuda")
+    want_amax = f32_scalar(0.0)
+    cfb.fp8_quantize_e4m3_record(u16_to_bf16(want), want8, scale, want_amax)
+    got8 = torch.zeros_like(want8)
+    got_amax = f32_scalar(0.0)
+    keep = torch.zeros_like(x)
+    cfb.rmsnorm_clip_quantize_e4m3_record(x, g2, keep, None, got8, scale, got_amax, rows, H, ceiling)
+    assert torch.equal(got8, want8) and torch.equal(got_amax, want_amax)
+    assert np.array_equal(u16(keep), want)
+
+
+@pytest.mark.parametrize("rows,H", [(40, 768), (9, 1000), (5, 12288), (21, 96)])
+def test_row_clip_three_pass_form_for_other_shapes(cfb, oracle, rows, H):
+    """Hidden sizes the one-pass kernel does not take (not a multiple of 512, or above 8192) run norm, clip and quantise
+    as three launches with the reference's reductions: bit-identical to rmsnorm_forward + the host clip + the quantiser."""
+    x, g = _inputs(rows, H, 29)
+    g = (g * 4).contiguous()
+    x[::3] *= 30
+    normed = torch.empty_like(x)
+    rms = torch.empty(rows, dtype=torch.float32, device="cuda")
+    cfb.rmsnorm_forward(x, g, normed, rms, rows, H, 1e-6)
+    n_host = u16(normed).copy()
+    norms = np.sqrt((oracle.bf16_to_f32(n_host).astype(np.float64) ** 2).sum(axis=1))
+    ceiling = float(np.float32(np.median(norms) * 1.0005))
+    oracle.act_row_clip(n_host, ceiling)
+    assert np.any(n_host != u16(normed))
+    got = torch.zeros_like(x)
+    got_rms = torch.zeros_like(rms)
+    cfb.rmsnorm_clip_forward(x, g, got, got_rms, rows, H, ceiling)
+    assert torch.equal(got_rms, rms) and np.array_equal(u16(got), n_host)
+    from gpu_util import u16_to_bf16
+    scale = f32_scalar(7.0)
+    want8 = torch.empty((rows, H), dtype=torch.uint8, device="cuda")
+    want_amax = f32_scalar(0.0)
+    cfb.fp8_quantize_e4m3_record(u16_to_bf16(n_host), want8, scale, want_amax)
+    got8 = torch.zeros_like(want8)
+    got_amax = f32_scalar(0.0)
+    keep = torch.zeros_like(x)
+    cfb.rmsnorm_clip_quantize_e4m3_record(x, g, keep, None, got8, scale, got_amax, rows, H, ceiling)
+    assert torch.equal(got8, want8) and torch.equal(got_amax, want_amax)

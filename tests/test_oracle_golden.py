@@ -204,7 +204,7 @@ def test_bias_orders(oracle):
 
 
 def test_config1_cpu_reference_case(oracle):
-    """BASELINE configuration 1: fp32 A[256x512]~N(0,1), W[512x512]~N(0,0.02), bias~N(0,0.01), seed 0."""
+    """The CPU reference case: fp32 A[256x512]~N(0,1), W[512x512]~N(0,0.02), bias~N(0,0.01), seed 0."""
     rng = np.random.default_rng(0)
     A = rng.standard_normal((256, 512)).astype(np.float32)
     W = (rng.standard_normal((512, 512)) * 0.02).astype(np.float32)
@@ -311,3 +311,13 @@ def test_act_row_clip_restatement(oracle):
     y = before.copy()
     oracle.act_row_clip(y, 0.0)
     assert np.array_equal(y, before)
+    # `if (norm <= ceiling) return;` (src/trainer.cu:3952): a NaN norm fails the test, the row is rescaled by
+    # ceiling / NaN and becomes NaN everywhere; an infinite norm gives ceiling / inf = 0 (inf * 0 = NaN for the element)
+    z = before.copy()
+    z[0, 7] = 0x7fc0          # NaN
+    z[1, 9] = 0x7f80          # +inf
+    oracle.act_row_clip(z, 70.0)
+    f = oracle.bf16_to_f32(z)
+    assert np.isnan(f[0]).all()
+    assert np.isnan(f[1, 9]) and np.all(f[1, np.arange(1024) != 9] == 0.0)
+    assert np.array_equal(z[2:], x[2:])

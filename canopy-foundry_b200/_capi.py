@@ -70,7 +70,9 @@ SIGNATURES = {
     "cf_gemm_fp8_tn_accum_bf16": (ci, [vp, ci, ci, ci, vp, fp, vp, fp, vp, ci, vp]),
     "cf_gemm_fp8_dw_accum_f32": (ci, [vp, ci, ci, ci, vp, ci, fp, vp, ci, fp, vp, ci, vp]),
     "cf_gemm_fp8_dw_accum_bf16": (ci, [vp, ci, ci, ci, vp, ci, fp, vp, ci, fp, vp, ci, vp]),
-    "cf_gemm_fp8_nt_reduce_scatter_f32": (ci, [vp, ci, ci, ci, vp, ci, ci, fp, vp, fp, C.POINTER(vp), ci, vp]),
+    "cf_gemm_fp8_nt_reduce_scatter_f32": (ci, [vp, ci, ci, ci, vp, ci, ci, fp, vp, fp, fp, fp, C.POINTER(vp), ci, vp]),
+    "cf_gemm_fp8_swiglu_bf16_rowamax": (ci, [vp, ci, ci, ci, vp, ci, ci, fp, fp, vp, fp, fp, vp, ci, fp, vp]),
+    "cf_fp8_quantize_rowwise_given_amax_e4m3": (ci, [vp, ci, vp, ci, fp, fp, fp, ci, ci, vp]),
     "cf_f32_to_bf16_and_zero": (ci, [fp, vp, sz, vp]),
     "cf_gemm_fp8_nt_grouped": (ci, [vp, ci, ci, ci, ci, ip, ip, vp, ci, ci, fp, ci, vp, fp, vp, ci, vp]),
     "cf_gemm_fp8_nt_segments": (ci, [vp, ci, ci, ip, ci, ci, ci, ip, ip, vp, ci, ci, fp, ci, vp, fp, vp, ci, vp]),

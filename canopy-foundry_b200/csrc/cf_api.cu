@@ -242,6 +242,7 @@ int cf_gemm_fp8_nt(cf_ctx* ctx, int M, int N, int K, const void* d_A, int lda, i
 
 int cf_gemm_fp8_nt_reduce_scatter_f32(cf_ctx* ctx, int M, int N, int K, const void* d_A, int lda, int a_is_e5m2,
                                       const float* d_a_descale, const void* d_B, const float* d_b_descale,
+                                      const float* d_a_row_descale_or_null, const float* d_b_col_descale_or_null,
                                       void* const* slices, int num_slices, void* stream) {
     CF_REQUIRE(ctx != nullptr, "cf_gemm_fp8_nt_reduce_scatter_f32: null context");
     CF_REQUIRE(M > 0 && N > 0 && K > 0 && lda >= K, "cf_gemm_fp8_nt_reduce_scatter_f32: bad shape");
@@ -252,6 +253,7 @@ int cf_gemm_fp8_nt_reduce_scatter_f32(cf_ctx* ctx, int M, int N, int K, const vo
     p.d_a_descale = d_a_descale; p.d_b_descale = d_b_descale;
     p.C = nullptr; p.ldc = N; p.out_kind = 2;
     p.a_e5m2 = a_is_e5m2 ? 1 : 0;
+    p.d_a_row_descale = d_a_row_descale_or_null; p.d_b_col_descale = d_b_col_descale_or_null;
     p.peer_out_host = slices; p.peer_count = num_slices; p.rows_per_peer = M / num_slices;
     Ctx* c = reinterpret_cast<Ctx*>(ctx);
     const int set = peer_set_lookup(c, 0, slices, num_slices, p.rows_per_peer, N, N, &p.peer_maps_ready);
@@ -650,6 +652,32 @@ int cf_gemm_fp8_swiglu_quant_act(cf_ctx* ctx, cf_act_slot* slot, int num_segment
     }
     return cf_fp8_update_delayed_scale(slot->amax, slot->fp8_max, slot->scale, slot->descale, slot->history, kHistoryLen,
                                        slot->history_cursor, slot->history_count, stream);
+}
+
+int cf_gemm_fp8_swiglu_bf16_rowamax(cf_ctx* ctx, int M, int F, int K, const void* d_A, int lda, int a_is_e5m2,
+                                    const float* d_a_descale, const float* d_a_row_descale_or_null,
+                                    const void* d_W_interleaved, const float* d_w_descale,
+                                    const float* d_w_col_descale_interleaved_or_null, void* d_h, int ldh, float* d_row_amax,
+                                    void* stream) {
+    CF_REQUIRE(ctx != nullptr, "cf_gemm_fp8_swiglu_bf16_rowamax: null context");
+    CF_REQUIRE(M >= 0 && F > 0 && K > 0 && lda >= K && ldh >= F, "cf_gemm_fp8_swiglu_bf16_rowamax: bad shape");
+    CF_REQUIRE(F % 32 == 0, "cf_gemm_fp8_swiglu_bf16_rowamax: F must be a multiple of 32 (gate/up rows interleave in groups of 32)");
+    if (M == 0) return CF_OK;
+    CF_REQUIRE(d_A && d_W_interleaved && d_h && d_row_amax, "cf_gemm_fp8_swiglu_bf16_rowamax: null pointer");
+    CF_REQUIRE(d_a_descale || d_a_row_descale_or_null, "cf_gemm_fp8_swiglu_bf16_rowamax: no activation descale");
+    CF_REQUIRE(d_w_descale || d_w_col_descale_interleaved_or_null, "cf_gemm_fp8_swiglu_bf16_rowamax: no weight descale");
+    GemmParams p;
+    p.M = M; p.N = 2 * F; p.K = K;
+    p.d_a_descale = d_a_descale ? d_a_descale : d_a_row_descale_or_null;
+    p.d_b_descale = d_w_descale ? d_w_descale : d_w_col_descale_interleaved_or_null;
+    p.d_a_row_descale = d_a_row_descale_or_null;
+    p.d_b_col_descale = d_w_col_descale_interleaved_or_null;
+    p.C = d_h; p.ldc = ldh; p.out_kind = 5;
+    p.a_e5m2 = a_is_e5m2 ? 1 : 0;
+    p.d_row_amax_out = d_row_amax;
+    p.d_status = reinterpret_cast<Ctx*>(ctx)->d_status;
+    const int tiles = ((M + gemm_tile_m() - 1) / gemm_tile_m()) * ((2 * F + gemm_tile_n() - 1) / gemm_tile_n());
+    return launch_gemm_fp8_nt(d_A, lda, M, d_W_interleaved, 2ll * F, p, tiles, as_stream(stream));
 }
 
 int cf_refresh_fp8_weight(const cf_fp8_weight* w, int recompute_amax, void* stream) {

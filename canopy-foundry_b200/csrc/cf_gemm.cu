@@ -526,6 +526,50 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 }
                 local_amax = warp_max(local_amax);
                 if (lane == 0 && local_amax > 0.0f) atomicMax(reinterpret_cast<int*>(p.d_amax_out), __float_as_int(local_amax));
+            } else if (p.out_kind == 5) {
+                // SwiGLU -> bf16 epilogue with a per-row amax, for per-token re-quantisation: same interleaved weight layout
+                // and rounding points as above (GEMM output to bf16 with the row's and the column's descale, silu(g)*u to
+                // bf16), but the product is stored as bf16 [., N/2] and max|h| of every row is accumulated into
+                // p.d_row_amax_out (integer atomicMax on the float bits; the caller zeroes it). The row-wise quantiser
+                // then reads h once: the [., N] gate/up intermediate never reaches HBM.
+                float local_amax = 0.0f;
+                uint16_t* orow = static_cast<uint16_t*>(tc.out_base) + grow * p.ldc + (tc.n0 >> 1);
+#pragma unroll 1
+                for (int c = col_half * 2; c < col_half * 2 + 2; ++c) {
+                    const int col0 = tc.n0 + c * 64;
+                    if (col0 >= p.N) break;                // warp-uniform
+                    uint32_t vg[32], vu[32];
+                    tmem_ld32(taddr + c * 64, vg);
+                    tmem_ld32(taddr + c * 64 + 32, vu);
+                    tmem_ld_wait();
+                    if (!row_ok) continue;
+                    uint32_t w[16];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float4 cg = make_float4(db_t, db_t, db_t, db_t), cu = cg;
+                        if (p.d_b_col_descale) {
+                            cg = __ldg(reinterpret_cast<const float4*>(p.d_b_col_descale + col0) + j);
+                            cu = __ldg(reinterpret_cast<const float4*>(p.d_b_col_descale + col0 + 32) + j);
+                        }
+                        const float sg[4] = {cg.x, cg.y, cg.z, cg.w}, su[4] = {cu.x, cu.y, cu.z, cu.w};
+                        float h[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float gb = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vg[4 * j + e]) * (da * sg[e])));
+                            const float ub = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vu[4 * j + e]) * (da * su[e])));
+                            h[e] = __bfloat162float(__float2bfloat16_rn(gb * swiglu_sigmoid(gb) * ub));
+                            local_amax = fmaxf(local_amax, fabsf(h[e]));
+                        }
+                        w[2 * j] = pack_bf16x2(h[0], h[1]);
+                        w[2 * j + 1] = pack_bf16x2(h[2], h[3]);
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+                }
+                if (row_ok && local_amax > 0.0f)
+                    atomicMax(reinterpret_cast<int*>(p.d_row_amax_out + static_cast<long long>(tc.row0) + row_in_tile),
+                              __float_as_int(local_amax));
             } else {
             // Full boxes of bf16 output go through shared memory and TMA stores (whole 128-byte lines per row);
             // ragged rows of a grouped tile, column tails and the fp32 / accumulate forms use direct stores.
@@ -562,16 +606,24 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 for (; ch < col_half * 4 + 4; ++ch) {
                     const int col0 = tc.n0 + ch * 32;
                     if (col0 + 32 > p.N) break;            // warp-uniform; the tail takes the direct path below
+                    float4 cq[8];
+                    if (p.d_b_col_descale) {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) cq[q] = __ldg(reinterpret_cast<const float4*>(p.d_b_col_descale + col0) + q);
+                    }
                     uint32_t v[32];
                     tmem_ld32(taddr + ch * 32, v);
                     tmem_ld_wait();
                     if (lane == 0) bulk_wait_read_0();
                     __syncwarp();
 #pragma unroll
-                    for (int q = 0; q < 8; ++q)
+                    for (int q = 0; q < 8; ++q) {
+                        float4 m4 = make_float4(dab, dab, dab, dab);
+                        if (p.d_b_col_descale) m4 = make_float4(da * cq[q].x, da * cq[q].y, da * cq[q].z, da * cq[q].w);
                         st_shared_v4(buf + row_off + ((static_cast<uint32_t>(q) ^ sw) << 4),
-                                     __float_as_uint(__uint_as_float(v[4 * q]) * dab), __float_as_uint(__uint_as_float(v[4 * q + 1]) * dab),
-                                     __float_as_uint(__uint_as_float(v[4 * q + 2]) * dab), __float_as_uint(__uint_as_float(v[4 * q + 3]) * dab));
+                                     __float_as_uint(__uint_as_float(v[4 * q]) * m4.x), __float_as_uint(__uint_as_float(v[4 * q + 1]) * m4.y),
+                                     __float_as_uint(__uint_as_float(v[4 * q + 2]) * m4.z), __float_as_uint(__uint_as_float(v[4 * q + 3]) * m4.w));
+                    }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {
@@ -598,7 +650,9 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     if (!row_ok) continue;
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
-                        if (col0 + j < p.N) store_one(p, tc.out_base, grow, col0 + j, __uint_as_float(v[j]), da, db_t);
+                        if (col0 + j < p.N)
+                            store_one(p, tc.out_base, grow, col0 + j, __uint_as_float(v[j]), da,
+                                      p.d_b_col_descale ? p.d_b_col_descale[col0 + j] : db_t);
                 }
             } else if (box_tma) {
                 const uint32_t buf = smem_c + static_cast<uint32_t>(warp - 2) * C_BOX_BYTES;
@@ -940,11 +994,20 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
         }
         p.c_vec = 0;
     }
+    if (p.out_kind == 5) {
+        // bf16 SwiGLU product of width N/2 with per-row amax: 16-byte stores, whole 64-column groups, dense rows only
+        if (!tma_ok || ca % 16 != 0 || p.ldc % 8 != 0 || p.N % 64 != 0 || !p.d_row_amax_out || p.d_group_out || p.bias ||
+            (p.d_b_col_descale && reinterpret_cast<uintptr_t>(p.d_b_col_descale) % 16 != 0)) {
+            set_error("swiglu bf16 epilogue: needs TMA-aligned operands, N %% 64 == 0, a 16-byte aligned bf16 output with ldc %% 8 == 0, a row amax array, 16-byte aligned column scales");
+            return CF_ERR_UNSUPPORTED;
+        }
+        p.c_vec = 0;
+    }
     // Row blocks per rasterisation band. Eight keeps the operand slabs of the ~74 tiles in flight smallest (8 + 74/8 row
     // and column blocks). The SwiGLU form over a weight block larger than L2 with a short K (gate/up projection, 28672 x
     // 4096: little output traffic, B re-streamed once per band) measured 2-6 % faster with twice the band height; the
     // bf16-output GEMM of the same shape measured 7 % slower with it and keeps eight.
-    if (p.out_kind == 4 && static_cast<long long>(p.N) * p.K > (64ll << 20) && p.K <= 4096) p.raster_m = 16;
+    if ((p.out_kind == 4 || p.out_kind == 5) && static_cast<long long>(p.N) * p.K > (64ll << 20) && p.K <= 4096) p.raster_m = 16;
     if (p.peer_out_host != nullptr && !tma_ok) {
         set_error("reduce-scatter GEMM: operands must be 16-byte aligned with K %% 16 == 0");
         return CF_ERR_UNSUPPORTED;
@@ -1011,8 +1074,8 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
         // every tile must lie inside one slice and take the TMA path as a whole (no ragged rows, no column tail)
         if (p.out_kind != 2 || p.d_counts != nullptr || p.peer_count < 1 || p.peer_count > 16 || p.d_peer_maps == nullptr ||
             p.rows_per_peer <= 0 || p.rows_per_peer % 256 != 0 || p.M != p.rows_per_peer * p.peer_count || p.N % 32 != 0 ||
-            !tma_ok || p.d_a_row_descale || p.d_b_col_descale) {
-            set_error("reduce-scatter GEMM: needs TMA-aligned operands, N %% 32 == 0, M = peers x rows_per_peer with rows_per_peer %% 256 == 0, per-tensor scales");
+            !tma_ok || (p.d_b_col_descale && reinterpret_cast<uintptr_t>(p.d_b_col_descale) % 16 != 0)) {
+            set_error("reduce-scatter GEMM: needs TMA-aligned operands, N %% 32 == 0, M = peers x rows_per_peer with rows_per_peer %% 256 == 0, 16-byte aligned column scales");
             return CF_ERR_UNSUPPORTED;
         }
         if (!p.peer_maps_ready) {
@@ -1034,7 +1097,8 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
         p.d_peer_maps = nullptr;
     }
     const bool f32_tma = (p.out_kind == 2 || p.out_kind == 1) && ca % 16 == 0 && p.ldc % 4 == 0 && p.N >= 32 &&
-                         p.d_group_out == nullptr && p.d_a_row_descale == nullptr && p.d_b_col_descale == nullptr;
+                         p.d_group_out == nullptr &&
+                         (p.d_b_col_descale == nullptr || reinterpret_cast<uintptr_t>(p.d_b_col_descale) % 16 == 0);
     p.tma_reduce = return_form ? 0 : p.d_peer_maps ? 1 : (f32_tma ? (p.out_kind == 2 ? 1 : 2) : 0);
     if (return_form) p.tma_store = 1;
     if (p.d_peer_maps) {

@@ -24,9 +24,11 @@ struct GemmParams {
     const float* d_b_col_descale = nullptr;
     void* C = nullptr;
     long long ldc = 0;
-    int out_kind = 0;               // 0 bf16 store, 1 f32 store, 2 f32 +=, 3 bf16 +=, 4 SwiGLU -> E4M3 [., N/2] (ldc in bytes)
+    int out_kind = 0;               // 0 bf16 store, 1 f32 store, 2 f32 +=, 3 bf16 +=, 4 SwiGLU -> E4M3 [., N/2] (ldc in bytes),
+                                    // 5 SwiGLU -> bf16 [., N/2] (ldc in elements) + per-row amax
     const float* d_quant_scale = nullptr;   // out_kind 4: scale the SwiGLU product is quantised with
     float* d_amax_out = nullptr;            // out_kind 4: amax of the bf16 SwiGLU product (integer atomicMax)
+    float* d_row_amax_out = nullptr;        // out_kind 5: per-row amax of the bf16 SwiGLU product, indexed like d_a_row_descale
     const uint16_t* bias = nullptr;
     int bias_mode = 0;
     int c_vec = 0;                  // filled by the launcher

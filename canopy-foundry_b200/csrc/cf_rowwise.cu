@@ -270,6 +270,54 @@ __global__ void __launch_bounds__(kRT) k_finish_f32(float* __restrict__ acc, uin
     }
 }
 
+// Row-wise quantiser for rows whose amax is already known (the GEMM that produced them recorded it, possibly reduced
+// over the ranks that hold other column slices of the same rows): a pure stream, 16 elements per thread per step (two
+// 16-byte loads, one 16-byte store), scale_r = 448 / max(amax_r, 1e-12) derived per row on the fly.
+__global__ void __launch_bounds__(kRT) k_rowwise_given_amax(const uint16_t* __restrict__ x, long long ld_x, uint8_t* __restrict__ out,
+                                                            long long ld_out, const float* __restrict__ row_amax,
+                                                            float* __restrict__ row_scale, float* __restrict__ row_descale,
+                                                            long long rows, int cols, int vec) {
+    const long long stride = static_cast<long long>(gridDim.x) * kRT;
+    if (vec) {
+        const int vpr = cols / 16;
+        const long long total = rows * vpr;
+        for (long long i = static_cast<long long>(blockIdx.x) * kRT + threadIdx.x; i < total; i += stride) {
+            const long long r = i / vpr;
+            const int c = static_cast<int>(i - r * vpr);
+            const uint4* src = reinterpret_cast<const uint4*>(x + r * ld_x) + 2 * c;
+            const uint4 v0 = __ldcs(src), v1 = __ldcs(src + 1);
+            const float a = fmaxf(row_amax[r], 1e-12f);
+            const float sc = __fdiv_rn(448.0f, a);
+            if (c == 0) {
+                if (row_scale) row_scale[r] = sc;
+                row_descale[r] = __fdiv_rn(a, 448.0f);
+            }
+            float f[8], g[8];
+            unpack8(v0, f);
+            unpack8(v1, g);
+            uint4 q;
+            q.x = cvt_fp8x4<false>(f[0] * sc, f[1] * sc, f[2] * sc, f[3] * sc);
+            q.y = cvt_fp8x4<false>(f[4] * sc, f[5] * sc, f[6] * sc, f[7] * sc);
+            q.z = cvt_fp8x4<false>(g[0] * sc, g[1] * sc, g[2] * sc, g[3] * sc);
+            q.w = cvt_fp8x4<false>(g[4] * sc, g[5] * sc, g[6] * sc, g[7] * sc);
+            __stcs(reinterpret_cast<uint4*>(out + r * ld_out) + c, q);
+        }
+        return;
+    }
+    const long long total = rows * cols;
+    for (long long i = static_cast<long long>(blockIdx.x) * kRT + threadIdx.x; i < total; i += stride) {
+        const long long r = i / cols;
+        const int c = static_cast<int>(i - r * cols);
+        const float a = fmaxf(row_amax[r], 1e-12f);
+        const float sc = __fdiv_rn(448.0f, a);
+        if (c == 0) {
+            if (row_scale) row_scale[r] = sc;
+            row_descale[r] = __fdiv_rn(a, 448.0f);
+        }
+        out[r * ld_out + c] = cvt_fp8<false>(bf16_bits_to_f32(x[r * ld_x + c]) * sc);
+    }
+}
+
 }  // namespace
 
 int swiglu_record_launch(const void* d_gate, const void* d_up, int ld_in, void* d_out, int ld_out, const float* d_scale,
@@ -333,6 +381,24 @@ int cf_swiglu_quantize_rowwise_e4m3(const void* d_gate, const void* d_up, int ld
                                                          ld_in, static_cast<uint8_t*>(d_out), ld_out, d_row_scale,
                                                          d_row_descale, cols, vec);
     CF_LAUNCH_CHECK("swiglu_quantize_rowwise_e4m3");
+    return CF_OK;
+}
+
+int cf_fp8_quantize_rowwise_given_amax_e4m3(const void* d_x, int ld_x, void* d_out, int ld_out, const float* d_row_amax,
+                                            float* d_row_scale, float* d_row_descale, int rows, int cols, void* stream) {
+    CF_REQUIRE(rows >= 0 && cols >= 0 && ld_x >= cols && ld_out >= cols, "cf_fp8_quantize_rowwise_given_amax_e4m3: bad shape");
+    if (rows == 0 || cols == 0) return CF_OK;
+    CF_REQUIRE(d_x && d_out && d_row_amax && d_row_descale, "cf_fp8_quantize_rowwise_given_amax_e4m3: null pointer");
+    const int vec = aligned16(d_x) && aligned16(d_out) && (ld_x % 8 == 0) && (ld_out % 16 == 0) && (cols % 16 == 0);
+    const size_t items = static_cast<size_t>(rows) * (vec ? cols / 16 : cols);
+    size_t blocks = (items + kRT - 1) / kRT;
+    const size_t cap = static_cast<size_t>(sm_count()) * 8;
+    if (blocks < 1) blocks = 1;
+    if (blocks > cap) blocks = cap;
+    k_rowwise_given_amax<<<static_cast<unsigned>(blocks), kRT, 0, as_stream(stream)>>>(
+        static_cast<const uint16_t*>(d_x), ld_x, static_cast<uint8_t*>(d_out), ld_out, d_row_amax, d_row_scale, d_row_descale,
+        rows, cols, vec);
+    CF_LAUNCH_CHECK("quantize_rowwise_given_amax_e4m3");
     return CF_OK;
 }
 

@@ -21,7 +21,7 @@ __all__ = [
     "fp8_elem_clip_count", "fp8_pack_bf16_e4m3_raw", "fp8_pack_bf16_e4m3_raw_and_dequant",
     "fp8_unpack_e4m3_raw_bf16", "lt_gemm_fp8_nt", "lt_gemm_fp8_tn_accum_f32", "gemm_fp8_dw_accum", "gemm_fp8_nt_reduce_scatter", "f32_to_bf16_and_zero", "gemm_fp8_nt_grouped", "gemm_fp8_nt_segments", "gemm_fp8_nt_segments_scatter",
     "fp8_quant_act", "fp8_swiglu_quant_act", "gemm_fp8_swiglu_quant_act", "fp8_interleave_gate_up", "refresh_fp8_weight", "fp8_linear_forward", "bias_add_strided_bf16", "swiglu_forward",
-    "gelu_forward", "lion_step", "fp8_quantize_rowwise_e4m3", "swiglu_quantize_rowwise_e4m3", "swiglu_quantize_e4m3_record",
+    "gelu_forward", "lion_step", "fp8_quantize_rowwise_e4m3", "fp8_quantize_rowwise_given_amax_e4m3", "gemm_fp8_swiglu_bf16_rowamax", "interleave_gate_up_vector", "swiglu_mlp_fp8_rowwise_fused", "swiglu_quantize_rowwise_e4m3", "swiglu_quantize_e4m3_record",
     "rmsnorm_forward", "rmsnorm_quantize_e4m3_record", "rmsnorm_quantize_rowwise_e4m3", "fp8_rmsnorm_quant_act", "rmsnorm_clip_forward", "rmsnorm_clip_quantize_e4m3_record", "fp8_rmsnorm_clip_quant_act",
     "moe_topk_route_f32", "moe_build_expert_row_lists", "moe_expert_offsets_from_counts",
     "moe_gather_rows_u8", "moe_gather_rows_bf16", "moe_scatter_accumulate_rows_bf16",
@@ -281,12 +281,13 @@ def gemm_fp8_dw_accum(ctx, M, N, K, X8, ldx, ds_x, dY8, ldy, ds_dy, dW, ldc):
     check(fn(ctx.handle, M, N, K, _p(X8), ldx, _p(ds_x), _p(dY8), ldy, _p(ds_dy), _p(dW), ldc, _s()))
 
 
-def gemm_fp8_nt_reduce_scatter(ctx, M, N, K_local, A, lda, a_is_e5m2, a_descale, B, b_descale, slice_ptrs):
+def gemm_fp8_nt_reduce_scatter(ctx, M, N, K_local, A, lda, a_is_e5m2, a_descale, B, b_descale, slice_ptrs,
+                               a_row_descale=None, b_col_descale=None):
     """Row-parallel GEMM whose epilogue adds every row slice of the fp32 product into its owner's accumulation slice
     (slice_ptrs: device addresses, one per rank, as mapped in this process)."""
     arr = (C.c_void_p * len(slice_ptrs))(*[C.c_void_p(int(x)) for x in slice_ptrs])
     check(_L().cf_gemm_fp8_nt_reduce_scatter_f32(ctx.handle, M, N, K_local, _p(A), lda, int(a_is_e5m2), _p(a_descale), _p(B),
-                                                 _p(b_descale), arr, len(slice_ptrs), _s()))
+                                                 _p(b_descale), _p(a_row_descale), _p(b_col_descale), arr, len(slice_ptrs), _s()))
 
 
 def f32_to_bf16_and_zero(acc, out):
@@ -349,6 +350,28 @@ def fp8_quantize_rowwise_e4m3(x, out, row_descale, row_scale=None, rows=None, co
     check(_L().cf_fp8_quantize_rowwise_e4m3(_p(x), x.stride(0) if ld_x is None else ld_x, _p(out),
                                             out.stride(0) if ld_out is None else ld_out, _p(row_scale), _p(row_descale),
                                             rows, cols, _s()))
+
+
+def fp8_quantize_rowwise_given_amax_e4m3(x, out, row_amax, row_descale, row_scale=None, rows=None, cols=None):
+    rows = x.shape[0] if rows is None else rows
+    cols = x.shape[1] if cols is None else cols
+    check(_L().cf_fp8_quantize_rowwise_given_amax_e4m3(_p(x), x.stride(0), _p(out), out.stride(0), _p(row_amax),
+                                                       _p(row_scale), _p(row_descale), rows, cols, _s()))
+
+
+def gemm_fp8_swiglu_bf16_rowamax(ctx, M, F, K, A, lda, a_is_e5m2, a_descale, a_row_descale, w_interleaved, w_descale,
+                                 w_col_descale_interleaved, h, row_amax):
+    """Gate/up GEMM + SwiGLU in one launch: h bf16 [M, F] and max|h| per row (row_amax, zeroed by the caller)."""
+    check(_L().cf_gemm_fp8_swiglu_bf16_rowamax(ctx.handle, M, F, K, _p(A), lda, int(a_is_e5m2), _p(a_descale),
+                                               _p(a_row_descale), _p(w_interleaved), _p(w_descale),
+                                               _p(w_col_descale_interleaved), _p(h), h.stride(0), _p(row_amax), _s()))
+
+
+def interleave_gate_up_vector(v, F):
+    """A per-output-row vector of the [2F, K] gate/up weight (gate rows first) in the 32-row interleaved order of
+    fp8_interleave_gate_up: [g0..g31, u0..u31, g32..g63, u32..u63, ...]."""
+    g, u = v[:F].reshape(F // 32, 32), v[F:].reshape(F // 32, 32)
+    return torch.stack([g, u], dim=1).reshape(2 * F).contiguous()
 
 
 def swiglu_quantize_rowwise_e4m3(gate, up, out, row_descale, rows, cols, ld_in, ld_out=None, row_scale=None):
@@ -521,6 +544,42 @@ def swiglu_mlp_fp8_rowwise(ctx, x, w_gateup8, w_gateup_descale, w_down8, w_down_
     swiglu_quantize_rowwise_e4m3(gu, gu.view(-1)[F:], h8, dh, M, F, F2)
     lt_gemm_fp8_nt(ctx, M, y.shape[1], F, h8, F, False, one, w_down8, one, y, y.stride(0), a_row_descale=dh,
                    b_col_descale=w_down_descale)
+    return work
+
+
+def swiglu_mlp_fp8_rowwise_fused(ctx, x, w_gateup8_il, w_gateup_descale_il, w_down8, w_down_descale, y, work=None,
+                                 amax_allreduce=None, down=None):
+    """The same MLP as swiglu_mlp_fp8_rowwise with the [M, 2F] bf16 gate/up intermediate fused away: the gate/up GEMM's
+    epilogue writes h = bf16(silu(gate) * up) as bf16 [M, F] and records max|h| per row, one row-wise pass quantises h
+    with that amax, the down GEMM follows. Bit-identical to the unfused composite. w_gateup8_il is the [2F, H] weight in
+    the 32-row interleaved layout (fp8_interleave_gate_up) with its per-row descales interleaved the same way
+    (interleave_gate_up_vector).
+    Sharded use (gate/up split by output features, down by its contraction dimension): F is this rank's share,
+    amax_allreduce(row_amax) max-reduces the per-row amax over the ranks before the quantiser, and down(h8, dh) replaces
+    the local down GEMM (partial products that the caller sums across ranks)."""
+    M, H = x.shape
+    F = w_gateup8_il.shape[0] // 2
+    dev = x.device
+    if work is None:
+        work = {}
+    x8 = work.setdefault("x8", torch.empty((M, H), dtype=torch.uint8, device=dev))
+    dx = work.setdefault("dx", torch.empty(M, dtype=torch.float32, device=dev))
+    h = work.setdefault("h", torch.empty((M, F), dtype=torch.bfloat16, device=dev))
+    h8 = work.setdefault("h8", torch.empty((M, F), dtype=torch.uint8, device=dev))
+    hmax = work.setdefault("hmax", torch.empty(M, dtype=torch.float32, device=dev))
+    dh = work.setdefault("dh", torch.empty(M, dtype=torch.float32, device=dev))
+    one = work.setdefault("one", torch.ones(4, dtype=torch.float32, device=dev))
+    fp8_quantize_rowwise_e4m3(x, x8, dx)
+    hmax.zero_()
+    gemm_fp8_swiglu_bf16_rowamax(ctx, M, F, H, x8, H, False, None, dx, w_gateup8_il, None, w_gateup_descale_il, h, hmax)
+    if amax_allreduce is not None:
+        amax_allreduce(hmax)
+    fp8_quantize_rowwise_given_amax_e4m3(h, h8, hmax, dh)
+    if down is not None:
+        down(h8, dh)
+    else:
+        lt_gemm_fp8_nt(ctx, M, y.shape[1], F, h8, F, False, one, w_down8, one, y, y.stride(0), a_row_descale=dh,
+                       b_col_descale=w_down_descale)
     return work
 
 

@@ -285,14 +285,16 @@ class RowParallelReduceScatterGemm:
         if self.world > 1:
             dist.all_reduce(self._fence, group=self.group)
 
-    def forward(self, a8_local, a_descale, w8_local, w_descale, out_slice_bf16):
+    def forward(self, a8_local, a_descale, w8_local, w_descale, out_slice_bf16, a_row_descale=None, b_col_descale=None):
         """a8_local [M, K_local] E4M3 (this rank's K slice of every row), w8_local [N, K_local]; out_slice_bf16
-        [M/world, N] receives this rank's rows of the full product."""
+        [M/world, N] receives this rank's rows of the full product. a_row_descale float[M] / b_col_descale float[N]:
+        per-token / per-output-channel scales shared by all ranks, applied before the partial products are summed."""
         b = self._flip
         self._flip ^= 1
         K_local = a8_local.shape[1]
         self.cfb.gemm_fp8_nt_reduce_scatter(self.ctx, self.M, self.N, K_local, a8_local, a8_local.stride(0), False, a_descale,
-                                            w8_local, w_descale, self.ptrs[b])
+                                            w8_local, w_descale, self.ptrs[b], a_row_descale=a_row_descale,
+                                            b_col_descale=b_col_descale)
         self._barrier()           # every rank's GEMM, and the adds it sent here, have completed
         self.cfb.f32_to_bf16_and_zero(self.acc[b], out_slice_bf16)
         return out_slice_bf16

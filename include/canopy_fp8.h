@@ -155,10 +155,13 @@ int cf_gemm_fp8_nt(cf_ctx* ctx, int M, int N, int K, const void* d_A, int lda, i
  * destination), so the transfer over NVLink overlaps the main loop tile by tile. `slices` is a HOST array of
  * num_slices (1..16) device pointers, 16-byte aligned. The caller zeroes its own slice beforehand and orders the
  * readers behind every rank's launch (a barrier after the call). Needs M/num_slices % 256 == 0, N % 32 == 0,
- * 16-byte aligned operands, K % 16 == 0, per-tensor scales. The context keeps the tensor maps of the last four
- * slice sets on the device; calls that share a context must be on one stream. */
+ * 16-byte aligned operands, K % 16 == 0. Scales: per tensor, or per row of A (float[M]) and / or per output column
+ * (float[N], 16-byte aligned) when those pointers are given; ranks that share one set of row / column scales sum
+ * products that are already scaled. The context keeps the tensor maps of the last four slice sets on the device; calls
+ * that share a context must be on one stream. */
 int cf_gemm_fp8_nt_reduce_scatter_f32(cf_ctx* ctx, int M, int N, int K, const void* d_A, int lda, int a_is_e5m2,
                                       const float* d_a_descale, const void* d_B, const float* d_b_descale,
+                                      const float* d_a_row_descale_or_null, const float* d_b_col_descale_or_null,
                                       void* const* slices, int num_slices, void* stream);
 /* Finishes a reduce-scatter: out[i] = bf16(acc[i]) and acc[i] = 0 (ready for the next accumulation). */
 int cf_f32_to_bf16_and_zero(float* d_acc, void* d_out, size_t n, void* stream);
@@ -272,6 +275,20 @@ int cf_gemm_fp8_swiglu_quant_act(cf_ctx* ctx, cf_act_slot* slot, int num_segment
                                  const int* d_offsets, const void* d_A, int lda, int a_is_e5m2, const float* d_a_descale,
                                  int per_segment_a_descale, const void* d_W_interleaved, const float* d_w_descale,
                                  void* d_h8, int ldh, void* stream);
+/* The per-token form of the same fusion (no counterpart in the reference, which scales per tensor): gate and up
+ * projection and SwiGLU in one GEMM launch, output h = bf16(silu(bf16 gate) * bf16 up) as bf16 [M, F] (row pitch ldh
+ * elements, ldh % 8 == 0, 16-byte aligned) together with max|h| of every row accumulated into d_row_amax[M] (integer
+ * atomicMax on the float bits; the caller zeroes it). cf_fp8_quantize_rowwise_given_amax_e4m3 then quantises h in one
+ * read: the [M, 2F] bf16 gate/up intermediate of the unfused sequence never reaches HBM, and the rows, their amax and
+ * the codes equal those of cf_gemm_fp8_nt + cf_swiglu_quantize_rowwise_e4m3 bit for bit. When the F dimension is
+ * sharded over ranks, max-reduce d_row_amax across them before quantising. Scales: *d_a_descale or one per row
+ * (d_a_row_descale, float[M]); *d_w_descale or one per interleaved weight row (float[2F] in the same 32-row
+ * interleaved order as the weight, 16-byte aligned). Dense rows only. */
+int cf_gemm_fp8_swiglu_bf16_rowamax(cf_ctx* ctx, int M, int F, int K, const void* d_A, int lda, int a_is_e5m2,
+                                    const float* d_a_descale, const float* d_a_row_descale_or_null,
+                                    const void* d_W_interleaved, const float* d_w_descale,
+                                    const float* d_w_col_descale_interleaved_or_null, void* d_h, int ldh, float* d_row_amax,
+                                    void* stream);
 /* out[e, (f/32)*64 + f%32, :] = gate[e, f, :], out[e, (f/32)*64 + 32 + f%32, :] = up[e, f, :]; F % 32 == 0, K % 16 == 0. */
 int cf_fp8_interleave_gate_up(const void* d_gate8, const void* d_up8, void* d_out8, int num_experts, int F, int K, void* stream);
 
@@ -306,7 +323,9 @@ int cf_fp8_linear_forward(cf_ctx* ctx, cf_act_slot* slot, const void* d_x, int M
  * the scale pair to quantise with (for delayed scaling: an ActSlot's snapshot pair) and all inputs and
  * outputs; the call itself uses no cudaMalloc, cudaFree or other allocating routine.
  *   y[M,N] bf16 (row stride ldy) = (*d_x_descale * *d_w_descale) * e4m3(x * *d_x_scale) . w8^T  [+ bias]
- * d_status_or_null: optional device int that receives a non-zero code if a bounded device-side wait gave up.
+ * d_status_or_null: optional device int that receives a non-zero code if a bounded device-side wait gave up
+ * (d_y is then incomplete). Without it the code goes to a word inside the array that no entry point reads, so
+ * such a failure is only observable when the caller passes its own word (and clears it before the call).
  * The first call on each device looks up the array's device address. All calls share the one array and it
  * keeps the previous call's contents (the call clears the word it needs zeroed): two calls that overlap on
  * the GPU, e.g. on different streams, race on it. */
@@ -379,6 +398,10 @@ int cf_gelu_forward(const void* d_x, void* d_out, size_t n, void* stream);
  * through cf_gemm_epilogue.d_a_row_descale. */
 int cf_fp8_quantize_rowwise_e4m3(const void* d_x, int ld_x, void* d_out, int ld_out, float* d_row_scale,
                                  float* d_row_descale, int rows, int cols, void* stream);
+/* The same quantiser for rows whose amax is already known (recorded by the kernel that produced them, e.g.
+ * cf_gemm_fp8_swiglu_bf16_rowamax, and max-reduced over ranks where the row is split): one read, one write. */
+int cf_fp8_quantize_rowwise_given_amax_e4m3(const void* d_x, int ld_x, void* d_out, int ld_out, const float* d_row_amax,
+                                            float* d_row_scale, float* d_row_descale, int rows, int cols, void* stream);
 /* The same on bf16(silu(gate) * up): swiglu_forward (kernels/activations.cu:28-40) and the re-quantisation before the
  * down projection (src/trainer.cu:7138-7146) in one pass; gate and up are [rows, cols] views with row stride ld_in. */
 int cf_swiglu_quantize_rowwise_e4m3(const void* d_gate, const void* d_up, int ld_in, void* d_out, int ld_out,

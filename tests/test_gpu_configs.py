@@ -161,6 +161,102 @@ def test_config3_full_size_sampled(cfb, ctx, oracle):
     del work
 
 
+def _interleaved(cfb, wgu8, dgu):
+    F = wgu8.shape[0] // 2
+    il = cfb.fp8_interleave_gate_up(wgu8.view(1, 2 * F, -1)).view(2 * F, -1)
+    return il, cfb.interleave_gate_up_vector(dgu, F)
+
+
+@pytest.mark.parametrize("M,H,F", [(384, 256, 640), (1000, 512, 96), (130, 128, 2048)])
+def test_fused_rowwise_mlp_equals_the_unfused_composite(cfb, ctx, oracle, M, H, F):
+    """Gate/up GEMM with the SwiGLU product and its per-row amax in the epilogue, then the given-amax quantiser: h, the row
+    scales, the E4M3 codes and the MLP output equal the unfused composite bit for bit, and the output meets the oracle."""
+    x = randn_bf16((M, H), seed=1, outlier_frac=0.002)
+    wgu8, dgu = _rowquant(cfb, randn_bf16((2 * F, H), std=0.05, seed=2))
+    wd8, dd = _rowquant(cfb, randn_bf16((H, F), std=0.05, seed=3))
+    y0 = torch.empty((M, H), dtype=torch.bfloat16, device="cuda")
+    w0 = cfb.swiglu_mlp_fp8_rowwise(ctx, x, wgu8, dgu, wd8, dd, y0)
+    il, dil = _interleaved(cfb, wgu8, dgu)
+    y1 = torch.full((M, H), float("nan"), dtype=torch.bfloat16, device="cuda")
+    w1 = cfb.swiglu_mlp_fp8_rowwise_fused(ctx, x, il, dil, wd8, dd, y1)
+    ctx.poll_status()
+    hs = torch.empty((M, F), dtype=torch.bfloat16, device="cuda")
+    cfb.swiglu_forward(w0["gu"][:, :F].contiguous(), w0["gu"][:, F:].contiguous(), hs)
+    assert torch.equal(w1["h"].view(torch.int16), hs.view(torch.int16))
+    assert torch.equal(w1["hmax"], hs.float().abs().amax(dim=1))
+    assert torch.equal(w1["dh"], w0["dh"]) and torch.equal(w1["h8"], w0["h8"])
+    assert torch.equal(y1.view(torch.int16), y0.view(torch.int16))
+    want = _mlp_oracle(oracle, bf16_to_u16(x), wgu8.cpu().numpy(), dgu.cpu().numpy(), wd8.cpu().numpy(), dd.cpu().numpy())
+    assert rel_fro(y1.float().cpu().numpy(), oracle.bf16_to_f32(want)) < TOL
+
+
+def test_fused_rowwise_mlp_sharded_as_two_ranks_would_run_it(cfb, ctx):
+    """Gate/up split by output features, down split by its contraction dimension, emulated rank after rank on one GPU:
+    the per-row amax is max-reduced over the feature shards before the quantiser, so every shard's codes equal the same
+    columns of the unsharded h8; the fp32 partial products of the down projection (row and column scales applied in the
+    epilogue) add up to the unsharded output within fp32 summation order."""
+    M, H, F, W = 512, 256, 1024, 2
+    x = randn_bf16((M, H), seed=5)
+    wgu8, dgu = _rowquant(cfb, randn_bf16((2 * F, H), std=0.05, seed=6))
+    wd8, dd = _rowquant(cfb, randn_bf16((H, F), std=0.05, seed=7))
+    il, dil = _interleaved(cfb, wgu8, dgu)
+    y_full = torch.empty((M, H), dtype=torch.bfloat16, device="cuda")
+    full = cfb.swiglu_mlp_fp8_rowwise_fused(ctx, x, il, dil, wd8, dd, y_full)
+    Fl = F // W
+    x8, dx = full["x8"], full["dx"]
+    hs, hmaxs = [], []
+    for r in range(W):
+        # rank r owns features [r*Fl, (r+1)*Fl): interleaved rows [2*r*Fl, 2*(r+1)*Fl)
+        il_r, dil_r = il[2 * r * Fl:2 * (r + 1) * Fl].contiguous(), dil[2 * r * Fl:2 * (r + 1) * Fl].contiguous()
+        h = torch.empty((M, Fl), dtype=torch.bfloat16, device="cuda")
+        hmax = torch.zeros(M, dtype=torch.float32, device="cuda")
+        cfb.gemm_fp8_swiglu_bf16_rowamax(ctx, M, Fl, H, x8, H, False, None, dx, il_r, None, dil_r, h, hmax)
+        hs.append(h); hmaxs.append(hmax)
+    hmax_all = torch.maximum(hmaxs[0], hmaxs[1])          # the max-all-reduce
+    assert torch.equal(hmax_all, full["hmax"])
+    acc = torch.zeros((M, H), dtype=torch.float32, device="cuda")
+    one = torch.ones(4, dtype=torch.float32, device="cuda")
+    for r in range(W):
+        h8 = torch.empty((M, Fl), dtype=torch.uint8, device="cuda")
+        dh = torch.empty(M, dtype=torch.float32, device="cuda")
+        cfb.fp8_quantize_rowwise_given_amax_e4m3(hs[r], h8, hmax_all, dh)
+        assert torch.equal(h8, full["h8"][:, r * Fl:(r + 1) * Fl]) and torch.equal(dh, full["dh"])
+        part = torch.empty((M, H), dtype=torch.float32, device="cuda")
+        cfb.lt_gemm_fp8_nt(ctx, M, H, Fl, h8, Fl, False, one, wd8[:, r * Fl:(r + 1) * Fl].contiguous(), one, part, H,
+                           a_row_descale=dh, b_col_descale=dd)
+        acc += part
+    ctx.poll_status()
+    assert rel_fro(acc.cpu().numpy(), y_full.float().cpu().numpy()) < 4e-3
+    # the reduce-scatter GEMM with row and column scales on one rank (its own slice only) gives the same fp32 sums
+    acc2 = torch.zeros((M, H), dtype=torch.float32, device="cuda")
+    for r in range(W):
+        h8 = torch.empty((M, Fl), dtype=torch.uint8, device="cuda")
+        dh = torch.empty(M, dtype=torch.float32, device="cuda")
+        cfb.fp8_quantize_rowwise_given_amax_e4m3(hs[r], h8, hmax_all, dh)
+        cfb.gemm_fp8_nt_reduce_scatter(ctx, M, H, Fl, h8, Fl, False, one, wd8[:, r * Fl:(r + 1) * Fl].contiguous(), one,
+                                       [acc2.data_ptr()], a_row_descale=dh, b_col_descale=dd)
+    ctx.poll_status()
+    assert rel_fro(acc2.cpu().numpy(), acc.cpu().numpy()) < 1e-6
+
+
+def test_fused_rowwise_mlp_full_size_sampled(cfb, ctx, oracle):
+    """M=16384, hidden 4096, ffn 14336: fused composite against sampled oracle rows and against the unfused one."""
+    M, H, F = 16384, 4096, 14336
+    x = randn_bf16((M, H), seed=1)
+    wgu8, dgu = _rowquant(cfb, randn_bf16((2 * F, H), std=0.02, seed=2))
+    wd8, dd = _rowquant(cfb, randn_bf16((H, F), std=0.02, seed=3))
+    il, dil = _interleaved(cfb, wgu8, dgu)
+    y = torch.empty((M, H), dtype=torch.bfloat16, device="cuda")
+    cfb.swiglu_mlp_fp8_rowwise_fused(ctx, x, il, dil, wd8, dd, y)
+    ctx.poll_status()
+    rows = [0, 127, 128, 255, 256, 8191, 16383]
+    want = _mlp_oracle(oracle, bf16_to_u16(x[rows]), wgu8.cpu().numpy(), dgu.cpu().numpy(), wd8.cpu().numpy(), dd.cpu().numpy())
+    assert rel_fro(y[rows].float().cpu().numpy(), oracle.bf16_to_f32(want)) < TOL
+    y0 = torch.empty((1024, H), dtype=torch.bfloat16, device="cuda")
+    cfb.swiglu_mlp_fp8_rowwise(ctx, x[2048:3072], wgu8, dgu, wd8, dd, y0)
+    assert torch.equal(y0.view(torch.int16), y[2048:3072].view(torch.int16))
+
+
 def _zipf_logits(rows, E, seed):
     g = torch.Generator(device="cuda").manual_seed(seed)
     p = torch.arange(1, E + 1, device="cuda", dtype=torch.float32) ** -1.1

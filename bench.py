@@ -920,6 +920,10 @@ def leg_sweep(args, env):
         cfb.lt_gemm_fp8_nt(ctx, Mm, Nl, Kk, a8, Kk, False, da, w8, dw, yout, Nl)
 
     def dgrad_gemm_bf16(i):
+        # the weight is read from the forward cache as it lies ([Nl, K] = [contraction, output] for this GEMM)
+        cfb.gemm_fp8_nn(ctx, Mm, Kk, Nl, dy8, Nl, True, dg, w8, Kk, dw, dx_b, Kk)
+
+    def dgrad_gemm_bf16_nt(i):
         cfb.lt_gemm_fp8_nt(ctx, Mm, Kk, Nl, dy8, Nl, True, dg, wt8, dw, dx_b, Kk)
 
     def dgrad_gemm_f32(i):
@@ -938,12 +942,15 @@ def leg_sweep(args, env):
     t_fwd = env.timed(fwd, steps, warmup, sampler)
     clocks = sampler.stop()
     t_dg = env.timed(dgrad_gemm_bf16, steps, warmup)
+    t_dg_nt = env.timed(dgrad_gemm_bf16_nt, steps, warmup)
     fl = SW_FLOP
     res = {"workload": "fp8_gemm_M32768_K8192_N28672_forward_e4m3_and_dgrad_e5m2xe4m3", "n_gpus": world, "steps": steps,
            "warmup": warmup, "scaling": "strong", "unit": UNIT,
            "sharding": "single GPU" if world == 1 else f"W sharded by output columns ({Nl} per rank): forward needs no exchange, dgrad sums partial dX over the ranks",
            "forward": {"ms": t_fwd, "tflops": fl / (t_fwd * 1e-3) / 1e12},
-           "dgrad_without_allreduce": {"ms": t_dg, "tflops": fl / (t_dg * 1e-3) / 1e12, "output": "bf16 (partial dX at N > 1)"}}
+           "dgrad_without_allreduce": {"ms": t_dg, "tflops": fl / (t_dg * 1e-3) / 1e12, "output": "bf16 (partial dX at N > 1)",
+                                       "weight_operand": "forward cache [N, K] read as it lies (no transposed cache)",
+                                       "ms_nt_on_transposed_cache": t_dg_nt}}
     if world > 1:
         t_f32 = env.timed(dgrad_f32_allreduce, steps, warmup)
         t_b16 = env.timed(dgrad_bf16_allreduce, steps, warmup)

@@ -74,6 +74,8 @@ SIGNATURES = {
     "cf_gemm_fp8_swiglu_bf16_rowamax": (ci, [vp, ci, ci, ci, vp, ci, ci, fp, fp, vp, fp, fp, vp, ci, fp, vp]),
     "cf_fp8_quantize_rowwise_given_amax_e4m3": (ci, [vp, ci, vp, ci, fp, fp, fp, ci, ci, vp]),
     "cf_f32_to_bf16_and_zero": (ci, [fp, vp, sz, vp]),
+    "cf_gemm_fp8_nn": (ci, [vp, ci, ci, ci, vp, ci, ci, fp, vp, ci, fp, vp, ci, ci, vp]),
+    "cf_gemm_fp8_nn_grouped": (ci, [vp, ci, ci, ci, ci, ip, ip, vp, ci, ci, fp, vp, fp, vp, ci, ci, vp]),
     "cf_gemm_fp8_nt_grouped": (ci, [vp, ci, ci, ci, ci, ip, ip, vp, ci, ci, fp, ci, vp, fp, vp, ci, vp]),
     "cf_gemm_fp8_nt_segments": (ci, [vp, ci, ci, ip, ci, ci, ci, ip, ip, vp, ci, ci, fp, ci, vp, fp, vp, ci, vp]),
     "cf_gemm_fp8_nt_segments_scatter": (ci, [vp, ci, ci, ip, ci, ci, ci, ip, ip, vp, ci, ci, fp, ci, vp, fp, vp, vp, vp, ci, vp]),
@@ -87,6 +89,8 @@ SIGNATURES = {
     "cf_fp8_linear_static_scratch": (ci, [vp, ci, ci, fp, fp, vp, fp, ci, vp, ci, vp, ci, ip, vp]),
     "cf_lion_step_f32_state": (ci, [vp, fp, fp, sz, cf, cf, cf, cf, vp, fp, C.c_uint]),
     "cf_lion_step_bf16_state": (ci, [vp, vp, fp, sz, cf, cf, cf, cf, vp, fp, C.c_uint]),
+    "cf_lion_step_f32_state_quantize": (ci, [vp, fp, fp, ci, ci, cf, cf, cf, cf, vp, fp, C.c_uint, fp, fp, fp, vp, vp]),
+    "cf_lion_step_bf16_state_quantize": (ci, [vp, vp, fp, ci, ci, cf, cf, cf, cf, vp, fp, C.c_uint, fp, fp, fp, vp, vp]),
     "cf_rmsnorm_forward": (ci, [vp, vp, vp, fp, ci, ci, cf, vp]),
     "cf_rmsnorm_quantize_e4m3_record": (ci, [vp, vp, vp, fp, vp, fp, fp, ci, ci, cf, vp]),
     "cf_rmsnorm_quantize_rowwise_e4m3": (ci, [vp, vp, vp, fp, vp, fp, fp, ci, ci, cf, vp]),

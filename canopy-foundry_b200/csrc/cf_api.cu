@@ -27,30 +27,33 @@ int cuda_fail(cudaError_t e, const char* what) {
     return CF_ERR_CUDA;
 }
 
+// Per-device caches below are written from any thread: relaxed atomics (every writer stores the same value).
 int sm_count() {
-    static int cached[64];
+    static std::atomic<int> cached[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    int& c = cached[dev & 63];
-    if (c == 0) {
-        int v = 0;
+    std::atomic<int>& c = cached[dev & 63];
+    int v = c.load(std::memory_order_relaxed);
+    if (v == 0) {
         if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
-        c = v;
+        c.store(v, std::memory_order_relaxed);
     }
-    return c;
+    return v;
 }
 
 int require_sm100() {
-    static int cached[64];   // 0 unknown, 1 ok, 2 unsupported
+    static std::atomic<int> cached[64];   // 0 unknown, 1 ok, 2 unsupported
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) { set_error("no CUDA device"); return CF_ERR_CUDA; }
-    int& c = cached[dev & 63];
-    if (c == 0) {
+    std::atomic<int>& c = cached[dev & 63];
+    int v = c.load(std::memory_order_relaxed);
+    if (v == 0) {
         int major = 0;
         cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
-        c = (major == 10) ? 1 : 2;
+        v = (major == 10) ? 1 : 2;
+        c.store(v, std::memory_order_relaxed);
     }
-    if (c != 1) { set_error("this library runs on compute capability 10.x (sm_100a) only"); return CF_ERR_UNSUPPORTED; }
+    if (v != 1) { set_error("this library runs on compute capability 10.x (sm_100a) only"); return CF_ERR_UNSUPPORTED; }
     return CF_OK;
 }
 
@@ -346,6 +349,45 @@ int cf_gemm_fp8_dw_accum_f32(cf_ctx* ctx, int M, int N, int K, const void* d_X_e
 int cf_gemm_fp8_dw_accum_bf16(cf_ctx* ctx, int M, int N, int K, const void* d_X_e4m3, int ldx, const float* d_ds_x,
                               const void* d_dY_e5m2, int ldy, const float* d_ds_dy, void* d_dW, int ldc, void* stream) {
     return dw_accum(ctx, M, N, K, d_X_e4m3, ldx, d_ds_x, d_dY_e5m2, ldy, d_ds_dy, d_dW, ldc, 3, as_stream(stream));
+}
+
+// C = A . B with the weight read as it lies in the forward cache ([K, N] per block): the dgrad direction without a
+// second, transposed weight cache.
+static int gemm_nn(cf_ctx* ctx, int groups, int rows, int N, int K, const int* d_counts, const int* d_offsets, const void* d_A,
+                   int lda, int a_is_e5m2, const float* d_a_descale, const void* d_B, int ldb, const float* d_b_descale,
+                   void* d_C, int ldc, int accumulate, cudaStream_t st) {
+    CF_REQUIRE(ctx != nullptr, "cf_gemm_fp8_nn: null context");
+    CF_REQUIRE(groups >= 1 && groups <= 1024 && rows >= 0 && N >= 0 && K > 0, "cf_gemm_fp8_nn: bad shape");
+    if (rows == 0 || N == 0) return CF_OK;
+    CF_REQUIRE(d_A && d_B && d_C && d_a_descale && d_b_descale, "cf_gemm_fp8_nn: null pointer");
+    CF_REQUIRE(lda >= K && ldb >= N && ldc >= N, "cf_gemm_fp8_nn: leading dimension smaller than the row length");
+    GemmParams p;
+    p.groups = groups;
+    p.M = rows; p.N = N; p.K = K;
+    p.d_counts = d_counts; p.d_offsets = d_offsets;
+    p.b_mn_major = 1; p.ldb = ldb;
+    p.d_a_descale = d_a_descale; p.d_b_descale = d_b_descale;
+    p.C = d_C; p.ldc = ldc; p.out_kind = accumulate ? 3 : 0;
+    p.a_e5m2 = a_is_e5m2 ? 1 : 0;
+    p.d_status = reinterpret_cast<Ctx*>(ctx)->d_status;
+    const int m_blocks = (rows + gemm_tile_m() - 1) / gemm_tile_m() + (d_counts ? groups : 0);
+    const int tiles = m_blocks * ((N + gemm_tile_n() - 1) / gemm_tile_n());
+    return launch_gemm_fp8_nt(d_A, lda, rows, d_B, static_cast<long long>(groups) * K, p, tiles, st);
+}
+
+int cf_gemm_fp8_nn(cf_ctx* ctx, int M, int N, int K, const void* d_A, int lda, int a_is_e5m2, const float* d_a_descale,
+                   const void* d_B_kn, int ldb, const float* d_b_descale, void* d_C, int ldc, int accumulate, void* stream) {
+    return gemm_nn(ctx, 1, M, N, K, nullptr, nullptr, d_A, lda, a_is_e5m2, d_a_descale, d_B_kn, ldb, d_b_descale, d_C, ldc,
+                   accumulate, as_stream(stream));
+}
+
+int cf_gemm_fp8_nn_grouped(cf_ctx* ctx, int num_groups, int max_total_rows, int N, int K, const int* d_counts,
+                           const int* d_offsets, const void* d_A, int lda, int a_is_e5m2, const float* d_a_descale,
+                           const void* d_B_stacked_kn, const float* d_b_descale, void* d_C, int ldc, int accumulate,
+                           void* stream) {
+    CF_REQUIRE(d_counts && d_offsets, "cf_gemm_fp8_nn_grouped: null counts or offsets");
+    return gemm_nn(ctx, num_groups, max_total_rows, N, K, d_counts, d_offsets, d_A, lda, a_is_e5m2, d_a_descale,
+                   d_B_stacked_kn, N, d_b_descale, d_C, ldc, accumulate, as_stream(stream));
 }
 
 int cf_gemm_fp8_nt_grouped(cf_ctx* ctx, int num_experts, int max_total_rows, int N, int K, const int* d_counts,

@@ -205,11 +205,11 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
 
 // kind::f8f6f4 instruction descriptor: D fp32 (bits 4-5 = 1), A format bits 7-9, B format bits 10-12
 // (0 = E4M3, 1 = E5M2), both operands K-major (bits 15,16 = 0), N>>3 in bits 17-22, M>>4 in bits 24-28.
-// mn_major: both operands are MN-major in shared memory (rows of the tile run along K, 128 contiguous bytes along
-// M / N): bits 15 and 16.
-__device__ __forceinline__ uint32_t make_idesc(int a_e5m2, int b_e5m2, int mma_m, int mn_major) {
+// An MN-major operand lies in shared memory with the rows of the tile running along K and 128 contiguous bytes along
+// M / N: bit 15 for A, bit 16 for B.
+__device__ __forceinline__ uint32_t make_idesc(int a_e5m2, int b_e5m2, int mma_m, int a_mn_major, int b_mn_major) {
     return (1u << 4) | (static_cast<uint32_t>(a_e5m2) << 7) | (static_cast<uint32_t>(b_e5m2) << 10) |
-           (mn_major ? ((1u << 15) | (1u << 16)) : 0u) |
+           (a_mn_major ? (1u << 15) : 0u) | (b_mn_major ? (1u << 16) : 0u) |
            (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(mma_m >> 4) << 24);
 }
 
@@ -219,6 +219,7 @@ struct TileCoord {
     int valid_rows;  // rows of the tile that belong to the expert (<= tile rows)
     int n0;          // first output column
     int b_row0;      // first row of the stacked [E*N, K] weight block
+    int weight;      // index of the weight block (0 for a dense problem)
     int group;
     void* out_base;  // where this tile's rows are written (p.C, or a per-segment buffer that may live on a peer GPU)
     long long out_row0;  // output row of the tile's first row inside out_base
@@ -248,6 +249,7 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, i
     c.n0 = nb * BN;
     if (p.groups <= 1 && p.d_counts == nullptr) {
         c.group = 0;
+        c.weight = 0;
         c.row0 = mb * TM;
         c.valid_rows = min(TM, p.M - c.row0);
         c.b_row0 = c.n0;
@@ -265,7 +267,8 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, i
     c.group = e;
     c.row0 = p.d_offsets[e] + mb * TM;
     c.valid_rows = min(TM, cnt - mb * TM);
-    c.b_row0 = (p.d_group_weight ? p.d_group_weight[e] : e) * p.N + c.n0;
+    c.weight = p.d_group_weight ? p.d_group_weight[e] : e;
+    c.b_row0 = c.weight * p.N + c.n0;
     if (p.d_group_out) {
         c.out_base = p.d_group_out[e];
         c.out_row0 = p.d_group_out_row0[e] + static_cast<long long>(mb) * TM;
@@ -398,8 +401,12 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                         // K-major operands: x runs along K; MN-major operands ([K, M] / [K, N] in memory): x runs
                         // along M / N and the box rows are K
                         const bool mn = WIDE && p.mn_major;
+                        const bool bmn = WIDE && (p.mn_major || p.b_mn_major);
                         const int ax = mn ? a_row : kb * BK, ay = mn ? kb * BK : a_row;
-                        const int bx = mn ? b_row : kb * BK, by = mn ? kb * BK : b_row;
+                        // MN-major B: the weight block lies as [K, N] (stacked blocks: [weights * K, N]); this CTA's half
+                        // of the tile's columns is one 128-byte box row, the box rows run along K
+                        const int bx = bmn ? tc.n0 + static_cast<int>(cta_rank) * C::B_ROWS : kb * BK;
+                        const int by = bmn ? tc.weight * p.K + kb * BK : b_row;
                         tma_load_2d_pair(smem_a + s * A_STAGE, &map_a, full_dst + 8 * s, ax, ay);
                         tma_load_2d_pair(smem_b + s * B_STAGE, &map_b, full_dst + 8 * s, bx, by);
                     } else {
@@ -421,7 +428,8 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
         if (lane == 0 && leader) {
             const bool mn = WIDE && p.mn_major;
-            const uint32_t idesc = make_idesc(p.a_e5m2, p.b_e5m2, TM, mn);
+            const bool bmn = WIDE && (p.mn_major || p.b_mn_major);
+            const uint32_t idesc = make_idesc(p.a_e5m2, p.b_e5m2, TM, mn, bmn);
             int it = 0, local_tile = 0;
             bool ok = true;
             for (int tile = unit; ok && tile < total_tiles; tile += n_units, ++local_tile) {
@@ -435,20 +443,13 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     tcgen05_fence_after();
                     const uint64_t adesc = make_smem_desc(smem_a + s * A_STAGE);
                     const uint64_t bdesc = make_smem_desc(smem_b + s * B_STAGE);
-                    if (WIDE && mn) {
-                        // MN-major: 32 elements of K are 32 rows of 128 bytes = +256 in the (addr >> 4) field
+                    // One MMA covers 32 elements of K. K-major operand: 32 bytes further inside the 128B swizzle atom = +2
+                    // in the descriptor's (address >> 4) field; MN-major operand: 32 rows of 128 bytes further = +256.
+                    const uint32_t a_step = (WIDE && mn) ? 256u : 2u, b_step = (WIDE && bmn) ? 256u : 2u;
 #pragma unroll
-                        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                            if (PAIR) umma_f8_pair(tmem_d, adesc + 256 * kk, bdesc + 256 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
-                            else umma_f8(tmem_d, adesc + 256 * kk, bdesc + 256 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
-                        }
-                    } else {
-                        // K-major: advancing 32 bytes inside the 128B swizzle atom = +2 in the (addr >> 4) field
-#pragma unroll
-                        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-                            if (PAIR) umma_f8_pair(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
-                            else umma_f8(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
-                        }
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        if (PAIR) umma_f8_pair(tmem_d, adesc + a_step * kk, bdesc + b_step * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
+                        else umma_f8(tmem_d, adesc + a_step * kk, bdesc + b_step * kk, idesc, (kb | kk) != 0 ? 1u : 0u);
                     }
                     // frees the stage (in both CTAs of a pair) once these MMAs have read it
                     if (PAIR) tcgen05_commit_pair(empty_bar + 8 * s); else tcgen05_commit(empty_bar + 8 * s);
@@ -978,8 +979,14 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     if (rc != CF_OK) return rc;
     const uintptr_t aa = reinterpret_cast<uintptr_t>(d_A), ba = reinterpret_cast<uintptr_t>(d_B);
     const bool tma_ok = p.mn_major ? ((aa % 16 == 0) && (ba % 16 == 0) && (lda % 16 == 0) && (p.ldb % 16 == 0))
-                                   : ((aa % 16 == 0) && (ba % 16 == 0) && (lda % 16 == 0) && (p.K % 16 == 0));
-    if (p.mn_major && !tma_ok) { set_error("MN-major operands need 16-byte aligned bases and row pitches"); return CF_ERR_UNSUPPORTED; }
+                      : p.b_mn_major ? ((aa % 16 == 0) && (ba % 16 == 0) && (lda % 16 == 0) && (p.K % 16 == 0) && (p.ldb % 16 == 0) && (p.N % 16 == 0))
+                                     : ((aa % 16 == 0) && (ba % 16 == 0) && (lda % 16 == 0) && (p.K % 16 == 0));
+    if ((p.mn_major || p.b_mn_major) && !tma_ok) { set_error("MN-major operands need 16-byte aligned bases and row pitches (and K, N multiples of 16)"); return CF_ERR_UNSUPPORTED; }
+    if (p.b_mn_major && p.groups > 1 && p.K % BK != 0) {
+        // a k-block that runs past one weight block would read the next block's rows
+        set_error("grouped GEMM over [K, N] weight blocks: K must be a multiple of %d", BK);
+        return CF_ERR_UNSUPPORTED;
+    }
     const uintptr_t ca = reinterpret_cast<uintptr_t>(p.C);
     // per-segment output buffers: the caller guarantees 16-byte aligned bases (checked at the API boundary)
     p.c_vec = (p.out_kind == 0 || p.out_kind == 3) && (p.d_group_out != nullptr || ca % 16 == 0) && (p.ldc % 8 == 0) &&
@@ -1021,7 +1028,7 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     // Paired CTAs (256-row tiles) pay off when the row blocks are mostly full; small or very ragged problems
     // keep the 128-row single-CTA tiles.
     const long long rows_per_group = (p.d_counts ? a_rows / (p.groups > 0 ? p.groups : 1) : p.M);
-    bool pair = p.mn_major || rows_per_group >= 512;
+    bool pair = p.mn_major || p.b_mn_major || rows_per_group >= 512;
     const int pairs = pair ? max_resident_pairs() : 0;
     if (pairs <= 0) pair = false;
 
@@ -1034,6 +1041,13 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
         r = make_map(&map_a, d_A, p.K, p.M, lda, BK);
         if (r != CF_OK) return r;
         r = make_map(&map_b, d_B, p.K, p.N, p.ldb, BK);
+        if (r != CF_OK) return r;
+    } else if (p.b_mn_major) {
+        // A is [rows, K] as usual; B is the stacked [weights * K, N] tensor with pitch p.ldb (b_rows counts its rows)
+        if (!pair) { set_error("[K, N] weight operands need the CTA-pair form (clusters available)"); return CF_ERR_UNSUPPORTED; }
+        r = make_map(&map_a, d_A, a_rows, p.K, lda, BM);
+        if (r != CF_OK) return r;
+        r = make_map(&map_b, d_B, b_rows, p.N, p.ldb, BK);
         if (r != CF_OK) return r;
     } else {
         r = make_map(&map_a, d_A, a_rows, p.K, lda, BM);
@@ -1114,7 +1128,7 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
     }
     int dev = 0;
     CF_CUDA(cudaGetDevice(&dev));
-    const bool wide = (p.out_kind >= 1 && p.out_kind <= 3) || p.d_out_runs != nullptr;
+    const bool wide = (p.out_kind >= 1 && p.out_kind <= 3) || p.d_out_runs != nullptr || p.b_mn_major;
     if (pair) {
         // tile_upper_bound counts 128-row blocks; a pair tile covers two of them
         const int n_blocks = (p.N + BN - 1) / BN;

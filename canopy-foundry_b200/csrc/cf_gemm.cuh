@@ -50,7 +50,8 @@ struct GemmParams {
     void* const* d_peer_bases = nullptr;
     int peer_maps_ready = 0;        // the maps at d_peer_maps already describe peer_out_host (cached by the caller)
     int mn_major = 0;               // operands are [K, M] and [K, N] in memory (un-transposed weight-gradient form)
-    long long ldb = 0;              // mn_major: row pitch of B in bytes
+    int b_mn_major = 0;             // only B is [K, N] in memory (weight blocks [weights * K, N] read as they lie): C = A . B
+    long long ldb = 0;              // mn_major / b_mn_major: row pitch of B in bytes
     int a_e5m2 = 0;
     int b_e5m2 = 0;
     int* d_status = nullptr;        // context status word (bounded-wait failures)

@@ -19,9 +19,9 @@ __all__ = [
     "fp8_quantize_e4m3_record", "fp8_quantize_e5m2_record", "fp8_update_delayed_scale",
     "fp8_quantize_transpose_e4m3", "fp8_quant_and_transpose_e4m3", "transpose_u8", "fp8_clip_probe",
     "fp8_elem_clip_count", "fp8_pack_bf16_e4m3_raw", "fp8_pack_bf16_e4m3_raw_and_dequant",
-    "fp8_unpack_e4m3_raw_bf16", "lt_gemm_fp8_nt", "lt_gemm_fp8_tn_accum_f32", "gemm_fp8_dw_accum", "gemm_fp8_nt_reduce_scatter", "f32_to_bf16_and_zero", "gemm_fp8_nt_grouped", "gemm_fp8_nt_segments", "gemm_fp8_nt_segments_scatter",
+    "fp8_unpack_e4m3_raw_bf16", "lt_gemm_fp8_nt", "gemm_fp8_nn", "gemm_fp8_nn_grouped", "lt_gemm_fp8_tn_accum_f32", "gemm_fp8_dw_accum", "gemm_fp8_nt_reduce_scatter", "f32_to_bf16_and_zero", "gemm_fp8_nt_grouped", "gemm_fp8_nt_segments", "gemm_fp8_nt_segments_scatter",
     "fp8_quant_act", "fp8_swiglu_quant_act", "gemm_fp8_swiglu_quant_act", "fp8_interleave_gate_up", "refresh_fp8_weight", "fp8_linear_forward", "bias_add_strided_bf16", "swiglu_forward",
-    "gelu_forward", "lion_step", "fp8_quantize_rowwise_e4m3", "fp8_quantize_rowwise_given_amax_e4m3", "gemm_fp8_swiglu_bf16_rowamax", "interleave_gate_up_vector", "swiglu_mlp_fp8_rowwise_fused", "swiglu_quantize_rowwise_e4m3", "swiglu_quantize_e4m3_record",
+    "gelu_forward", "lion_step", "lion_step_quantize", "fp8_quantize_rowwise_e4m3", "fp8_quantize_rowwise_given_amax_e4m3", "gemm_fp8_swiglu_bf16_rowamax", "interleave_gate_up_vector", "swiglu_mlp_fp8_rowwise_fused", "swiglu_quantize_rowwise_e4m3", "swiglu_quantize_e4m3_record",
     "rmsnorm_forward", "rmsnorm_quantize_e4m3_record", "rmsnorm_quantize_rowwise_e4m3", "fp8_rmsnorm_quant_act", "rmsnorm_clip_forward", "rmsnorm_clip_quantize_e4m3_record", "fp8_rmsnorm_clip_quant_act",
     "moe_topk_route_f32", "moe_build_expert_row_lists", "moe_expert_offsets_from_counts",
     "moe_gather_rows_u8", "moe_gather_rows_bf16", "moe_scatter_accumulate_rows_bf16",
@@ -294,6 +294,20 @@ def f32_to_bf16_and_zero(acc, out):
     check(_L().cf_f32_to_bf16_and_zero(_p(acc), _p(out), acc.numel(), _s()))
 
 
+def gemm_fp8_nn(ctx, M, N, K, A, lda, a_is_e5m2, a_descale, B_kn, ldb, b_descale, Cout, ldc, accumulate=False):
+    """C[M,N] = A[M,K] . B[K,N]: the dgrad direction, reading the forward weight cache ([out,in] = [K,N]) as it lies."""
+    check(_L().cf_gemm_fp8_nn(ctx.handle, M, N, K, _p(A), lda, int(a_is_e5m2), _p(a_descale), _p(B_kn), ldb, _p(b_descale),
+                              _p(Cout), ldc, int(accumulate), _s()))
+
+
+def gemm_fp8_nn_grouped(ctx, num_groups, max_total_rows, N, K, counts, offsets, A, lda, a_is_e5m2, a_descale, B_stacked_kn,
+                        b_descale, Cout, ldc, accumulate=False):
+    """Ragged per-expert dgrad over the stacked forward cache [E, K, N] (no transposed cache)."""
+    check(_L().cf_gemm_fp8_nn_grouped(ctx.handle, num_groups, max_total_rows, N, K, _p(counts), _p(offsets), _p(A), lda,
+                                      int(a_is_e5m2), _p(a_descale), _p(B_stacked_kn), _p(b_descale), _p(Cout), ldc,
+                                      int(accumulate), _s()))
+
+
 def gemm_fp8_nt_grouped(ctx, num_experts, max_total_rows, N, K, counts, offsets, A, lda, a_is_e5m2, a_descale,
                         per_expert_a_descale, B, b_descale, Cout, ldc):
     check(_L().cf_gemm_fp8_nt_grouped(ctx.handle, num_experts, max_total_rows, N, K, _p(counts), _p(offsets), _p(A),
@@ -338,6 +352,16 @@ def lion_step(w, m, grad, lr, beta1, beta2, wd, weight_amax=None, sr_seed=0):
     """lion_step (include/ida_native/kernels.hpp:1089-1108); m float32 or bfloat16 selects the overload."""
     fn = _L().cf_lion_step_f32_state if m.dtype == torch.float32 else _L().cf_lion_step_bf16_state
     check(fn(_p(w), _p(m), _p(grad), w.numel(), lr, beta1, beta2, wd, _s(), _p(weight_amax), sr_seed))
+
+
+def lion_step_quantize(w, m, grad, lr, beta1, beta2, wd, weight_amax, quant_amax, scale_out, descale_out, w8,
+                       w8_transposed=None, sr_seed=0):
+    """lion_step that also writes the E4M3 cache(s) of the [rows, cols] weight in the same pass (scale from quant_amax,
+    the amax an earlier step left; this step's amax goes to weight_amax)."""
+    rows, cols = w.shape
+    fn = _L().cf_lion_step_f32_state_quantize if m.dtype == torch.float32 else _L().cf_lion_step_bf16_state_quantize
+    check(fn(_p(w), _p(m), _p(grad), rows, cols, lr, beta1, beta2, wd, _s(), _p(weight_amax), sr_seed, _p(quant_amax),
+             _p(scale_out), _p(descale_out), _p(w8), _p(w8_transposed)))
 
 
 def gelu_forward(x, out):

@@ -19,17 +19,29 @@
 #include <string>
 
 #include "canopy_fp8.h"
+#include "ida_native/gemm_trace.hpp"
 
 namespace cf_shim {
 inline void check(int rc, const char* fn) {
     if (rc != CF_OK) throw std::runtime_error(std::string(fn) + ": " + cf_last_error());
 }
+// The context the ida_native:: operators without a context parameter (moe_grouped_expert_forward_fp8) use on this
+// thread. The trainer owns it: cf_ctx_create + cf_ctx_reserve_workspace in build_fp8_ctx, set_thread_context on every
+// training-body thread that shares it (the reference runs one body per thread, include/ida_native/kernels.hpp:599-604),
+// set_thread_context(nullptr) and cf_ctx_destroy at teardown. The shim never creates, grows or frees a context.
+inline cf_ctx*& thread_context_slot() {
+    thread_local cf_ctx* ctx = nullptr;
+    return ctx;
+}
+inline void set_thread_context(cf_ctx* ctx) { thread_context_slot() = ctx; }
+inline cf_ctx* thread_context() { return thread_context_slot(); }
 }  // namespace cf_shim
 
 template <class Fp8CtxT>
 static void lt_gemm_fp8_nt(Fp8CtxT& f, int M, int N, int K, const void* A, int lda, cudaDataType_t a_type,
                            const float* a_descale, const void* B, const float* b_descale, __nv_bfloat16* C, int ldc,
                            cudaStream_t s) {
+    ::ida_native::gemm_trace::record_current(static_cast<long long>(M), static_cast<long long>(N), static_cast<long long>(K));   // :4506
     cf_shim::check(cf_gemm_fp8_nt(f.cf, M, N, K, A, lda, a_type == CUDA_R_8F_E5M2 ? 1 : 0, a_descale, B, b_descale, C, ldc,
                                   nullptr, s), "lt_gemm_fp8_nt");
 }
@@ -37,6 +49,7 @@ static void lt_gemm_fp8_nt(Fp8CtxT& f, int M, int N, int K, const void* A, int l
 template <class Fp8CtxT>
 static void lt_gemm_fp8_tn_accum_f32(Fp8CtxT& f, int M, int N, int K, const void* Xt_e4m3, const float* ds_x,
                                      const void* dYt_e5m2, const float* ds_dy, float* dW, int ldc_dw, cudaStream_t s) {
+    ::ida_native::gemm_trace::record_current(static_cast<long long>(M), static_cast<long long>(N), static_cast<long long>(K));   // :4606
     cf_shim::check(cf_gemm_fp8_tn_accum_f32(f.cf, M, N, K, Xt_e4m3, ds_x, dYt_e5m2, ds_dy, dW, ldc_dw, s),
                    "lt_gemm_fp8_tn_accum_f32");
 }
@@ -45,6 +58,7 @@ template <class Fp8CtxT>
 static void lt_gemm_fp8_tn_accum_f32(Fp8CtxT& f, int M, int N, int K, const void* Xt_e4m3, const float* ds_x,
                                      const void* dYt_e5m2, const float* ds_dy, __nv_bfloat16* dW, int ldc_dw,
                                      cudaStream_t s) {
+    ::ida_native::gemm_trace::record_current(static_cast<long long>(M), static_cast<long long>(N), static_cast<long long>(K));   // :4678
     cf_shim::check(cf_gemm_fp8_tn_accum_bf16(f.cf, M, N, K, Xt_e4m3, ds_x, dYt_e5m2, ds_dy, dW, ldc_dw, s),
                    "lt_gemm_fp8_tn_accum_f32(bf16)");
 }

@@ -8,21 +8,27 @@
 // Signatures, default arguments and argument meaning are the reference's; nothing in trainer.cu changes
 // for these calls.
 #include "ida_native/kernels.hpp"
+#include "ida_native/pack_trace.hpp"
 
 #include <stdexcept>
 #include <string>
 
 #include "canopy_fp8.h"
+#include "cf_trainer_shim.hpp"
 
 namespace {
 inline void cf_check(int rc, const char* fn) {
     if (rc != CF_OK) throw std::runtime_error(std::string(fn) + ": " + cf_last_error());
 }
-// Operators whose reference signature has no context parameter but whose tensor-core implementation needs
-// one (status word, workspace) share a lazily created per-thread context.
-cf_ctx* default_ctx() {
-    thread_local cf_ctx* ctx = nullptr;
-    if (!ctx) cf_check(cf_ctx_create(&ctx, 0), "cf_ctx_create");
+// Operators whose reference signature has no context parameter but whose tensor-core implementation needs one
+// (status word, workspace) use the context the integrator registered for the calling thread with
+// cf_shim::set_thread_context (cf_trainer_shim.hpp): created once at set-up next to the trainer's own Fp8Ctx, with its
+// workspace reserved there, and destroyed by its owner. Nothing on the call path allocates.
+cf_ctx* thread_ctx(const char* fn) {
+    cf_ctx* ctx = cf_shim::thread_context();
+    if (!ctx)
+        throw std::runtime_error(std::string(fn) + ": no cf_ctx registered for this thread (call cf_shim::set_thread_context "
+                                                   "at set-up, after cf_ctx_create and cf_ctx_reserve_workspace)");
     return ctx;
 }
 }  // namespace
@@ -37,24 +43,32 @@ void fp8_scale_from_amax(const float* d_amax, float fp8_max, float* d_scale, flo
     cf_check(cf_fp8_scale_from_amax(d_amax, fp8_max, d_scale, d_descale, s), "fp8_scale_from_amax");
 }
 void fp8_quantize_e4m3(const __nv_bfloat16* d_x, void* d_out, const float* d_scale, std::size_t n, cudaStream_t s) {
+    pack_trace::record(pack_trace::K_FP8_PACK, n, n * sizeof(__nv_bfloat16), n);      // kernels/fp8.cu:264-266
     cf_check(cf_fp8_quantize_e4m3(d_x, d_out, d_scale, n, s), "fp8_quantize_e4m3");
 }
 void fp8_quantize_e5m2(const __nv_bfloat16* d_x, void* d_out, const float* d_scale, std::size_t n, cudaStream_t s) {
+    pack_trace::record(pack_trace::K_FP8_PACK, n, n * sizeof(__nv_bfloat16), n);      // kernels/fp8.cu:274-276
     cf_check(cf_fp8_quantize_e5m2(d_x, d_out, d_scale, n, s), "fp8_quantize_e5m2");
 }
 void fp8_quantize_transpose_e4m3(const __nv_bfloat16* d_w, void* d_out, const float* d_scale, int K, int N, cudaStream_t s) {
+    const std::size_t elements = static_cast<std::size_t>(K) * N;
+    pack_trace::record(pack_trace::K_FP8_PACK_TRANSPOSE, elements, elements * sizeof(__nv_bfloat16), elements);   // :285-287
     cf_check(cf_fp8_quantize_transpose_e4m3(d_w, d_out, d_scale, K, N, s), "fp8_quantize_transpose_e4m3");
 }
 void fp8_quant_and_transpose_e4m3(const __nv_bfloat16* d_in, void* d_act8_out, void* d_snap_out, const float* d_scale,
                                   int K, int N, cudaStream_t s) {
+    const std::size_t elements = static_cast<std::size_t>(K) * N;
+    pack_trace::record(pack_trace::K_FP8_PACK_FUSED_TRANSPOSE, elements, elements * sizeof(__nv_bfloat16), 2 * elements);   // :297-299
     cf_check(cf_fp8_quant_and_transpose_e4m3(d_in, d_act8_out, d_snap_out, d_scale, K, N, s), "fp8_quant_and_transpose_e4m3");
 }
 void fp8_quantize_e4m3_record(const __nv_bfloat16* d_x, void* d_out, const float* d_scale, float* d_amax, std::size_t n,
                               cudaStream_t s) {
+    pack_trace::record(pack_trace::K_FP8_PACK, n, n * sizeof(__nv_bfloat16), n);      // kernels/fp8.cu:314-316
     cf_check(cf_fp8_quantize_e4m3_record(d_x, d_out, d_scale, d_amax, n, s), "fp8_quantize_e4m3_record");
 }
 void fp8_quantize_e5m2_record(const __nv_bfloat16* d_x, void* d_out, const float* d_scale, float* d_amax, std::size_t n,
                               cudaStream_t s) {
+    pack_trace::record(pack_trace::K_FP8_PACK, n, n * sizeof(__nv_bfloat16), n);      // kernels/fp8.cu:325-327
     cf_check(cf_fp8_quantize_e5m2_record(d_x, d_out, d_scale, d_amax, n, s), "fp8_quantize_e5m2_record");
 }
 void fp8_clip_probe(const float* d_amax, const float* d_scale, float fp8_max, float* d_stats, cudaStream_t s) {
@@ -72,11 +86,14 @@ void fp8_update_delayed_scale(const float* d_amax, float fp8_max, float* d_scale
 // kernels/fp8.cu:491-528
 void fp8_pack_bf16_e4m3_raw(const __nv_bfloat16* d_x, std::uint8_t* d_out, float* d_amax, float* d_scale, float* d_descale,
                             int* d_bad_count, std::size_t n, cudaStream_t s) {
+    pack_trace::record(pack_trace::K_FP8_PACK, n, n * sizeof(__nv_bfloat16), n);      // kernels/fp8.cu:502
     cf_check(cf_fp8_pack_bf16_e4m3_raw(d_x, d_out, d_amax, d_scale, d_descale, d_bad_count, n, s), "fp8_pack_bf16_e4m3_raw");
 }
 void fp8_pack_bf16_e4m3_raw_and_dequant(const __nv_bfloat16* d_x, std::uint8_t* d_out, __nv_bfloat16* d_dequant,
                                         float* d_amax, float* d_scale, float* d_descale, int* d_bad_count, std::size_t n,
                                         cudaStream_t s) {
+    pack_trace::record(pack_trace::K_FP8_PACK_DEQUANT, n, n * sizeof(__nv_bfloat16),
+                       n * sizeof(std::uint8_t) + n * sizeof(__nv_bfloat16));          // kernels/fp8.cu:517-520
     cf_check(cf_fp8_pack_bf16_e4m3_raw_and_dequant(d_x, d_out, d_dequant, d_amax, d_scale, d_descale, d_bad_count, n, s),
              "fp8_pack_bf16_e4m3_raw_and_dequant");
 }
@@ -153,10 +170,9 @@ void moe_grouped_expert_forward_fp8(const void* d_hidden, const float* d_fcin_de
                                     const int* d_row_indices, const void* d_fc_in_w, const float* d_fc_in_descale,
                                     const void* d_fc_out_w, const float* d_fc_out_descale, __nv_bfloat16* d_mixed, int rows,
                                     int H, int Ie, int num_experts, int total_selected_rows, cudaStream_t stream) {
-    cf_ctx* ctx = default_ctx();
-    // Workspace grows only when a larger problem than any before arrives (set-up cost, not steady state).
-    const std::size_t need = static_cast<std::size_t>(total_selected_rows) * (3 * static_cast<std::size_t>(H) + 4 * static_cast<std::size_t>(Ie)) + 4096;
-    cf_check(cf_ctx_reserve_workspace(ctx, need), "cf_ctx_reserve_workspace");
+    // The tensor-core form needs total_selected_rows * (3 H + 4 Ie) + 4 KiB of workspace from the registered context;
+    // with less reserved the call fails with CF_ERR_LIMIT (surfaced as std::runtime_error) instead of allocating.
+    cf_ctx* ctx = thread_ctx("moe_grouped_expert_forward_fp8");
     cf_check(cf_moe_grouped_expert_forward_fp8(ctx, d_hidden, d_fcin_descale, fcin_is_e5m2, d_route_weights, d_counts,
                                                d_offsets, d_row_indices, d_fc_in_w, d_fc_in_descale, d_fc_out_w,
                                                d_fc_out_descale, d_mixed, rows, H, Ie, num_experts, total_selected_rows,

@@ -186,6 +186,24 @@ int cf_gemm_fp8_dw_accum_f32(cf_ctx* ctx, int M, int N, int K, const void* d_X_e
 int cf_gemm_fp8_dw_accum_bf16(cf_ctx* ctx, int M, int N, int K, const void* d_X_e4m3, int ldx, const float* d_ds_x,
                               const void* d_dY_e5m2, int ldy, const float* d_ds_dy, void* d_dW, int ldc, void* stream);
 
+/* The data-gradient direction of the FP8 linear, dX[M,N] = dY[M,K] . W[K,N], reading the weight from the FORWARD cache
+ * as it lies ([out, in] = [K, N] row-major with pitch ldb): the tensor cores take B as an MN-major operand, so the second,
+ * transposed weight cache of src/trainer.cu:3284-3294 (bwd8) and the transposed quantise that fills it (kernels/fp8.cu:
+ * 281-290) are not needed for src/trainer.cu:8282-8314. A is E5M2 (a_is_e5m2 = 1, the gradient) or E4M3, [M, K] with row
+ * pitch lda; C is bf16 [M, N] with pitch ldc, stored (accumulate = 0) or added to in fp32 with one rounding
+ * (accumulate = 1, the beta = 1 calls of the reference). Results equal cf_gemm_fp8_nt on the transposed weight.
+ * Needs 16-byte aligned bases and pitches, K % 16 == 0, N % 16 == 0, the CTA-pair form. */
+int cf_gemm_fp8_nn(cf_ctx* ctx, int M, int N, int K, const void* d_A, int lda, int a_is_e5m2, const float* d_a_descale,
+                   const void* d_B_kn, int ldb, const float* d_b_descale, void* d_C, int ldc, int accumulate, void* stream);
+/* The same for ragged expert groups: group g multiplies compact rows [d_offsets[g], +d_counts[g]) of A with block g of
+ * the stacked forward cache [num_groups, K, N] (contiguous blocks). This is the dgrad of the MoE expert bank that
+ * src/trainer.cu:7829-7856 leaves in bf16 because the reference's transposed cache of a multi-expert block is not
+ * per-expert-correct: here no transposed cache exists, every expert's own [K, N] block is read in place. K % 128 == 0. */
+int cf_gemm_fp8_nn_grouped(cf_ctx* ctx, int num_groups, int max_total_rows, int N, int K, const int* d_counts,
+                           const int* d_offsets, const void* d_A, int lda, int a_is_e5m2, const float* d_a_descale,
+                           const void* d_B_stacked_kn, const float* d_b_descale, void* d_C, int ldc, int accumulate,
+                           void* stream);
+
 /* The ragged per-expert GEMMs of src/trainer.cu:6893-6927 as ONE launch with a device-side schedule:
  * for every expert e, rows [d_offsets[e], d_offsets[e]+d_counts[e]) of the compact A8 [total_rows,K]
  * are multiplied with B8[e] ([N,K] slice of a [E,N,K] block) into the same rows of compact C [.,ldc].
@@ -341,6 +359,26 @@ int cf_lion_step_f32_state(void* d_w, float* d_m, const float* d_grad, size_t n,
                            void* stream, float* d_weight_amax, unsigned sr_seed);
 int cf_lion_step_bf16_state(void* d_w, void* d_m, const float* d_grad, size_t n, float lr, float beta1, float beta2, float wd,
                             void* stream, float* d_weight_amax, unsigned sr_seed);
+/* kernels/lion.cu:39-119 and src/trainer.cu:4694-4712 in ONE pass (no counterpart as a single call): the Lion step of a
+ * [rows, cols] weight that also writes its E4M3 caches, so the weight refresh needs no pass of its own. Weights,
+ * momentum and the amax recorded into d_weight_amax (caller-zeroed) equal cf_lion_step_*_state bit for bit. The
+ * stochastically rounded bf16 value just written is quantised with scale = 448 / max(*d_quant_amax, 1e-12) (published to
+ * d_scale_out / d_descale_out like cf_refresh_fp8_weight does) into d_w8, the cache in the master's own layout
+ * [rows, cols], and, when d_w8_transposed_or_null is given, into the other layout [cols, rows]: the bytes
+ * cf_refresh_fp8_weight(recompute_amax = 0) would produce from that amax. *d_quant_amax is the amax an EARLIER step left
+ * (delayed by one step: this step's amax is complete only when the pass ends), so it must be a different word from
+ * d_weight_amax; a trainer alternates two words per weight. Needs cols % 4 == 0, an 8-byte aligned master, 16-byte
+ * aligned gradient and fp32 state (8-byte aligned bf16 state), a 4-byte aligned d_w8; CF_ERR_UNSUPPORTED otherwise (run
+ * the plain step and cf_refresh_fp8_weight then). With cf_gemm_fp8_nn the dgrad GEMMs read the native-layout cache as
+ * it lies, so the transposed cache is only needed by callers that keep the reference's NT dgrad. */
+int cf_lion_step_f32_state_quantize(void* d_w, float* d_m, const float* d_grad, int rows, int cols, float lr, float beta1,
+                                    float beta2, float wd, void* stream, float* d_weight_amax, unsigned sr_seed,
+                                    const float* d_quant_amax, float* d_scale_out, float* d_descale_out, void* d_w8,
+                                    void* d_w8_transposed_or_null);
+int cf_lion_step_bf16_state_quantize(void* d_w, void* d_m, const float* d_grad, int rows, int cols, float lr, float beta1,
+                                     float beta2, float wd, void* stream, float* d_weight_amax, unsigned sr_seed,
+                                     const float* d_quant_amax, float* d_scale_out, float* d_descale_out, void* d_w8,
+                                     void* d_w8_transposed_or_null);
 
 /* ------------------------------------------------------------------ RMSNorm feeding the quantiser */
 

@@ -331,3 +331,65 @@ def test_reduce_scatter_epilogue_on_one_gpu(cfb, slices):
     with pytest.raises(cfb.CanopyError):      # 300-row slices are not multiples of 256
         cfb.gemm_fp8_nt_reduce_scatter(ctx, 600, N, h, a8[:600, :h], K, False, da, w8[:, :h].contiguous(), dw, ptrs[:2])
     ctx.poll_status()
+
+
+@pytest.mark.parametrize("M,N,K,e5m2", [(640, 384, 512, True), (128, 256, 128, False), (1000, 400, 2064, True),
+                                        (33, 16, 48, True), (2048, 8192, 3584, True)])
+def test_dgrad_from_the_forward_cache_equals_the_nt_gemm_on_the_transposed_weight(cfb, ctx, oracle, M, N, K, e5m2):
+    """dX = dY . W with W read as it lies in the forward cache ([K, N] row-major, an MN-major tensor-core operand) against
+    the NT kernel on the byte-transposed weight (what the reference's second cache would hold) and against the oracle."""
+    dy = randn_bf16((M, K), std=1e-3 if e5m2 else 1.0, seed=M + K, outlier_frac=0.001)
+    w = randn_bf16((K, N), std=0.02, seed=N)                 # forward cache layout: [out = K of this GEMM, in = N]
+    a8, da = _quant(cfb, dy, e5m2=e5m2)
+    w8, dw = _quant(cfb, w)
+    wt8 = torch.empty((N, K), dtype=torch.uint8, device="cuda")
+    cfb.transpose_u8(w8, wt8, K, N)
+    want = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    cfb.lt_gemm_fp8_nt(ctx, M, N, K, a8, K, e5m2, da, wt8, dw, want, N)
+    got = torch.full((M + 1, N), 3.0, dtype=torch.bfloat16, device="cuda")
+    cfb.gemm_fp8_nn(ctx, M, N, K, a8, K, e5m2, da, w8, N, dw, got, N)
+    ctx.poll_status()
+    assert torch.equal(got[:M].view(torch.int16), want.view(torch.int16))
+    assert (got[M:] == 3.0).all()
+    if M * N * K <= 1 << 30:
+        ref = oracle.gemm_fp8_nt(a8.cpu().numpy(), wt8.cpu().numpy(), da[0].item(), dw[0].item(), a_is_e5m2=e5m2)
+        assert rel_fro(oracle.bf16_to_f32(bf16_to_u16(got[:M])), oracle.bf16_to_f32(ref)) < TIGHT
+    # beta = 1: one fp32 addition and one rounding per element
+    base = randn_bf16((M, N), std=0.5, seed=3)
+    acc = base.clone()
+    cfb.gemm_fp8_nn(ctx, M, N, K, a8, K, e5m2, da, w8, N, dw, acc, N, accumulate=True)
+    ctx.poll_status()
+    exp = (base.float() + want.float()).to(torch.bfloat16)
+    assert rel_fro(acc.float().cpu().numpy(), exp.float().cpu().numpy()) < TIGHT
+
+
+@pytest.mark.parametrize("counts,N,K", [([300, 0, 777, 5], 320, 256), ([1024, 513], 4096, 1792), ([0, 0, 64], 64, 128)])
+def test_grouped_expert_dgrad_reads_every_experts_own_block(cfb, ctx, oracle, counts, N, K):
+    """The MoE expert bank's dgrad (src/trainer.cu:7829-7856): ragged groups against the stacked forward cache
+    [E, K, N]; every group must see its own expert's block, which is where a transposed multi-expert cache goes wrong."""
+    E = len(counts)
+    total = sum(counts)
+    dy = randn_bf16((total, K), std=1e-3, seed=total)
+    a8, da = _quant(cfb, dy, e5m2=True)
+    w = randn_bf16((E, K, N), std=0.02, seed=K)
+    w8, dw = _quant(cfb, w)
+    cnt = torch.tensor(counts, dtype=torch.int32, device="cuda")
+    off = torch.tensor(np.concatenate([[0], np.cumsum(counts)[:-1]]).astype(np.int32), device="cuda")
+    got = torch.full((total + 1, N), 5.0, dtype=torch.bfloat16, device="cuda")
+    cfb.gemm_fp8_nn_grouped(ctx, E, total, N, K, cnt, off, a8, K, True, da, w8, dw, got, N)
+    ctx.poll_status()
+    assert (got[total:] == 5.0).all()
+    o = 0
+    for e, c in enumerate(counts):
+        if c == 0:
+            continue
+        wt8 = torch.empty((N, K), dtype=torch.uint8, device="cuda")
+        cfb.transpose_u8(w8[e], wt8, K, N)
+        want = torch.empty((c, N), dtype=torch.bfloat16, device="cuda")
+        cfb.lt_gemm_fp8_nt(ctx, c, N, K, a8[o:o + c], K, True, da, wt8, dw, want, N)
+        assert torch.equal(got[o:o + c].view(torch.int16), want.view(torch.int16)), e
+        if c * N * K <= 1 << 28:
+            ref = oracle.gemm_fp8_nt(a8[o:o + c].cpu().numpy(), wt8.cpu().numpy(), da[0].item(), dw[0].item(), a_is_e5m2=True)
+            assert rel_fro(oracle.bf16_to_f32(bf16_to_u16(got[o:o + c])), oracle.bf16_to_f32(ref)) < TIGHT
+        o += c
+    ctx.poll_status()

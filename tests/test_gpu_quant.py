@@ -375,3 +375,54 @@ def test_lion_step_with_fused_weight_amax(cfb, oracle, refgpu, n, bf16_state):
         cfb.refresh_fp8_weight(fw, recompute_amax=False)
         s_o, _ = oracle.scale_from_amax(am[0].item(), 448.0)
         assert np.array_equal(fw.fwd8.cpu().numpy(), oracle.quantize_bf16(bf16_to_u16(wt), s_o))
+
+
+@pytest.mark.parametrize("bf16_state", [False, True])
+@pytest.mark.parametrize("rows,cols", [(256, 512), (100, 68), (4096, 1024), (33, 4)])
+def test_lion_step_with_fused_quantise_equals_step_plus_refresh(cfb, oracle, rows, cols, bf16_state):
+    """The optimiser pass that also writes both E4M3 caches: weights, momentum and the recorded amax equal the plain step
+    bit for bit, and the caches equal cf_refresh_fp8_weight(recompute_amax=0) run on the updated master with the amax the
+    fused call quantised with (the one an earlier step left). Two steps in a row, alternating the two amax words."""
+    n = rows * cols
+    g = torch.Generator(device="cuda").manual_seed(n + int(bf16_state))
+    w0 = torch.randn((rows, cols), generator=g, device="cuda").to(torch.bfloat16)
+    m0 = torch.randn((rows, cols), generator=g, device="cuda") * 0.1
+    if bf16_state:
+        m0 = m0.to(torch.bfloat16)
+    hp = (3e-3, 0.9, 0.99, 0.1)
+    w_a, m_a = w0.clone(), m0.clone()          # plain step + refresh
+    w_b, m_b = w0.clone(), m0.clone()          # fused
+    amax = [f32_scalar(), f32_scalar()]        # two words, alternating: [quantise with, record into]
+    cfb.fp8_amax_bf16(w0, amax[0])             # what "the previous step" left
+    sc, de = f32_scalar(), f32_scalar()
+    w8 = torch.zeros((rows, cols), dtype=torch.uint8, device="cuda")
+    w8t = torch.zeros((cols, rows), dtype=torch.uint8, device="cuda")
+    for step in range(2):
+        grad = torch.randn((rows, cols), generator=g, device="cuda")
+        q, r = amax[step & 1], amax[(step + 1) & 1]
+        am_a = f32_scalar()
+        cfb.lion_step(w_a.view(-1), m_a.view(-1), grad.view(-1), *hp, weight_amax=am_a, sr_seed=5 + step)
+        fw = cfb.Fp8Weight(w_a, stored_out_major=True)
+        fw.amax[0] = q[0]
+        cfb.refresh_fp8_weight(fw, recompute_amax=False)
+        r.zero_()
+        cfb.lion_step_quantize(w_b, m_b, grad, *hp, r, q, sc, de, w8, w8t, sr_seed=5 + step)
+        assert torch.equal(w_b.view(torch.int16), w_a.view(torch.int16))
+        assert torch.equal(m_b.view(torch.int16) if bf16_state else m_b, m_a.view(torch.int16) if bf16_state else m_a)
+        assert r[0].item() == am_a[0].item()
+        assert torch.equal(w8, fw.fwd8) and torch.equal(w8t, fw.bwd8), step
+        assert sc[0].item() == fw.scale[0].item() and de[0].item() == fw.descale[0].item()
+        s_o, _ = oracle.scale_from_amax(q[0].item(), 448.0)
+        assert np.array_equal(w8.cpu().numpy(), oracle.quantize_bf16(bf16_to_u16(w_b), s_o))
+    # the native-layout cache alone
+    w8_only = torch.zeros_like(w8)
+    w_c, m_c = w_b.clone(), m_b.clone()
+    cfb.lion_step_quantize(w_c, m_c, grad, *hp, f32_scalar(), amax[0], sc, de, w8_only, None, sr_seed=9)
+    s_o, _ = oracle.scale_from_amax(amax[0][0].item(), 448.0)
+    assert np.array_equal(w8_only.cpu().numpy(), oracle.quantize_bf16(bf16_to_u16(w_c), s_o))
+    # shapes the vector path cannot take are refused, and the two amax words must differ
+    with pytest.raises(cfb.CanopyError):
+        cfb.lion_step_quantize(w_c[:, :3].contiguous(), m_c[:, :3].contiguous(), grad[:, :3].contiguous(), *hp, f32_scalar(),
+                               amax[0], sc, de, w8_only, None)
+    with pytest.raises(cfb.CanopyError):
+        cfb.lion_step_quantize(w_c, m_c, grad, *hp, amax[0], amax[0], sc, de, w8_only, None)

@@ -33,6 +33,17 @@ class ActSlotStruct(C.Structure):
                 ("calib_max", fp), ("ticket", vp)]
 
 
+EP_MAX_EXPERTS, EP_MAX_RANKS = 256, 64
+EP_MAX_REPLICAS = EP_MAX_EXPERTS + EP_MAX_RANKS
+
+
+class EpPlacementStruct(C.Structure):
+    _fields_ = [("world", ci), ("num_experts", ci), ("num_replicas", ci), ("replica_expert", ci * EP_MAX_REPLICAS),
+                ("replica_rank", ci * EP_MAX_REPLICAS), ("replica_share", C.c_double * EP_MAX_REPLICAS),
+                ("replica_cum_share", C.c_double * EP_MAX_REPLICAS), ("replica_start", ci * (EP_MAX_EXPERTS + 1)),
+                ("rank_lo", ci * EP_MAX_RANKS), ("rank_hi", ci * EP_MAX_RANKS)]
+
+
 class Fp8WeightStruct(C.Structure):
     _fields_ = [("w", vp), ("fwd8", vp), ("bwd8", vp), ("amax", fp), ("scale", fp), ("descale", fp),
                 ("in_dim", ci), ("out_dim", ci), ("stored_out_major", ci)]
@@ -115,6 +126,8 @@ SIGNATURES = {
     "cf_moe_combine_all_bf16": (ci, [vp, vp, fp, ip, ip, ip, ci, ci, ci, vp]),
     "cf_moe_combine_sorted_bf16": (ci, [vp, vp, fp, ip, ip, ip, ci, ci, ci, ci, vp]),
     "cf_moe_expand_route_replicas": (ci, [fp, fp, ci, ci, ci, ip, fp, C.c_uint, vp]),
+    "cf_shard_range": (ci, [C.c_longlong, ci, ci, ci, C.POINTER(C.c_longlong), C.POINTER(C.c_longlong)]),
+    "cf_ep_placement_build": (ci, [C.POINTER(C.c_double), ci, ci, C.c_double, C.POINTER(EpPlacementStruct)]),
     "cf_moe_ep_plan": (ci, [ip, ci, ci, ci, ip, ip, vp, ip, ip, vp, C.c_longlong, vp, vp]),
     "cf_moe_send_row_runs": (ci, [vp, ip, C.c_longlong, vp, ci, ci, vp, C.c_longlong, fp, vp, ci, C.c_longlong, vp, vp]),
     "cf_gemm_fp8_nt_grouped_return": (ci, [vp, ci, ci, ci, ci, ip, ip, vp, ci, ci, fp, vp, fp, vp, ci, C.POINTER(vp), ci, ci, ci, vp]),

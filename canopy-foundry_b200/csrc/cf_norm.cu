@@ -360,7 +360,29 @@ __global__ void __launch_bounds__(kWarpRowThreads) k_rmsnorm_warp(const uint16_t
                 v[i].w = pack2(__fmul_rn(__fmul_rn(f[6], inv_rms), gg[6]), __fmul_rn(__fmul_rn(f[7], inv_rms), gg[7]));
             }
         }
-        if (CLIP) {
+        // Largest magnitude of the bf16 row from the packed words (two elements per instruction; a NaN anywhere makes
+        // the lane's value NaN). It decides whether the clip's norm has to be computed at all: the row norm cannot
+        // exceed sqrt(H) * amax, and the fp32 sum the reference forms exceeds the exact one by far less than the 1 %
+        // margin below, so a row that passes the test is left alone by the reference too. Rows with a NaN or an
+        // infinity fail the test and take the exact path. With the ceiling the reference uses by default (1000 on
+        // normalised rows) every ordinary row passes, and the second reduction over the row is skipped.
+        bool need_clip = CLIP;
+        float lane_amax = 0.0f;
+        if (CLIP || MODE != 0) {
+            __nv_bfloat162 pm = __floats2bfloat162_rn(0.0f, 0.0f);
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                if (i < nv) {
+                    const uint32_t w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) pm = __hmax2_nan(pm, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w4[q])));
+                }
+            }
+            const float lo = __low2float(pm), hi = __high2float(pm);
+            lane_amax = (lo != lo || hi != hi) ? __int_as_float(0x7fc00000) : fmaxf(lo, hi);
+            if (CLIP) need_clip = __any_sync(0xffffffffu, !(lane_amax * (sqrtf(static_cast<float>(H)) * 1.01f) < clip_ceiling));
+        }
+        if (CLIP && need_clip) {
             // squared norm of the bf16 row in the clip kernel's order: c[e] is its thread 8j + e
             float c[8];
 #pragma unroll
@@ -401,7 +423,10 @@ __global__ void __launch_bounds__(kWarpRowThreads) k_rmsnorm_warp(const uint16_t
                 }
             }
         }
-        float rmax = 0.0f;
+        // amax of the row this lane holds: already known unless the row went through the clip path (rescaled, or holding
+        // a NaN, which the recorded amax ignores like fmaxf does): those rows are scanned again below
+        const bool rescan = CLIP && need_clip;
+        float rmax = rescan ? 0.0f : lane_amax;
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             if (i < nv) {
@@ -410,8 +435,10 @@ __global__ void __launch_bounds__(kWarpRowThreads) k_rmsnorm_warp(const uint16_t
                 if (MODE != 0) {
                     float f[8];
                     unpack8(v[i], f);
+                    if (rescan) {
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) rmax = fmaxf(rmax, fabsf(f[e]));
+                        for (int e = 0; e < 8; ++e) rmax = fmaxf(rmax, fabsf(f[e]));
+                    }
                     if (MODE == 1) {
                         uint2 q;
                         q.x = cvt_fp8x4<false>(f[0] * s1, f[1] * s1, f[2] * s1, f[3] * s1);

@@ -25,12 +25,13 @@ import torch.distributed as dist
 
 def shard_range(n, world, rank, multiple=1):
     """Contiguous balanced shard [start, stop) of range(n) for `rank`; shard sizes are multiples of `multiple`
-    except possibly the last one."""
-    units = (n + multiple - 1) // multiple
-    base, extra = divmod(units, world)
-    start_u = rank * base + min(rank, extra)
-    stop_u = start_u + base + (1 if rank < extra else 0)
-    return min(start_u * multiple, n), min(stop_u * multiple, n)
+    except possibly the last one (cf_shard_range, the library's host-side sharding glue)."""
+    import ctypes as C
+
+    from . import _capi
+    lo, hi = C.c_longlong(), C.c_longlong()
+    _capi.check(_capi.lib().cf_shard_range(int(n), int(world), int(rank), int(multiple), C.byref(lo), C.byref(hi)))
+    return int(lo.value), int(hi.value)
 
 
 def allreduce_max_(t, group=None):
@@ -101,56 +102,19 @@ class ReplicaPlacement:
     @classmethod
     def build(cls, popularity, world, min_share=0.02):
         """popularity: expected share of the rows per expert (any positive scale). Overlaps below `min_share` of a
-        rank's piece are not worth a weight copy: they are merged into the expert's neighbouring replica."""
+        rank's piece are not worth a weight copy: they are merged into the expert's largest replica. The layout is
+        computed by the library (cf_ep_placement_build), the same call a C++ trainer makes."""
+        import ctypes as C
+
+        from . import _capi
         E = len(popularity)
-        tot = float(sum(popularity))
-        assert tot > 0 and all(p >= 0 for p in popularity)
-        p = [float(x) / tot for x in popularity]
-        piece = 1.0 / world
-        rep_e, rep_r, rep_len = [], [], []
-        pos = 0.0
-        for e in range(E):
-            lo, hi = pos, pos + p[e]
-            pos = hi
-            g0 = min(int(lo / piece + 1e-12), world - 1)
-            g1 = min(int((hi - 1e-12) / piece), world - 1) if hi > lo else g0
-            parts = []
-            for g in range(g0, max(g1, g0) + 1):
-                ov = min(hi, (g + 1) * piece) - max(lo, g * piece)
-                parts.append([g, max(ov, 0.0)])
-            # drop slivers (keep at least one part)
-            keep = [q for q in parts if q[1] >= min_share * piece]
-            if not keep:
-                keep = [max(parts, key=lambda q: q[1])]
-            lost = sum(q[1] for q in parts) - sum(q[1] for q in keep)
-            keep[max(range(len(keep)), key=lambda i: keep[i][1])][1] += lost
-            for g, ov in keep:
-                rep_e.append(e); rep_r.append(g); rep_len.append(ov)
-        start, cum, share = [0] * (E + 1), [], []
-        v = 0
-        for e in range(E):
-            start[e] = v
-            ids = [i for i in range(len(rep_e)) if rep_e[i] == e]
-            tot_e = sum(rep_len[i] for i in ids) or 1.0
-            run = 0.0
-            for n, i in enumerate(ids):
-                sh = rep_len[i] / tot_e if p[e] > 0 else 1.0 / len(ids)
-                run += sh
-                share.append(sh)
-                cum.append(1.0 if n == len(ids) - 1 else run)
-                v += 1
-        start[E] = v
-        ranges = []
-        for g in range(world):
-            ids = [i for i in range(v) if rep_r[i] == g]
-            ranges.append((ids[0], ids[-1] + 1) if ids else (0, 0))
-        # ranks along the line are non-decreasing, so each rank's ids are contiguous; an empty rank gets an empty range
-        # placed where it belongs in the order
-        for g in range(world):
-            if ranges[g] == (0, 0):
-                prev_hi = max([ranges[q][1] for q in range(g) if ranges[q] != (0, 0)], default=0)
-                ranges[g] = (prev_hi, prev_hi)
-        return cls(world, E, rep_e, rep_r, share, start, cum, ranges)
+        pop = (C.c_double * E)(*[float(x) for x in popularity])
+        pl = _capi.EpPlacementStruct()
+        _capi.check(_capi.lib().cf_ep_placement_build(pop, E, int(world), float(min_share), C.byref(pl)))
+        V = pl.num_replicas
+        return cls(world, E, list(pl.replica_expert[:V]), list(pl.replica_rank[:V]), list(pl.replica_share[:V]),
+                   list(pl.replica_start[:E + 1]), list(pl.replica_cum_share[:V]),
+                   [(pl.rank_lo[g], pl.rank_hi[g]) for g in range(world)])
 
     def local_experts(self, rank):
         lo, hi = self.rank_ranges[rank]

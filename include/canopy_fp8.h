@@ -499,6 +499,38 @@ int cf_moe_expand_route_replicas(const float* d_route_weights, float* d_replica_
                                  int num_replicas, const int* d_replica_start, const float* d_replica_cum_share,
                                  unsigned first_row, void* stream);
 
+/* ------------------------------------------------------------------ sharding glue (host side, no device work) */
+
+/* Contiguous balanced shard [*lo, *hi) of range(n) for `rank` of `world`; shard sizes are multiples of `multiple`
+ * except possibly the last one. Used for column-sharded weights (output columns) and row-parallel GEMMs (K). */
+int cf_shard_range(long long n, int world, int rank, int multiple, long long* lo, long long* hi);
+
+/* Expert placement of an expert-parallel MoE layer under a skewed load: the layout behind the reference's
+ * ParallelMode::ExpertSharded (include/canopy_foundry/parallel/plan.hpp:9-13, a mode name with no handling in
+ * src/parallel/plan.cpp:5-12). The experts are laid end to end on a line, each as long as its expected share of the rows
+ * (popularity[e], any positive scale), and the line is cut into `world` equal pieces, one per rank: every
+ * (expert, rank) overlap is a replica of that expert on that rank and receives the overlapping fraction of the expert's
+ * rows; overlaps below min_share of a piece are merged into the expert's largest replica. Replica ids ascend along the
+ * line, so every rank owns a contiguous id range [rank_lo, rank_hi), ids ascend with the expert id, and every rank
+ * expects the same number of rows. A uniform load with world | num_experts degenerates to plain expert sharding. The
+ * arrays feed cf_moe_expand_route_replicas (replica_start, replica_cum_share) and cf_moe_ep_plan (rank_lo, rank_hi). */
+#define CF_EP_MAX_EXPERTS 256
+#define CF_EP_MAX_RANKS 64
+#define CF_EP_MAX_REPLICAS (CF_EP_MAX_EXPERTS + CF_EP_MAX_RANKS)
+typedef struct cf_ep_placement {
+    int world;
+    int num_experts;
+    int num_replicas;
+    int replica_expert[CF_EP_MAX_REPLICAS];        /* expert of each replica */
+    int replica_rank[CF_EP_MAX_REPLICAS];          /* rank that holds it */
+    double replica_share[CF_EP_MAX_REPLICAS];      /* fraction of its expert's rows it takes */
+    double replica_cum_share[CF_EP_MAX_REPLICAS];  /* cumulative share inside the expert (last replica of an expert: 1) */
+    int replica_start[CF_EP_MAX_EXPERTS + 1];      /* first replica id of each expert */
+    int rank_lo[CF_EP_MAX_RANKS];                  /* replica id range served by each rank */
+    int rank_hi[CF_EP_MAX_RANKS];
+} cf_ep_placement;
+int cf_ep_placement_build(const double* popularity, int num_experts, int world, double min_share, cf_ep_placement* out);
+
 /* A run of rows on its way to another buffer: `rows` rows starting at src_row (ignored when the call gathers through an
  * index table) go to row dst_row of destination buffer number dst. */
 typedef struct cf_row_run {

@@ -180,3 +180,79 @@ def test_replica_placement_drops_slivers_and_degenerates_to_sharding():
     # a 1 % overlap with the next rank's piece is not worth a copy of the weights
     pl = par.ReplicaPlacement.build([0.505, 0.495], 2, min_share=0.05)
     assert pl.replica_expert == [0, 1] and pl.replica_rank == [0, 1]
+
+
+def _placement_in_python(popularity, world, min_share=0.02):
+    """The placement rule written out in Python (experts on a line cut into `world` equal pieces, slivers merged into
+    the expert's largest replica): the independent statement cf_ep_placement_build is checked against."""
+    E = len(popularity)
+    tot = float(sum(popularity))
+    p = [float(x) / tot for x in popularity]
+    piece = 1.0 / world
+    rep_e, rep_r, rep_len = [], [], []
+    pos = 0.0
+    for e in range(E):
+        lo, hi = pos, pos + p[e]
+        pos = hi
+        g0 = min(int(lo / piece + 1e-12), world - 1)
+        g1 = min(int((hi - 1e-12) / piece), world - 1) if hi > lo else g0
+        parts = [[g, max(min(hi, (g + 1) * piece) - max(lo, g * piece), 0.0)] for g in range(g0, max(g1, g0) + 1)]
+        keep = [q for q in parts if q[1] >= min_share * piece] or [max(parts, key=lambda q: q[1])]
+        lost = sum(q[1] for q in parts) - sum(q[1] for q in keep)
+        keep[max(range(len(keep)), key=lambda i: keep[i][1])][1] += lost
+        for g, ov in keep:
+            rep_e.append(e); rep_r.append(g); rep_len.append(ov)
+    start, cum, share = [0] * (E + 1), [], []
+    v = 0
+    for e in range(E):
+        start[e] = v
+        ids = [i for i in range(len(rep_e)) if rep_e[i] == e]
+        tot_e = sum(rep_len[i] for i in ids) or 1.0
+        run = 0.0
+        for n, i in enumerate(ids):
+            sh = rep_len[i] / tot_e if p[e] > 0 else 1.0 / len(ids)
+            run += sh
+            share.append(sh)
+            cum.append(1.0 if n == len(ids) - 1 else run)
+            v += 1
+    start[E] = v
+    ranges, prev_hi = [], 0
+    for g in range(world):
+        ids = [i for i in range(v) if rep_r[i] == g]
+        if ids:
+            ranges.append((ids[0], ids[-1] + 1))
+            prev_hi = ids[-1] + 1
+        else:
+            ranges.append((prev_hi, prev_hi))
+    return rep_e, rep_r, share, start, cum, ranges
+
+
+def test_expert_placement_from_the_library_matches_the_rule_written_in_python():
+    import random
+    par = package().parallel
+    rnd = random.Random(7)
+    cases = [([(e + 1) ** -1.1 for e in range(8)], w, 0.02) for w in (1, 2, 4, 8)]
+    cases += [([1.0] * 8, 4, 0.02), ([0.505, 0.495], 2, 0.05), ([5.0, 1.0, 1.0, 1.0], 2, 0.02), ([0.0, 3.0, 0.0, 1.0], 3, 0.0)]
+    for _ in range(200):
+        E, w = rnd.randint(1, 40), rnd.randint(1, 16)
+        pop = [rnd.random() ** 3 for _ in range(E)]
+        if rnd.random() < 0.3:
+            pop[rnd.randrange(E)] = 0.0
+        if sum(pop) == 0:
+            pop[0] = 1.0
+        cases.append((pop, w, rnd.choice([0.0, 0.02, 0.1])))
+    for pop, w, ms in cases:
+        pl = par.ReplicaPlacement.build(pop, w, min_share=ms)
+        e_, r_, sh_, st_, cum_, rg_ = _placement_in_python(pop, w, ms)
+        assert pl.replica_expert == e_ and pl.replica_rank == r_ and pl.replica_start == st_
+        assert [tuple(x) for x in pl.rank_ranges] == rg_
+        assert np.allclose(pl.replica_share, sh_, rtol=0, atol=1e-12) and np.allclose(pl.replica_cum_share, cum_, rtol=0, atol=1e-12)
+        # invariants: shares of an expert sum to 1, ranks ascend, every rank's range is contiguous
+        for e in range(len(pop)):
+            assert abs(sum(pl.replica_share[pl.replica_start[e]:pl.replica_start[e + 1]]) - 1.0) < 1e-9
+        assert pl.replica_rank == sorted(pl.replica_rank)
+    # limits are refused, not overrun
+    with pytest.raises(Exception):
+        par.ReplicaPlacement.build([1.0] * 300, 2)
+    with pytest.raises(Exception):
+        par.ReplicaPlacement.build([1.0, -1.0], 2)

@@ -812,6 +812,44 @@ def leg_mlp(args, env):
         dist.reduce_scatter_tensor(part_rs, partial)
         cfb.f32_to_bf16_and_zero(part_rs, y)
 
+    # Pipelined form: the rows are cut into chunks (per-token scales make row chunks independent); the reduce-scatter of
+    # chunk c runs on a second stream while the GEMMs of chunk c + 1 run. The small max-all-reduce of the row amax uses
+    # its own communicator so that it does not queue behind the large reduce-scatter of the previous chunk. Rank r ends
+    # with rows [r Mc/N, (r + 1) Mc/N) of every chunk.
+    CH = 4
+    Mc = Mm // CH
+    pipelined_ok = world > 1 and Mc % (256 * world) == 0
+    if pipelined_ok:
+        comm = torch.cuda.Stream(device=dev)
+        amax_group = dist.new_group(backend="nccl")
+        ev_g = [torch.cuda.Event() for _ in range(CH)]
+        ev_r = [torch.cuda.Event() for _ in range(CH)]
+        y_p = torch.empty((rows_out, H), dtype=torch.bfloat16, device=dev)
+        rs_out = torch.empty((rows_out, H), dtype=torch.float32, device=dev)
+        rc = Mc // world
+
+    def step_pipelined(i):
+        x = xs[i & 1]
+        main = torch.cuda.current_stream()
+        for c in range(CH):
+            r0, r1 = c * Mc, (c + 1) * Mc
+            cfb.fp8_quantize_rowwise_e4m3(x[r0:r1], x8[r0:r1], dx[r0:r1])
+            hmax[r0:r1].zero_()
+            cfb.gemm_fp8_swiglu_bf16_rowamax(ctx, Mc, Fl, H, x8[r0:r1], H, False, None, dx[r0:r1], il, None, dil, h[r0:r1],
+                                             hmax[r0:r1])
+            dist.all_reduce(hmax[r0:r1], op=dist.ReduceOp.MAX, group=amax_group)
+            cfb.fp8_quantize_rowwise_given_amax_e4m3(h[r0:r1], h8[r0:r1], hmax[r0:r1], dh[r0:r1])
+            cfb.lt_gemm_fp8_nt(ctx, Mc, H, Fl, h8[r0:r1], Fl, False, one, wd8_l, one, partial[r0:r1], H,
+                               a_row_descale=dh[r0:r1], b_col_descale=dd)
+            ev_g[c].record(main)
+            with torch.cuda.stream(comm):
+                comm.wait_event(ev_g[c])
+                dist.reduce_scatter_tensor(rs_out[c * rc:(c + 1) * rc], partial[r0:r1])
+                cfb.f32_to_bf16_and_zero(rs_out[c * rc:(c + 1) * rc], y_p[c * rc:(c + 1) * rc])
+                ev_r[c].record(comm)
+        for c in range(CH):
+            main.wait_event(ev_r[c])
+
     res = {"workload": "swiglu_mlp_fp8_M16384_H4096_F14336_per_token_x_per_channel_scales", "n_gpus": world,
            "steps": steps, "warmup": warmup, "scaling": "strong", "unit": UNIT,
            "sharding": "single GPU" if world == 1 else f"gate/up by output features ({Fl} per rank), down by its contraction dimension, X replicated, Y rows scattered"}
@@ -824,23 +862,30 @@ def leg_mlp(args, env):
     else:
         arms["nccl_reduce_scatter"] = env.timed(step_nccl, steps, warmup, sampler)
         arms["gemm_fused_reduce_scatter"] = env.timed(step_fused, steps, warmup)
+        if pipelined_ok:
+            arms["nccl_reduce_scatter_pipelined_4_row_chunks"] = env.timed(step_pipelined, steps, warmup)
         used = min(arms, key=arms.get)
     clocks = sampler.stop()
     ctx.poll_status()
     ms = arms[used]
     # parity outside the timed region: sampled rows of this rank's slice against the host oracle on the full weights
-    (step_single if world == 1 else (step_fused if used == "gemm_fused_reduce_scatter" else step_nccl))(0)
+    piped = used.startswith("nccl_reduce_scatter_pipelined")
+    (step_single if world == 1 else step_pipelined if piped else step_fused if used == "gemm_fused_reduce_scatter" else step_nccl)(0)
     torch.cuda.synchronize()
     err = None
     if rank == 0:
         orc = oracle()
-        sample = [0, 255, 256, rows_out - 1]
+        local = [0, 255, 256, rows_out - 1]
+        # rank 0's local row j is global row j, or (chunk, row in the chunk's share) in the pipelined form
+        sample = [(j // rc) * Mc + j % rc for j in local] if piped else local
+        if piped:
+            y = y_p
         xr = xs[0][sample].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
         q8, _, qd = orc.quantize_rowwise_e4m3(xr)
         gu = orc.gemm_fp8_nt(q8, wgu8.cpu().numpy(), qd, dgu.cpu().numpy())
         hq, _, hd = orc.quantize_rowwise_e4m3(np.ascontiguousarray(gu[:, :F]), np.ascontiguousarray(gu[:, F:]))
         want = orc.bf16_to_f32(orc.gemm_fp8_nt(hq, wd8.cpu().numpy(), hd, dd.cpu().numpy()))
-        got = y[sample].float().cpu().numpy()
+        got = y[local].float().cpu().numpy()
         err = float(np.linalg.norm(got - want) / np.linalg.norm(want))
     nv_bytes = 0 if world == 1 else (world - 1) / world * Mm * H * 4
     res.update({"value": MLP_FLOP / (ms * 1e-3) / 1e12, "ms_per_step": ms, "exchange_used": used,
@@ -920,11 +965,12 @@ def leg_sweep(args, env):
         cfb.lt_gemm_fp8_nt(ctx, Mm, Nl, Kk, a8, Kk, False, da, w8, dw, yout, Nl)
 
     def dgrad_gemm_bf16(i):
-        # the weight is read from the forward cache as it lies ([Nl, K] = [contraction, output] for this GEMM)
-        cfb.gemm_fp8_nn(ctx, Mm, Kk, Nl, dy8, Nl, True, dg, w8, Kk, dw, dx_b, Kk)
-
-    def dgrad_gemm_bf16_nt(i):
+        # the reference's form: NT GEMM against the transposed weight cache (bwd8)
         cfb.lt_gemm_fp8_nt(ctx, Mm, Kk, Nl, dy8, Nl, True, dg, wt8, dw, dx_b, Kk)
+
+    def dgrad_gemm_bf16_nn(i):
+        # the same product with the weight read from the forward cache as it lies ([Nl, K] = [contraction, output])
+        cfb.gemm_fp8_nn(ctx, Mm, Kk, Nl, dy8, Nl, True, dg, w8, Kk, dw, dx_b, Kk)
 
     def dgrad_gemm_f32(i):
         cfb.lt_gemm_fp8_nt(ctx, Mm, Kk, Nl, dy8, Nl, True, dg, wt8, dw, dx_f, Kk)
@@ -937,27 +983,51 @@ def leg_sweep(args, env):
         dgrad_gemm_bf16(i)
         dist.all_reduce(dx_b)
 
+    CH = 4
+    Mc = Mm // CH
+    if world > 1:
+        comm = torch.cuda.Stream(device=dev)
+        ev_g = [torch.cuda.Event() for _ in range(CH)]
+        ev_r = [torch.cuda.Event() for _ in range(CH)]
+
+    def dgrad_f32_allreduce_pipelined(i):
+        # row chunks: the all-reduce of chunk c runs on a second stream while the GEMM of chunk c + 1 runs
+        main = torch.cuda.current_stream()
+        for c in range(CH):
+            r0, r1 = c * Mc, (c + 1) * Mc
+            cfb.lt_gemm_fp8_nt(ctx, Mc, Kk, Nl, dy8[r0:r1], Nl, True, dg, wt8, dw, dx_f[r0:r1], Kk)
+            ev_g[c].record(main)
+            with torch.cuda.stream(comm):
+                comm.wait_event(ev_g[c])
+                dist.all_reduce(dx_f[r0:r1])
+                ev_r[c].record(comm)
+        for c in range(CH):
+            main.wait_event(ev_r[c])
+
     l0 = cfb.launch_count()
     sampler = ClockSampler(env.local, 0.002)
     t_fwd = env.timed(fwd, steps, warmup, sampler)
     clocks = sampler.stop()
     t_dg = env.timed(dgrad_gemm_bf16, steps, warmup)
-    t_dg_nt = env.timed(dgrad_gemm_bf16_nt, steps, warmup)
+    t_dg_nn = env.timed(dgrad_gemm_bf16_nn, steps, warmup)
     fl = SW_FLOP
     res = {"workload": "fp8_gemm_M32768_K8192_N28672_forward_e4m3_and_dgrad_e5m2xe4m3", "n_gpus": world, "steps": steps,
            "warmup": warmup, "scaling": "strong", "unit": UNIT,
            "sharding": "single GPU" if world == 1 else f"W sharded by output columns ({Nl} per rank): forward needs no exchange, dgrad sums partial dX over the ranks",
            "forward": {"ms": t_fwd, "tflops": fl / (t_fwd * 1e-3) / 1e12},
            "dgrad_without_allreduce": {"ms": t_dg, "tflops": fl / (t_dg * 1e-3) / 1e12, "output": "bf16 (partial dX at N > 1)",
-                                       "weight_operand": "forward cache [N, K] read as it lies (no transposed cache)",
-                                       "ms_nt_on_transposed_cache": t_dg_nt}}
+                                       "weight_operand": "transposed E4M3 cache [K, N] (the reference's bwd8), K-major tensor-core operand",
+                                       "ms_reading_the_forward_cache_as_it_lies": t_dg_nn}}
     if world > 1:
         t_f32 = env.timed(dgrad_f32_allreduce, steps, warmup)
         t_b16 = env.timed(dgrad_bf16_allreduce, steps, warmup)
+        t_pipe = env.timed(dgrad_f32_allreduce_pipelined, steps, warmup)
         nbytes = Mm * Kk * 4
         res["dgrad_with_allreduce"] = {"ms": t_f32, "tflops": fl / (t_f32 * 1e-3) / 1e12,
                                        "exchange": "NCCL all-reduce(sum) of the fp32 [32768 x 8192] partial dX (1.07 GB)",
                                        "allreduce_bus_bound_ms_at_725GBps": 2 * (world - 1) / world * nbytes / 725e9 * 1e3}
+        res["dgrad_with_allreduce_pipelined"] = {"ms": t_pipe, "tflops": fl / (t_pipe * 1e-3) / 1e12,
+                                                 "exchange": "the same fp32 all-reduce in 4 row chunks on a second stream, overlapped with the GEMM of the next chunk"}
         res["dgrad_with_allreduce_bf16_partials"] = {"ms": t_b16, "tflops": fl / (t_b16 * 1e-3) / 1e12,
                                                      "exchange": "NCCL all-reduce(sum) of bf16 partial dX (0.54 GB); partial sums rounded to bf16 per hop"}
     ctx.poll_status()

@@ -210,6 +210,42 @@ def row_parallel_gemm_fp8(cfb, ctx, M, N, K_local, a8_local, a_descale, w8_local
     return out_bf16
 
 
+class PeerBarrier:
+    """Orders the work every rank enqueues after wait() behind the work every rank enqueued before it, on the current
+    stream and without a host round trip. kind "device": cf_peer_barrier (every rank stores an epoch into its word of
+    every peer's flag array in symmetric memory and waits, bounded by limit_ms, for its own array to fill up: one tiny
+    kernel); kind "nccl": a one-float all-reduce. Construction is collective over the group."""
+
+    def __init__(self, cfb, ctx, group=None, device="cuda", kind="device", limit_ms=2000):
+        assert kind in ("device", "nccl")
+        self.cfb, self.ctx, self.group, self.limit_ms = cfb, ctx, group, int(limit_ms)
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self._fence = torch.zeros(1, dtype=torch.float32, device=device)
+        self._flags, self._epoch, self._keep = None, 0, None
+        if self.world > 1 and kind == "device":
+            import torch.distributed._symmetric_memory as symm_mem
+            flags = symm_mem.empty((64,), dtype=torch.int32, device=device)
+            hdl = symm_mem.rendezvous(flags, group if group is not None else dist.group.WORLD)
+            views = [hdl.get_buffer(r, (64,), torch.int32) for r in range(self.world)]
+            flags.zero_()
+            self._keep = (flags, hdl, views)
+            self._flags = torch.tensor([v.data_ptr() for v in views], dtype=torch.int64, device=device)
+        if self.world > 1:
+            # every rank's flag words are zero before any rank may store into them
+            dist.all_reduce(self._fence, group=self.group)
+            torch.cuda.current_stream().synchronize()
+
+    def wait(self):
+        if self.world == 1:
+            return
+        if self._flags is not None:
+            self._epoch += 1
+            self.cfb.peer_barrier(self.ctx, self._flags, self.world, self.rank, self._epoch, self.limit_ms)
+        else:
+            dist.all_reduce(self._fence, group=self.group)
+
+
 class RowParallelReduceScatterGemm:
     """K-sharded (row-parallel) NT GEMM whose epilogue IS the reduce-scatter: every rank adds the row slices of its fp32
     partial product straight into the owning rank's accumulation slice (bulk reduce-add copies into symmetric memory,
@@ -218,8 +254,9 @@ class RowParallelReduceScatterGemm:
     Two accumulation slices alternate: the one used by call i is zeroed again while it is read out, and the barrier of
     call i + 1 orders that behind every rank's next use of it."""
 
-    def __init__(self, cfb, ctx, M, N, group=None, device="cuda"):
+    def __init__(self, cfb, ctx, M, N, group=None, device="cuda", barrier="device"):
         self.cfb, self.ctx, self.group, self.M, self.N = cfb, ctx, group, M, N
+        self._pb = PeerBarrier(cfb, ctx, group, device, kind=barrier)
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         assert M % self.world == 0 and (M // self.world) % 256 == 0, "row slices must be multiples of 256 rows"
@@ -241,13 +278,11 @@ class RowParallelReduceScatterGemm:
             a.zero_()
             self.acc.append(a)
             self.ptrs.append(ptrs)
-        self._fence = torch.zeros(1, dtype=torch.float32, device=device)
         self._flip = 0
         self._barrier()           # every slice is zero before anyone adds to it
 
     def _barrier(self):
-        if self.world > 1:
-            dist.all_reduce(self._fence, group=self.group)
+        self._pb.wait()
 
     def forward(self, a8_local, a_descale, w8_local, w_descale, out_slice_bf16, a_row_descale=None, b_col_descale=None):
         """a8_local [M, K_local] E4M3 (this rank's K slice of every row), w8_local [N, K_local]; out_slice_bf16
@@ -395,9 +430,11 @@ class EpMoeSwigluFp8Direct:
     Weights: gate/up interleaved (fp8_interleave_gate_up), stacked in placement.local_experts(rank) order."""
 
     def __init__(self, cfb, ctx, rows, H, F, num_experts, top_k, placement=None, group=None, device="cuda",
-                 fused_return=True):
+                 fused_return=True, barrier="device", barrier_limit_ms=2000):
         """fused_return: the down GEMM's epilogue stores every run of result rows straight into the owner's buffer
-        (cf_gemm_fp8_nt_grouped_return) instead of writing them locally and copying them out afterwards."""
+        (cf_gemm_fp8_nt_grouped_return) instead of writing them locally and copying them out afterwards.
+        barrier: "device" orders readers behind writers with cf_peer_barrier (flag words in the peers' memory, one tiny
+        kernel, bounded wait of barrier_limit_ms); "nccl" uses a one-float all-reduce instead."""
         self.cfb, self.ctx, self.group = cfb, ctx, group
         self.fused_return = bool(fused_return) and H % 64 == 0
         self.rows, self.H, self.F, self.E, self.k = rows, H, F, num_experts, top_k
@@ -444,7 +481,7 @@ class EpMoeSwigluFp8Direct:
         self.peer_recv_dx = torch.tensor(pdx, dtype=torch.int64, device=dev)
         self.peer_back = torch.tensor(pback, dtype=torch.int64, device=dev)
         self.back_ptrs = list(pback)
-        self._fence = torch.zeros(1, dtype=f32, device=dev)
+        self._pb = PeerBarrier(cfb, ctx, group, dev, kind=barrier, limit_ms=barrier_limit_ms)
         self._barrier()
 
     def _shared(self, shape, dtype):
@@ -462,8 +499,7 @@ class EpMoeSwigluFp8Direct:
         return t, [v.data_ptr() for v in views]
 
     def _barrier(self):
-        if self.world > 1:
-            dist.all_reduce(self._fence, group=self.group)
+        self._pb.wait()
 
     def forward(self, x, route_weights, w_gateup8_local, w_gateup_descale, w_down8_local, w_down_descale, mixed,
                 accumulate=True):

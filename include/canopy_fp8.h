@@ -566,6 +566,17 @@ int cf_moe_send_row_runs(const void* d_src, const int* d_row_indices_or_null, lo
                          int num_runs, int max_rows_per_run, void* const* d_dst_bases, long long row_bytes,
                          const float* d_tag_value_or_null, float* const* d_tag_bases_or_null, int num_dst, long long dst_rows,
                          cf_ctx* ctx_or_null, void* stream);
+/* No counterpart in the reference (single GPU). Barrier between the ranks of one box without a collective launch: every
+ * rank calls it with the same epoch (a counter that grows by one per barrier; the flag words start at zero). The kernel
+ * stores `epoch` into word `rank` of every rank's flag array and waits until all `world` words of its own array have
+ * reached it, so the work enqueued behind it on `stream` starts once every rank's earlier work on ITS stream, including
+ * its stores into peers' buffers, is complete and visible. d_flag_arrays is a DEVICE array of `world` pointers, entry r =
+ * rank r's array of `world` unsigned words as mapped in this process (peer-mapped memory for r != rank). The ranks must
+ * run on different GPUs. The wait is bounded: after limit_ms (1..60000) the kernel gives up, the launches behind it still
+ * run (on incomplete data) and the next cf_ctx_poll_status returns CF_ERR_DEVICE_WAIT. */
+int cf_peer_barrier(cf_ctx* ctx, unsigned* const* d_flag_arrays, int world, int rank, unsigned epoch, int limit_ms,
+                    void* stream);
+
 /* The down projection of a device-planned expert-parallel layer with the return leg in its epilogue: a ragged grouped
  * NT GEMM (as cf_gemm_fp8_nt_grouped) whose output rows leave straight for the buffers of the ranks that own the tokens.
  * Inside group g the rows are the runs d_return_runs[g * runs_per_group + s] in ascending src_row (compact rows of A);

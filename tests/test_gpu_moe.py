@@ -409,6 +409,44 @@ def test_a_run_that_leaves_its_destination_is_skipped_and_reported(cfb):
     ctx.close()
 
 
+def test_peer_barrier_passes_when_every_word_arrived_and_gives_up_within_its_limit(cfb):
+    """cf_peer_barrier on one GPU: with the peer's word already at the epoch the kernel returns at once; with a word
+    nothing ever sets the bounded wait runs out after its limit (5 ms), the kernel records a status code and returns
+    normally, cf_ctx_poll_status reports CF_ERR_DEVICE_WAIT once and the context stays usable. Two kernels that wait on
+    each other are never launched on one GPU: the second rank is a flag array this test writes itself."""
+    ctx = cfb.Fp8Ctx(0)
+    mine = torch.zeros(64, dtype=torch.int32, device="cuda")
+    peer = torch.zeros(64, dtype=torch.int32, device="cuda")
+    arrays = torch.tensor([mine.data_ptr(), peer.data_ptr()], dtype=torch.int64, device="cuda")
+    # world of one: nothing to wait for
+    one = torch.tensor([mine.data_ptr()], dtype=torch.int64, device="cuda")
+    cfb.peer_barrier(ctx, one, 1, 0, 1, limit_ms=5)
+    ctx.poll_status()
+    assert mine[0].item() == 1
+    # "rank 1" has already announced epoch 7
+    mine.zero_()
+    mine[1] = 7
+    cfb.peer_barrier(ctx, arrays, 2, 0, 7, limit_ms=5)
+    ctx.poll_status()
+    assert mine[0].item() == 7 and peer[0].item() == 7          # this rank's word in both arrays
+    # an older epoch in the peer's word is not enough; the wait gives up
+    cfb.peer_barrier(ctx, arrays, 2, 0, 8, limit_ms=5)
+    with pytest.raises(cfb.CanopyError) as ei:
+        ctx.poll_status()
+    assert ei.value.code == cfb._capi.CF_ERR_DEVICE_WAIT
+    ctx.poll_status()
+    # epochs compare modulo 2^32
+    mine[1] = 3
+    cfb.peer_barrier(ctx, arrays, 2, 0, 0xFFFFFFFE, limit_ms=5)
+    with pytest.raises(cfb.CanopyError):
+        ctx.poll_status()
+    mine[1] = 3
+    peer.zero_()
+    cfb.peer_barrier(ctx, arrays, 2, 0, 2, limit_ms=5)
+    ctx.poll_status()
+    ctx.close()
+
+
 def test_route_expansion_over_replicas_keeps_weights_and_follows_the_shares(cfb):
     """Every selected (row, expert) keeps its weight on exactly one replica of that expert, unselected experts stay
     zero, and the rows of an expert split over its replicas in proportion to their shares."""

@@ -197,6 +197,30 @@ def _worker(rank, world, port, ret):
             ep6.forward(xs[rank], rw6, wgu_il_loc, dgu, wd8[loc].contiguous(), dd, mixed_e, accumulate=False)
             ctx.poll_status()
         assert ep5.fused_return and torch.equal(mixed_e.view(torch.int16), mixed_r.view(torch.int16))
+        # ... and with a library all-reduce in place of the flag-word barrier between the ranks
+        ep7 = par.EpMoeSwigluFp8Direct(cfb, ctx, rows, H, F, E, k, placement=pl, device=dev, barrier="nccl")
+        mixed_n = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
+        for step in range(2):
+            rw7 = logits[rank].clone()
+            ep7.forward(xs[rank], rw7, wgu_il_loc, dgu, wd8[loc].contiguous(), dd, mixed_n, accumulate=False)
+            ctx.poll_status()
+        assert torch.equal(mixed_n.view(torch.int16), mixed_r.view(torch.int16))
+        # the flag-word barrier many times in a row, every rank checking what the others wrote before the barrier
+        pb = par.PeerBarrier(cfb, ctx, device=dev)
+        import torch.distributed._symmetric_memory as symm_mem
+        box = symm_mem.empty((world,), dtype=torch.float32, device=dev)
+        hb = symm_mem.rendezvous(box, dist.group.WORLD)
+        peers = [hb.get_buffer(r, (world,), torch.float32) for r in range(world)]
+        box.zero_()
+        dist.barrier()
+        for it in range(1, 40):
+            for r in range(world):
+                peers[r][rank] = float(it * 10 + rank)        # a store into every rank's box (peer memory)
+            pb.wait()
+            got = box.clone()
+            pb.wait()                                          # nobody overwrites before everybody has read
+            assert got.cpu().tolist() == [float(it * 10 + r) for r in range(world)], (it, got)
+        ctx.poll_status()
         # and against the single-GPU layer on all tokens: a different scale granularity (one activation scale per rank
         # instead of one over all tokens), so the two differ by FP8 quantisation noise, not by more
         single = cfb.MoeSwigluFp8(ctx, rows * world, H, F, E, k, device=dev)

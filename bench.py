@@ -1203,6 +1203,20 @@ def run_quantize(args):
         ("rmsnorm_clip_record_quantise_e4m3_only", 3, n, lambda: cfb.rmsnorm_clip_quantize_e4m3_record(nx(), gamma, None, rms, out8, scale, amax, rows, H, 1000.0)),
         ("rmsnorm_rowwise_quantise_e4m3_only", 3, n, lambda: cfb.rmsnorm_quantize_rowwise_e4m3(nx(), gamma, None, rms, out8, rowd, rows, H)),
     ]
+    # optimiser pass: plain Lion step (fp32 state: 4 B gradient + 8 B momentum + 4 B master per element), Lion step that
+    # also writes both E4M3 caches (+ 2 B), and the stand-alone refresh it replaces (2 B read + 2 B written)
+    lw = xs[0].clone()
+    lm = torch.zeros((rows, H), dtype=torch.float32, device=dev)
+    lg = torch.randn((rows, H), generator=g, device=dev, dtype=torch.float32)
+    am_a, am_b = torch.ones(4, dtype=torch.float32, device=dev), torch.zeros(4, dtype=torch.float32, device=dev)
+    fwl = cfb.Fp8Weight(lw, stored_out_major=True)
+    fwl.amax.fill_(4.0)
+    hp = (1e-4, 0.9, 0.99, 0.0)
+    kernels += [
+        ("lion_step_f32_state", 16, n, lambda: cfb.lion_step(lw.view(-1), lm.view(-1), lg.view(-1), *hp, weight_amax=am_b, sr_seed=1)),
+        ("lion_step_f32_state_with_both_e4m3_caches", 18, n, lambda: cfb.lion_step_quantize(lw, lm, lg, *hp, am_b, am_a, sc2, de2, out8, out8t, sr_seed=1)),
+        ("weight_refresh_both_layouts", 4, n, lambda: cfb.refresh_fp8_weight(fwl, recompute_amax=False)),
+    ]
     sampler = ClockSampler(0)
     sampler.start()
     l0 = cfb.launch_count()

@@ -435,14 +435,14 @@ def test_peer_barrier_passes_when_every_word_arrived_and_gives_up_within_its_lim
         ctx.poll_status()
     assert ei.value.code == cfb._capi.CF_ERR_DEVICE_WAIT
     ctx.poll_status()
-    # epochs compare modulo 2^32
+    # epochs compare modulo 2^32: a word that has wrapped past the epoch counts as arrived, one just behind it does not
     mine[1] = 3
+    cfb.peer_barrier(ctx, arrays, 2, 0, 0xFFFFFFFE, limit_ms=5)
+    ctx.poll_status()
+    mine[1] = -16                                    # 0xFFFFFFF0: fourteen epochs behind 0xFFFFFFFE
     cfb.peer_barrier(ctx, arrays, 2, 0, 0xFFFFFFFE, limit_ms=5)
     with pytest.raises(cfb.CanopyError):
         ctx.poll_status()
-    mine[1] = 3
-    peer.zero_()
-    cfb.peer_barrier(ctx, arrays, 2, 0, 2, limit_ms=5)
     ctx.poll_status()
     ctx.close()
 

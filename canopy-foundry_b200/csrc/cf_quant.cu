@@ -6,6 +6,7 @@
 // max() is order-free, so wider threads/vectors change no bit of the result.
 #include "cf_common.cuh"
 #include "cf_internal.cuh"
+#include "cf_lion.cuh"
 
 namespace cf {
 namespace {
@@ -63,6 +64,12 @@ __device__ __forceinline__ void fused_tail(const RingTail& t, float* amax) {
 __device__ __forceinline__ uint4 ldg_stream16(const void* p) {
     uint4 v;
     asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float4 ldg_stream_f4(const float* p) {
+    float4 v;
+    asm volatile("ld.global.cs.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
     return v;
 }
 
@@ -412,12 +419,16 @@ __device__ __forceinline__ int tile_word(int k, int wc) {
     return ((k ^ ((k >> 7) & 1)) << 4) + (wc ^ ((k >> 3) & 15));
 }
 
-template <bool SRC_BF16>
+// SRC: 0 = byte source (plain transpose), 1 = bf16 source (quantised on the way in), 2 = the Lion step: the tile's
+// weights are updated in place (gradient, momentum and master read and written as kernels/lion.cu does) and the value
+// just stored is what gets quantised, so the optimiser pass leaves both E4M3 caches behind.
+template <int SRC>
 __global__ void __launch_bounds__(kThreads) k_tile_transpose(const void* __restrict__ src, uint8_t* __restrict__ direct,
                                                              uint8_t* __restrict__ transposed,
                                                              const float* __restrict__ scale, int R, int Ccols,
                                                              int src_vec, int direct_vec, int trans_vec,
-                                                             const ScaleFromAmax sfa) {
+                                                             const ScaleFromAmax sfa, const LionArgs la) {
+    constexpr bool SRC_BF16 = SRC != 0;
     __shared__ uint32_t tile[kTR * 16];
     const int r0 = blockIdx.y * kTR, c0 = blockIdx.x * kTC;
     const int tid = threadIdx.x;
@@ -437,7 +448,62 @@ __global__ void __launch_bounds__(kThreads) k_tile_transpose(const void* __restr
         }
     }
 
-    if (SRC_BF16) {
+    if (SRC == 2) {
+        // 8 threads x 8 columns per row, 32 rows per pass, 8 passes (vector accesses: the launcher requires
+        // cols % 8 == 0 and aligned bases); rows and columns outside the tensor leave zeros in the tile
+        const int cg = (tid & 7) * 8, rl = tid >> 3;
+        float local = 0.0f;
+#pragma unroll 2
+        for (int p = 0; p < kTR / 32; ++p) {
+            const int k = p * 32 + rl;
+            const int r = r0 + k, c = c0 + cg;
+            uint2 q = make_uint2(0u, 0u);
+            if (r < R && c < Ccols) {
+                const size_t off = static_cast<size_t>(r) * Ccols + c;
+                const uint4 wv = *reinterpret_cast<const uint4*>(la.w + off);
+                const float4 g0 = ldg_stream_f4(la.grad + off), g1 = ldg_stream_f4(la.grad + off + 4);
+                float wf[8], mp[8];
+                unpack8(wv, wf);
+                if (la.bf16_state) {
+                    unpack8(*reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(la.mstate) + off), mp);
+                } else {
+                    const float4 m0 = *reinterpret_cast<const float4*>(static_cast<const float*>(la.mstate) + off);
+                    const float4 m1 = *reinterpret_cast<const float4*>(static_cast<const float*>(la.mstate) + off + 4);
+                    mp[0] = m0.x; mp[1] = m0.y; mp[2] = m0.z; mp[3] = m0.w; mp[4] = m1.x; mp[5] = m1.y; mp[6] = m1.z; mp[7] = m1.w;
+                }
+                const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                uint16_t wn[8], mn16[8];
+                float mn[8], f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    float w_new;
+                    lion_elem(g[e], mp[e], wf[e], la.lr, la.beta1, la.beta2, la.wd, mn[e], w_new);
+                    const unsigned h = sr_hash(off + e, la.sr_seed);
+                    if (la.bf16_state) mn16[e] = f32_to_bf16_sr(mn[e], h ^ 0x9e3779b9u);
+                    wn[e] = f32_to_bf16_sr(w_new, h);
+                    local = fmaxf(local, fabsf(w_new));
+                    f[e] = bf16_bits_to_f32(wn[e]);
+                }
+                *reinterpret_cast<uint4*>(la.w + off) =
+                    make_uint4(wn[0] | (static_cast<uint32_t>(wn[1]) << 16), wn[2] | (static_cast<uint32_t>(wn[3]) << 16),
+                               wn[4] | (static_cast<uint32_t>(wn[5]) << 16), wn[6] | (static_cast<uint32_t>(wn[7]) << 16));
+                if (la.bf16_state) {
+                    *reinterpret_cast<uint4*>(static_cast<uint16_t*>(la.mstate) + off) =
+                        make_uint4(mn16[0] | (static_cast<uint32_t>(mn16[1]) << 16), mn16[2] | (static_cast<uint32_t>(mn16[3]) << 16),
+                                   mn16[4] | (static_cast<uint32_t>(mn16[5]) << 16), mn16[6] | (static_cast<uint32_t>(mn16[7]) << 16));
+                } else {
+                    float* md = static_cast<float*>(la.mstate) + off;
+                    *reinterpret_cast<float4*>(md) = make_float4(mn[0], mn[1], mn[2], mn[3]);
+                    *reinterpret_cast<float4*>(md + 4) = make_float4(mn[4], mn[5], mn[6], mn[7]);
+                }
+                q = quant8<false>(f, s);
+                if (direct) *reinterpret_cast<uint2*>(direct + off) = q;
+            }
+            tile[tile_word(k, cg >> 2)] = q.x;
+            tile[tile_word(k, (cg >> 2) + 1)] = q.y;
+        }
+        if (la.amax_out) block_amax_commit(local, la.amax_out);      // a block barrier: every thread gets here
+    } else if (SRC_BF16) {
         // 8 threads x 8 columns per source row, 32 rows per pass, 8 passes; all loads of a thread issued first
         const uint16_t* in = static_cast<const uint16_t*>(src);
         const int cg = (tid & 7) * 8, rl = tid >> 3;
@@ -548,9 +614,11 @@ __global__ void __launch_bounds__(kThreads) k_tile_transpose(const void* __restr
     }
 }
 
-template <bool SRC_BF16>
+template <int SRC>
 int launch_tile_transpose(const void* src, void* direct, void* transposed, const float* scale, int R, int Ccols,
-                          cudaStream_t st, const char* name, const ScaleFromAmax sfa = ScaleFromAmax()) {
+                          cudaStream_t st, const char* name, const ScaleFromAmax sfa = ScaleFromAmax(),
+                          const LionArgs la = LionArgs()) {
+    constexpr bool SRC_BF16 = SRC != 0;
     if (R == 0 || Ccols == 0) return CF_OK;
     const uintptr_t sa = reinterpret_cast<uintptr_t>(src), da = reinterpret_cast<uintptr_t>(direct),
                     ta = reinterpret_cast<uintptr_t>(transposed);
@@ -559,8 +627,8 @@ int launch_tile_transpose(const void* src, void* direct, void* transposed, const
     const int direct_vec = direct && (da % 8 == 0) && (Ccols % 8 == 0);
     const int trans_vec = transposed && (ta % 8 == 0) && (R % 8 == 0);
     dim3 grid((Ccols + kTC - 1) / kTC, (R + kTR - 1) / kTR);
-    CF_CUDA(launch_pdl(k_tile_transpose<SRC_BF16>, grid, dim3(kThreads), 0, st, src, static_cast<uint8_t*>(direct),
-                       static_cast<uint8_t*>(transposed), scale, R, Ccols, src_vec, direct_vec, trans_vec, sfa));
+    CF_CUDA(launch_pdl(k_tile_transpose<SRC>, grid, dim3(kThreads), 0, st, src, static_cast<uint8_t*>(direct),
+                       static_cast<uint8_t*>(transposed), scale, R, Ccols, src_vec, direct_vec, trans_vec, sfa, la));
     CF_LAUNCH_CHECK(name);
     return CF_OK;
 }
@@ -580,9 +648,21 @@ int quantize_record_fused(const void* d_x, void* d_out, const float* d_scale, fl
                 : launch_stream<false, true, true>(d_x, d_out, d_scale, d_amax, n, st, "quantize_e4m3_record_fused", tail);
 }
 
+int lion_quant_tile_launch(const LionArgs& la, void* d_direct, void* d_transposed_or_null, const ScaleFromAmax& sfa, int rows,
+                           int cols, cudaStream_t st) {
+    const bool ok = (cols % 8 == 0) && (reinterpret_cast<uintptr_t>(la.w) % 16 == 0) &&
+                    (reinterpret_cast<uintptr_t>(la.grad) % 16 == 0) && (reinterpret_cast<uintptr_t>(la.mstate) % 16 == 0) &&
+                    (reinterpret_cast<uintptr_t>(d_direct) % 8 == 0);
+    if (!ok) {
+        set_error("lion step with fused quantise: needs cols %% 8 == 0, 16-byte aligned weights, gradients and state, an 8-byte aligned E4M3 output; run the plain step and cf_refresh_fp8_weight instead");
+        return CF_ERR_UNSUPPORTED;
+    }
+    return launch_tile_transpose<2>(la.w, d_direct, d_transposed_or_null, nullptr, rows, cols, st, "lion_step_quantize", sfa, la);
+}
+
 int quant_dual_from_amax(const void* d_in, void* d_direct, void* d_transposed, const ScaleFromAmax& sfa, int R, int Ccols,
                          cudaStream_t st) {
-    return launch_tile_transpose<true>(d_in, d_direct, d_transposed, nullptr, R, Ccols, st, "quant_dual_from_amax", sfa);
+    return launch_tile_transpose<1>(d_in, d_direct, d_transposed, nullptr, R, Ccols, st, "quant_dual_from_amax", sfa);
 }
 
 }  // namespace cf
@@ -643,7 +723,7 @@ int cf_fp8_calib_minmax_update(const float* d_amax, float* d_calib_min, float* d
 int cf_fp8_quantize_transpose_e4m3(const void* d_w, void* d_out, const float* d_scale, int K, int N, void* stream) {
     CF_REQUIRE(K >= 0 && N >= 0, "cf_fp8_quantize_transpose_e4m3: negative shape");
     CF_REQUIRE(d_scale && (K == 0 || N == 0 || (d_w && d_out)), "cf_fp8_quantize_transpose_e4m3: null pointer");
-    return launch_tile_transpose<true>(d_w, nullptr, d_out, d_scale, K, N, as_stream(stream), "quantize_transpose_e4m3");
+    return launch_tile_transpose<1>(d_w, nullptr, d_out, d_scale, K, N, as_stream(stream), "quantize_transpose_e4m3");
 }
 
 int cf_fp8_quant_and_transpose_e4m3(const void* d_in, void* d_act8_out, void* d_snap_out, const float* d_scale, int K,
@@ -651,14 +731,14 @@ int cf_fp8_quant_and_transpose_e4m3(const void* d_in, void* d_act8_out, void* d_
     CF_REQUIRE(K >= 0 && N >= 0, "cf_fp8_quant_and_transpose_e4m3: negative shape");
     CF_REQUIRE(d_scale && (K == 0 || N == 0 || d_in), "cf_fp8_quant_and_transpose_e4m3: null pointer");
     CF_REQUIRE(d_act8_out || d_snap_out, "cf_fp8_quant_and_transpose_e4m3: both outputs null");
-    return launch_tile_transpose<true>(d_in, d_act8_out, d_snap_out, d_scale, K, N, as_stream(stream),
+    return launch_tile_transpose<1>(d_in, d_act8_out, d_snap_out, d_scale, K, N, as_stream(stream),
                                        "quant_and_transpose_e4m3");
 }
 
 int cf_transpose_u8(const void* d_in, void* d_out, int rows, int cols, void* stream) {
     CF_REQUIRE(rows >= 0 && cols >= 0, "cf_transpose_u8: negative shape");
     CF_REQUIRE(rows == 0 || cols == 0 || (d_in && d_out), "cf_transpose_u8: null pointer");
-    return launch_tile_transpose<false>(d_in, nullptr, d_out, nullptr, rows, cols, as_stream(stream), "transpose_u8");
+    return launch_tile_transpose<0>(d_in, nullptr, d_out, nullptr, rows, cols, as_stream(stream), "transpose_u8");
 }
 
 int cf_fp8_clip_probe(const float* d_amax, const float* d_scale, float fp8_max, float* d_stats, void* stream) {

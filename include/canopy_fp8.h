@@ -367,8 +367,8 @@ int cf_lion_step_bf16_state(void* d_w, void* d_m, const float* d_grad, size_t n,
  * [rows, cols], and, when d_w8_transposed_or_null is given, into the other layout [cols, rows]: the bytes
  * cf_refresh_fp8_weight(recompute_amax = 0) would produce from that amax. *d_quant_amax is the amax an EARLIER step left
  * (delayed by one step: this step's amax is complete only when the pass ends), so it must be a different word from
- * d_weight_amax; a trainer alternates two words per weight. Needs cols % 4 == 0, an 8-byte aligned master, 16-byte
- * aligned gradient and fp32 state (8-byte aligned bf16 state), a 4-byte aligned d_w8; CF_ERR_UNSUPPORTED otherwise (run
+ * d_weight_amax; a trainer alternates two words per weight. Needs cols % 8 == 0, 16-byte aligned master, gradient and
+ * state, an 8-byte aligned d_w8; CF_ERR_UNSUPPORTED otherwise (run
  * the plain step and cf_refresh_fp8_weight then). With cf_gemm_fp8_nn the dgrad GEMMs read the native-layout cache as
  * it lies, so the transposed cache is only needed by callers that keep the reference's NT dgrad. */
 int cf_lion_step_f32_state_quantize(void* d_w, float* d_m, const float* d_grad, int rows, int cols, float lr, float beta1,

@@ -378,7 +378,7 @@ def test_lion_step_with_fused_weight_amax(cfb, oracle, refgpu, n, bf16_state):
 
 
 @pytest.mark.parametrize("bf16_state", [False, True])
-@pytest.mark.parametrize("rows,cols", [(256, 512), (100, 68), (4096, 1024), (33, 4)])
+@pytest.mark.parametrize("rows,cols", [(256, 512), (100, 72), (4096, 1024), (33, 8), (300, 4104)])
 def test_lion_step_with_fused_quantise_equals_step_plus_refresh(cfb, oracle, rows, cols, bf16_state):
     """The optimiser pass that also writes both E4M3 caches: weights, momentum and the recorded amax equal the plain step
     bit for bit, and the caches equal cf_refresh_fp8_weight(recompute_amax=0) run on the updated master with the amax the

@@ -389,7 +389,7 @@ def leg_linear(args, env):
            "host_enqueue_ms": host_enqueue_ms}
 
     state = dict(ctx=ctx, fw=fw, slot=slot, act8=act8, xs=xs, y=y, bias=bias, step=step, gemm=gemm)
-    out["incumbent"] = linear_incumbent(args, env, state) if env.rank == 0 else None
+    out["incumbent"] = linear_incumbent(args, env, state) if (env.rank == 0 and not args.no_incumbent) else None
     out["sustained"] = linear_sustained(args, env, state)
     out["e2e"] = None if args.no_e2e else linear_e2e(args, env, state)
     ctx.poll_status()
@@ -1336,6 +1336,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the host-buffer leg (default: steps, within 20..40)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-incumbent", action="store_true", help="skip the library-GEMM comparison (profiling runs)")
     ap.add_argument("--bias-mode", type=int, default=2, help="2 = reference rounding order, 1 = single rounding")
     ap.add_argument("--sustain-seconds", type=float, default=2.0, help="length of the sustained loop of the headline leg (0 = skip)")
     ap.add_argument("--legs", default="linear,moe,mlp,sweep",

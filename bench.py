@@ -1298,7 +1298,7 @@ def run_default(args):
             "e2e": lin["e2e"],
             "gpu_launches": lin["launches"],
             "host_enqueue_ms_per_step": lin["host_enqueue_ms"],
-            "clocks": lin["clocks"],
+            "clocks": dict(lin["clocks"], note="sampled during the timed region of the headline leg (milliseconds at a small --steps); roofline.sustained carries thousands of samples over seconds"),
         }
         line.update(extra)
         if env.world == 1 and not args.no_cpu_baseline:

@@ -147,18 +147,23 @@ def test_tn_weight_gradient_accumulate(cfb, ctx, oracle, out_dtype):
     ctx.poll_status()
 
 
-def test_against_cublaslt(cfb, ctx):
-    """Same FP8 bytes through torch._scaled_mm (cuBLASLt) — the incumbent kernel the reference calls."""
+@pytest.mark.parametrize("M,N,K", [(512, 768, 1024), (8192, 4096, 4096), (4096, 14336, 4096)])
+def test_against_cublaslt(cfb, ctx, M, N, K):
+    """Same FP8 bytes through torch._scaled_mm (cuBLASLt) — the incumbent kernel the reference calls — from a small
+    shape up to the full 8192 x 4096 x 4096 linear. The two kernels add exact FP8 products in fp32 in their own
+    orders, so the outputs may differ in the last bf16 bit of a few elements at most (they have been bit-identical in
+    every run so far; the test allows 0.1 % of the elements to differ by one rounding)."""
     if not hasattr(torch, "_scaled_mm"):
         pytest.skip("torch._scaled_mm not available")
-    M, N, K = 512, 768, 1024
     a8, da = _quant(cfb, randn_bf16((M, K), seed=31))
     w8, dw = _quant(cfb, randn_bf16((N, K), std=0.02, seed=32))
     c = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
     cfb.lt_gemm_fp8_nt(ctx, M, N, K, a8, K, False, da, w8, dw, c, N)
     ref = torch._scaled_mm(a8.view(torch.float8_e4m3fn), w8.view(torch.float8_e4m3fn).t(), scale_a=da[0:1],
                            scale_b=dw[0:1], out_dtype=torch.bfloat16)
-    assert rel_fro(c.float().cpu().numpy(), ref.float().cpu().numpy()) < TIGHT
+    assert rel_fro(c.float().cpu().numpy(), ref.float().cpu().numpy()) < 1e-3
+    differing = (c.view(torch.int16) != ref.view(torch.int16)).float().mean().item()
+    assert differing < 1e-3, differing
 
 
 def test_full_size_properties(cfb, ctx, oracle):

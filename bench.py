@@ -712,6 +712,13 @@ def leg_moe(args, env):
     launches = int((cfb.launch_count() - l0) * steps / (steps + warmup))
     ctx.poll_status()
     lmax = env.max_over_ranks(float(layer.grp_counts.sum().item()))
+    # where the time of one layer goes on this rank: CUDA events between the stages of one extra call (not timed above;
+    # the events serialise the launches a little, so the stages add up to slightly more than a step)
+    layer.stage_marks = []
+    step(0)
+    torch.cuda.synchronize()
+    marks, layer.stage_marks = layer.stage_marks, None
+    stages = {marks[i][0]: round(marks[i - 1][1].elapsed_time(marks[i][1]), 4) for i in range(1, len(marks))}
     # ---- parity, outside the timed region: sampled tokens of rank 0 against the host oracle with the scales the ranks
     # used, and rank 0's rows against the single-GPU layer (other scale granularity: FP8 noise, reported, not gated)
     hs = layer.slot_h.scalars()
@@ -732,7 +739,7 @@ def leg_moe(args, env):
             "n1_ms_same_box": single["ms"], "n1_clocks": single["clocks"],
             "efficiency_vs_n1_same_box": single["ms"] / (world * ms),
             "max_rows_on_one_rank": int(lmax), "mean_rows_per_rank": TOK * TOPK / world, "clocks": clocks,
-            "gpu_launches": launches,
+            "gpu_launches": launches, "stage_ms_rank0": stages,
             "moe_parity": {"rel_fro": err, "ok": bool(err < 1e-2 and single["rel_fro_vs_oracle"] < 1e-2), "tolerance": 1e-2,
                            "against": "CPU oracle on sampled tokens of rank 0 with the scales the serving ranks used",
                            "n1_layer_rel_fro_vs_oracle": single["rel_fro_vs_oracle"],
@@ -850,6 +857,14 @@ def leg_mlp(args, env):
         for c in range(CH):
             main.wait_event(ev_r[c])
 
+    partial_b = torch.empty((Mm, H), dtype=torch.bfloat16, device=dev) if world > 1 else None
+
+    def step_nccl_bf16(i):
+        # partial products rounded to bf16 before the exchange: half the bytes on the wire, one extra rounding per rank
+        front(i)
+        cfb.lt_gemm_fp8_nt(ctx, Mm, H, Fl, h8, Fl, False, one, wd8_l, one, partial_b, H, a_row_descale=dh, b_col_descale=dd)
+        dist.reduce_scatter_tensor(y, partial_b)
+
     res = {"workload": "swiglu_mlp_fp8_M16384_H4096_F14336_per_token_x_per_channel_scales", "n_gpus": world,
            "steps": steps, "warmup": warmup, "scaling": "strong", "unit": UNIT,
            "sharding": "single GPU" if world == 1 else f"gate/up by output features ({Fl} per rank), down by its contraction dimension, X replicated, Y rows scattered"}
@@ -864,7 +879,8 @@ def leg_mlp(args, env):
         arms["gemm_fused_reduce_scatter"] = env.timed(step_fused, steps, warmup)
         if pipelined_ok:
             arms["nccl_reduce_scatter_pipelined_4_row_chunks"] = env.timed(step_pipelined, steps, warmup)
-        used = min(arms, key=arms.get)
+        used = min(arms, key=arms.get)          # among the forms that sum the partial products in fp32
+        t_bf16 = env.timed(step_nccl_bf16, steps, warmup)
     clocks = sampler.stop()
     ctx.poll_status()
     ms = arms[used]
@@ -887,9 +903,25 @@ def leg_mlp(args, env):
         want = orc.bf16_to_f32(orc.gemm_fp8_nt(hq, wd8.cpu().numpy(), hd, dd.cpu().numpy()))
         got = y[local].float().cpu().numpy()
         err = float(np.linalg.norm(got - want) / np.linalg.norm(want))
+    bf16_arm = None
+    if world > 1:
+        step_nccl_bf16(0)
+        torch.cuda.synchronize()
+        if rank == 0:
+            got_b = y[[0, 255, 256, rows_out - 1]].float().cpu().numpy()
+            want_b = want
+            if piped:      # the bf16 arm scatters plain row slices: recompute the oracle rows for those
+                xr2 = xs[0][[0, 255, 256, rows_out - 1]].contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+                q2, _, qd2 = orc.quantize_rowwise_e4m3(xr2)
+                gu2 = orc.gemm_fp8_nt(q2, wgu8.cpu().numpy(), qd2, dgu.cpu().numpy())
+                hq2, _, hd2 = orc.quantize_rowwise_e4m3(np.ascontiguousarray(gu2[:, :F]), np.ascontiguousarray(gu2[:, F:]))
+                want_b = orc.bf16_to_f32(orc.gemm_fp8_nt(hq2, wd8.cpu().numpy(), hd2, dd.cpu().numpy()))
+            bf16_arm = {"ms_per_step": t_bf16, "tflops": MLP_FLOP / (t_bf16 * 1e-3) / 1e12,
+                        "rel_fro_vs_oracle": float(np.linalg.norm(got_b - want_b) / np.linalg.norm(want_b)),
+                        "note": "partial products rounded to bf16 and summed by NCCL in bf16: half the bytes, not bit-comparable with the fp32 sum"}
     nv_bytes = 0 if world == 1 else (world - 1) / world * Mm * H * 4
     res.update({"value": MLP_FLOP / (ms * 1e-3) / 1e12, "ms_per_step": ms, "exchange_used": used,
-                "ms_per_step_by_exchange": arms,
+                "ms_per_step_by_exchange": arms, "bf16_partials": bf16_arm,
                 "exchange": "none" if world == 1 else "max-all-reduce of float[M] row amax + reduce-scatter of the fp32 [M,H] partial products",
                 "nvlink_bytes_sent_per_rank_per_step": nv_bytes,
                 "nvlink_bound_ms_at_770GBps": nv_bytes / 770e9 * 1e3,
@@ -983,6 +1015,13 @@ def leg_sweep(args, env):
         dgrad_gemm_bf16(i)
         dist.all_reduce(dx_b)
 
+    dx_rs = torch.empty((Mm // world, Kk), dtype=torch.float32, device=dev) if world > 1 else None
+
+    def dgrad_f32_reduce_scatter(i):
+        # rank r keeps rows [r M/N, (r+1) M/N) of dX (sequence-parallel consumer): half the bytes of the all-reduce
+        dgrad_gemm_f32(i)
+        dist.reduce_scatter_tensor(dx_rs, dx_f)
+
     CH = 4
     Mc = Mm // CH
     if world > 1:
@@ -1022,12 +1061,15 @@ def leg_sweep(args, env):
         t_f32 = env.timed(dgrad_f32_allreduce, steps, warmup)
         t_b16 = env.timed(dgrad_bf16_allreduce, steps, warmup)
         t_pipe = env.timed(dgrad_f32_allreduce_pipelined, steps, warmup)
+        t_rs = env.timed(dgrad_f32_reduce_scatter, steps, warmup)
         nbytes = Mm * Kk * 4
         res["dgrad_with_allreduce"] = {"ms": t_f32, "tflops": fl / (t_f32 * 1e-3) / 1e12,
                                        "exchange": "NCCL all-reduce(sum) of the fp32 [32768 x 8192] partial dX (1.07 GB)",
                                        "allreduce_bus_bound_ms_at_725GBps": 2 * (world - 1) / world * nbytes / 725e9 * 1e3}
         res["dgrad_with_allreduce_pipelined"] = {"ms": t_pipe, "tflops": fl / (t_pipe * 1e-3) / 1e12,
                                                  "exchange": "the same fp32 all-reduce in 4 row chunks on a second stream, overlapped with the GEMM of the next chunk"}
+        res["dgrad_with_reduce_scatter"] = {"ms": t_rs, "tflops": fl / (t_rs * 1e-3) / 1e12,
+                                            "exchange": "NCCL reduce-scatter of the fp32 partial dX: every rank keeps its M/N rows (for a consumer that is sharded by rows)"}
         res["dgrad_with_allreduce_bf16_partials"] = {"ms": t_b16, "tflops": fl / (t_b16 * 1e-3) / 1e12,
                                                      "exchange": "NCCL all-reduce(sum) of bf16 partial dX (0.54 GB); partial sums rounded to bf16 per hop"}
     ctx.poll_status()

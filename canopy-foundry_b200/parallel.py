@@ -482,6 +482,7 @@ class EpMoeSwigluFp8Direct:
         self.peer_back = torch.tensor(pback, dtype=torch.int64, device=dev)
         self.back_ptrs = list(pback)
         self._pb = PeerBarrier(cfb, ctx, group, dev, kind=barrier, limit_ms=barrier_limit_ms)
+        self.stage_marks = None   # set to a list to receive (stage name, CUDA event) pairs from the next forward()
         self._barrier()
 
     def _shared(self, shape, dtype):
@@ -505,11 +506,21 @@ class EpMoeSwigluFp8Direct:
                 accumulate=True):
         cfb, ctx = self.cfb, self.ctx
         rows, H, F, V, W = self.rows, self.H, self.F, self.V, self.world
+        marks = self.stage_marks          # None, or a list that receives (stage name, CUDA event) pairs of this call
+
+        def mark(name):
+            if marks is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        mark("start")
         cfb.moe_topk_route_f32(route_weights, rows, self.E, self.k)
         cfb.moe_expand_route_replicas(route_weights, self.rwv, rows, self.E, V, self.rep_start, self.rep_cum,
                                       first_row=self.rank * rows)
         cfb.moe_build_expert_row_lists(self.rwv, self.counts, self.idx, rows, V)
         cfb.moe_expert_offsets_from_counts(self.counts, self.offsets, V)
+        mark("route + replica choice + dispatch lists")
         gathered = None
         if W > 1:
             # the count table travels while the activation is being quantised
@@ -519,15 +530,19 @@ class EpMoeSwigluFp8Direct:
         cfb.fp8_quant_act(ctx, self.slot_x, x, self.x8)
         if gathered is not None:
             gathered.wait()
+        mark("quantise x (count table gathered meanwhile)")
         cfb.moe_ep_plan(self.counts_all, W, self.rank, V, self.range_lo, self.range_hi, self.send_runs, self.grp_counts,
                         self.grp_offsets, self.ret_runs, recv_capacity_rows=self.cap, ctx=ctx)
         # permute + dispatch in one pass; every row carries the descale of the rank that quantised it
         cfb.moe_send_row_runs(self.x8, self.idx, rows, self.send_runs, V, rows, self.peer_recv8, H, W, self.cap,
                               tag_value=cfb.ops._DevPtr(self.slot_x.c.descale_snapshot), tag_bases=self.peer_recv_dx, ctx=ctx)
+        mark("plan + permute and store rows into the serving ranks")
         self._barrier()          # every rank's rows have arrived
+        mark("barrier: rows arrived")
         cfb.gemm_fp8_swiglu_quant_act(ctx, self.slot_h, self.n_local, self.n_local, None, self.cap, F, H, self.grp_counts,
                                       self.grp_offsets, self.recv8, H, False, self.recv_dx, 2, w_gateup8_local,
                                       w_gateup_descale, self.h8, F)
+        mark("gate/up GEMM + SwiGLU + re-quantise")
         if self.fused_return:
             cfb.gemm_fp8_nt_grouped_return(ctx, self.n_local, self.cap, H, F, self.grp_counts, self.grp_offsets, self.h8, F,
                                            False, cfb.ops._DevPtr(self.slot_h.c.descale_snapshot), w_down8_local,
@@ -538,8 +553,11 @@ class EpMoeSwigluFp8Direct:
                                     self.yc, H)
             cfb.moe_send_row_runs(self.yc, None, 0, self.ret_runs, self.n_local * W, rows, self.peer_back, 2 * H, W, self.T,
                                   ctx=ctx)
+        mark("down GEMM with the return leg")
         self._barrier()          # every rank's results are back
+        mark("barrier: results back")
         cfb.moe_combine_sorted_bf16(mixed, self.back, self.rwv, self.idx, self.counts, self.offsets, rows, V, H, accumulate)
+        mark("combine")
 
 
 def _copy_device_scalar(cfb, dst_tensor, src_addr):

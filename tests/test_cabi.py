@@ -102,3 +102,17 @@ int main() {
     assert r.returncode == 0, r.stdout[-3000:]
     run = subprocess.run([str(exe)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     assert run.returncode == 0, run.stdout
+
+
+def test_bench_line_contract_without_a_gpu():
+    """bench.py imports without a GPU, offers the legs the default line carries, and the reference arm prints the
+    same `config` keys as the GPU arm (the driver compares the two)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    assert set(bench.LEGS) == {"moe", "mlp", "sweep"}
+    cfg = bench.linear_config(2, 1)
+    assert {"workload", "M", "N", "K", "step", "bias_mode", "sharding", "l2"} <= set(cfg)
+    assert cfg["M"] * cfg["N"] * cfg["K"] * 2.0 == bench.FLOP_PER_STEP
+    assert bench.load_peaks()["hbm_gbs"] > 0

@@ -129,6 +129,7 @@ SIGNATURES = {
     "cf_shard_range": (ci, [C.c_longlong, ci, ci, ci, C.POINTER(C.c_longlong), C.POINTER(C.c_longlong)]),
     "cf_ep_placement_build": (ci, [C.POINTER(C.c_double), ci, ci, C.c_double, C.POINTER(EpPlacementStruct)]),
     "cf_peer_barrier": (ci, [vp, vp, ci, ci, C.c_uint, ci, vp]),
+    "cf_peer_share_i32": (ci, [vp, ip, ci, vp, vp, ci, ci, C.c_uint, ci, vp]),
     "cf_moe_ep_plan": (ci, [ip, ci, ci, ci, ip, ip, vp, ip, ip, vp, C.c_longlong, vp, vp]),
     "cf_moe_send_row_runs": (ci, [vp, ip, C.c_longlong, vp, ci, ci, vp, C.c_longlong, fp, vp, ci, C.c_longlong, vp, vp]),
     "cf_gemm_fp8_nt_grouped_return": (ci, [vp, ci, ci, ci, ci, ip, ip, vp, ci, ci, fp, vp, fp, vp, ci, C.POINTER(vp), ci, ci, ci, vp]),

@@ -49,10 +49,50 @@ __global__ void k_peer_barrier(unsigned* const* __restrict__ flags, int world, i
     }
 }
 
+// Small all-gather by stores: this rank's n words go to row `rank` of every rank's [world, n] table, followed by the
+// barrier above in the same launch, so when the kernel ends every rank's row is in this rank's table.
+__global__ void __launch_bounds__(256) k_peer_share(const int* __restrict__ src, int n, int* const* __restrict__ tables,
+                                                    unsigned* const* __restrict__ flags, int world, int rank, unsigned epoch,
+                                                    unsigned long long limit_ns, int* __restrict__ status) {
+    for (int i = threadIdx.x; i < world * n; i += blockDim.x) {
+        const int p = i / n, v = i - p * n;
+        tables[p][rank * n + v] = src[v];
+    }
+    __syncthreads();                       // the stores of all threads happen before the announcements below
+    const int t = threadIdx.x;
+    if (t >= world) return;
+    __threadfence_system();
+    st_release_sys(flags[t] + rank, epoch);
+    const unsigned* mine = flags[rank] + t;
+    const unsigned long long t0 = now_ns();
+    unsigned spins = 0;
+    while (static_cast<int>(ld_acquire_sys(mine) - epoch) < 0) {
+        if ((++spins & 63u) == 0u && now_ns() - t0 > limit_ns) {
+            atomicExch(status, 0x600 | 2);
+            return;
+        }
+        __nanosleep(100);
+    }
+}
+
 }  // namespace
 }  // namespace cf
 
 using namespace cf;
+
+extern "C" int cf_peer_share_i32(cf_ctx* ctx, const int* d_src, int n, int* const* d_tables, unsigned* const* d_flag_arrays,
+                                 int world, int rank, unsigned epoch, int limit_ms, void* stream) {
+    CF_REQUIRE(ctx && d_src && d_tables && d_flag_arrays, "cf_peer_share_i32: null pointer");
+    CF_REQUIRE(n >= 1 && n <= 4096, "cf_peer_share_i32: 1..4096 words");
+    CF_REQUIRE(world >= 1 && world <= 64 && rank >= 0 && rank < world, "cf_peer_share_i32: 1..64 ranks");
+    CF_REQUIRE(limit_ms >= 1 && limit_ms <= 60000, "cf_peer_share_i32: limit must be 1..60000 ms");
+    const int rc = require_sm100();
+    if (rc != CF_OK) return rc;
+    k_peer_share<<<1, 256, 0, as_stream(stream)>>>(d_src, n, d_tables, d_flag_arrays, world, rank, epoch,
+                                                    static_cast<unsigned long long>(limit_ms) * 1000000ull, ctx_status(ctx));
+    CF_LAUNCH_CHECK("peer_share_i32");
+    return CF_OK;
+}
 
 extern "C" int cf_peer_barrier(cf_ctx* ctx, unsigned* const* d_flag_arrays, int world, int rank, unsigned epoch, int limit_ms,
                                void* stream) {

@@ -25,7 +25,7 @@ __all__ = [
     "rmsnorm_forward", "rmsnorm_quantize_e4m3_record", "rmsnorm_quantize_rowwise_e4m3", "fp8_rmsnorm_quant_act", "rmsnorm_clip_forward", "rmsnorm_clip_quantize_e4m3_record", "fp8_rmsnorm_clip_quant_act",
     "moe_topk_route_f32", "moe_build_expert_row_lists", "moe_expert_offsets_from_counts",
     "moe_gather_rows_u8", "moe_gather_rows_bf16", "moe_scatter_accumulate_rows_bf16",
-    "moe_scale_accumulate_bf16", "moe_gather_all_u8", "moe_combine_all_bf16", "moe_combine_sorted_bf16", "moe_expand_route_replicas", "moe_ep_plan", "gemm_fp8_nt_grouped_return", "moe_send_row_runs", "peer_barrier", "ROW_RUN_BYTES",
+    "moe_scale_accumulate_bf16", "moe_gather_all_u8", "moe_combine_all_bf16", "moe_combine_sorted_bf16", "moe_expand_route_replicas", "moe_ep_plan", "gemm_fp8_nt_grouped_return", "moe_send_row_runs", "peer_barrier", "peer_share_i32", "ROW_RUN_BYTES",
     "moe_grouped_expert_forward_fp8", "launch_count", "swiglu_mlp_fp8_rowwise", "MoeSwigluFp8", "FfnSwigluFp8",
 ]
 
@@ -504,6 +504,13 @@ def peer_barrier(ctx, flag_arrays, world, rank, epoch, limit_ms=2000):
     """Barrier between the ranks of one box done by the GPUs (flag words in peer-mapped memory); flag_arrays: int64
     device tensor of the ranks' flag-array addresses as mapped in this process."""
     check(_L().cf_peer_barrier(ctx.handle, _p(flag_arrays), world, rank, int(epoch) & 0xffffffff, int(limit_ms), _s()))
+
+
+def peer_share_i32(ctx, src, n, tables, flag_arrays, world, rank, epoch, limit_ms=2000):
+    """This rank's n int32 words into row `rank` of every rank's [world, n] table, then the flag-word barrier, in one
+    launch (tables / flag_arrays: int64 device tensors of addresses as mapped in this process)."""
+    check(_L().cf_peer_share_i32(ctx.handle, _p(src), int(n), _p(tables), _p(flag_arrays), world, rank,
+                                 int(epoch) & 0xffffffff, int(limit_ms), _s()))
 
 
 ROW_RUN_BYTES = 24      # sizeof(cf_row_run): two int64 and two int32

@@ -245,6 +245,17 @@ class PeerBarrier:
         else:
             dist.all_reduce(self._fence, group=self.group)
 
+    @property
+    def on_device(self):
+        return self._flags is not None
+
+    def share_i32(self, src, n, tables):
+        """All-gather of n int32 words per rank into every rank's [world, n] table by peer stores, with the barrier in the
+        same launch (device kind only). tables: int64 device tensor of the ranks' table addresses as mapped here."""
+        assert self._flags is not None
+        self._epoch += 1
+        self.cfb.peer_share_i32(self.ctx, src, n, tables, self._flags, self.world, self.rank, self._epoch, self.limit_ms)
+
 
 class RowParallelReduceScatterGemm:
     """K-sharded (row-parallel) NT GEMM whose epilogue IS the reduce-scatter: every rank adds the row slices of its fp32
@@ -461,7 +472,6 @@ class EpMoeSwigluFp8Direct:
         self.counts = torch.zeros(V, dtype=i32, device=dev)
         self.offsets = torch.zeros(V, dtype=i32, device=dev)
         self.idx = torch.zeros((V, rows), dtype=i32, device=dev)
-        self.counts_all = torch.zeros((self.world, V), dtype=i32, device=dev)
         self.x8 = torch.empty((rows, H), dtype=torch.uint8, device=dev)
         self.h8 = torch.empty((cap, F), dtype=torch.uint8, device=dev)
         # compact results of the down GEMM: only the copied-return form keeps them locally
@@ -473,6 +483,9 @@ class EpMoeSwigluFp8Direct:
         self.slot_x = cfb.ActSlot(ctx, cfb.E4M3_MAX)
         self.slot_h = cfb.ActSlot(ctx, cfb.E4M3_MAX)
         self._keep = []
+        self.counts_all, pcounts = self._shared((self.world, V), i32)
+        self.counts_all.zero_()
+        self.peer_counts_all = torch.tensor(pcounts, dtype=torch.int64, device=dev)
         self.recv8, p8 = self._shared((cap, H), torch.uint8)
         self.recv_dx, pdx = self._shared((cap,), f32)
         self.back, pback = self._shared((T, H), torch.bfloat16)
@@ -522,14 +535,17 @@ class EpMoeSwigluFp8Direct:
         cfb.moe_expert_offsets_from_counts(self.counts, self.offsets, V)
         mark("route + replica choice + dispatch lists")
         gathered = None
-        if W > 1:
+        if W > 1 and not self._pb.on_device:
             # the count table travels while the activation is being quantised
             gathered = dist.all_gather_into_tensor(self.counts_all, self.counts, group=self.group, async_op=True)
-        else:
+        elif W == 1:
             self.counts_all.copy_(self.counts.view(1, V))
         cfb.fp8_quant_act(ctx, self.slot_x, x, self.x8)
         if gathered is not None:
             gathered.wait()
+        elif W > 1:
+            # every rank stores its counts into every rank's table and waits for the others' (one launch)
+            self._pb.share_i32(self.counts, V, self.peer_counts_all)
         mark("quantise x (count table gathered meanwhile)")
         cfb.moe_ep_plan(self.counts_all, W, self.rank, V, self.range_lo, self.range_hi, self.send_runs, self.grp_counts,
                         self.grp_offsets, self.ret_runs, recv_capacity_rows=self.cap, ctx=ctx)

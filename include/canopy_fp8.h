@@ -577,6 +577,14 @@ int cf_moe_send_row_runs(const void* d_src, const int* d_row_indices_or_null, lo
 int cf_peer_barrier(cf_ctx* ctx, unsigned* const* d_flag_arrays, int world, int rank, unsigned epoch, int limit_ms,
                     void* stream);
 
+/* A small all-gather done the same way, in the same launch as the barrier: this rank's n words (1..4096) are stored into
+ * row `rank` of every rank's [world, n] table (d_tables: DEVICE array of `world` table pointers as mapped here), then the
+ * barrier protocol of cf_peer_barrier runs with `epoch`, so the work behind the call sees every rank's row in its own
+ * table. The expert-parallel layer exchanges its per-replica row counts with it (a library all-gather of 36 integers
+ * costs several times as much). Same bounded wait and status reporting. No counterpart in the reference. */
+int cf_peer_share_i32(cf_ctx* ctx, const int* d_src, int n, int* const* d_tables, unsigned* const* d_flag_arrays, int world,
+                      int rank, unsigned epoch, int limit_ms, void* stream);
+
 /* The down projection of a device-planned expert-parallel layer with the return leg in its epilogue: a ragged grouped
  * NT GEMM (as cf_gemm_fp8_nt_grouped) whose output rows leave straight for the buffers of the ranks that own the tokens.
  * Inside group g the rows are the runs d_return_runs[g * runs_per_group + s] in ascending src_row (compact rows of A);

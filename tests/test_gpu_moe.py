@@ -435,6 +435,21 @@ def test_peer_barrier_passes_when_every_word_arrived_and_gives_up_within_its_lim
         ctx.poll_status()
     assert ei.value.code == cfb._capi.CF_ERR_DEVICE_WAIT
     ctx.poll_status()
+    # the small all-gather that rides on the barrier: this rank's words land in row 0 of both tables
+    n = 9
+    src = torch.arange(100, 100 + n, dtype=torch.int32, device="cuda")
+    t_mine = torch.full((2, n), -1, dtype=torch.int32, device="cuda")
+    t_peer = torch.full((2, n), -1, dtype=torch.int32, device="cuda")
+    tables = torch.tensor([t_mine.data_ptr(), t_peer.data_ptr()], dtype=torch.int64, device="cuda")
+    mine[1] = 9                                                      # "rank 1" is already at epoch 9
+    cfb.peer_share_i32(ctx, src, n, tables, arrays, 2, 0, 9, limit_ms=5)
+    ctx.poll_status()
+    assert torch.equal(t_mine[0], src) and torch.equal(t_peer[0], src)
+    assert (t_mine[1] == -1).all() and (t_peer[1] == -1).all()      # the other rank's rows are its own business
+    cfb.peer_share_i32(ctx, src, n, tables, arrays, 2, 0, 10, limit_ms=5)   # nobody announces epoch 10
+    with pytest.raises(cfb.CanopyError) as ei:
+        ctx.poll_status()
+    assert ei.value.code == cfb._capi.CF_ERR_DEVICE_WAIT
     # epochs compare modulo 2^32: a word that has wrapped past the epoch counts as arrived, one just behind it does not
     mine[1] = 3
     cfb.peer_barrier(ctx, arrays, 2, 0, 0xFFFFFFFE, limit_ms=5)

@@ -301,7 +301,8 @@ __global__ void __launch_bounds__(kThreads) k_pack_raw_stats(const uint16_t* __r
     int local_bad = 0;
     const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
     const size_t nvec = vec ? n / 8 : 0;
-    auto scan = [&](const uint4& v) {
+    for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < nvec; i += stride) {
+        const uint4 v = __ldcs(reinterpret_cast<const uint4*>(x) + i);
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -312,16 +313,8 @@ __global__ void __launch_bounds__(kThreads) k_pack_raw_stats(const uint16_t* __r
                 else local = fmaxf(local, bf16_bits_to_f32(b & 0x7fffu));
             }
         }
-    };
-    // four 16-byte loads in flight per thread
-    size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x;
-    for (; i + 3 * stride < nvec; i += 4 * stride) {
-        const uint4 v0 = __ldcs(reinterpret_cast<const uint4*>(x) + i), v1 = __ldcs(reinterpret_cast<const uint4*>(x) + i + stride);
-        const uint4 v2 = __ldcs(reinterpret_cast<const uint4*>(x) + i + 2 * stride), v3 = __ldcs(reinterpret_cast<const uint4*>(x) + i + 3 * stride);
-        scan(v0); scan(v1); scan(v2); scan(v3);
     }
-    for (; i < nvec; i += stride) scan(__ldcs(reinterpret_cast<const uint4*>(x) + i));
-    for (i = nvec * 8 + static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) {
+    for (size_t i = nvec * 8 + static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) {
         const uint32_t b = x[i];
         if ((b & 0x7f80u) == 0x7f80u) local_bad = 1;            // Inf or NaN
         else local = fmaxf(local, bf16_bits_to_f32(b & 0x7fffu));
@@ -354,7 +347,8 @@ __global__ void __launch_bounds__(kThreads) k_pack_raw(const uint16_t* __restric
     int nbad = 0;
     const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
     const size_t nvec = vec ? n / 8 : 0;          // 8 elements per thread: 16 bytes in, 8 bytes (+16 bytes) out
-    auto emit = [&](size_t i, const uint4& v) {
+    for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < nvec; i += stride) {
+        const uint4 v = __ldcs(reinterpret_cast<const uint4*>(x) + i);
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
         uint32_t codes[2] = {0u, 0u}, dq[4];
 #pragma unroll
@@ -368,18 +362,10 @@ __global__ void __launch_bounds__(kThreads) k_pack_raw(const uint16_t* __restric
                 dq[j] = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16(unpack_e4m3(static_cast<uint8_t>(c0)) * d))) |
                         (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16(unpack_e4m3(static_cast<uint8_t>(c1)) * d))) << 16);
         }
-        __stcs(reinterpret_cast<uint2*>(out) + i, make_uint2(codes[0], codes[1]));
-        if (DEQUANT) __stcs(reinterpret_cast<uint4*>(dequant) + i, make_uint4(dq[0], dq[1], dq[2], dq[3]));
-    };
-    // two 16-byte loads in flight per thread
-    size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x;
-    for (; i + stride < nvec; i += 2 * stride) {
-        const uint4 v0 = __ldcs(reinterpret_cast<const uint4*>(x) + i), v1 = __ldcs(reinterpret_cast<const uint4*>(x) + i + stride);
-        emit(i, v0);
-        emit(i + stride, v1);
+        reinterpret_cast<uint2*>(out)[i] = make_uint2(codes[0], codes[1]);
+        if (DEQUANT) reinterpret_cast<uint4*>(dequant)[i] = make_uint4(dq[0], dq[1], dq[2], dq[3]);
     }
-    for (; i < nvec; i += stride) emit(i, __ldcs(reinterpret_cast<const uint4*>(x) + i));
-    for (i = nvec * 8 + static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) {
+    for (size_t i = nvec * 8 + static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) {
         int nf = 0;
         const uint8_t c = pack_e4m3(bf16_bits_to_f32(x[i]) * s, nf);
         nbad += nf;
@@ -444,10 +430,7 @@ __global__ void __launch_bounds__(kThreads) k_tile_transpose(const void* __restr
                                                              const ScaleFromAmax sfa, const LionArgs la) {
     constexpr bool SRC_BF16 = SRC != 0;
     __shared__ uint32_t tile[kTR * 16];
-    // a byte-source block moves two adjacent column tiles, so that the two 64-byte halves of every 128-byte source line are
-    // requested together
-    constexpr int SUB = SRC == 0 ? 2 : 1;
-    const int r0 = blockIdx.y * kTR, c0 = blockIdx.x * kTC * SUB;
+    const int r0 = blockIdx.y * kTR, c0 = blockIdx.x * kTC;
     const int tid = threadIdx.x;
     pdl_wait();
     float s = 0.0f;
@@ -465,7 +448,6 @@ __global__ void __launch_bounds__(kThreads) k_tile_transpose(const void* __restr
         }
     }
 
-    uint4 bq[SUB][kTR / 64];           // byte source only: the thread's loads of both column tiles
     if (SRC == 2) {
         // 8 threads x 8 columns per row, 32 rows per pass, 8 passes (vector accesses: the launcher requires
         // cols % 8 == 0 and aligned bases); rows and columns outside the tensor leave zeros in the tile
@@ -565,58 +547,39 @@ __global__ void __launch_bounds__(kThreads) k_tile_transpose(const void* __restr
             tile[tile_word(k, (cg >> 2) + 1)] = q.y;
         }
     } else {
-        // 4 threads x 16 bytes per source row, 64 rows per pass, 4 passes, two column tiles: all eight loads of a thread
-        // are issued before the first tile is filled
+        // 4 threads x 16 bytes per source row, 64 rows per pass, 4 passes
         const uint8_t* in = static_cast<const uint8_t*>(src);
         const int cg = (tid & 3) * 16, rl = tid >> 2;
 #pragma unroll
-        for (int sub = 0; sub < SUB; ++sub) {
+        for (int p = 0; p < kTR / 64; ++p) {
+            const int k = p * 64 + rl;
+            const int r = r0 + k, c = c0 + cg;
+            uint4 q = make_uint4(0u, 0u, 0u, 0u);
+            if (r < R && c < Ccols) {
+                const size_t off = static_cast<size_t>(r) * Ccols + c;
+                if (src_vec && c + 16 <= Ccols) {
+                    q = ldg_stream16(in + off);
+                } else {
+                    uint32_t w[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-            for (int p = 0; p < kTR / 64; ++p) {
-                const int k = p * 64 + rl;
-                const int r = r0 + k, c = c0 + sub * kTC + cg;
-                uint4 q = make_uint4(0u, 0u, 0u, 0u);
-                if (r < R && c < Ccols) {
-                    const size_t off = static_cast<size_t>(r) * Ccols + c;
-                    if (src_vec && c + 16 <= Ccols) {
-                        q = ldg_stream16(in + off);
-                    } else {
-                        uint32_t w[4] = {0u, 0u, 0u, 0u};
-#pragma unroll
-                        for (int b = 0; b < 16; ++b)
-                            if (c + b < Ccols) w[b >> 2] |= static_cast<uint32_t>(in[off + b]) << (8 * (b & 3));
-                        q = make_uint4(w[0], w[1], w[2], w[3]);
-                    }
+                    for (int b = 0; b < 16; ++b)
+                        if (c + b < Ccols) w[b >> 2] |= static_cast<uint32_t>(in[off + b]) << (8 * (b & 3));
+                    q = make_uint4(w[0], w[1], w[2], w[3]);
                 }
-                bq[sub][p] = q;
             }
+            const int wc = cg >> 2;
+            tile[tile_word(k, wc)] = q.x;
+            tile[tile_word(k, wc + 1)] = q.y;
+            tile[tile_word(k, wc + 2)] = q.z;
+            tile[tile_word(k, wc + 3)] = q.w;
         }
     }
-    if (SRC != 0) {
-        __syncthreads();
-        if (!transposed) return;
-    }
+    __syncthreads();
+    if (!transposed) return;
 
     // Lane = 8 consecutive source rows (kc8), warp = two word columns (ng): 8 word reads, two 4x4 byte
     // transposes, four 8-byte stores; the 32 lanes of one store cover one whole 256-byte output row.
     const int kc8 = tid & 31, warp = tid >> 5;
-#pragma unroll 1
-    for (int sub = 0; sub < SUB; ++sub) {
-    const int c0s = c0 + sub * kTC;
-    if (SRC == 0) {
-        if (sub > 0) __syncthreads();          // the previous tile has been written out
-        const int cg = (tid & 3) * 16, rl = tid >> 2, wc = cg >> 2;
-#pragma unroll
-        for (int p = 0; p < kTR / 64; ++p) {
-            const int k = p * 64 + rl;
-            tile[tile_word(k, wc)] = bq[sub][p].x;
-            tile[tile_word(k, wc + 1)] = bq[sub][p].y;
-            tile[tile_word(k, wc + 2)] = bq[sub][p].z;
-            tile[tile_word(k, wc + 3)] = bq[sub][p].w;
-        }
-        __syncthreads();
-        if (c0s >= Ccols) break;               // block-uniform
-    }
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         const int ng = warp * 2 + half;
@@ -637,7 +600,7 @@ __global__ void __launch_bounds__(kThreads) k_tile_transpose(const void* __restr
         const int ocol = r0 + kc8 * 8;           // output column = source row
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const int orow = c0s + ng * 4 + j;   // output row = source column
+            const int orow = c0 + ng * 4 + j;    // output row = source column
             if (orow >= Ccols || ocol >= R) continue;
             uint8_t* dst = transposed + static_cast<size_t>(orow) * R + ocol;
             if (trans_vec && ocol + 8 <= R) {
@@ -648,7 +611,6 @@ __global__ void __launch_bounds__(kThreads) k_tile_transpose(const void* __restr
                     if (ocol + b < R) dst[b] = static_cast<uint8_t>(o[j][b >> 2] >> (8 * (b & 3)));
             }
         }
-    }
     }
 }
 
@@ -664,8 +626,7 @@ int launch_tile_transpose(const void* src, void* direct, void* transposed, const
     const int src_vec = (sa % 16 == 0) && ((static_cast<size_t>(Ccols) * esz) % 16 == 0);
     const int direct_vec = direct && (da % 8 == 0) && (Ccols % 8 == 0);
     const int trans_vec = transposed && (ta % 8 == 0) && (R % 8 == 0);
-    constexpr int cols_per_block = kTC * (SRC == 0 ? 2 : 1);
-    dim3 grid((Ccols + cols_per_block - 1) / cols_per_block, (R + kTR - 1) / kTR);
+    dim3 grid((Ccols + kTC - 1) / kTC, (R + kTR - 1) / kTR);
     CF_CUDA(launch_pdl(k_tile_transpose<SRC>, grid, dim3(kThreads), 0, st, src, static_cast<uint8_t*>(direct),
                        static_cast<uint8_t*>(transposed), scale, R, Ccols, src_vec, direct_vec, trans_vec, sfa, la));
     CF_LAUNCH_CHECK(name);

@@ -695,7 +695,8 @@ def leg_moe(args, env):
     cfb.moe_topk_route_f32(rw0, rows, E, TOPK)
     load = (rw0 > 0).sum(dim=0).to(torch.float32)          # observed load of a calibration routing, summed over ranks
     dist.all_reduce(load)
-    placement = par.ReplicaPlacement.build(load.cpu().tolist(), world)
+    # pieces sized for equal tile work (rows + expected padding of each replica's last 256-row tile), not equal rows
+    placement = par.ReplicaPlacement.build(load.cpu().tolist(), world, total_rows=TOK * TOPK, tile_rows=256)
     local_ids = placement.local_experts(rank)
     wgu8, dgu_l, wd8, dd_l = moe_weights(env, local_ids, allreduce=True)
     wgu8 = cfb.fp8_interleave_gate_up(wgu8)

@@ -100,17 +100,23 @@ class ReplicaPlacement:
         return len(self.replica_expert)
 
     @classmethod
-    def build(cls, popularity, world, min_share=0.02):
+    def build(cls, popularity, world, min_share=0.02, total_rows=None, tile_rows=256):
         """popularity: expected share of the rows per expert (any positive scale). Overlaps below `min_share` of a
         rank's piece are not worth a weight copy: they are merged into the expert's largest replica. The layout is
-        computed by the library (cf_ep_placement_build), the same call a C++ trainer makes."""
+        computed by the library (cf_ep_placement_build), the same call a C++ trainer makes. With total_rows (selected
+        rows of all ranks per layer) the pieces are sized for equal tile work instead of equal rows
+        (cf_ep_placement_build_balanced): a rank with several small replicas pays about tile_rows / 2 padded rows each."""
         import ctypes as C
 
         from . import _capi
         E = len(popularity)
         pop = (C.c_double * E)(*[float(x) for x in popularity])
         pl = _capi.EpPlacementStruct()
-        _capi.check(_capi.lib().cf_ep_placement_build(pop, E, int(world), float(min_share), C.byref(pl)))
+        if total_rows:
+            _capi.check(_capi.lib().cf_ep_placement_build_balanced(pop, E, int(world), float(min_share), float(total_rows),
+                                                                   int(tile_rows), C.byref(pl)))
+        else:
+            _capi.check(_capi.lib().cf_ep_placement_build(pop, E, int(world), float(min_share), C.byref(pl)))
         V = pl.num_replicas
         return cls(world, E, list(pl.replica_expert[:V]), list(pl.replica_rank[:V]), list(pl.replica_share[:V]),
                    list(pl.replica_start[:E + 1]), list(pl.replica_cum_share[:V]),

@@ -530,6 +530,13 @@ typedef struct cf_ep_placement {
     int rank_hi[CF_EP_MAX_RANKS];
 } cf_ep_placement;
 int cf_ep_placement_build(const double* popularity, int num_experts, int world, double min_share, cf_ep_placement* out);
+/* The same placement with the pieces of the line sized so that the ranks share the TILE WORK rather than the rows: the
+ * grouped GEMM processes every replica in tiles of tile_rows rows (256 in the CTA-pair form), so a rank that holds
+ * several small replicas pays about tile_rows / 2 padded rows for each of them (at 8 ranks and a Zipf load the rank
+ * with four replicas does 9 % more tile work than the rank with one, and every rank waits for it). expected_total_rows:
+ * selected rows of all ranks per layer (tokens * top_k). Never worse than the equal-rows placement by its own cost model. */
+int cf_ep_placement_build_balanced(const double* popularity, int num_experts, int world, double min_share,
+                                   double expected_total_rows, int tile_rows, cf_ep_placement* out);
 
 /* A run of rows on its way to another buffer: `rows` rows starting at src_row (ignored when the call gathers through an
  * index table) go to row dst_row of destination buffer number dst. */

@@ -256,3 +256,43 @@ def test_expert_placement_from_the_library_matches_the_rule_written_in_python():
         par.ReplicaPlacement.build([1.0] * 300, 2)
     with pytest.raises(Exception):
         par.ReplicaPlacement.build([1.0, -1.0], 2)
+
+
+def test_placement_balanced_by_tile_work_is_never_worse_and_keeps_the_invariants():
+    """cf_ep_placement_build_balanced sizes the ranks' pieces for equal rows + expected padding; by its own cost model
+    (rows + half a tile per replica) the busiest rank is never busier than with equal rows, and at 8 ranks under a Zipf
+    load it is clearly less busy."""
+    import math
+    import random
+    par = package().parallel
+    rnd = random.Random(11)
+    zipf = [25089, 14832, 9032, 5887, 4045, 2940, 2079, 1632]
+    cases = [(zipf, w) for w in (1, 2, 4, 8)] + [([rnd.random() ** 2 + 0.01 for _ in range(rnd.randint(2, 32))], rnd.randint(2, 16))
+                                                 for _ in range(100)]
+
+    def worst(pl, load, total, tile):
+        tot = sum(load)
+        out = 0.0
+        for g in range(pl.world):
+            lo, hi = pl.rank_ranges[g]
+            c = sum(load[pl.replica_expert[v]] / tot * total * pl.replica_share[v] + tile / 2 for v in range(lo, hi))
+            out = max(out, c)
+        return out
+
+    for load, w in cases:
+        total, tile = 65536, 256
+        a = par.ReplicaPlacement.build(load, w)
+        b = par.ReplicaPlacement.build(load, w, total_rows=total, tile_rows=tile)
+        assert worst(b, load, total, tile) <= worst(a, load, total, tile) + 1e-6
+        for e in range(len(load)):
+            assert abs(sum(b.replica_share[b.replica_start[e]:b.replica_start[e + 1]]) - 1.0) < 1e-9
+        assert b.replica_rank == sorted(b.replica_rank) and b.replica_expert == sorted(b.replica_expert)
+        ids = [v for g in range(w) for v in range(*b.rank_ranges[g])]
+        assert ids == list(range(b.num_replicas))
+    a = par.ReplicaPlacement.build(zipf, 8)
+    b = par.ReplicaPlacement.build(zipf, 8, total_rows=65536, tile_rows=256)
+
+    def tiles(pl):
+        return max(sum(math.ceil(zipf[pl.replica_expert[v]] * pl.replica_share[v] / 256) * 256 for v in range(*pl.rank_ranges[g]))
+                   for g in range(8))
+    assert tiles(b) <= tiles(a) - 256

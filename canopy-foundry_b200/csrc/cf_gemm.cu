@@ -227,13 +227,23 @@ struct TileCoord {
 
 // Maps a linear tile index to coordinates. Dense: one group of p.M rows. Grouped: the m-blocks of
 // all experts are concatenated in expert order; counts/offsets are read from device memory.
-__device__ __forceinline__ int total_m_blocks(const GemmParams& p, int TM) {
+// The group table of a ragged problem as the tile mapping reads it: a shared-memory copy made once per CTA (the
+// mapping walks the counts for every tile, in each of the three roles; from global memory that walk costs the TMA
+// producer a chain of L2 round trips at every tile start, long enough to drain its stage ring), or the arrays in
+// global memory when there are more groups than the copy holds.
+constexpr int kGroupsInSmem = 96;
+struct GroupView {
+    const int* counts;
+    const int* offsets;
+    const int* weight;      // null = group index
+};
+__device__ __forceinline__ int total_m_blocks(const GemmParams& p, const GroupView& gv, int TM) {
     if (p.groups <= 1 && p.d_counts == nullptr) return (p.M + TM - 1) / TM;
     int t = 0;
-    for (int e = 0; e < p.groups; ++e) t += (max(p.d_counts[e], 0) + TM - 1) / TM;
+    for (int e = 0; e < p.groups; ++e) t += (max(gv.counts[e], 0) + TM - 1) / TM;
     return t;
 }
-__device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, int m_blocks, int TM) {
+__device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, const GroupView& gv, int tile, int m_blocks, int TM) {
     TileCoord c;
     // Band rasterisation: consecutive tile indices walk RASTER_M row blocks down, then one column block
     // right, so the tiles in flight at any time share few A and B slabs (L2 reuse).
@@ -259,15 +269,15 @@ __device__ __forceinline__ TileCoord tile_coord(const GemmParams& p, int tile, i
     }
     int e = 0, cnt = 0;
     for (; e < p.groups; ++e) {
-        cnt = max(p.d_counts[e], 0);
+        cnt = max(gv.counts[e], 0);
         const int blocks = (cnt + TM - 1) / TM;
         if (mb < blocks) break;
         mb -= blocks;
     }
     c.group = e;
-    c.row0 = p.d_offsets[e] + mb * TM;
+    c.row0 = gv.offsets[e] + mb * TM;
     c.valid_rows = min(TM, cnt - mb * TM);
-    c.weight = p.d_group_weight ? p.d_group_weight[e] : e;
+    c.weight = gv.weight ? gv.weight[e] : e;
     c.b_row0 = c.weight * p.N + c.n0;
     if (p.d_group_out) {
         c.out_base = p.d_group_out[e];
@@ -376,7 +386,20 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
     // reads what earlier kernels of the stream wrote (operands, scales, counts).
     pdl_wait();
 
-    const int m_blocks = total_m_blocks(p, TM);
+    __shared__ int s_groups[3 * kGroupsInSmem];
+    GroupView gv = {p.d_counts, p.d_offsets, p.d_group_weight};
+    if (p.d_counts != nullptr && p.groups <= kGroupsInSmem) {          // kernel-uniform
+        for (int e = threadIdx.x; e < p.groups; e += NUM_THREADS) {
+            s_groups[e] = p.d_counts[e];
+            s_groups[kGroupsInSmem + e] = p.d_offsets[e];
+            if (p.d_group_weight) s_groups[2 * kGroupsInSmem + e] = p.d_group_weight[e];
+        }
+        __syncthreads();
+        gv.counts = s_groups;
+        gv.offsets = s_groups + kGroupsInSmem;
+        gv.weight = p.d_group_weight ? s_groups + 2 * kGroupsInSmem : nullptr;
+    }
+    const int m_blocks = total_m_blocks(p, gv, TM);
     const int n_blocks = (p.N + BN - 1) / BN;
     const int total_tiles = m_blocks * n_blocks;
     const int k_iters = (p.K + BK - 1) / BK;
@@ -389,7 +412,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
             // the byte count of a stage is credited to the leader's barrier
             const uint32_t full_dst = PAIR ? mapa(full_bar, 0) : full_bar;
             for (int tile = unit; ok && tile < total_tiles; tile += n_units) {
-                const TileCoord tc = tile_coord(p, tile, m_blocks, TM);
+                const TileCoord tc = tile_coord(p, gv, tile, m_blocks, TM);
                 const int a_row = tc.row0 + static_cast<int>(cta_rank) * BM;
                 const int b_row = tc.b_row0 + static_cast<int>(cta_rank) * C::B_ROWS;
                 for (int kb = 0; kb < k_iters; ++kb, ++it) {
@@ -476,7 +499,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
         bool ok = true;
         for (int tile = unit; ok && tile < total_tiles; tile += n_units, ++local_tile) {
             const int acc = local_tile & 1;
-            const TileCoord tc = tile_coord(p, tile, m_blocks, TM);
+            const TileCoord tc = tile_coord(p, gv, tile, m_blocks, TM);
             if (!mbar_wait(tfull_bar + 8 * acc, (local_tile >> 1) & 1, s_abort)) { ok = false; break; }
             tcgen05_fence_after();
             const int row_in_tile = static_cast<int>(cta_rank) * BM + trow;
@@ -607,11 +630,6 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 for (; ch < col_half * 4 + 4; ++ch) {
                     const int col0 = tc.n0 + ch * 32;
                     if (col0 + 32 > p.N) break;            // warp-uniform; the tail takes the direct path below
-                    float4 cq[8];
-                    if (p.d_b_col_descale) {
-#pragma unroll
-                        for (int q = 0; q < 8; ++q) cq[q] = __ldg(reinterpret_cast<const float4*>(p.d_b_col_descale + col0) + q);
-                    }
                     uint32_t v[32];
                     tmem_ld32(taddr + ch * 32, v);
                     tmem_ld_wait();
@@ -620,7 +638,10 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
 #pragma unroll
                     for (int q = 0; q < 8; ++q) {
                         float4 m4 = make_float4(dab, dab, dab, dab);
-                        if (p.d_b_col_descale) m4 = make_float4(da * cq[q].x, da * cq[q].y, da * cq[q].z, da * cq[q].w);
+                        if (p.d_b_col_descale) {       // the same address in every lane: one broadcast load per four columns
+                            const float4 cq = __ldg(reinterpret_cast<const float4*>(p.d_b_col_descale + col0) + q);
+                            m4 = make_float4(da * cq.x, da * cq.y, da * cq.z, da * cq.w);
+                        }
                         st_shared_v4(buf + row_off + ((static_cast<uint32_t>(q) ^ sw) << 4),
                                      __float_as_uint(__uint_as_float(v[4 * q]) * m4.x), __float_as_uint(__uint_as_float(v[4 * q + 1]) * m4.y),
                                      __float_as_uint(__uint_as_float(v[4 * q + 2]) * m4.z), __float_as_uint(__uint_as_float(v[4 * q + 3]) * m4.w));

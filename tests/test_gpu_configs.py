@@ -257,6 +257,50 @@ def test_fused_rowwise_mlp_full_size_sampled(cfb, ctx, oracle):
     assert torch.equal(y0.view(torch.int16), y[2048:3072].view(torch.int16))
 
 
+@pytest.mark.parametrize("rows,cols", [(5, 100), (64, 4096), (33, 1000), (7, 16), (3, 1)])
+def test_rowwise_quantise_with_a_given_amax_equals_the_two_pass_kernel(cfb, oracle, rows, cols):
+    """Given each row's own amax, the one-pass quantiser writes the codes and descales of cf_fp8_quantize_rowwise_e4m3
+    (vector path for 16-byte multiples, element path otherwise); a larger amax (as after a max over shards) scales down."""
+    x = randn_bf16((rows, cols), seed=rows + cols, outlier_frac=0.01)
+    x[0] = 0
+    want8 = torch.empty((rows, cols), dtype=torch.uint8, device="cuda")
+    want_d = torch.empty(rows, dtype=torch.float32, device="cuda")
+    want_s = torch.empty(rows, dtype=torch.float32, device="cuda")
+    cfb.fp8_quantize_rowwise_e4m3(x, want8, want_d, row_scale=want_s)
+    amax = x.float().abs().amax(dim=1).contiguous()
+    got8 = torch.full((rows, cols), 0xAB, dtype=torch.uint8, device="cuda")
+    got_d = torch.empty(rows, dtype=torch.float32, device="cuda")
+    got_s = torch.empty(rows, dtype=torch.float32, device="cuda")
+    cfb.fp8_quantize_rowwise_given_amax_e4m3(x, got8, amax, got_d, row_scale=got_s)
+    assert torch.equal(got8, want8) and torch.equal(got_d, want_d) and torch.equal(got_s, want_s)
+    w, s_o, d_o = oracle.quantize_rowwise_e4m3(bf16_to_u16(x))
+    assert np.array_equal(got8.cpu().numpy(), w) and np.array_equal(got_d.cpu().numpy(), d_o)
+    big = (amax * 2 + 1).contiguous()
+    cfb.fp8_quantize_rowwise_given_amax_e4m3(x, got8, big, got_d)
+    ref = oracle.bf16_to_f32(bf16_to_u16(x)) * (np.float32(448.0) / big.cpu().numpy())[:, None]
+    dec = oracle.decode(got8.cpu().numpy())
+    assert np.all(np.abs(dec - ref) <= np.maximum(np.abs(ref) * 2.0 ** -4, 2.0 ** -9) + 1e-6)
+
+
+def test_swiglu_bf16_rowamax_epilogue_with_per_tensor_scales(cfb, ctx):
+    """The same epilogue under per-tensor scales (the reference's granularity): h and the row amax equal the unfused
+    GEMM + swiglu_forward, ragged row counts included."""
+    for M, H, F in [(300, 128, 96), (1024, 256, 512)]:
+        a8, da = _tensorquant(cfb, randn_bf16((M, H), seed=M))
+        w8, dw = _tensorquant(cfb, randn_bf16((2 * F, H), std=0.05, seed=F))
+        gu = torch.empty((M, 2 * F), dtype=torch.bfloat16, device="cuda")
+        cfb.lt_gemm_fp8_nt(ctx, M, 2 * F, H, a8, H, False, da, w8, dw, gu, 2 * F)
+        want = torch.empty((M, F), dtype=torch.bfloat16, device="cuda")
+        cfb.swiglu_forward(gu[:, :F].contiguous(), gu[:, F:].contiguous(), want)
+        il = cfb.fp8_interleave_gate_up(w8.view(1, 2 * F, H)).view(2 * F, H)
+        h = torch.full((M + 1, F), 9.0, dtype=torch.bfloat16, device="cuda")
+        hmax = torch.zeros(M + 1, dtype=torch.float32, device="cuda")
+        cfb.gemm_fp8_swiglu_bf16_rowamax(ctx, M, F, H, a8, H, False, da, None, il, dw, None, h, hmax)
+        ctx.poll_status()
+        assert torch.equal(h[:M].view(torch.int16), want.view(torch.int16)) and (h[M] == 9.0).all()
+        assert torch.equal(hmax[:M], want.float().abs().amax(dim=1)) and hmax[M].item() == 0.0
+
+
 def _zipf_logits(rows, E, seed):
     g = torch.Generator(device="cuda").manual_seed(seed)
     p = torch.arange(1, E + 1, device="cuda", dtype=torch.float32) ** -1.1

@@ -192,6 +192,122 @@ int launch_rowwise_fast(const uint16_t* a, const uint16_t* b, long long ld_in, u
     return CF_OK;
 }
 
+// The same scheme for rows that are not 16-byte aligned or whose length is not a multiple of 8: each row is cut into a
+// head of up to 7 elements (up to the first 16-byte boundary of the input), whole 16-byte vectors, and a tail of up to 7
+// elements. Head and tail live in one register each of the threads 0..6; the vectors are stored as 8-byte words when the
+// output address allows it and byte by byte otherwise. SWIGLU: gate and up must share their alignment (checked by the
+// launcher).
+template <bool SWIGLU, int NV>
+__global__ void __launch_bounds__(kFastT) k_rowwise_ragged(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b,
+                                                           long long ld_in, uint8_t* __restrict__ out, long long ld_out,
+                                                           float* __restrict__ row_scale, float* __restrict__ row_descale,
+                                                           int rows, int cols) {
+    __shared__ float s_m[2][2];
+    const int j = threadIdx.x;
+    int par = 0;
+    for (long long row = blockIdx.x; row < rows; row += gridDim.x, par ^= 1) {
+        const uint16_t* arow = a + row * ld_in;
+        const uint16_t* brow = SWIGLU ? b + row * ld_in : nullptr;
+        const int head = min(cols, static_cast<int>((8u - static_cast<unsigned>((reinterpret_cast<uintptr_t>(arow) >> 1) & 7u)) & 7u));
+        const int nvec = (cols - head) >> 3;
+        const int tail0 = head + (nvec << 3), tail = cols - tail0;
+        const uint4* ar = reinterpret_cast<const uint4*>(arow + head);
+        const uint4* br = SWIGLU ? reinterpret_cast<const uint4*>(brow + head) : nullptr;
+        uint4 v[NV];
+        float hx = 0.0f, tx = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+            if (j + kFastT * i < nvec) v[i] = __ldcs(ar + j + kFastT * i);
+        if (j < head) {
+            hx = bf16_bits_to_f32(arow[j]);
+            if (SWIGLU) hx = bf16_round(hx * stable_sigmoid(hx) * bf16_bits_to_f32(brow[j]));
+        }
+        if (j < tail) {
+            tx = bf16_bits_to_f32(arow[tail0 + j]);
+            if (SWIGLU) tx = bf16_round(tx * stable_sigmoid(tx) * bf16_bits_to_f32(brow[tail0 + j]));
+        }
+        float local = fmaxf(fabsf(hx), fabsf(tx));
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (j + kFastT * i < nvec) {
+                float f[8];
+                unpack8(v[i], f);
+                if (SWIGLU) {
+                    float u[8];
+                    unpack8(__ldcs(br + j + kFastT * i), u);
+                    v[i].x = pack2_bf16(f[0] * stable_sigmoid(f[0]) * u[0], f[1] * stable_sigmoid(f[1]) * u[1]);
+                    v[i].y = pack2_bf16(f[2] * stable_sigmoid(f[2]) * u[2], f[3] * stable_sigmoid(f[3]) * u[3]);
+                    v[i].z = pack2_bf16(f[4] * stable_sigmoid(f[4]) * u[4], f[5] * stable_sigmoid(f[5]) * u[5]);
+                    v[i].w = pack2_bf16(f[6] * stable_sigmoid(f[6]) * u[6], f[7] * stable_sigmoid(f[7]) * u[7]);
+                    unpack8(v[i], f);
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) local = fmaxf(local, fabsf(f[e]));
+            }
+        }
+        local = warp_max(local);
+        if ((j & 31) == 0) s_m[par][j >> 5] = local;
+        __syncthreads();
+        const float amax = fmaxf(fmaxf(s_m[par][0], s_m[par][1]), 1e-12f);
+        const float s = __fdiv_rn(448.0f, amax);
+        if (j == 0) {
+            if (row_scale) row_scale[row] = s;
+            row_descale[row] = __fdiv_rn(amax, 448.0f);
+        }
+        uint8_t* orow = out + row * ld_out;
+        if (j < head) orow[j] = cvt_fp8<false>(hx * s);
+        if (j < tail) orow[tail0 + j] = cvt_fp8<false>(tx * s);
+        uint8_t* ob = orow + head;
+        const bool word = (reinterpret_cast<uintptr_t>(ob) & 7u) == 0;      // the same for every vector of the row
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (j + kFastT * i < nvec) {
+                float f[8];
+                unpack8(v[i], f);
+                uint2 q;
+                q.x = cvt_fp8x4<false>(f[0] * s, f[1] * s, f[2] * s, f[3] * s);
+                q.y = cvt_fp8x4<false>(f[4] * s, f[5] * s, f[6] * s, f[7] * s);
+                uint8_t* o = ob + (static_cast<size_t>(j + kFastT * i) << 3);
+                if (word) {
+                    *reinterpret_cast<uint2*>(o) = q;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        o[e] = static_cast<uint8_t>(q.x >> (8 * e));
+                        o[4 + e] = static_cast<uint8_t>(q.y >> (8 * e));
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <bool SWIGLU, int NV>
+int launch_rowwise_ragged(const uint16_t* a, const uint16_t* b, long long ld_in, uint8_t* out, long long ld_out, float* row_scale,
+                          float* row_descale, int rows, int cols, cudaStream_t st) {
+    int per_sm = 0;
+    CF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_rowwise_ragged<SWIGLU, NV>, kFastT, 0));
+    if (per_sm < 1) per_sm = 1;
+    long long grid = static_cast<long long>(sm_count()) * per_sm;
+    if (grid > rows) grid = rows;
+    k_rowwise_ragged<SWIGLU, NV><<<static_cast<unsigned>(grid), kFastT, 0, st>>>(a, b, ld_in, out, ld_out, row_scale, row_descale,
+                                                                                rows, cols);
+    return CF_OK;
+}
+
+static_assert(kFastT * 32 * 8 >= kRT * kMaxVec * 8, "the ragged form covers every row length the entry points accept");
+
+template <bool SWIGLU>
+int launch_rowwise_ragged_nv(const uint16_t* a, const uint16_t* b, long long ld_in, uint8_t* out, long long ld_out,
+                             float* row_scale, float* row_descale, int rows, int cols, cudaStream_t st) {
+    const int nv = (cols / 8 + kFastT - 1) / kFastT;
+    if (nv <= 2) return launch_rowwise_ragged<SWIGLU, 2>(a, b, ld_in, out, ld_out, row_scale, row_descale, rows, cols, st);
+    if (nv <= 4) return launch_rowwise_ragged<SWIGLU, 4>(a, b, ld_in, out, ld_out, row_scale, row_descale, rows, cols, st);
+    if (nv <= 8) return launch_rowwise_ragged<SWIGLU, 8>(a, b, ld_in, out, ld_out, row_scale, row_descale, rows, cols, st);
+    if (nv <= 16) return launch_rowwise_ragged<SWIGLU, 16>(a, b, ld_in, out, ld_out, row_scale, row_descale, rows, cols, st);
+    return launch_rowwise_ragged<SWIGLU, 32>(a, b, ld_in, out, ld_out, row_scale, row_descale, rows, cols, st);
+}
+
 template <bool SWIGLU>
 int launch_rowwise_fast_nv(const uint16_t* a, const uint16_t* b, long long ld_in, uint8_t* out, long long ld_out,
                            float* row_scale, float* row_descale, int rows, int cols, cudaStream_t st) {
@@ -355,9 +471,9 @@ int cf_fp8_quantize_rowwise_e4m3(const void* d_x, int ld_x, void* d_out, int ld_
         CF_LAUNCH_CHECK("quantize_rowwise_e4m3");
         return CF_OK;
     }
-    k_rowwise<false><<<rows, kRT, 0, as_stream(stream)>>>(static_cast<const uint16_t*>(d_x), nullptr, ld_x,
-                                                          static_cast<uint8_t*>(d_out), ld_out, d_row_scale, d_row_descale,
-                                                          cols, vec);
+    // any other alignment or length (cols <= 16384 was checked above): head / vectors / tail per row
+    CF_TRY_RET(launch_rowwise_ragged_nv<false>(static_cast<const uint16_t*>(d_x), nullptr, ld_x, static_cast<uint8_t*>(d_out), ld_out,
+                                               d_row_scale, d_row_descale, rows, cols, as_stream(stream)));
     CF_LAUNCH_CHECK("quantize_rowwise_e4m3");
     return CF_OK;
 }
@@ -374,6 +490,14 @@ int cf_swiglu_quantize_rowwise_e4m3(const void* d_gate, const void* d_up, int ld
         CF_TRY_RET(launch_rowwise_fast_nv<true>(static_cast<const uint16_t*>(d_gate), static_cast<const uint16_t*>(d_up), ld_in,
                                                 static_cast<uint8_t*>(d_out), ld_out, d_row_scale, d_row_descale, rows, cols,
                                                 as_stream(stream)));
+        CF_LAUNCH_CHECK("swiglu_quantize_rowwise_e4m3");
+        return CF_OK;
+    }
+    if (((reinterpret_cast<uintptr_t>(d_gate) ^ reinterpret_cast<uintptr_t>(d_up)) & 15) == 0) {
+        // gate and up rows share their alignment: head / vectors / tail per row
+        CF_TRY_RET(launch_rowwise_ragged_nv<true>(static_cast<const uint16_t*>(d_gate), static_cast<const uint16_t*>(d_up), ld_in,
+                                                  static_cast<uint8_t*>(d_out), ld_out, d_row_scale, d_row_descale, rows, cols,
+                                                  as_stream(stream)));
         CF_LAUNCH_CHECK("swiglu_quantize_rowwise_e4m3");
         return CF_OK;
     }

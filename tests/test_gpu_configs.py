@@ -41,7 +41,8 @@ def _tensorquant(cfb, x, e5m2=False):
     return q, de
 
 
-@pytest.mark.parametrize("rows,cols", [(1, 1), (3, 7), (17, 64), (64, 4096), (33, 14336), (5, 1000), (8, 16384)])
+@pytest.mark.parametrize("rows,cols", [(1, 1), (3, 7), (17, 64), (64, 4096), (33, 14336), (5, 1000), (8, 16384),
+                                       (9, 37), (21, 4100), (4, 16383), (300, 523)])
 def test_rowwise_quantize_bit_exact(cfb, oracle, rows, cols):
     x = randn_bf16((rows, cols), seed=rows * cols, outlier_frac=0.01)
     x[0] = 0                                      # an all-zero row: amax clamps to 1e-12
@@ -63,6 +64,47 @@ def test_rowwise_quantize_bit_exact(cfb, oracle, rows, cols):
             ref = np.ascontiguousarray(bf16_to_u16(x).reshape(-1)[1:1 + (rows - 1) * cols].reshape(rows - 1, cols)[:, :cols - 1])
             w2, _, d2 = oracle.quantize_rowwise_e4m3(ref)
             assert np.array_equal(out2.cpu().numpy()[:, :cols - 1], w2) and np.array_equal(de2.cpu().numpy(), d2)
+
+
+@pytest.mark.parametrize("rows,cols,in_off,out_off", [(13, 4100, 0, 0), (13, 4100, 3, 5), (6, 45, 1, 2), (40, 1023, 7, 1),
+                                                      (5, 6, 5, 3)])
+def test_rowwise_quantize_of_rows_that_are_not_16_byte_multiples(cfb, oracle, rows, cols, in_off, out_off):
+    """Rows of any length at any 2-byte (input) / 1-byte (output) alignment: head, whole vectors and tail of every row give
+    the oracle's codes, scales and descales, and nothing outside the rows is written."""
+    flat = randn_bf16((rows * cols + 16,), seed=cols + in_off, outlier_frac=0.02)
+    xv = flat[in_off:in_off + rows * cols]
+    out_flat = torch.full((rows * cols + 32,), 0xCD, dtype=torch.uint8, device="cuda")
+    ov = out_flat[out_off:]
+    sc = torch.empty(rows, dtype=torch.float32, device="cuda")
+    de = torch.empty(rows, dtype=torch.float32, device="cuda")
+    cfb.fp8_quantize_rowwise_e4m3(xv, ov, de, row_scale=sc, rows=rows, cols=cols, ld_x=cols, ld_out=cols)
+    w, s_o, d_o = oracle.quantize_rowwise_e4m3(np.ascontiguousarray(bf16_to_u16(xv).reshape(rows, cols)))
+    got = out_flat.cpu().numpy()
+    assert np.array_equal(got[out_off:out_off + rows * cols].reshape(rows, cols), w)
+    assert (got[:out_off] == 0xCD).all() and (got[out_off + rows * cols:] == 0xCD).all()
+    assert np.array_equal(sc.cpu().numpy(), s_o) and np.array_equal(de.cpu().numpy(), d_o)
+
+
+@pytest.mark.parametrize("rows,F", [(11, 37), (7, 1003)])
+def test_swiglu_rowwise_quantise_of_odd_rows_matches_the_two_step_sequence(cfb, rows, F):
+    g = randn_bf16((rows, F), std=2.0, seed=F)
+    u = randn_bf16((rows, F), std=2.0, seed=F + 1)
+    h = torch.empty((rows, F), dtype=torch.bfloat16, device="cuda")
+    cfb.swiglu_forward(g, u, h)
+    want8 = torch.empty((rows, F), dtype=torch.uint8, device="cuda")
+    want_d = torch.empty(rows, dtype=torch.float32, device="cuda")
+    cfb.fp8_quantize_rowwise_e4m3(h, want8, want_d)
+    got8 = torch.empty((rows, F), dtype=torch.uint8, device="cuda")
+    got_d = torch.empty(rows, dtype=torch.float32, device="cuda")
+    cfb.swiglu_quantize_rowwise_e4m3(g, u, got8, got_d, rows, F, F)
+    assert torch.equal(got8, want8) and torch.equal(got_d, want_d)
+    # gate and up at different alignments: the one-row-per-block form
+    flat = randn_bf16((2 * rows * F + 8,), std=2.0, seed=F + 2)
+    g2, u2 = flat[:rows * F], flat[rows * F + 2:2 * rows * F + 2]
+    cfb.swiglu_forward(g2.view(rows, F).contiguous(), u2.reshape(rows, F).contiguous(), h)
+    cfb.fp8_quantize_rowwise_e4m3(h, want8, want_d)
+    cfb.swiglu_quantize_rowwise_e4m3(g2, u2, got8, got_d, rows, F, F)
+    assert torch.equal(got8, want8) and torch.equal(got_d, want_d)
 
 
 @pytest.mark.parametrize("rows,F", [(9, 40), (64, 1024), (32, 14336)])

@@ -126,6 +126,8 @@ SIGNATURES = {
     "cf_moe_combine_all_bf16": (ci, [vp, vp, fp, ip, ip, ip, ci, ci, ci, vp]),
     "cf_moe_combine_sorted_bf16": (ci, [vp, vp, fp, ip, ip, ip, ci, ci, ci, ci, vp]),
     "cf_moe_expand_route_replicas": (ci, [fp, fp, ci, ci, ci, ip, fp, C.c_uint, vp]),
+    "cf_moe_route_dispatch_scratch_ints": (C.c_size_t, [ci, ci]),
+    "cf_moe_route_dispatch_lists": (ci, [fp, ci, ci, ci, ci, fp, fp, fp, ci, ip, fp, C.c_uint, ip, ip, ip, ip, C.c_size_t, vp]),
     "cf_shard_range": (ci, [C.c_longlong, ci, ci, ci, C.POINTER(C.c_longlong), C.POINTER(C.c_longlong)]),
     "cf_ep_placement_build": (ci, [C.POINTER(C.c_double), ci, ci, C.c_double, C.POINTER(EpPlacementStruct)]),
     "cf_ep_placement_build_balanced": (ci, [C.POINTER(C.c_double), ci, ci, C.c_double, C.c_double, ci, C.POINTER(EpPlacementStruct)]),

@@ -101,12 +101,10 @@ __global__ void __launch_bounds__(kT) k_act(const uint16_t* __restrict__ a, cons
 
 // ---- routing: softmax -> hard top-k -> renormalise; one thread per row ---------------------------
 // kernels/cross_entropy.cu:167-191 (max-subtract, expf, * 1/sum) then kernels/moe.cu:374-407.
-__global__ void __launch_bounds__(128) k_topk_route(float* __restrict__ scores, float* __restrict__ row_sum_save,
-                                                    float* __restrict__ scores_save, int rows, int E, int top_k,
-                                                    int normalize) {
-    const int row = blockIdx.x * 128 + threadIdx.x;
-    if (row >= rows) return;
-    float* s = scores + static_cast<size_t>(row) * E;
+// Returns the set of experts the row keeps (bit e = expert e; E <= 64).
+__device__ __forceinline__ unsigned long long route_one_row(float* __restrict__ s, float* __restrict__ row_sum_save,
+                                                            float* __restrict__ scores_save, int row, int E, int top_k,
+                                                            int normalize) {
     float mx = -3.402823466e+38f;
     for (int e = 0; e < E; ++e) mx = fmaxf(mx, s[e]);
     float sum = 0.0f;
@@ -132,6 +130,15 @@ __global__ void __launch_bounds__(128) k_topk_route(float* __restrict__ scores, 
     if (row_sum_save) row_sum_save[row] = ks;
     const float invk = (normalize && ks > 0.0f) ? __fdiv_rn(1.0f, ks) : 1.0f;
     for (int e = 0; e < E; ++e) s[e] = ((kept >> e) & 1ull) ? s[e] * invk : 0.0f;
+    return kept;
+}
+
+__global__ void __launch_bounds__(128) k_topk_route(float* __restrict__ scores, float* __restrict__ row_sum_save,
+                                                    float* __restrict__ scores_save, int rows, int E, int top_k,
+                                                    int normalize) {
+    const int row = blockIdx.x * 128 + threadIdx.x;
+    if (row >= rows) return;
+    route_one_row(scores + static_cast<size_t>(row) * E, row_sum_save, scores_save, row, E, top_k, normalize);
 }
 
 // ---- dispatch lists: one block per expert, ordered compaction (ascending rows) -------------------
@@ -383,6 +390,111 @@ __global__ void __launch_bounds__(kT) k_expand_route(const float* __restrict__ r
         const int last = vstart[e + 1] - 1;
         while (v < last && u >= vcum[v]) ++v;
         out[v] = w;
+    }
+}
+
+// ---- dispatch front end in two launches -----------------------------------------------------------
+// Route (kernels/moe.cu:374-407), replica choice, dispatch lists in ascending row order (the order the compaction
+// kernel above gives), counts and offsets (kernels/moe.cu:565-580, 702-710, 785-795) for every row in parallel:
+// launch 1 routes one row per thread and leaves how many rows of its 256-row chunk go to every list in
+// chunk_counts[chunk][list]; launch 2 sums the chunks in front of its own, ranks its rows inside the chunk with warp
+// ballots and writes the lists; the block of the last chunk also writes counts and offsets. No block waits for another.
+constexpr int kFrontT = 256;
+
+template <bool REPLICAS>
+__global__ void __launch_bounds__(kFrontT) k_front_route(float* __restrict__ scores, float* __restrict__ rwv,
+                                                         float* __restrict__ row_sum_save, float* __restrict__ scores_save,
+                                                         int rows, int E, int V, int top_k, int normalize,
+                                                         const int* __restrict__ vstart, const float* __restrict__ vcum,
+                                                         unsigned row0, int* __restrict__ chunk_counts) {
+    __shared__ int s_cnt[kFrontT / 32][64];
+    const int row = blockIdx.x * kFrontT + threadIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int L = REPLICAS ? V : E;
+    unsigned long long sel = 0;            // lists this row is on
+    if (row < rows) {
+        float* sr = scores + static_cast<size_t>(row) * E;
+        route_one_row(sr, row_sum_save, scores_save, row, E, top_k, normalize);
+        if (REPLICAS) {
+            float* out = rwv + static_cast<size_t>(row) * V;
+            for (int v = 0; v < V; ++v) out[v] = 0.0f;
+            for (int e = 0; e < E; ++e) {
+                const float w = sr[e];
+                if (!(w > 0.0f)) continue;
+                const float u = replica_u01(row0 + static_cast<unsigned>(row), static_cast<unsigned>(e));
+                int v = vstart[e];
+                const int last = vstart[e + 1] - 1;
+                while (v < last && u >= vcum[v]) ++v;
+                out[v] = w;
+                sel |= 1ull << v;
+            }
+        } else {
+            for (int e = 0; e < E; ++e)
+                if (sr[e] > 0.0f) sel |= 1ull << e;
+        }
+    }
+    for (int v = 0; v < L; ++v) {
+        const unsigned m = __ballot_sync(0xffffffffu, (sel >> v) & 1ull);
+        if (lane == 0) s_cnt[warp][v] = __popc(m);
+    }
+    __syncthreads();
+    if (threadIdx.x < L) {
+        int t = 0;
+#pragma unroll
+        for (int w = 0; w < kFrontT / 32; ++w) t += s_cnt[w][threadIdx.x];
+        chunk_counts[static_cast<size_t>(blockIdx.x) * L + threadIdx.x] = t;
+    }
+}
+
+__global__ void __launch_bounds__(kFrontT) k_front_lists(const float* __restrict__ w, int rows, int L,
+                                                         const int* __restrict__ chunk_counts, int* __restrict__ counts,
+                                                         int* __restrict__ offsets, int* __restrict__ row_indices) {
+    __shared__ int s_base[64];
+    __shared__ int s_cnt[kFrontT / 32][64];
+    const int row = blockIdx.x * kFrontT + threadIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x < 64) s_base[threadIdx.x] = 0;
+    __syncthreads();
+    pdl_wait();
+    // rows in front of this chunk, per list
+    const int before_items = blockIdx.x * L;
+    for (int i = threadIdx.x; i < before_items; i += kFrontT) {
+        const int c = chunk_counts[i];
+        if (c) atomicAdd(&s_base[i % L], c);
+    }
+    unsigned long long sel = 0;
+    if (row < rows) {
+        const float* wr = w + static_cast<size_t>(row) * L;
+        for (int v = 0; v < L; ++v)
+            if (wr[v] > 0.0f) sel |= 1ull << v;
+    }
+    for (int v = 0; v < L; ++v) {
+        const unsigned m = __ballot_sync(0xffffffffu, (sel >> v) & 1ull);
+        if (lane == 0) s_cnt[warp][v] = __popc(m);
+    }
+    __syncthreads();
+    for (int v = 0; v < L; ++v) {
+        const unsigned m = __ballot_sync(0xffffffffu, (sel >> v) & 1ull);
+        if ((sel >> v) & 1ull) {
+            int pos = s_base[v] + __popc(m & ((1u << lane) - 1u));
+            for (int ww = 0; ww < warp; ++ww) pos += s_cnt[ww][v];
+            row_indices[static_cast<size_t>(v) * rows + pos] = row;
+        }
+    }
+    if (blockIdx.x == gridDim.x - 1) {
+        __syncthreads();
+        if (threadIdx.x < L) {
+            int t = s_base[threadIdx.x];
+#pragma unroll
+            for (int ww = 0; ww < kFrontT / 32; ++ww) t += s_cnt[ww][threadIdx.x];
+            counts[threadIdx.x] = t;
+            s_base[threadIdx.x] = t;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int acc = 0;
+            for (int v = 0; v < L; ++v) { offsets[v] = acc; acc += s_base[v]; }
+        }
     }
 }
 
@@ -685,6 +797,64 @@ int cf_moe_expand_route_replicas(const float* d_route_weights, float* d_replica_
     k_expand_route<<<(rows + kT - 1) / kT, kT, 0, as_stream(stream)>>>(d_route_weights, d_replica_weights, rows, num_experts,
                                                                        num_replicas, d_replica_start, d_replica_cum_share, first_row);
     CF_LAUNCH_CHECK("moe_expand_route_replicas");
+    return CF_OK;
+}
+
+size_t cf_moe_route_dispatch_scratch_ints(int rows, int num_lists) {
+    if (rows <= 0 || num_lists <= 0) return 0;
+    return static_cast<size_t>((rows + kFrontT - 1) / kFrontT) * static_cast<size_t>(num_lists);
+}
+
+int cf_moe_route_dispatch_lists(float* d_scores, int rows, int num_experts, int top_k, int normalize_topk,
+                                float* d_row_sum_save_or_null, float* d_scores_save_or_null, float* d_replica_weights_or_null,
+                                int num_replicas, const int* d_replica_start, const float* d_replica_cum_share,
+                                unsigned first_row, int* d_counts, int* d_offsets, int* d_row_indices, int* d_scratch,
+                                size_t scratch_ints, void* stream) {
+    const bool rep = d_replica_weights_or_null != nullptr;
+    CF_REQUIRE(rows >= 0 && num_experts >= 1 && num_experts <= 64 && top_k >= 0,
+               "cf_moe_route_dispatch_lists: bad shape (1 <= experts <= 64)");
+    CF_REQUIRE(!rep || (num_replicas >= num_experts && d_replica_start && d_replica_cum_share),
+               "cf_moe_route_dispatch_lists: replica tables missing");
+    const int L = rep ? num_replicas : num_experts;
+    CF_REQUIRE(d_counts && d_offsets, "cf_moe_route_dispatch_lists: null pointer");
+    cudaStream_t st = as_stream(stream);
+    if (rows == 0) {
+        CF_CUDA(cudaMemsetAsync(d_counts, 0, sizeof(int) * L, st));
+        CF_CUDA(cudaMemsetAsync(d_offsets, 0, sizeof(int) * L, st));
+        return CF_OK;
+    }
+    CF_REQUIRE(d_scores && d_row_indices, "cf_moe_route_dispatch_lists: null pointer");
+    if (L > 64) {
+        // more lists than one 64-bit set per row holds: the same result from the separate kernels
+        int rc = cf_moe_topk_route_f32(d_scores, rows, num_experts, top_k, stream, d_row_sum_save_or_null, d_scores_save_or_null,
+                                       normalize_topk);
+        if (rc != CF_OK) return rc;
+        rc = cf_moe_expand_route_replicas(d_scores, d_replica_weights_or_null, rows, num_experts, num_replicas, d_replica_start,
+                                          d_replica_cum_share, first_row, stream);
+        if (rc != CF_OK) return rc;
+        rc = cf_moe_build_expert_row_lists(d_replica_weights_or_null, d_counts, d_row_indices, rows, num_replicas, stream);
+        if (rc != CF_OK) return rc;
+        return cf_moe_expert_offsets_from_counts(d_counts, d_offsets, num_replicas, stream);
+    }
+    const size_t need = cf_moe_route_dispatch_scratch_ints(rows, L);
+    if (d_scratch == nullptr || scratch_ints < need) {
+        set_error("cf_moe_route_dispatch_lists: scratch of %zu ints needed (cf_moe_route_dispatch_scratch_ints)", need);
+        return CF_ERR_LIMIT;
+    }
+    const int chunks = (rows + kFrontT - 1) / kFrontT;
+    if (rep)
+        k_front_route<true><<<chunks, kFrontT, 0, st>>>(d_scores, d_replica_weights_or_null, d_row_sum_save_or_null,
+                                                        d_scores_save_or_null, rows, num_experts, num_replicas, top_k,
+                                                        normalize_topk, d_replica_start, d_replica_cum_share, first_row, d_scratch);
+    else
+        k_front_route<false><<<chunks, kFrontT, 0, st>>>(d_scores, nullptr, d_row_sum_save_or_null, d_scores_save_or_null, rows,
+                                                         num_experts, num_experts, top_k, normalize_topk, nullptr, nullptr, first_row,
+                                                         d_scratch);
+    CF_LAUNCH_CHECK("moe_route_dispatch_lists(route)");
+    CF_CUDA(launch_pdl(k_front_lists, dim3(chunks), dim3(kFrontT), 0, st,
+                       static_cast<const float*>(rep ? d_replica_weights_or_null : d_scores), rows, L,
+                       static_cast<const int*>(d_scratch), d_counts, d_offsets, d_row_indices));
+    CF_LAUNCH_CHECK("moe_route_dispatch_lists(lists)");
     return CF_OK;
 }
 

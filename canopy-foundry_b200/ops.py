@@ -25,7 +25,7 @@ __all__ = [
     "rmsnorm_forward", "rmsnorm_quantize_e4m3_record", "rmsnorm_quantize_rowwise_e4m3", "fp8_rmsnorm_quant_act", "rmsnorm_clip_forward", "rmsnorm_clip_quantize_e4m3_record", "fp8_rmsnorm_clip_quant_act",
     "moe_topk_route_f32", "moe_build_expert_row_lists", "moe_expert_offsets_from_counts",
     "moe_gather_rows_u8", "moe_gather_rows_bf16", "moe_scatter_accumulate_rows_bf16",
-    "moe_scale_accumulate_bf16", "moe_gather_all_u8", "moe_combine_all_bf16", "moe_combine_sorted_bf16", "moe_expand_route_replicas", "moe_ep_plan", "gemm_fp8_nt_grouped_return", "moe_send_row_runs", "peer_barrier", "peer_share_i32", "ROW_RUN_BYTES",
+    "moe_scale_accumulate_bf16", "moe_gather_all_u8", "moe_combine_all_bf16", "moe_combine_sorted_bf16", "moe_expand_route_replicas", "moe_route_dispatch_lists", "moe_route_dispatch_scratch_ints", "moe_ep_plan", "gemm_fp8_nt_grouped_return", "moe_send_row_runs", "peer_barrier", "peer_share_i32", "ROW_RUN_BYTES",
     "moe_grouped_expert_forward_fp8", "launch_count", "swiglu_mlp_fp8_rowwise", "MoeSwigluFp8", "FfnSwigluFp8",
 ]
 
@@ -500,6 +500,21 @@ def moe_expand_route_replicas(route_weights, replica_weights, rows, num_experts,
                                             _p(replica_start), _p(replica_cum_share), int(first_row) & 0xffffffff, _s()))
 
 
+def moe_route_dispatch_scratch_ints(rows, num_lists):
+    return int(_L().cf_moe_route_dispatch_scratch_ints(rows, num_lists))
+
+
+def moe_route_dispatch_lists(scores, rows, num_experts, top_k, counts, offsets, row_indices, scratch, normalize=True,
+                             replica_weights=None, num_replicas=0, replica_start=None, replica_cum_share=None, first_row=0,
+                             row_sum_save=None, scores_save=None):
+    """Route + (replica choice) + ascending dispatch lists + counts + offsets in one call: the outputs of
+    moe_topk_route_f32, [moe_expand_route_replicas,] moe_build_expert_row_lists and moe_expert_offsets_from_counts."""
+    check(_L().cf_moe_route_dispatch_lists(_p(scores), rows, num_experts, top_k, int(normalize), _p(row_sum_save),
+                                           _p(scores_save), _p(replica_weights), num_replicas, _p(replica_start),
+                                           _p(replica_cum_share), int(first_row) & 0xffffffff, _p(counts), _p(offsets),
+                                           _p(row_indices), _p(scratch), scratch.numel(), _s()))
+
+
 def peer_barrier(ctx, flag_arrays, world, rank, epoch, limit_ms=2000):
     """Barrier between the ranks of one box done by the GPUs (flag words in peer-mapped memory); flag_arrays: int64
     device tensor of the ranks' flag-array addresses as mapped in this process."""
@@ -644,14 +659,13 @@ class MoeSwigluFp8:
         self.yc = torch.empty((T, H), dtype=torch.bfloat16, device=device)
         self.slot_x = ActSlot(ctx, E4M3_MAX)
         self.slot_h = ActSlot(ctx, E4M3_MAX)
+        self.front_scratch = torch.empty(max(1, moe_route_dispatch_scratch_ints(rows, E)), dtype=torch.int32, device=device)
 
     def forward(self, x, route_weights, w_gateup8, w_gateup_descale, w_down8, w_down_descale, mixed, accumulate=True):
         """route_weights: float32 [rows,E] router logits, overwritten in place by the sparse route weights.
         accumulate=False: mixed is overwritten (as if it had been zero-filled first) instead of added to."""
         rows, H, F, E, T = self.rows, self.H, self.F, self.E, self.T
-        moe_topk_route_f32(route_weights, rows, E, self.k)
-        moe_build_expert_row_lists(route_weights, self.counts, self.idx, rows, E)
-        moe_expert_offsets_from_counts(self.counts, self.offsets, E)
+        moe_route_dispatch_lists(route_weights, rows, E, self.k, self.counts, self.offsets, self.idx, self.front_scratch)
         fp8_quant_act(self.ctx, self.slot_x, x, self.x8)
         moe_gather_all_u8(self.x8, self.xc, self.idx, self.counts, self.offsets, rows, E, H)
         if self.fused_swiglu:

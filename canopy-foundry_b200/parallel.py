@@ -475,6 +475,7 @@ class EpMoeSwigluFp8Direct:
         self.range_lo = torch.tensor([r[0] for r in placement.rank_ranges], dtype=i32, device=dev)
         self.range_hi = torch.tensor([r[1] for r in placement.rank_ranges], dtype=i32, device=dev)
         self.rwv = torch.zeros((rows, V), dtype=f32, device=dev)
+        self.front_scratch = torch.empty(max(1, cfb.moe_route_dispatch_scratch_ints(rows, V)), dtype=torch.int32, device=dev)
         self.counts = torch.zeros(V, dtype=i32, device=dev)
         self.offsets = torch.zeros(V, dtype=i32, device=dev)
         self.idx = torch.zeros((V, rows), dtype=i32, device=dev)
@@ -534,11 +535,9 @@ class EpMoeSwigluFp8Direct:
                 marks.append((name, ev))
 
         mark("start")
-        cfb.moe_topk_route_f32(route_weights, rows, self.E, self.k)
-        cfb.moe_expand_route_replicas(route_weights, self.rwv, rows, self.E, V, self.rep_start, self.rep_cum,
-                                      first_row=self.rank * rows)
-        cfb.moe_build_expert_row_lists(self.rwv, self.counts, self.idx, rows, V)
-        cfb.moe_expert_offsets_from_counts(self.counts, self.offsets, V)
+        cfb.moe_route_dispatch_lists(route_weights, rows, self.E, self.k, self.counts, self.offsets, self.idx,
+                                     self.front_scratch, replica_weights=self.rwv, num_replicas=V,
+                                     replica_start=self.rep_start, replica_cum_share=self.rep_cum, first_row=self.rank * rows)
         mark("route + replica choice + dispatch lists")
         gathered = None
         if W > 1 and not self._pb.on_device:

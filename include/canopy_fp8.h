@@ -498,6 +498,22 @@ int cf_moe_combine_sorted_bf16(void* d_mixed, const void* d_compact, const float
 int cf_moe_expand_route_replicas(const float* d_route_weights, float* d_replica_weights, int rows, int num_experts,
                                  int num_replicas, const int* d_replica_start, const float* d_replica_cum_share,
                                  unsigned first_row, void* stream);
+/* Dispatch front end of a routed layer in one call (two launches, no block waits for another): what
+ * cf_moe_topk_route_f32 (kernels/moe.cu:374-422), [cf_moe_expand_route_replicas,] cf_moe_build_expert_row_lists
+ * (kernels/moe.cu:565-580, 702-710) and cf_moe_expert_offsets_from_counts (kernels/moe.cu:785-795, 859-863) produce one
+ * after the other, bit for bit and list entry for list entry: d_scores [rows, num_experts] is overwritten by the sparse
+ * route weights; with d_replica_weights_or_null != NULL the replica form [rows, num_replicas] is written too and the lists
+ * are built over the replicas, otherwise over the experts (the replica arguments are then ignored). The lists hold the row
+ * numbers in ascending order; d_counts, d_offsets: one int per list; d_row_indices: [lists, rows]. It replaces the
+ * host-synchronised list building of src/trainer.cu:6876-6880. d_scratch: cf_moe_route_dispatch_scratch_ints(rows, lists)
+ * ints owned by the caller, contents irrelevant (CF_ERR_LIMIT if too small); more than 64 lists run the separate
+ * kernels. */
+size_t cf_moe_route_dispatch_scratch_ints(int rows, int num_lists);
+int cf_moe_route_dispatch_lists(float* d_scores, int rows, int num_experts, int top_k, int normalize_topk,
+                                float* d_row_sum_save_or_null, float* d_scores_save_or_null, float* d_replica_weights_or_null,
+                                int num_replicas, const int* d_replica_start, const float* d_replica_cum_share,
+                                unsigned first_row, int* d_counts, int* d_offsets, int* d_row_indices, int* d_scratch,
+                                size_t scratch_ints, void* stream);
 
 /* ------------------------------------------------------------------ sharding glue (host side, no device work) */
 

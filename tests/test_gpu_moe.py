@@ -490,3 +490,86 @@ def test_route_expansion_over_replicas_keeps_weights_and_follows_the_shares(cfb)
     rwv2 = torch.zeros_like(rwv)
     cfb.moe_expand_route_replicas(rw, rwv2, rows, E, V, start, cum, first_row=99999)
     assert not torch.equal(rwv, rwv2)
+
+
+@pytest.mark.parametrize("rows,E,k,replicas", [(1, 3, 2, False), (255, 8, 2, False), (256, 8, 2, True), (257, 8, 2, True),
+                                               (4096, 8, 2, True), (32768, 8, 2, False), (1000, 11, 3, True),
+                                               (5000, 64, 8, False), (700, 4, 4, False), (3000, 40, 2, True)])
+def test_dispatch_front_end_equals_the_separate_kernels(cfb, rows, E, k, replicas):
+    """cf_moe_route_dispatch_lists leaves the route weights, replica weights, counts, offsets and list entries of the
+    four separate calls, bit for bit (lists in ascending row order); cells of the lists it does not fill stay untouched."""
+    par = cfb.parallel
+    logits = _zipf_logits(rows, E, rows + E).contiguous()
+    logits[0] = 0.0                               # ties
+    V = E
+    start = cum = None
+    if replicas:
+        pl = par.ReplicaPlacement.build([(e + 1) ** -1.1 for e in range(E)], 8)
+        V = pl.num_replicas
+        start = torch.tensor(pl.replica_start, dtype=torch.int32, device="cuda")
+        cum = torch.tensor(pl.replica_cum_share, dtype=torch.float32, device="cuda")
+    # the separate kernels
+    rw0 = logits.clone()
+    cfb.moe_topk_route_f32(rw0, rows, E, k)
+    lists_src = rw0
+    rwv0 = None
+    if replicas:
+        rwv0 = torch.full((rows, V), -1.0, dtype=torch.float32, device="cuda")
+        cfb.moe_expand_route_replicas(rw0, rwv0, rows, E, V, start, cum, first_row=777)
+        lists_src = rwv0
+    c0 = torch.full((V,), 5, dtype=torch.int32, device="cuda")
+    i0 = torch.full((V, rows), -7, dtype=torch.int32, device="cuda")
+    o0 = torch.full((V,), 5, dtype=torch.int32, device="cuda")
+    cfb.moe_build_expert_row_lists(lists_src, c0, i0, rows, V)
+    cfb.moe_expert_offsets_from_counts(c0, o0, V)
+    # one call
+    rw1 = logits.clone()
+    rwv1 = torch.full((rows, V), -1.0, dtype=torch.float32, device="cuda") if replicas else None
+    c1 = torch.full((V,), 9, dtype=torch.int32, device="cuda")
+    i1 = torch.full((V, rows), -7, dtype=torch.int32, device="cuda")
+    o1 = torch.full((V,), 9, dtype=torch.int32, device="cuda")
+    need = cfb.moe_route_dispatch_scratch_ints(rows, V)
+    scratch = torch.full((need + 3,), 0x5A5A5A5A, dtype=torch.int32, device="cuda")     # contents irrelevant
+    cfb.moe_route_dispatch_lists(rw1, rows, E, k, c1, o1, i1, scratch, replica_weights=rwv1, num_replicas=V,
+                                 replica_start=start, replica_cum_share=cum, first_row=777)
+    assert torch.equal(rw1, rw0)
+    if replicas:
+        assert torch.equal(rwv1, rwv0)
+    assert torch.equal(c1, c0) and torch.equal(o1, o0) and torch.equal(i1, i0)
+    assert (scratch[need:] == 0x5A5A5A5A).all()
+    if need > 1 and V <= 64:
+        with pytest.raises(cfb.CanopyError):
+            cfb.moe_route_dispatch_lists(rw1, rows, E, k, c1, o1, i1, scratch[:need - 1], replica_weights=rwv1, num_replicas=V,
+                                         replica_start=start, replica_cum_share=cum, first_row=777)
+
+
+def test_dispatch_front_end_with_no_rows_and_with_more_than_64_lists(cfb):
+    par = cfb.parallel
+    E = 8
+    c = torch.full((E,), 9, dtype=torch.int32, device="cuda")
+    o = torch.full((E,), 9, dtype=torch.int32, device="cuda")
+    i = torch.empty((E, 1), dtype=torch.int32, device="cuda")
+    s = torch.empty(1, dtype=torch.int32, device="cuda")
+    cfb.moe_route_dispatch_lists(torch.empty((0, E), device="cuda"), 0, E, 2, c, o, i, s)
+    assert c.cpu().tolist() == [0] * E and o.cpu().tolist() == [0] * E
+    # 60 experts over 8 ranks: more than 64 replicas, served by the separate kernels behind the same call
+    E, rows, k = 60, 900, 2
+    pl = par.ReplicaPlacement.build([1.0 + 0.01 * e for e in range(E)], 8, min_share=0.0)
+    V = pl.num_replicas
+    assert V > 64
+    start = torch.tensor(pl.replica_start, dtype=torch.int32, device="cuda")
+    cum = torch.tensor(pl.replica_cum_share, dtype=torch.float32, device="cuda")
+    logits = _zipf_logits(rows, E, 3).contiguous()
+    rw0, rw1 = logits.clone(), logits.clone()
+    rwv0 = torch.zeros((rows, V), device="cuda")
+    rwv1 = torch.zeros((rows, V), device="cuda")
+    c0 = torch.zeros(V, dtype=torch.int32, device="cuda"); c1 = torch.zeros_like(c0)
+    o0 = torch.zeros_like(c0); o1 = torch.zeros_like(c0)
+    i0 = torch.full((V, rows), -1, dtype=torch.int32, device="cuda"); i1 = i0.clone()
+    cfb.moe_topk_route_f32(rw0, rows, E, k)
+    cfb.moe_expand_route_replicas(rw0, rwv0, rows, E, V, start, cum)
+    cfb.moe_build_expert_row_lists(rwv0, c0, i0, rows, V)
+    cfb.moe_expert_offsets_from_counts(c0, o0, V)
+    cfb.moe_route_dispatch_lists(rw1, rows, E, k, c1, o1, i1, s, replica_weights=rwv1, num_replicas=V, replica_start=start,
+                                 replica_cum_share=cum)
+    assert torch.equal(rwv1, rwv0) and torch.equal(c1, c0) and torch.equal(o1, o0) and torch.equal(i1, i0)

@@ -745,11 +745,20 @@ def leg_moe(args, env):
     lmax = env.max_over_ranks(float(layer.grp_counts.sum().item()))
     # where the time of one layer goes on this rank: CUDA events between the stages of one extra call (not timed above;
     # the events serialise the launches a little, so the stages add up to slightly more than a step)
+    step(0)                       # keeps the GPU busy while the marked call is being queued (no launch gaps in it)
     layer.stage_marks = []
     step(0)
     torch.cuda.synchronize()
     marks, layer.stage_marks = layer.stage_marks, None
     stages = {marks[i][0]: round(marks[i - 1][1].elapsed_time(marks[i][1]), 4) for i in range(1, len(marks))}
+    # the two GEMM stages and the rows served, of every rank (what the closing barrier of a layer waits for)
+    mine_g = torch.tensor([stages.get("gate/up GEMM + SwiGLU + re-quantise", 0.0), stages.get("down GEMM with the return leg", 0.0),
+                           float(layer.grp_counts.sum().item()), float((layer.grp_counts > 0).sum().item())],
+                          dtype=torch.float32, device=dev)
+    all_g = [torch.empty_like(mine_g) for _ in range(world)]
+    dist.all_gather(all_g, mine_g)
+    gemm_by_rank = [{"gate_up_ms": round(t[0].item(), 4), "down_ms": round(t[1].item(), 4), "rows": int(t[2].item()),
+                     "groups": int(t[3].item())} for t in all_g]
     # ---- parity, outside the timed region: sampled tokens of rank 0 against the host oracle with the scales the ranks
     # used, and rank 0's rows against the single-GPU layer (other scale granularity: FP8 noise, reported, not gated)
     hs = layer.slot_h.scalars()
@@ -770,7 +779,7 @@ def leg_moe(args, env):
             "n1_ms_same_box": single["ms"], "n1_clocks": single["clocks"],
             "efficiency_vs_n1_same_box": single["ms"] / (world * ms),
             "max_rows_on_one_rank": int(lmax), "mean_rows_per_rank": TOK * TOPK / world, "clocks": clocks,
-            "gpu_launches": launches, "stage_ms_rank0": stages,
+            "gpu_launches": launches, "stage_ms_rank0": stages, "gemm_stages_by_rank": gemm_by_rank,
             "moe_parity": {"rel_fro": err, "ok": bool(err < 1e-2 and single["rel_fro_vs_oracle"] < 1e-2), "tolerance": 1e-2,
                            "against": "CPU oracle on sampled tokens of rank 0 with the scales the serving ranks used",
                            "n1_layer_rel_fro_vs_oracle": single["rel_fro_vs_oracle"],

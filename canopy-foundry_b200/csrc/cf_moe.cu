@@ -101,19 +101,20 @@ __global__ void __launch_bounds__(kT) k_act(const uint16_t* __restrict__ a, cons
 
 // ---- routing: softmax -> hard top-k -> renormalise; one thread per row ---------------------------
 // kernels/cross_entropy.cu:167-191 (max-subtract, expf, * 1/sum) then kernels/moe.cu:374-407.
-// Returns the set of experts the row keeps (bit e = expert e; E <= 64).
+// Returns the set of experts the row keeps (bit e = expert e; E <= 64). The row is worked on in a thread-private
+// copy (one read and one write of global memory per element); the arithmetic and its order are those of the reference.
 __device__ __forceinline__ unsigned long long route_one_row(float* __restrict__ s, float* __restrict__ row_sum_save,
                                                             float* __restrict__ scores_save, int row, int E, int top_k,
                                                             int normalize) {
+    float p[64];
     float mx = -3.402823466e+38f;
-    for (int e = 0; e < E; ++e) mx = fmaxf(mx, s[e]);
+    for (int e = 0; e < E; ++e) { p[e] = s[e]; mx = fmaxf(mx, p[e]); }
     float sum = 0.0f;
-    for (int e = 0; e < E; ++e) sum += expf(s[e] - mx);
+    for (int e = 0; e < E; ++e) sum += expf(p[e] - mx);
     const float inv = __fdiv_rn(1.0f, sum);
     for (int e = 0; e < E; ++e) {
-        const float pr = expf(s[e] - mx) * inv;
-        s[e] = pr;
-        if (scores_save) scores_save[static_cast<size_t>(row) * E + e] = pr;
+        p[e] = expf(p[e] - mx) * inv;
+        if (scores_save) scores_save[static_cast<size_t>(row) * E + e] = p[e];
     }
     unsigned long long kept = 0;       // E <= 64
     const int k = top_k < E ? top_k : E;
@@ -121,15 +122,15 @@ __device__ __forceinline__ unsigned long long route_one_row(float* __restrict__ 
         int best = -1;
         float best_v = -1.0f;
         for (int e = 0; e < E; ++e)
-            if (!((kept >> e) & 1ull) && s[e] > best_v) { best_v = s[e]; best = e; }
+            if (!((kept >> e) & 1ull) && p[e] > best_v) { best_v = p[e]; best = e; }
         if (best < 0) break;
         kept |= 1ull << best;
     }
     float ks = 0.0f;
-    for (int e = 0; e < E; ++e) if ((kept >> e) & 1ull) ks += s[e];
+    for (int e = 0; e < E; ++e) if ((kept >> e) & 1ull) ks += p[e];
     if (row_sum_save) row_sum_save[row] = ks;
     const float invk = (normalize && ks > 0.0f) ? __fdiv_rn(1.0f, ks) : 1.0f;
-    for (int e = 0; e < E; ++e) s[e] = ((kept >> e) & 1ull) ? s[e] * invk : 0.0f;
+    for (int e = 0; e < E; ++e) s[e] = ((kept >> e) & 1ull) ? p[e] * invk : 0.0f;
     return kept;
 }
 

@@ -432,6 +432,24 @@ def linear_incumbent(args, env, st):
             "this_library_tflops": FLOP_PER_STEP / (ms_own * 1e-3) / 1e12, "this_library_ms": ms_own,
             "rel_fro_between_them": (diff.norm() / y_lib.float().norm()).item(),
             "bit_identical": bool(torch.equal(y_lib.view(torch.int16), y_own.view(torch.int16)))}
+        # the same two kernels looped for about a second each (library first, then this one, then the library again): what
+        # each holds under the power cap, with the SM clock it ran at
+        if args.sustain_seconds > 0:
+            def held(fn, ms_est):
+                n = max(50, int(math.ceil(0.5 * args.sustain_seconds * 1e3 / max(ms_est, 1e-3))))
+                sampler = ClockSampler(env.local, 0.0005)
+                torch.cuda.synchronize()
+                sampler.start()
+                ms = time_alone(torch, fn, n, warmup=2)
+                clk = sampler.stop()
+                return {"tflops": FLOP_PER_STEP / (ms * 1e-3) / 1e12, "ms": ms, "seconds": ms * n * 1e-3,
+                        "sm_mhz_median": clk["sm_mhz"], "reasons": clk["reasons"]}
+            lib1 = held(lib_gemm, ms_lib)
+            own1 = held(own_gemm, ms_own)
+            lib2 = held(lib_gemm, ms_lib)
+            res["8192x4096x4096"]["sustained"] = {"incumbent_cublaslt_first": lib1, "this_library": own1,
+                                                  "incumbent_cublaslt_again": lib2}
+            keep.pop("y", None)
         del x8, y_lib, y_own, diff
         # 8192^3 on seeded random E4M3 codes
         S = 8192

@@ -301,6 +301,12 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
 }
+// max(a, |b|) on two packed bf16 values (a holds non-negative values); a NaN in b leaves a unchanged, like fmaxf.
+__device__ __forceinline__ uint32_t bf16x2_absmax(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b & 0x7fff7fffu));
+    return r;
+}
 __device__ __forceinline__ uint16_t to_bf16_bits(float v) { return __bfloat16_as_ushort(__float2bfloat16_rn(v)); }
 
 // One output value through the epilogue contract (used by the scalar store paths and by the SIMT kernel).
@@ -520,7 +526,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 // of kernels/fp8.cu:67-84 with the slot's scale; the amax of the bf16 product goes to p.d_amax_out.
                 const float hs = *p.d_quant_scale;
                 const float dab = da * db_t;
-                float local_amax = 0.0f;
+                uint32_t amax2 = 0u;                       // two running maxima of |h| as bf16
                 uint8_t* orow = static_cast<uint8_t*>(tc.out_base) + grow * p.ldc + (tc.n0 >> 1);
                 // Every lane stores the 32 codes of a chunk as two 16-byte words (one whole sector of its row); staging the
                 // warp's rows for a TMA store, as the bf16 form below does, measured no faster here.
@@ -538,11 +544,17 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     for (int j = 0; j < 8; ++j) {
                         float h[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float gb = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vg[4 * j + e]) * dab));
-                            const float ub = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vu[4 * j + e]) * dab));
-                            h[e] = __bfloat162float(__float2bfloat16_rn(gb * swiglu_sigmoid(gb) * ub));
-                            local_amax = fmaxf(local_amax, fabsf(h[e]));
+                        for (int e = 0; e < 4; e += 2) {
+                            // every bf16 rounding of the unfused sequence is done on a pair (cvt.rn.bf16x2); the amax is
+                            // taken on the packed product
+                            const uint32_t g2 = pack_bf16x2(__uint_as_float(vg[4 * j + e]) * dab, __uint_as_float(vg[4 * j + e + 1]) * dab);
+                            const uint32_t u2 = pack_bf16x2(__uint_as_float(vu[4 * j + e]) * dab, __uint_as_float(vu[4 * j + e + 1]) * dab);
+                            const float g0 = __uint_as_float(g2 << 16), g1 = __uint_as_float(g2 & 0xffff0000u);
+                            const uint32_t h2 = pack_bf16x2(g0 * swiglu_sigmoid(g0) * __uint_as_float(u2 << 16),
+                                                            g1 * swiglu_sigmoid(g1) * __uint_as_float(u2 & 0xffff0000u));
+                            amax2 = bf16x2_absmax(amax2, h2);
+                            h[e] = __uint_as_float(h2 << 16);
+                            h[e + 1] = __uint_as_float(h2 & 0xffff0000u);
                         }
                         q[j] = cvt_fp8x4<false>(h[0] * hs, h[1] * hs, h[2] * hs, h[3] * hs);
                     }
@@ -550,6 +562,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                     dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
                     dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
                 }
+                float local_amax = fmaxf(__uint_as_float(amax2 << 16), __uint_as_float(amax2 & 0xffff0000u));
                 local_amax = warp_max(local_amax);
                 if (lane == 0 && local_amax > 0.0f) atomicMax(reinterpret_cast<int*>(p.d_amax_out), __float_as_int(local_amax));
             } else if (p.out_kind == 5) {
@@ -563,7 +576,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                 // Four 16-byte stores from every lane to its own row measured 5 % slower on the 16384 x 28672 x 4096
                 // gate/up GEMM (tensor pipe 82 % busy against 86 %) at unchanged DRAM traffic: fewer store
                 // instructions and L2 write requests per tile, not fewer bytes.
-                float local_amax = 0.0f;
+                uint32_t amax2 = 0u;                       // two running maxima of |h| as bf16
                 const uint32_t buf = smem_c + static_cast<uint32_t>(warp - 2) * C_BOX_BYTES;
                 const uint32_t row_off = static_cast<uint32_t>(lane) * 128u;
                 const uint32_t sw = static_cast<uint32_t>(lane & 7);
@@ -590,14 +603,22 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                         const float sg[4] = {cg.x, cg.y, cg.z, cg.w}, su[4] = {cu.x, cu.y, cu.z, cu.w};
                         float h[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float gb = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vg[4 * j + e]) * (da * sg[e])));
-                            const float ub = __bfloat162float(__float2bfloat16_rn(__uint_as_float(vu[4 * j + e]) * (da * su[e])));
-                            h[e] = __bfloat162float(__float2bfloat16_rn(gb * swiglu_sigmoid(gb) * ub));
-                            local_amax = fmaxf(local_amax, fabsf(h[e]));      // committed for rows of the matrix only
+                        for (int e = 0; e < 4; e += 2) {
+                            // gate and up as the bf16 values the unfused GEMM would have stored: rounded two at a time
+                            const uint32_t g2 = pack_bf16x2(__uint_as_float(vg[4 * j + e]) * (da * sg[e]),
+                                                            __uint_as_float(vg[4 * j + e + 1]) * (da * sg[e + 1]));
+                            const uint32_t u2 = pack_bf16x2(__uint_as_float(vu[4 * j + e]) * (da * su[e]),
+                                                            __uint_as_float(vu[4 * j + e + 1]) * (da * su[e + 1]));
+                            const float g0 = __uint_as_float(g2 << 16), g1 = __uint_as_float(g2 & 0xffff0000u);
+                            h[e] = g0 * swiglu_sigmoid(g0) * __uint_as_float(u2 << 16);
+                            h[e + 1] = g1 * swiglu_sigmoid(g1) * __uint_as_float(u2 & 0xffff0000u);
                         }
+                        // the pack is the bf16 rounding of the product; the row amax is taken on the packed pairs
+                        // (max of |bf16| values, NaN ignored like fmaxf: committed for rows of the matrix only)
                         w[2 * j] = pack_bf16x2(h[0], h[1]);
                         w[2 * j + 1] = pack_bf16x2(h[2], h[3]);
+                        amax2 = bf16x2_absmax(amax2, w[2 * j]);
+                        amax2 = bf16x2_absmax(amax2, w[2 * j + 1]);
                     }
                     const uint32_t half = static_cast<uint32_t>(c & 1) * 4u;       // which 64 bytes of the 128-byte box row
 #pragma unroll
@@ -613,6 +634,7 @@ k_gemm_fp8_nt(const __grid_constant__ CUtensorMap map_a, const __grid_constant__
                         bulk_commit();
                     }
                 }
+                const float local_amax = fmaxf(__uint_as_float(amax2 << 16), __uint_as_float(amax2 & 0xffff0000u));
                 if (row_ok && local_amax > 0.0f)
                     atomicMax(reinterpret_cast<int*>(p.d_row_amax_out + static_cast<long long>(tc.row0) + row_in_tile),
                               __float_as_int(local_amax));

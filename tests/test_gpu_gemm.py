@@ -398,3 +398,20 @@ def test_grouped_expert_dgrad_reads_every_experts_own_block(cfb, ctx, oracle, co
             assert rel_fro(oracle.bf16_to_f32(bf16_to_u16(got[o:o + c])), oracle.bf16_to_f32(ref)) < TIGHT
         o += c
     ctx.poll_status()
+
+
+def test_cpp_caller_through_the_reference_declarations_and_the_shim():
+    """oracle/_ref/shim_check is a C++ program compiled against the reference's own include/ida_native/kernels.hpp and
+    fp8_e4m3.hpp with the drop-in shim (shim/ida_native_kernels.cu, shim/cf_trainer_shim.hpp) over libcanopy_fp8.so: the
+    ida_native:: quantisers against the reference header's encoder, SwiGLU, routing and dispatch lists, the trainer's
+    lt_gemm_fp8_nt, and the exception convention. It is built where the reference tree is present (oracle/Makefile) and
+    travels as a binary; the test skips where it was not built."""
+    import os
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = os.path.join(root, "oracle", "_ref", "shim_check")
+    if not os.path.isfile(exe):
+        pytest.skip("oracle/_ref/shim_check not built (needs the reference headers at build time)")
+    r = subprocess.run([exe], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300)
+    assert r.returncode == 0 and "shim_check: PASS" in r.stdout, r.stdout[-2000:]

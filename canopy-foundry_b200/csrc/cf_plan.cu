@@ -230,8 +230,8 @@ extern "C" int cf_ep_placement_build_balanced(const double* popularity, int num_
     double best = -1.0;
     // Fixed-point iteration on the cut points: a rank that holds n replicas gives up n half-tiles of rows, so that rows +
     // expected padding, the tile work, is what the ranks have in common. The replica count changes as the cuts move; the
-    // best of a few rounds is kept (round 0 is the equal-rows placement, so the result is never worse than that).
-    for (int round = 0; round < 6; ++round) {
+    // best of a few passes is kept (the first pass is the equal-rows placement, so the result is never worse than that).
+    for (int pass = 0; pass < 6; ++pass) {
         const int rc = place_with_cuts(p, num_experts, world, min_share, cut, &cand, rep_len);
         if (rc != CF_OK) { cf::set_error("cf_ep_placement_build_balanced: more than %d replicas", CF_EP_MAX_REPLICAS); return rc; }
         const double cost = worst_rank_cost(cand, rep_len, half_tile);

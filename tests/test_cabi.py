@@ -35,6 +35,14 @@ def test_argument_validation_without_a_device():
     assert lib.cf_swiglu_forward(None, None, None, -1, None) == cfb._capi.CF_ERR_INVALID_ARG
     assert lib.cf_fp8_quantize_e4m3(None, None, C.c_void_p(16), 0, None) == cfb._capi.CF_OK     # n == 0 is a no-op
     assert lib.cf_moe_topk_route_f32(None, 4, 100, 2, None, None, None, 1) == cfb._capi.CF_ERR_INVALID_ARG
+    # dispatch front end: scratch sizing (one int per 256-row chunk and list) and argument checks
+    assert lib.cf_moe_route_dispatch_scratch_ints(0, 8) == 0
+    assert lib.cf_moe_route_dispatch_scratch_ints(256, 8) == 8
+    assert lib.cf_moe_route_dispatch_scratch_ints(257, 15) == 30
+    assert lib.cf_moe_route_dispatch_lists(None, 4, 100, 2, 1, None, None, None, 0, None, None, 0, None, None, None, None, 0,
+                                           None) == cfb._capi.CF_ERR_INVALID_ARG
+    assert lib.cf_moe_route_dispatch_lists(None, 4, 8, 2, 1, None, None, None, 0, None, None, 0, None, None, None, None, 0,
+                                           None) == cfb._capi.CF_ERR_INVALID_ARG      # counts / offsets missing
 
 
 def test_shim_compiles_against_the_reference_headers(tmp_path):

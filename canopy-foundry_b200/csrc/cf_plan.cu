@@ -196,11 +196,12 @@ int place_with_cuts(const double* p, int num_experts, int world, double min_shar
 
 // Expected tile work of the busiest rank, as a fraction of all rows: a replica with r rows costs the tiles it fills,
 // ceil(r / tile) * tile; with r only known in expectation that is r + tile / 2.
-double worst_rank_cost(const cf_ep_placement& pl, const double* rep_len, double half_tile) {
+double worst_rank_cost(const cf_ep_placement& pl, const double* rep_len, double half_tile, const double* speed) {
     double worst = 0.0;
     for (int g = 0; g < pl.world; ++g) {
         double c = 0.0;
         for (int v = pl.rank_lo[g]; v < pl.rank_hi[g]; ++v) c += rep_len[v] + half_tile;
+        c /= speed[g];                                   // time, in units of the mean rank's time per row
         if (c > worst) worst = c;
     }
     return worst;
@@ -210,6 +211,12 @@ double worst_rank_cost(const cf_ep_placement& pl, const double* rep_len, double 
 
 extern "C" int cf_ep_placement_build_balanced(const double* popularity, int num_experts, int world, double min_share,
                                               double expected_total_rows, int tile_rows, cf_ep_placement* out) {
+    return cf_ep_placement_build_weighted(popularity, num_experts, world, min_share, expected_total_rows, tile_rows, nullptr, out);
+}
+
+extern "C" int cf_ep_placement_build_weighted(const double* popularity, int num_experts, int world, double min_share,
+                                              double expected_total_rows, int tile_rows, const double* rank_speed_or_null,
+                                              cf_ep_placement* out) {
     CF_REQUIRE(popularity && out, "cf_ep_placement_build_balanced: null pointer");
     CF_REQUIRE(num_experts >= 1 && num_experts <= CF_EP_MAX_EXPERTS, "cf_ep_placement_build_balanced: 1..%d experts", CF_EP_MAX_EXPERTS);
     CF_REQUIRE(world >= 1 && world <= CF_EP_MAX_RANKS, "cf_ep_placement_build_balanced: 1..%d ranks", CF_EP_MAX_RANKS);
@@ -224,8 +231,18 @@ extern "C" int cf_ep_placement_build_balanced(const double* popularity, int num_
     static thread_local double p[CF_EP_MAX_EXPERTS], rep_len[CF_EP_MAX_REPLICAS], best_len[CF_EP_MAX_REPLICAS];
     for (int e = 0; e < num_experts; ++e) p[e] = popularity[e] / tot;
     const double half_tile = 0.5 * tile_rows / expected_total_rows;      // expected padding of one replica, as a share of all rows
+    // relative speed of every rank (mean 1): a rank that needs less time per row takes a longer piece of the line
+    double speed[CF_EP_MAX_RANKS], speed_sum = 0.0;
+    for (int g = 0; g < world; ++g) {
+        speed[g] = rank_speed_or_null ? rank_speed_or_null[g] : 1.0;
+        CF_REQUIRE(speed[g] > 0.0, "cf_ep_placement_build_weighted: rank speeds must be positive");
+        speed_sum += speed[g];
+    }
+    for (int g = 0; g < world; ++g) speed[g] *= world / speed_sum;
     double cut[CF_EP_MAX_RANKS + 1];
-    for (int g = 0; g <= world; ++g) cut[g] = static_cast<double>(g) / world;
+    cut[0] = 0.0;
+    for (int g = 0; g < world; ++g) cut[g + 1] = cut[g] + speed[g] / world;
+    cut[world] = 1.0;
     cf_ep_placement cand;
     double best = -1.0;
     // Fixed-point iteration on the cut points: a rank that holds n replicas gives up n half-tiles of rows, so that rows +
@@ -234,16 +251,16 @@ extern "C" int cf_ep_placement_build_balanced(const double* popularity, int num_
     for (int pass = 0; pass < 6; ++pass) {
         const int rc = place_with_cuts(p, num_experts, world, min_share, cut, &cand, rep_len);
         if (rc != CF_OK) { cf::set_error("cf_ep_placement_build_balanced: more than %d replicas", CF_EP_MAX_REPLICAS); return rc; }
-        const double cost = worst_rank_cost(cand, rep_len, half_tile);
+        const double cost = worst_rank_cost(cand, rep_len, half_tile, speed);
         if (best < 0.0 || cost < best) {
             best = cost;
             *out = cand;
             std::memcpy(best_len, rep_len, sizeof(double) * cand.num_replicas);
         }
-        const double level = (1.0 + half_tile * cand.num_replicas) / world;       // tile work every rank should end up with
+        const double level = (1.0 + half_tile * cand.num_replicas) / world;       // tile work a rank of mean speed should end up with
         double piece[CF_EP_MAX_RANKS], sum = 0.0;
         for (int g = 0; g < world; ++g) {
-            piece[g] = level - half_tile * (cand.rank_hi[g] - cand.rank_lo[g]);
+            piece[g] = level * speed[g] - half_tile * (cand.rank_hi[g] - cand.rank_lo[g]);
             if (piece[g] < 0.25 / world) piece[g] = 0.25 / world;
             sum += piece[g];
         }

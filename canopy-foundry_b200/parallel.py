@@ -100,19 +100,26 @@ class ReplicaPlacement:
         return len(self.replica_expert)
 
     @classmethod
-    def build(cls, popularity, world, min_share=0.02, total_rows=None, tile_rows=256):
+    def build(cls, popularity, world, min_share=0.02, total_rows=None, tile_rows=256, rank_speed=None):
         """popularity: expected share of the rows per expert (any positive scale). Overlaps below `min_share` of a
         rank's piece are not worth a weight copy: they are merged into the expert's largest replica. The layout is
         computed by the library (cf_ep_placement_build), the same call a C++ trainer makes. With total_rows (selected
         rows of all ranks per layer) the pieces are sized for equal tile work instead of equal rows
-        (cf_ep_placement_build_balanced): a rank with several small replicas pays about tile_rows / 2 padded rows each."""
+        (cf_ep_placement_build_balanced): a rank with several small replicas pays about tile_rows / 2 padded rows each.
+        rank_speed (needs total_rows): measured throughput of every rank on this work, any common unit; slower ranks
+        get shorter pieces (cf_ep_placement_build_weighted)."""
         import ctypes as C
 
         from . import _capi
         E = len(popularity)
         pop = (C.c_double * E)(*[float(x) for x in popularity])
         pl = _capi.EpPlacementStruct()
-        if total_rows:
+        if total_rows and rank_speed is not None:
+            assert len(rank_speed) == world
+            spd = (C.c_double * world)(*[float(x) for x in rank_speed])
+            _capi.check(_capi.lib().cf_ep_placement_build_weighted(pop, E, int(world), float(min_share), float(total_rows),
+                                                                   int(tile_rows), spd, C.byref(pl)))
+        elif total_rows:
             _capi.check(_capi.lib().cf_ep_placement_build_balanced(pop, E, int(world), float(min_share), float(total_rows),
                                                                    int(tile_rows), C.byref(pl)))
         else:

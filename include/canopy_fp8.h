@@ -553,6 +553,13 @@ int cf_ep_placement_build(const double* popularity, int num_experts, int world, 
  * selected rows of all ranks per layer (tokens * top_k). Never worse than the equal-rows placement by its own cost model. */
 int cf_ep_placement_build_balanced(const double* popularity, int num_experts, int world, double min_share,
                                    double expected_total_rows, int tile_rows, cf_ep_placement* out);
+/* The balanced placement for ranks of unequal speed: rank_speed_or_null[g] > 0 is rank g's measured throughput on this
+ * work in any common unit (rows of tile work per millisecond of its GEMM stages, say; NULL = all equal). The GPUs of one box
+ * differ by several percent under their power cap, and every rank waits for the slowest at the closing barrier of a layer;
+ * the pieces of the line are sized so that tile work / speed is what the ranks have in common. */
+int cf_ep_placement_build_weighted(const double* popularity, int num_experts, int world, double min_share,
+                                   double expected_total_rows, int tile_rows, const double* rank_speed_or_null,
+                                   cf_ep_placement* out);
 
 /* A run of rows on its way to another buffer: `rows` rows starting at src_row (ignored when the call gathers through an
  * index table) go to row dst_row of destination buffer number dst. */

@@ -296,3 +296,48 @@ def test_placement_balanced_by_tile_work_is_never_worse_and_keeps_the_invariants
         return max(sum(math.ceil(zipf[pl.replica_expert[v]] * pl.replica_share[v] / 256) * 256 for v in range(*pl.rank_ranges[g]))
                    for g in range(8))
     assert tiles(b) <= tiles(a) - 256
+
+
+def test_placement_weighted_by_rank_speed_equalises_time_and_keeps_the_invariants():
+    """cf_ep_placement_build_weighted: equal speeds give the balanced placement; with unequal speeds the slowest finishing
+    time (tile work / speed) is never later than with the balanced placement, and clearly earlier when one rank is slow."""
+    import random
+    par = package().parallel
+    zipf = [25089, 14832, 9032, 5887, 4045, 2940, 2079, 1632]
+    total, tile = 65536, 256
+
+    def finish(pl, load, speed):
+        tot = sum(load)
+        out = 0.0
+        for g in range(pl.world):
+            lo, hi = pl.rank_ranges[g]
+            c = sum(load[pl.replica_expert[v]] / tot * total * pl.replica_share[v] + tile / 2 for v in range(lo, hi))
+            out = max(out, c / speed[g])
+        return out
+
+    for w in (2, 4, 8):
+        a = par.ReplicaPlacement.build(zipf, w, total_rows=total, tile_rows=tile)
+        b = par.ReplicaPlacement.build(zipf, w, total_rows=total, tile_rows=tile, rank_speed=[1.0] * w)
+        assert (a.replica_expert, a.replica_rank, a.rank_ranges) == (b.replica_expert, b.replica_rank, b.rank_ranges)
+        assert np.allclose(a.replica_share, b.replica_share, atol=1e-12)
+    rnd = random.Random(5)
+    for _ in range(60):
+        w = rnd.choice([2, 4, 8])
+        load = zipf if rnd.random() < 0.5 else [rnd.random() ** 2 + 0.01 for _ in range(rnd.randint(w, 24))]
+        speed = [1.0 + 0.12 * (rnd.random() - 0.5) for _ in range(w)]
+        a = par.ReplicaPlacement.build(load, w, total_rows=total, tile_rows=tile)
+        b = par.ReplicaPlacement.build(load, w, total_rows=total, tile_rows=tile, rank_speed=speed)
+        mean = sum(speed) / w
+        sp = [x / mean for x in speed]
+        assert finish(b, load, sp) <= finish(a, load, sp) * (1 + 1e-9)
+        for e in range(len(load)):
+            assert abs(sum(b.replica_share[b.replica_start[e]:b.replica_start[e + 1]]) - 1.0) < 1e-9
+        ids = [v for g in range(w) for v in range(*b.rank_ranges[g])]
+        assert ids == list(range(b.num_replicas))
+    slow = [1.0, 0.9, 1.0, 1.0]
+    a = par.ReplicaPlacement.build(zipf, 4, total_rows=total, tile_rows=tile)
+    b = par.ReplicaPlacement.build(zipf, 4, total_rows=total, tile_rows=tile, rank_speed=slow)
+    m = sum(slow) / 4
+    assert finish(b, zipf, [x / m for x in slow]) < 0.95 * finish(a, zipf, [x / m for x in slow])
+    with pytest.raises(Exception):
+        par.ReplicaPlacement.build(zipf, 4, total_rows=total, tile_rows=tile, rank_speed=[1.0, 0.0, 1.0, 1.0])

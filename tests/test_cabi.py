@@ -112,6 +112,90 @@ int main() {
     assert run.returncode == 0, run.stdout
 
 
+def test_route_plan_glue_compiles_and_runs_against_the_reference_contracts(tmp_path):
+    """cf_contracts_shim.hpp publishes the dispatch front end's buffers through the reference's RoutePlanStore and
+    SchedulerWorkspaceCache and the FP8 weight caches through its ExecutionViewCache: compile a small program against the
+    reference's headers and its own src/moe/route_plan.cpp, scheduler.cpp and src/precision/execution_view.cpp (where the
+    reference tree is available) and run it on the CPU: publish, backward reuse by generation, duplicate and stale
+    rejections, schedule build and reuse, one weight refresh per tensor generation whatever the number of roles."""
+    import shutil
+    import subprocess
+
+    import pytest
+    ref = os.environ.get("CANOPY_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
+    if not os.path.isfile(os.path.join(ref, "src", "moe", "route_plan.cpp")) or shutil.which("g++") is None:
+        pytest.skip("reference tree or g++ not present")
+    src = tmp_path / "route_glue.cpp"
+    src.write_text(r"""
+#include <cstdio>
+#include "cf_contracts_shim.hpp"
+int main() {
+    using namespace canopy_foundry;
+    static int counts[8], offsets[8], idx[8 * 64];
+    static float rw[64 * 8];
+    cf_shim::DispatchBuffers b;
+    b.d_counts = counts; b.d_offsets = offsets; b.d_row_indices = idx; b.d_route_weights = rw;
+    b.lists = 8; b.rows = 64; b.top_k = 2;
+    RoutePlanStore store;
+    const RoutePlanKey key{7, 3};
+    const RoutePlan& p = cf_shim::publish_dispatch(store, key, RouteGeneration{1}, b);
+    if (!p.valid() || p.routes != 128 || p.experts != 8 || p.actual_rows != -1) return 2;
+    const RoutePlan& again = store.require_for_backward(key, RouteGeneration{1});
+    const cf_shim::DispatchBuffers back = cf_shim::buffers_of(again);
+    if (back.d_counts != counts || back.d_row_indices != idx || back.d_route_weights != rw || back.rows != 64) return 3;
+    try { store.require_for_backward(key, RouteGeneration{2}); return 4; } catch (const RoutePlanError&) {}
+    try { cf_shim::publish_dispatch(store, key, RouteGeneration{2}, b); return 5; } catch (const RoutePlanError&) {}
+    try { cf_shim::publish_dispatch(store, RoutePlanKey{8, 3}, RouteGeneration{1}, b); return 6; } catch (const RoutePlanError&) {}
+    cf_shim::DispatchBuffers other = b; other.top_k = 1;
+    if (cf_shim::dispatch_fingerprint(other) == cf_shim::dispatch_fingerprint(b)) return 7;
+    SchedulerWorkspaceCache cache;
+    const SchedulerWorkspace& w = cf_shim::require_schedule(cache, RouteGeneration{1}, b, 28672, 4096, 0);
+    if (!w.schedule_valid || w.key.n_tiles != 112 || w.key.k_chunks != 32 || w.tile_capacity != (1 + 8) * 112u) return 8;
+    cf_shim::require_schedule(cache, RouteGeneration{1}, b, 28672, 4096, 0);
+    cf_shim::require_schedule(cache, RouteGeneration{1}, b, 4096, 14336, 0);
+    if (cache.stats().builds != 2 || cache.stats().reuses != 1) return 9;
+    cache.invalidate_route(RouteGeneration{2});
+    try { cf_shim::require_schedule(cache, RouteGeneration{1}, b, 28672, 4096, 0); return 10; } catch (const SchedulerWorkspaceError&) {}
+    // weights: one refresh per tensor generation, shared by the roles
+    static unsigned char fwd[16], bwd[16];
+    cf_fp8_weight wt{};
+    wt.fwd8 = fwd; wt.bwd8 = bwd; wt.in_dim = 4; wt.out_dim = 4;
+    int refreshes = 0;
+    auto fake = [&refreshes](const cf_fp8_weight&, void*) { ++refreshes; return 0; };
+    ExecutionViewCache views;
+    const PackedExecutionView& f1 = cf_shim::require_weight_view(views, 42, TensorGeneration{1}, ExecutionRole::Forward, wt, nullptr, fake);
+    if (refreshes != 1 || f1.storage_token != cf_shim::token_of(fwd) || f1.key.layout.orientation != PackedOrientation::RowMajor) return 11;
+    const PackedExecutionView& d1 = cf_shim::require_weight_view(views, 42, TensorGeneration{1}, ExecutionRole::BackwardDx, wt, nullptr, fake);
+    if (refreshes != 1 || d1.storage_token != cf_shim::token_of(bwd) || d1.key.layout.orientation != PackedOrientation::Transposed) return 12;
+    cf_shim::require_weight_view(views, 42, TensorGeneration{1}, ExecutionRole::Forward, wt, nullptr, fake);
+    if (refreshes != 1 || views.stats().reuses != 1) return 13;
+    views.invalidate(42, TensorGeneration{2});                   // the optimiser stepped
+    cf_shim::require_weight_view(views, 42, TensorGeneration{2}, ExecutionRole::ExpertForward, wt, nullptr, fake);
+    if (refreshes != 2) return 14;
+    try { cf_shim::require_weight_view(views, 42, TensorGeneration{1}, ExecutionRole::Forward, wt, nullptr, fake); return 15; }
+    catch (const ExecutionViewError&) {}
+    cf_fp8_weight single = wt;
+    single.bwd8 = nullptr;                                       // dgrad reads the forward cache MN-major
+    const PackedExecutionView& d2 = cf_shim::require_weight_view(views, 43, TensorGeneration{1}, ExecutionRole::ExpertDx, single, nullptr, fake);
+    if (d2.storage_token != cf_shim::token_of(fwd) || d2.key.layout.orientation != PackedOrientation::ColumnMajor) return 16;
+    auto failing = [](const cf_fp8_weight&, void*) { return 3; };
+    try { cf_shim::require_weight_view(views, 44, TensorGeneration{1}, ExecutionRole::Forward, wt, nullptr, failing); return 17; }
+    catch (const ExecutionViewError&) {}
+    std::puts("route plan glue: ok");
+    return 0;
+}
+""")
+    exe = tmp_path / "route_glue"
+    libdir = os.path.join(ROOT, "canopy-foundry_b200", "lib")
+    r = subprocess.run(["g++", "-std=c++20", f"-I{ref}/include", f"-I{ROOT}/include", f"-I{ROOT}/canopy-foundry_b200/shim", str(src),
+                        os.path.join(ref, "src", "moe", "route_plan.cpp"), os.path.join(ref, "src", "moe", "scheduler.cpp"),
+                        os.path.join(ref, "src", "precision", "execution_view.cpp"), f"-L{libdir}", "-lcanopy_fp8",
+                        f"-Wl,-rpath,{libdir}", "-o", str(exe)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    assert r.returncode == 0, r.stdout[-3000:]
+    r = subprocess.run([str(exe)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    assert r.returncode == 0 and "route plan glue: ok" in r.stdout, (r.returncode, r.stdout)
+
+
 def test_bench_line_contract_without_a_gpu():
     """bench.py imports without a GPU, offers the legs the default line carries, and the reference arm prints the
     same `config` keys as the GPU arm (the driver compares the two)."""

@@ -507,7 +507,9 @@ int cf_moe_expand_route_replicas(const float* d_route_weights, float* d_replica_
  * numbers in ascending order; d_counts, d_offsets: one int per list; d_row_indices: [lists, rows]. It replaces the
  * host-synchronised list building of src/trainer.cu:6876-6880. d_scratch: cf_moe_route_dispatch_scratch_ints(rows, lists)
  * ints owned by the caller, contents irrelevant (CF_ERR_LIMIT if too small); more than 64 lists run the separate
- * kernels. */
+ * kernels. Every 256-row chunk sums the counts of the chunks in front of it, so the second launch reads
+ * (rows / 256)^2 / 2 x lists integers in total: negligible up to a few hundred thousand rows per call, which is what a
+ * layer routes; beyond that, call it per slab of rows. */
 size_t cf_moe_route_dispatch_scratch_ints(int rows, int num_lists);
 int cf_moe_route_dispatch_lists(float* d_scores, int rows, int num_experts, int top_k, int normalize_topk,
                                 float* d_row_sum_save_or_null, float* d_scores_save_or_null, float* d_replica_weights_or_null,

@@ -509,7 +509,7 @@ int cf_moe_expand_route_replicas(const float* d_route_weights, float* d_replica_
  * ints owned by the caller, contents irrelevant (CF_ERR_LIMIT if too small); more than 64 lists run the separate
  * kernels. Every 256-row chunk sums the counts of the chunks in front of it, so the second launch reads
  * (rows / 256)^2 / 2 x lists integers in total: negligible up to a few hundred thousand rows per call, which is what a
- * layer routes; beyond that, call it per slab of rows. */
+ * layer routes. */
 size_t cf_moe_route_dispatch_scratch_ints(int rows, int num_lists);
 int cf_moe_route_dispatch_lists(float* d_scores, int rows, int num_experts, int top_k, int normalize_topk,
                                 float* d_row_sum_save_or_null, float* d_scores_save_or_null, float* d_replica_weights_or_null,

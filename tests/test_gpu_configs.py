@@ -556,3 +556,31 @@ def test_dense_ffn_fused_against_reference_sequence_and_oracle(cfb, ctx, oracle)
             y_o = oracle.gemm_fp8_nt(oracle.quantize_bf16(h_o, s_h), wd8.cpu().numpy(), d_h, dd[0].item())
             assert rel_fro(y[rows].float().cpu().numpy(), oracle.bf16_to_f32(y_o)) < TOL, (M, step)
         del ffn
+
+
+def test_rowwise_quantize_random_shapes_and_alignments(cfb, oracle):
+    """Forty seeded random (rows, cols, input offset, output offset, row pitch) cases of the per-token quantiser, from one
+    column to 16384, against the oracle: codes, scales, descales, and an untouched guard band around the output."""
+    import random
+    rnd = random.Random(2024)
+    for case in range(40):
+        cols = rnd.choice([1, 2, 7, 8, 9, 15, 16, 17, 63, 64, 65, 255, 511, 513, 1000, 4095, 4096, 4097, 8191, 16384]) \
+            if case % 2 == 0 else rnd.randint(1, 3000)
+        rows = rnd.randint(1, 40)
+        pad_in, pad_out = rnd.choice([0, 0, 1, 3, 8]), rnd.choice([0, 0, 1, 5, 16])
+        ld_in, ld_out = cols + pad_in, cols + pad_out
+        in_off, out_off = rnd.randint(0, 9), rnd.randint(0, 17)
+        flat = randn_bf16((in_off + rows * ld_in + 16,), seed=1000 + case, outlier_frac=0.02)
+        out_flat = torch.full((out_off + rows * ld_out + 64,), 0x5C, dtype=torch.uint8, device="cuda")
+        sc = torch.empty(rows, dtype=torch.float32, device="cuda")
+        de = torch.empty(rows, dtype=torch.float32, device="cuda")
+        cfb.fp8_quantize_rowwise_e4m3(flat[in_off:], out_flat[out_off:], de, row_scale=sc, rows=rows, cols=cols, ld_x=ld_in,
+                                      ld_out=ld_out)
+        src = bf16_to_u16(flat)[in_off:in_off + rows * ld_in].reshape(rows, ld_in)[:, :cols]
+        w, s_o, d_o = oracle.quantize_rowwise_e4m3(np.ascontiguousarray(src))
+        got = out_flat.cpu().numpy()
+        body = got[out_off:out_off + rows * ld_out].reshape(rows, ld_out)
+        key = (case, rows, cols, ld_in, ld_out, in_off, out_off)
+        assert np.array_equal(body[:, :cols], w), key
+        assert (body[:, cols:] == 0x5C).all() and (got[:out_off] == 0x5C).all() and (got[out_off + rows * ld_out:] == 0x5C).all(), key
+        assert np.array_equal(sc.cpu().numpy(), s_o) and np.array_equal(de.cpu().numpy(), d_o), key

@@ -474,3 +474,37 @@ def test_the_three_launch_linear_step_replays_from_a_cuda_graph(cfb, ctx):
         assert torch.equal(y_g, want[i]), i
     assert slot_g.scalars() == slot_e.scalars()
     ctx.poll_status()
+
+
+def test_dense_nt_random_shapes_pitches_and_types(cfb, ctx, oracle):
+    """Thirty seeded random cases across the call-site matrix of the NT GEMM: any M and N, K a multiple of 16 (tensor-core
+    form, single-CTA or CTA-pair by M) or not (SIMT form), E4M3 or E5M2 activations, A read and C written as column
+    slices of wider buffers (lda, ldc > the slice), against the oracle on random codes, with an untouched guard band in C."""
+    import random
+    rnd = random.Random(99)
+    for case in range(30):
+        M = rnd.choice([1, 3, 127, 128, 129, 255, 511, 512, 513, 640, 1000, 1025])
+        N = rnd.choice([8, 16, 40, 64, 200, 256, 264, 520, 1024])
+        K = rnd.choice([16, 32, 48, 128, 144, 512, 1040, 2048]) if case % 5 else rnd.choice([24, 40, 100])
+        e5m2 = bool(rnd.getrandbits(1))
+        a_off, c_off = rnd.choice([0, 16, 32]), rnd.choice([0, 8, 16, 64])
+        lda, ldc = K + a_off + rnd.choice([0, 16, 48]), N + c_off + rnd.choice([0, 8, 24])
+        g = torch.Generator(device="cuda").manual_seed(500 + case)
+        hi = 0x7B if e5m2 else 0x78                           # finite codes of either sign
+        a_buf = torch.randint(0, hi, (M, lda), generator=g, dtype=torch.uint8, device="cuda")
+        a_buf |= (torch.randint(0, 2, (M, lda), generator=g, dtype=torch.uint8, device="cuda") << 7)
+        w8 = torch.randint(0, 0x78, (N, K), generator=g, dtype=torch.uint8, device="cuda")
+        w8 |= (torch.randint(0, 2, (N, K), generator=g, dtype=torch.uint8, device="cuda") << 7)
+        da, dw = f32_scalar(2.0 ** -rnd.randint(3, 9)), f32_scalar(2.0 ** -rnd.randint(3, 9))
+        if e5m2:
+            da = f32_scalar(2.0 ** -22)
+        c_buf = torch.full((M, ldc), 3.0, dtype=torch.bfloat16, device="cuda")
+        cfb.lt_gemm_fp8_nt(ctx, M, N, K, a_buf.view(-1)[a_off:], lda, e5m2, da, w8, dw, c_buf.view(-1)[c_off:], ldc)
+        ctx.poll_status()
+        a_np = np.ascontiguousarray(a_buf.cpu().numpy()[:, a_off:a_off + K])
+        want = oracle.gemm_fp8_nt(a_np, w8.cpu().numpy(), da[0].item(), dw[0].item(), a_is_e5m2=e5m2)
+        got_all = c_buf.cpu()
+        got = bf16_to_u16(got_all[:, c_off:c_off + N].contiguous())
+        key = (case, M, N, K, e5m2, lda, ldc, a_off, c_off)
+        assert rel_fro(oracle.bf16_to_f32(got), oracle.bf16_to_f32(want)) < TIGHT, key
+        assert (got_all[:, :c_off] == 3.0).all() and (got_all[:, c_off + N:] == 3.0).all(), key

@@ -573,3 +573,38 @@ def test_dispatch_front_end_with_no_rows_and_with_more_than_64_lists(cfb):
     cfb.moe_route_dispatch_lists(rw1, rows, E, k, c1, o1, i1, s, replica_weights=rwv1, num_replicas=V, replica_start=start,
                                  replica_cum_share=cum)
     assert torch.equal(rwv1, rwv0) and torch.equal(c1, c0) and torch.equal(o1, o0) and torch.equal(i1, i0)
+
+
+def test_grouped_gemm_random_ragged_counts(cfb, ctx, oracle):
+    """Twenty seeded random ragged schedules (1 to 12 groups, counts from 0 to a few tiles, some exactly on tile
+    boundaries), plain and fused-SwiGLU forms, against the oracle group by group; rows past the last group stay untouched."""
+    import random
+    rnd = random.Random(7)
+    for case in range(20):
+        E = rnd.randint(1, 12)
+        counts_l = [rnd.choice([0, 1, 31, 32, 33, 127, 128, 129, 255, 256, 257, 300, 512, 700]) for _ in range(E)]
+        if sum(counts_l) == 0:
+            counts_l[rnd.randrange(E)] = 5
+        N = rnd.choice([64, 128, 256, 320, 512])
+        K = rnd.choice([64, 128, 256, 528])
+        total = sum(counts_l)
+        offs_l = [sum(counts_l[:e]) for e in range(E)]
+        counts = torch.tensor(counts_l, dtype=torch.int32, device="cuda")
+        offs = torch.tensor(offs_l, dtype=torch.int32, device="cuda")
+        g = torch.Generator(device="cuda").manual_seed(900 + case)
+        xc = torch.randint(0, 0x70, (total, K), generator=g, dtype=torch.uint8, device="cuda")
+        xc |= (torch.randint(0, 2, (total, K), generator=g, dtype=torch.uint8, device="cuda") << 7)
+        w8 = torch.randint(0, 0x70, (E, N, K), generator=g, dtype=torch.uint8, device="cuda")
+        w8 |= (torch.randint(0, 2, (E, N, K), generator=g, dtype=torch.uint8, device="cuda") << 7)
+        da, dw = f32_scalar(2.0 ** -6), f32_scalar(2.0 ** -7)
+        out = torch.full((total + 5, N), 9.0, dtype=torch.bfloat16, device="cuda")
+        cfb.gemm_fp8_nt_grouped(ctx, E, total, N, K, counts, offs, xc, K, False, da, False, w8, dw, out, N)
+        ctx.poll_status()
+        xcn, w8n = xc.cpu().numpy(), w8.cpu().numpy()
+        for e in range(E):
+            if counts_l[e] == 0:
+                continue
+            want = oracle.gemm_fp8_nt(np.ascontiguousarray(xcn[offs_l[e]:offs_l[e] + counts_l[e]]), w8n[e], 2.0 ** -6, 2.0 ** -7)
+            got = bf16_to_u16(out[offs_l[e]:offs_l[e] + counts_l[e]])
+            assert rel_fro(oracle.bf16_to_f32(got), oracle.bf16_to_f32(want)) < 5e-3, (case, e, counts_l, N, K)
+        assert (out[total:] == 9.0).all(), (case, counts_l)

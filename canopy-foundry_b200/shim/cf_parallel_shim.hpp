@@ -44,8 +44,12 @@ struct ExpertShardedLayout {
 
 // expected_load[e]: rows expert e is expected to receive (any positive scale; a trainer takes it from the previous
 // steps' routing counts). min_share: overlaps below this fraction of a rank's piece get no weight copy.
+// expected_total_rows > 0 (selected rows of all ranks per layer, tokens * top_k) sizes the ranks' pieces for equal tile
+// work of the grouped GEMM instead of equal rows (cf_ep_placement_build_balanced); rank_speed, one positive number per
+// device, additionally shortens the pieces of slower devices (cf_ep_placement_build_weighted).
 inline ExpertShardedLayout expert_sharded_layout(const canopy_foundry::ParallelPlan& plan,
-                                                 const std::vector<double>& expected_load, double min_share = 0.02) {
+                                                 const std::vector<double>& expected_load, double min_share = 0.02,
+                                                 double expected_total_rows = 0.0, const std::vector<double>& rank_speed = {}) {
     using canopy_foundry::ParallelMode;
     using canopy_foundry::TransportKind;
     if (plan.mode != ParallelMode::ExpertSharded)
@@ -56,8 +60,13 @@ inline ExpertShardedLayout expert_sharded_layout(const canopy_foundry::ParallelP
                                     canopy_foundry::transport_kind_name(plan.transport));
     ExpertShardedLayout out;
     out.devices = plan.devices;
-    const int rc = cf_ep_placement_build(expected_load.data(), static_cast<int>(expected_load.size()),
-                                         static_cast<int>(plan.devices.size()), min_share, &out.placement);
+    const int experts = static_cast<int>(expected_load.size()), world = static_cast<int>(plan.devices.size());
+    if (!rank_speed.empty() && (rank_speed.size() != plan.devices.size() || expected_total_rows <= 0.0))
+        throw std::invalid_argument("expert_sharded_layout: rank_speed needs one entry per device and expected_total_rows");
+    const int rc = expected_total_rows > 0.0
+                       ? cf_ep_placement_build_weighted(expected_load.data(), experts, world, min_share, expected_total_rows, 256,
+                                                        rank_speed.empty() ? nullptr : rank_speed.data(), &out.placement)
+                       : cf_ep_placement_build(expected_load.data(), experts, world, min_share, &out.placement);
     if (rc != CF_OK) throw std::runtime_error(std::string("expert_sharded_layout: ") + cf_last_error());
     return out;
 }

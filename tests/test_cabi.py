@@ -95,6 +95,14 @@ int main() {
         std::printf("rank %d replicas [%d,%d) share %.4f\n", r, lay.placement.rank_lo[r], lay.placement.rank_hi[r], rows);
         if (std::fabs(rows - 0.25) > 0.02) return 2;
     }
+    // pieces by tile work, the second device 10 % slower: it expects clearly fewer rows than the others
+    cf_shim::ExpertShardedLayout w = cf_shim::expert_sharded_layout(plan, load, 0.02, 65536.0, {1.0, 0.9, 1.0, 1.0});
+    double rows_w[4] = {0, 0, 0, 0};
+    for (int r = 0; r < 4; ++r)
+        for (int v = w.placement.rank_lo[r]; v < w.placement.rank_hi[r]; ++v)
+            rows_w[r] += load[w.placement.replica_expert[v]] / tot * w.placement.replica_share[v];
+    if (!(rows_w[1] < 0.95 * rows_w[0] && rows_w[1] < 0.95 * rows_w[2])) return 5;
+    try { cf_shim::expert_sharded_layout(plan, load, 0.02, 0.0, {1.0, 1.0, 1.0, 1.0}); return 6; } catch (const std::invalid_argument&) {}
     plan.transport = canopy_foundry::TransportKind::HostStaged;
     try { cf_shim::expert_sharded_layout(plan, load); return 3; } catch (const std::invalid_argument&) {}
     plan.mode = canopy_foundry::ParallelMode::LayerPipeline;

@@ -1076,10 +1076,21 @@ int launch_gemm_fp8_nt(const void* d_A, long long lda, long long a_rows, const v
         p.c_vec = 0;
     }
     // Row blocks per rasterisation band. Eight keeps the operand slabs of the ~74 tiles in flight smallest (8 + 74/8 row
-    // and column blocks). The SwiGLU form over a weight block larger than L2 with a short K (gate/up projection, 28672 x
-    // 4096: little output traffic, B re-streamed once per band) measured 2-6 % faster with twice the band height; the
-    // bf16-output GEMM of the same shape measured 7 % slower with it and keeps eight.
-    if ((p.out_kind == 4 || p.out_kind == 5) && static_cast<long long>(p.N) * p.K > (64ll << 20) && p.K <= 4096) p.raster_m = 16;
+    // and column blocks). When the weight operand is larger than L2 (N x K > 64 MB) it is re-streamed from HBM once per
+    // band, and a taller band pays as long as the band's own A rows (band x 256 x K bytes) stay within about 32 MB:
+    // measured over seconds under the power cap (shorter timings follow the power controller's history, not the
+    // rasterisation), dense bf16-output GEMMs: 16384 x 28672 x 4096: 1.472 / 1.429 / 1.419 ms with 8 / 16 / 32;
+    // 32768 x 28672 x 8192: 5.63 / 5.52 / 6.01 ms; 32768 x 14336 x 8192: 2.82 / 2.76 / 3.02 ms; 32768 x 8192 x 28672
+    // (A band 58 MB at 8): 5.61 / 5.54 / 5.96 ms with 4 / 8 / 16. The SwiGLU forms (gate/up projections, 28672 x 4096) take
+    // 16, ragged ones included: a taller band would span several experts' weight blocks.
+    if (static_cast<long long>(p.N) * p.K > (64ll << 20)) {
+        if (p.out_kind == 4 || p.out_kind == 5) {
+            if (p.K <= 4096) p.raster_m = 16;
+        } else if (p.d_counts == nullptr && !p.mn_major) {
+            if (p.K <= 4096) p.raster_m = 32;
+            else if (p.K <= 8192) p.raster_m = 16;
+        }
+    }
     if (p.peer_out_host != nullptr && !tma_ok) {
         set_error("reduce-scatter GEMM: operands must be 16-byte aligned with K %% 16 == 0");
         return CF_ERR_UNSUPPORTED;
